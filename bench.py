@@ -1,0 +1,363 @@
+#!/usr/bin/env python
+"""Benchmark of the Universal Attention hot path (operator forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2]
+
+Prints ONE JSON line on rank 0.  A step is one forward + one backward of the
+operator over one batch of seeded synthetic inputs of the named workload:
+
+* ``value``  tokens/s (tokens = batch * L per step, summed over ranks) with all
+  inputs and upstream gradients resident in HBM, timed with CUDA events.
+* ``e2e``    the same metric through the public autograd entry points with HOST
+  (pinned) inputs: host->device copies, operator, SMVecMatMul, loss, backward,
+  and the device->host read of the loss and the five gradients are all timed.
+* ``roofline``      the dominant kernel's algorithmic FLOPs / measured time against
+  the measured bf16 tensor peak (MEASURED_PEAKS.json) or the stated fallback.
+* ``cpu_baseline``  the CPU oracle (a port of the reference's PyTorch path) on a
+  bounded sample of the same workload, on this host's cores.
+
+``--impl reference`` times that CPU path alone and prints the same line shape.
+For N > 1 launch with ``python -m torch.distributed.run --nproc-per-node N``;
+every rank processes its own batch shard (weak scaling, no collective on the
+data path).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: B, H, R, L, chunk, D, dtype, qkv_std, gate_mean, gate_std, fwd_only
+    "c1": dict(B=1, H=2, R=2, L=256, c=64, D=64, dtype="f32", std=1.0, gm=0.0, gs=1.0, fwd_only=False),
+    "c2": dict(B=4, H=8, R=4, L=4096, c=128, D=64, dtype="bf16", std=1.0, gm=0.0, gs=1.0, fwd_only=False),
+    "c3": dict(B=16, H=8, R=4, L=8192, c=128, D=128, dtype="bf16", std=0.5, gm=0.0, gs=1.0, fwd_only=True),
+    "c5": dict(B=8, H=16, R=1, L=16384, c=128, D=128, dtype="bf16", std=1.0, gm=-4.0, gs=2.0, fwd_only=False),
+}
+METRIC = "fwd+bwd tokens/sec"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def flops(w):
+    n = w["L"] // w["c"]
+    base = 2.0 * w["B"] * w["H"] * w["L"] ** 2 * w["D"] * (n + 1) / (2 * n)
+    f_fwd = base * (1 + 2 * w["R"])
+    f_bwd = 0.0 if w["fwd_only"] else base * (3 + 5 * w["R"])
+    return f_fwd, f_bwd
+
+
+def hbm_bytes(w):
+    e = 2 if w["dtype"] == "bf16" else 4
+    bh = w["B"] * w["H"]
+    n = w["L"] // w["c"]
+    inputs = (2 * w["L"] * w["D"] + w["R"] * w["L"] * w["D"] + 2 * w["L"]) * bh * e
+    out = bh * w["R"] * w["L"] * w["D"] * n * e
+    den = bh * w["R"] * w["L"] * n
+    return inputs + out + den * e, (0 if w["fwd_only"] else 2 * inputs + out + den * 4)
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return {k: float(d[k]) for k in FALLBACK_PEAKS}, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            text = ""
+        sm, mx, reasons = [], [], set()
+        for line in text.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_device_inputs(w, seed, device):
+    from universal_attention_triton_b200 import ops  # noqa: F401  (import check: fails loudly without the library)
+    dt = torch.bfloat16 if w["dtype"] == "bf16" else torch.float32
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    B, H, R, L, c, D = w["B"], w["H"], w["R"], w["L"], w["c"], w["D"]
+    n = L // c
+    xq = (torch.randn(B, H, R, L, D, generator=g) * w["std"]).to(dt)
+    kc = (torch.randn(B, H, n, c, D, generator=g) * w["std"]).to(dt)
+    vc = (torch.randn(B, H, n, c, D, generator=g) * w["std"]).to(dt)
+    ss = (torch.randn(B, H, n, c, generator=g) * w["gs"] + w["gm"]).sigmoid().to(dt)
+    sd = (torch.randn(B, H, L, generator=g) * w["gs"] + w["gm"]).sigmoid().to(dt)
+    host = [t.pin_memory() for t in (kc, vc, xq, ss, sd)]
+    dev = [t.to(device) for t in host]
+    return host, dev
+
+
+def cpu_reference_step_time(w, steps, warmup, unit_budget_s=25.0):
+    """Times the CPU oracle (port of the reference's PyTorch operator, fp32) on ONE
+    (batch, kv-head) unit of the workload, driver flow of main.py:55-62."""
+    from oracle import ua_oracle as O
+    torch.set_num_threads(os.cpu_count() or 1)
+    L = w["L"]
+    scale = 1.0
+    while L > 4096:          # keep the L x L plane in host memory; extrapolate with L^2
+        L //= 2
+        scale *= 4.0
+    ins = O.make_inputs(1, 1, w["R"], L, w["c"], w["D"], dtype=torch.float32, seed=0, qkv_std=w["std"],
+                        gate_mean=w["gm"], gate_std=w["gs"])
+    times = []
+    for it in range(warmup + steps):
+        t0 = time.perf_counter()
+        if w["fwd_only"]:
+            O.ua_forward(*ins)
+        else:
+            O.driver_step(*ins)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+        if sum(times) > unit_budget_s and len(times) >= 1:
+            break
+    t_unit = statistics.median(times) * scale
+    tokens_per_unit = w["L"] / w["H"]            # one (b,h) unit is 1/H of a batch row
+    sample = (f"1 of {w['B'] * w['H']} (batch, kv-head) units, R={w['R']} L={L} chunk={w['c']} D={w['D']} fp32, "
+              f"op+merge+loss fwd+bwd, median of {len(times)}" + (f", time scaled x{scale:g} to L={w['L']}" if scale > 1 else ""))
+    return tokens_per_unit / t_unit, t_unit, sample
+
+
+def run_reference(args, w, rank):
+    if rank != 0:
+        return
+    val, t_unit, sample = cpu_reference_step_time(w, max(1, args.steps), max(0, min(args.warmup, 1)))
+    cores = os.cpu_count() or 1
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_unit * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, **{k: w[k] for k in ("B", "H", "R", "L", "c", "D")}},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # convenience: re-launch under torchrun
+        port = os.environ.get("MASTER_PORT", "29531")
+        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                                   f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1", "--master-port", port,
+                                   os.path.abspath(__file__)] + sys.argv[1:])
+
+    if args.impl == "reference":
+        run_reference(args, w, rank)
+        return
+
+    import torch.distributed as dist
+    from universal_attention_triton_b200 import SMVecMatMul, UniversalAttention, _lib, ops, set_strict_masked_grads
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the operator)")
+    _lib.load()
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    W, K = max(args.warmup, 3), max(args.steps, 1)
+    host, dev = make_device_inputs(w, seed=rank, device=device)
+    kc, vc, xq, ss, sd = dev
+    B, H, R, L, c, D = w["B"], w["H"], w["R"], w["L"], w["c"], w["D"]
+    n = L // c
+    dt = xq.dtype
+    f_fwd, f_bwd = flops(w)
+    b_fwd, b_bwd = hbm_bytes(w)
+
+    # resident upstream gradients in the library's chunk-major layout
+    gen = torch.Generator(device=device).manual_seed(1234 + rank)
+    g_out_cm = None if w["fwd_only"] else torch.randn(B, H, n, R, L, D, generator=gen, device=device, dtype=dt)
+    g_lse_cm = None if w["fwd_only"] else torch.randn(B, H, n, R, L, generator=gen, device=device, dtype=torch.float32)
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    fwd_ms, bwd_ms = [], []
+
+    def step(record):
+        e0, e1, e2 = ev(), ev(), ev()
+        e0.record()
+        out_cm, lse_cm, denom_cm = ops.forward_cm(kc, vc, xq, ss, sd)
+        e1.record()
+        if not w["fwd_only"]:
+            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm)
+        e2.record()
+        if record:
+            fwd_ms.append((e0, e1)); bwd_ms.append((e1, e2))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        step(False)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_start, t_end = ev(), ev()
+    t_start.record()
+    for _ in range(K):
+        step(True)
+    t_end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t_start.elapsed_time(t_end)
+    if world > 1:
+        tt = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_ms = tt.item()
+    ms_per_step = total_ms / K
+    tokens = B * L * world
+    value = tokens / (ms_per_step * 1e-3)
+    fwd_avg = statistics.mean(a.elapsed_time(b) for a, b in fwd_ms)
+    bwd_avg = statistics.mean(a.elapsed_time(b) for a, b in bwd_ms) if not w["fwd_only"] else 0.0
+
+    # ---- end to end through the autograd entry points, host buffers -----------------
+    e2e = None
+    if not args.no_e2e:
+        h2d = sum(t.numel() * t.element_size() for t in host)
+        d2h = 4 + (0 if w["fwd_only"] else h2d)
+        set_strict_masked_grads(False)      # SMVecMatMul is upstream: the masked-block gradient is exactly zero
+        host_grads = [torch.empty_like(t).pin_memory() for t in host]
+        host_loss = torch.empty((), dtype=torch.float32).pin_memory()
+
+        def e2e_step():
+            xs = [t.to(device, non_blocking=True) for t in host]
+            if w["fwd_only"]:
+                with torch.no_grad():
+                    out, denom = UniversalAttention.apply(*xs)
+                    merged = SMVecMatMul.apply(out, denom)
+                host_loss.copy_(merged.float().pow(2).sum(), non_blocking=True)
+            else:
+                xs = [t.requires_grad_() for t in xs]
+                out, denom = UniversalAttention.apply(*xs)
+                merged = SMVecMatMul.apply(out, denom)
+                loss = merged.float().pow(2).sum()
+                loss.backward()
+                host_loss.copy_(loss.detach(), non_blocking=True)
+                for hg, x in zip(host_grads, xs):
+                    hg.copy_(x.grad, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        for _ in range(2):
+            e2e_step()
+        barrier()
+        a, b = ev(), ev()
+        a.record()
+        for _ in range(K):
+            e2e_step()
+        b.record()
+        barrier()
+        e_ms = a.elapsed_time(b)
+        if world > 1:
+            tt = torch.tensor([e_ms], device=device, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            e_ms = tt.item()
+        set_strict_masked_grads(True)
+        e2e = {"value": tokens / (e_ms / K * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms / K,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "path": "UniversalAttention.apply -> SMVecMatMul.apply -> pow(2).sum() -> backward (main.py:55-62 flow)"}
+
+    if rank == 0:
+        peaks, peak_src = load_peaks()
+        dom_is_bwd = bwd_avg >= fwd_avg
+        dom_f, dom_ms = (f_bwd, bwd_avg) if dom_is_bwd else (f_fwd, fwd_avg)
+        achieved = dom_f / (dom_ms * 1e-3) / 1e12
+        peak = peaks["bf16_tflops_sustained"]
+        line = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": w["dtype"], "data": "synthetic",
+            "config": {"workload": f"{args.workload}: B={B} (per GPU) H_kv={H} R={R} L={L} chunk={c} D={D} {w['dtype']} "
+                                   f"fwd{'' if w['fwd_only'] else '+bwd'}, random upstream grads, masked-block grads included",
+                       "global_batch": B * world, "seq_len": L, "parallelism": f"batch-shard x{world}, no collective",
+                       "l2_policy": "working set (out + g_out > 4 GB) exceeds the 126 MB L2; no explicit flush"},
+            "tflops": (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12,
+            "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms_per_step * 1e-3) / 1e12 / peak,
+            "fwd_ms": fwd_avg, "bwd_ms": bwd_avg,
+            "gpu_launches": K * (1 + (0 if w["fwd_only"] else 6)),
+            "clocks": clocks,
+            "roofline": {"kernel": "ua backward" if dom_is_bwd else "ua forward", "bound": "tensor",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "traffic": None, "peak_source": f"{peak_src} (bf16_tflops_sustained)",
+                         "algorithmic_flops_per_launch": dom_f,
+                         "hbm_view": {"bytes": b_bwd if dom_is_bwd else b_fwd,
+                                      "achieved_gbs": (b_bwd if dom_is_bwd else b_fwd) / (dom_ms * 1e-3) / 1e9,
+                                      "peak_gbs": peaks["hbm_gbs"]}},
+            "e2e": e2e,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            val, t_unit, sample = cpu_reference_step_time(w, 2, 1)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                                    "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,134 @@
+/*
+ * C ABI of the B200 (sm_100a) Universal Attention library  --  libua_b200.so
+ *
+ * Plain pointers and sizes only; every pointer is DEVICE memory owned by the
+ * caller, every call is asynchronous on the given CUDA stream (passed as a
+ * void* holding a cudaStream_t; NULL = the default stream), nothing is
+ * allocated, nothing synchronises.  Return value: 0 on success, otherwise a
+ * UA_ERR_* code (ua_error_string() gives the text).  The library keeps no
+ * state between calls and may be called from any host thread.
+ *
+ * These entry points are what a binding of the reference's operator boundary
+ * attaches to.  Reference interfaces they replace:
+ *   - UniversalAttention.forward / .backward, 1-D signature
+ *       universal_attention_autograd.py:9-38, :47-99
+ *   - UniversalAttention2.forward / .backward, 2-D signature
+ *       universal_attention_autograd.py:104-163, :172-276
+ *   - the Triton launchers _universal_attention_fwd / _universal_attention_bwd
+ *       Universal_Attention/triton/universal_attention_kernel.py:192-239, :793-862
+ *   - SMVecMatMul (merge over key chunks)
+ *       universal_attention_autograd.py:278-297
+ *
+ * Tensor layouts.  b = batch, h = kv heads, r = query heads per kv head,
+ * n = key chunks, c = keys per chunk, L = n*c rows, d = head dim.
+ *   kc, vc        (b,h,n,c,d)   contiguous                    [dtype]
+ *   xq            (b,h,r,L,d)   contiguous (the 2-D form (b,h,r,_n,_c,d) is the same memory)
+ *   static_src    (b,h,n,c)     gates in (0,1)                [gate_dtype]
+ *   static_dest   (b,h,L)       gates in (0,1)                [gate_dtype]
+ *   out_cm        (b,h,n,r,L,d) "chunk-major": the reference's out (b,h,r,L,d,n)
+ *                               is out_cm viewed with its axes permuted (0,1,3,4,5,2)
+ *   lse_cm        (b,h,n,r,L)   fp32 log-sum-exp per (row, key chunk); the
+ *                               reference's denom (b,h,r,L,n) is the (0,1,3,4,2) view
+ *   denom_cm      (b,h,n,r,L)   lse rounded to dtype (may be NULL)
+ */
+#ifndef UA_B200_H_
+#define UA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct UaDims {
+  int32_t batch;      /* b  */
+  int32_t kv_heads;   /* h  */
+  int32_t q_per_kv;   /* r  */
+  int32_t n_chunks;   /* n_ */
+  int32_t chunk;      /* c_ */
+  int32_t head_dim;   /* d  */
+} UaDims;
+
+enum { UA_F32 = 0, UA_BF16 = 1 };
+
+enum {
+  UA_OK = 0,
+  UA_ERR_BAD_DIMS = 1,       /* non-positive dims, chunk not a multiple of 16, head_dim not a multiple of 4 ... */
+  UA_ERR_BAD_DTYPE = 2,
+  UA_ERR_NULL_POINTER = 3,
+  UA_ERR_WORKSPACE = 4,      /* workspace missing, too small or not 256-byte aligned */
+  UA_ERR_UNSUPPORTED = 5,    /* no kernel for this shape (tile does not fit shared memory) */
+  UA_ERR_CUDA = 6,           /* a CUDA runtime call failed; cudaGetLastError() has the cause */
+  UA_ERR_ALIGNMENT = 7,      /* a tensor pointer is not 16-byte aligned */
+  UA_ERR_DEVICE = 8          /* wrong GPU architecture (needs compute capability 10.x) */
+};
+
+/* Flags for ua_fwd / ua_bwd. */
+enum {
+  /* Backward: skip the gradient that flows through fully masked blocks (rows
+   * before a key chunk, where the reference's softmax is uniform).  That
+   * gradient is exactly zero whenever SMVecMatMul consumes (out, denom), as in
+   * the reference driver (main.py:55-62); it is non-zero for arbitrary
+   * upstream gradients (universal_attention_kernel.py:1261-1262). */
+  UA_FLAG_SKIP_MASKED_GRADS = 1,
+  /* Forward: do not write the fully masked blocks of out/lse/denom (the caller
+   * promises never to read them). */
+  UA_FLAG_SKIP_MASKED_FILL = 2,
+  /* Force the generic fp32 SIMT kernels even where a tensor-core kernel exists. */
+  UA_FLAG_FORCE_SIMT = 4
+};
+
+int ua_version(void);
+const char* ua_error_string(int code);
+
+/* Bytes of scratch ua_fwd / ua_bwd need for these dims (256-byte aligned
+ * device memory, contents irrelevant on entry, garbage on exit). */
+size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags);
+size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags);
+
+/* Forward.  Replaces UniversalAttention(2).forward (universal_attention_autograd.py:9-38,
+ * :104-163) and _universal_attention_fwd (universal_attention_kernel.py:192-239).
+ * Writes out_cm, lse_cm and, if not NULL, denom_cm. */
+int ua_fwd(const UaDims* dims, int dtype, int gate_dtype,
+           const void* kc, const void* vc, const void* xq,
+           const void* static_src, const void* static_dest,
+           void* out_cm, float* lse_cm, void* denom_cm,
+           void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* Backward.  Replaces UniversalAttention(2).backward (universal_attention_autograd.py:47-99,
+ * :172-276) and _universal_attention_bwd (universal_attention_kernel.py:793-862).
+ * Only the five inputs are needed (everything is recomputed, as the reference
+ * does: universal_attention_autograd.py:166-169).  g_out_cm has the layout of
+ * out_cm, g_denom_cm that of lse_cm with element type g_denom_dtype (the
+ * reference receives fp32 there under mixed precision, :48).  Gradients have
+ * the layout and dtype of their inputs and are overwritten. */
+int ua_bwd(const UaDims* dims, int dtype, int gate_dtype,
+           const void* kc, const void* vc, const void* xq,
+           const void* static_src, const void* static_dest,
+           const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype,
+           void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+           void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* Layout converters between chunk-major storage and the reference's contiguous
+ * layouts: out (b,h,r,L,d,n) <-> out_cm (b,h,n,r,L,d), with inner = d; and
+ * denom (b,h,r,L,n) <-> denom_cm (b,h,n,r,L) with inner = 1.  Element size
+ * elem_bytes in {2,4}.  to_reference != 0: chunk-major -> reference layout. */
+int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference,
+                const void* src, void* dst, void* stream);
+
+/* Merge over key chunks on chunk-major storage: SMVecMatMul.forward
+ * (universal_attention_autograd.py:280-283): merged (b,h,r,L,d) =
+ * sum_i softmax_i(lse)[i] * out[..., i].  weights are taken from lse_cm (fp32). */
+int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
+                 void* merged, void* stream);
+
+/* SMVecMatMul.backward (universal_attention_autograd.py:291-297) producing
+ * chunk-major gradients: g_out_cm (dtype) and g_lse_cm (fp32). */
+int ua_merge_bwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
+                 const void* g_merged, void* g_out_cm, float* g_lse_cm, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UA_B200_H_ */

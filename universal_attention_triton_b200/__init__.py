@@ -1,0 +1,13 @@
+"""Universal Attention for NVIDIA B200 (sm_100a): hand-written CUDA kernels
+behind the reference's autograd entry points."""
+from . import _lib, ops  # noqa: F401
+from .universal_attention_autograd import (  # noqa: F401
+    SMVecMatMul,
+    UniversalAttention,
+    UniversalAttention2,
+    set_output_layout,
+    set_strict_masked_grads,
+)
+
+__all__ = ["UniversalAttention", "UniversalAttention2", "SMVecMatMul", "set_output_layout",
+           "set_strict_masked_grads", "ops"]

@@ -1,0 +1,68 @@
+"""ctypes binding of libua_b200.so (the C ABI declared in include/ua_b200.h).
+
+There is no fallback: if the library cannot be loaded every operator raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+PKG_DIR = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG_DIR, "libua_b200.so")
+
+UA_F32, UA_BF16 = 0, 1
+FLAG_SKIP_MASKED_GRADS = 1
+FLAG_SKIP_MASKED_FILL = 2
+FLAG_FORCE_SIMT = 4
+
+
+class UaDims(ctypes.Structure):
+    _fields_ = [("batch", ctypes.c_int32), ("kv_heads", ctypes.c_int32), ("q_per_kv", ctypes.c_int32),
+                ("n_chunks", ctypes.c_int32), ("chunk", ctypes.c_int32), ("head_dim", ctypes.c_int32)]
+
+
+class UaLibraryError(RuntimeError):
+    pass
+
+
+_vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
+_dp = ctypes.POINTER(UaDims)
+
+# name -> (restype, argtypes); every symbol include/ua_b200.h declares
+SIGNATURES = {
+    "ua_version": (_i, []),
+    "ua_error_string": (ctypes.c_char_p, [_i]),
+    "ua_fwd_workspace_bytes": (_sz, [_dp, _i, _i]),
+    "ua_bwd_workspace_bytes": (_sz, [_dp, _i, _i]),
+    "ua_fwd": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "ua_bwd": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "ua_relayout": (_i, [_dp, _i, _i, _i, _vp, _vp, _vp]),
+    "ua_merge_fwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp]),
+    "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once; raises UaLibraryError when it is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise UaLibraryError(
+            f"{LIB_PATH} is missing: build it with `python -m universal_attention_triton_b200.build` "
+            "(there is no CPU or PyTorch fallback for the Universal Attention kernels)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str):
+    if code != 0:
+        msg = load().ua_error_string(code).decode()
+        raise UaLibraryError(f"{what} failed: {msg} (code {code})")

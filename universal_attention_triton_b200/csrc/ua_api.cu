@@ -1,0 +1,272 @@
+// C ABI of libua_b200.so: argument checking and kernel dispatch.
+// Declarations and the reference interfaces they replace: include/ua_b200.h.
+#include "../../include/ua_b200.h"
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include "ua_aux.cuh"
+#include "ua_simt.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr size_t kMaxDynSmem = 227 * 1024;
+
+inline size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+int check_dims(const UaDims* d) {
+  if (!d) return UA_ERR_NULL_POINTER;
+  if (d->batch <= 0 || d->kv_heads <= 0 || d->q_per_kv <= 0 || d->n_chunks <= 0 || d->chunk <= 0 || d->head_dim <= 0)
+    return UA_ERR_BAD_DIMS;
+  if (d->chunk % 16 != 0 || d->head_dim % 4 != 0) return UA_ERR_BAD_DIMS;
+  return UA_OK;
+}
+
+ua::Shape to_shape(const UaDims* d) {
+  ua::Shape s;
+  s.B = d->batch; s.H = d->kv_heads; s.R = d->q_per_kv; s.N = d->n_chunks; s.C = d->chunk; s.D = d->head_dim;
+  s.L = s.N * s.C;
+  return s;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// rows per tile of the SIMT kernels: the largest of {32, 16} that divides the chunk and fits shared memory
+int simt_rows(int C, int D, bool bwd) {
+  const int cands[2] = {32, 16};
+  for (int rt : cands) {
+    if (C % rt) continue;
+    size_t need = bwd ? ua::simt::bwd_smem_bytes(C, D, rt) : ua::simt::fwd_smem_bytes(C, D, rt);
+    if (need <= kMaxDynSmem) return rt;
+  }
+  return 0;
+}
+
+struct BwdWorkspace {
+  size_t off_dk, off_dv, off_dq, off_ds, off_dt, off_carry, acc_bytes, total;
+};
+
+BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
+  BwdWorkspace w;
+  const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
+  size_t o = 0;
+  w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
+  w.off_dv = o; o = align_up(o + BH * s.L * s.D * f, 256);
+  w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
+  w.off_ds = o; o = align_up(o + BH * s.L * f, 256);
+  w.off_dt = o; o = align_up(o + BH * s.L * f, 256);
+  w.acc_bytes = o;
+  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)(s.L / rt) * s.C * f, 256);
+  w.total = o;
+  return w;
+}
+
+template <typename T, typename TG>
+int launch_simt_fwd(const ua::simt::FwdParams& p, cudaStream_t st) {
+  size_t smem = ua::simt::fwd_smem_bytes(p.s.C, p.s.D, p.rt);
+  auto kern = ua::simt::fwd_kernel<T, TG>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return UA_ERR_CUDA;
+  kern<<<p.s.B * p.s.H * p.s.N, ua::simt::kThreads, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+template <typename T, typename TG>
+int launch_simt_bwd(const ua::simt::BwdParams& p, cudaStream_t st) {
+  size_t smem = ua::simt::bwd_smem_bytes(p.s.C, p.s.D, p.rt);
+  auto kern = ua::simt::bwd_kernel<T, TG>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return UA_ERR_CUDA;
+  kern<<<p.s.B * p.s.H * p.s.N, ua::simt::kThreads, smem, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+template <typename T>
+int launch_convert(const float* src, void* dst, size_t n, cudaStream_t st) {
+  int blocks = (int)((n + 1023) / 1024);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  ua::simt::convert_kernel<T><<<blocks, 256, 0, st>>>(src, static_cast<T*>(dst), n);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int convert_any(int dtype, const float* src, void* dst, size_t n, cudaStream_t st) {
+  return dtype == UA_F32 ? launch_convert<float>(src, dst, n, st) : launch_convert<bf16>(src, dst, n, st);
+}
+
+bool dtype_ok(int dtype, int gate_dtype) {
+  if (dtype != UA_F32 && dtype != UA_BF16) return false;
+  if (gate_dtype != UA_F32 && gate_dtype != UA_BF16) return false;
+  if (dtype == UA_F32 && gate_dtype == UA_BF16) return false;
+  return true;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ua_version(void) { return 1; }
+
+const char* ua_error_string(int code) {
+  switch (code) {
+    case UA_OK: return "ok";
+    case UA_ERR_BAD_DIMS: return "bad dims (all > 0, chunk a multiple of 16, head_dim a multiple of 4)";
+    case UA_ERR_BAD_DTYPE: return "unsupported dtype combination";
+    case UA_ERR_NULL_POINTER: return "null pointer argument";
+    case UA_ERR_WORKSPACE: return "workspace missing, too small or not 256-byte aligned";
+    case UA_ERR_UNSUPPORTED: return "no kernel for this shape";
+    case UA_ERR_CUDA: return "CUDA runtime error";
+    case UA_ERR_ALIGNMENT: return "tensor pointer not 16-byte aligned";
+    case UA_ERR_DEVICE: return "device is not compute capability 10.x";
+    default: return "unknown error code";
+  }
+}
+
+size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
+  (void)dims; (void)dtype; (void)flags;
+  return 0;
+}
+
+size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
+  (void)dtype; (void)flags;
+  if (check_dims(dims) != UA_OK) return 0;
+  ua::Shape s = to_shape(dims);
+  int rt = simt_rows(s.C, s.D, true);
+  if (!rt) return 0;
+  return bwd_layout(s, rt).total;
+}
+
+int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+           const void* static_src, const void* static_dest, void* out_cm, float* lse_cm, void* denom_cm,
+           void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  (void)workspace; (void)workspace_bytes;
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq || !static_src || !static_dest || !out_cm || !lse_cm) return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(out_cm)) return UA_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ua::Shape s = to_shape(dims);
+
+  ua::simt::FwdParams p;
+  p.s = s; p.kc = kc; p.vc = vc; p.xq = xq; p.ssrc = static_src; p.sdest = static_dest;
+  p.out = out_cm; p.lse = lse_cm; p.denom = denom_cm;
+  p.skip_masked_fill = (flags & UA_FLAG_SKIP_MASKED_FILL) ? 1 : 0;
+  p.rt = simt_rows(s.C, s.D, false);
+  if (!p.rt) return UA_ERR_UNSUPPORTED;
+  if (dtype == UA_F32) return launch_simt_fwd<float, float>(p, st);
+  if (gate_dtype == UA_F32) return launch_simt_fwd<bf16, float>(p, st);
+  return launch_simt_fwd<bf16, bf16>(p, st);
+}
+
+int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+           const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
+           int g_denom_dtype, void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+           void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (g_denom_dtype != UA_F32 && g_denom_dtype != dtype) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq || !static_src || !static_dest || !g_out_cm || !g_denom_cm || !dkc || !dvc || !dxq ||
+      !dstatic_src || !dstatic_dest)
+    return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(g_out_cm)) return UA_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  ua::Shape s = to_shape(dims);
+  const int rt = simt_rows(s.C, s.D, true);
+  if (!rt) return UA_ERR_UNSUPPORTED;
+  BwdWorkspace w = bwd_layout(s, rt);
+  if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
+
+  ua::simt::BwdParams p;
+  p.s = s; p.kc = kc; p.vc = vc; p.xq = xq; p.ssrc = static_src; p.sdest = static_dest;
+  p.g_out = g_out_cm; p.g_denom = g_denom_cm; p.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+  p.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
+  p.acc_dv = reinterpret_cast<float*>(ws + w.off_dv);
+  p.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
+  p.acc_ds = reinterpret_cast<float*>(ws + w.off_ds);
+  p.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+  p.carry = reinterpret_cast<float*>(ws + w.off_carry);
+  p.rt = rt;
+  p.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
+  if (dtype == UA_F32) e = launch_simt_bwd<float, float>(p, st);
+  else if (gate_dtype == UA_F32) e = launch_simt_bwd<bf16, float>(p, st);
+  else e = launch_simt_bwd<bf16, bf16>(p, st);
+  if (e) return e;
+
+  const size_t BH = (size_t)s.B * s.H;
+  if ((e = convert_any(dtype, p.acc_dk, dkc, BH * s.L * s.D, st))) return e;
+  if ((e = convert_any(dtype, p.acc_dv, dvc, BH * s.L * s.D, st))) return e;
+  if ((e = convert_any(dtype, p.acc_dq, dxq, BH * s.R * s.L * s.D, st))) return e;
+  if ((e = convert_any(gate_dtype, p.acc_ds, dstatic_src, BH * s.L, st))) return e;
+  if ((e = convert_any(gate_dtype, p.acc_dt, dstatic_dest, BH * s.L, st))) return e;
+  return UA_OK;
+}
+
+int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference, const void* src, void* dst,
+                void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!src || !dst) return UA_ERR_NULL_POINTER;
+  if (inner <= 0) return UA_ERR_BAD_DIMS;
+  if (elem_bytes != 2 && elem_bytes != 4) return UA_ERR_BAD_DTYPE;
+  ua::Shape s = to_shape(dims);
+  const long long X = (long long)s.L * inner;
+  const long long G = (long long)s.B * s.H * s.R;
+  if (G > 65535) return UA_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)((X + 31) / 32), (unsigned)((s.N + 31) / 32), (unsigned)G);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (elem_bytes == 2)
+    ua::aux::relayout_kernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(src),
+                                                             static_cast<uint16_t*>(dst), s.N, s.R, X, to_reference);
+  else
+    ua::aux::relayout_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(src),
+                                                             static_cast<uint32_t*>(dst), s.N, s.R, X, to_reference);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, void* merged, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
+  if (!out_cm || !lse_cm || !merged) return UA_ERR_NULL_POINTER;
+  ua::Shape s = to_shape(dims);
+  const long long rows = (long long)s.B * s.H * s.R * s.L;
+  long long blocks = (rows + ua::aux::kMergeWarps - 1) / ua::aux::kMergeWarps;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == UA_F32)
+    ua::aux::merge_fwd_kernel<float><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, 0, st>>>(
+        static_cast<const float*>(out_cm), lse_cm, static_cast<float*>(merged), s.B * s.H, s.N, s.R, s.L, s.D);
+  else
+    ua::aux::merge_fwd_kernel<bf16><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, 0, st>>>(
+        static_cast<const bf16*>(out_cm), lse_cm, static_cast<bf16*>(merged), s.B * s.H, s.N, s.R, s.L, s.D);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_merge_bwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, const void* g_merged,
+                 void* g_out_cm, float* g_lse_cm, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
+  if (!out_cm || !lse_cm || !g_merged || !g_out_cm || !g_lse_cm) return UA_ERR_NULL_POINTER;
+  ua::Shape s = to_shape(dims);
+  const long long rows = (long long)s.B * s.H * s.R * s.L;
+  long long blocks = (rows + ua::aux::kMergeWarps - 1) / ua::aux::kMergeWarps;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  const size_t smem = sizeof(float) * ua::aux::kMergeWarps * 2 * s.N;
+  if (smem > 48 * 1024) return UA_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == UA_F32)
+    ua::aux::merge_bwd_kernel<float><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, smem, st>>>(
+        static_cast<const float*>(out_cm), lse_cm, static_cast<const float*>(g_merged), static_cast<float*>(g_out_cm),
+        g_lse_cm, s.B * s.H, s.N, s.R, s.L, s.D);
+  else
+    ua::aux::merge_bwd_kernel<bf16><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, smem, st>>>(
+        static_cast<const bf16*>(out_cm), lse_cm, static_cast<const bf16*>(g_merged), static_cast<bf16*>(g_out_cm),
+        g_lse_cm, s.B * s.H, s.N, s.R, s.L, s.D);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -1,0 +1,206 @@
+"""Tensor-level calls into the CUDA library on chunk-major storage.
+
+Chunk-major storage keeps the key-chunk axis outside the row axis:
+``out_cm (b,h,n,r,L,d)`` and ``lse_cm (b,h,n,r,L)``.  The reference's
+``out (b,h,r,L,d,n)`` / ``denom (b,h,r,L,n)`` are permuted views of them
+(``as_reference_out`` / ``as_reference_denom``): same shape, dtype and values,
+different strides, so that every kernel reads and writes whole contiguous
+``(rows, d)`` tiles.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import UaDims
+
+
+def _dtype_code(t: torch.dtype) -> int:
+    if t == torch.float32:
+        return _lib.UA_F32
+    if t == torch.bfloat16:
+        return _lib.UA_BF16
+    raise TypeError(f"Universal Attention kernels support float32 and bfloat16, got {t}")
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("Universal Attention has no CPU path: tensors must live on a CUDA device")
+
+
+def make_dims(kc, xq):
+    b, h, n, c, d = kc.shape
+    r = xq.shape[2]
+    return UaDims(b, h, r, n, c, d)
+
+
+def _gate_cast(g, dtype):
+    # kernels take gates either in the q/k/v dtype or in fp32
+    if g.dtype == dtype or g.dtype == torch.float32:
+        return g.contiguous()
+    return g.float().contiguous()
+
+
+def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0):
+    """Returns (out_cm, lse_cm fp32, denom_cm).  ``denom_cm`` is ``lse_cm`` itself in fp32 mode."""
+    _require_cuda(kc, vc, xq, static_src, static_dest)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq.shape[2]
+    L = n * c
+    dt = xq.dtype
+    code = _dtype_code(dt)
+    kc, vc = kc.contiguous(), vc.contiguous()
+    q = xq.reshape(b, h, r, L, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest.reshape(b, h, L), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    dims = UaDims(b, h, r, n, c, d)
+    with torch.cuda.device(kc.device):
+        out_cm = torch.empty(b, h, n, r, L, d, dtype=dt, device=kc.device)
+        lse_cm = torch.empty(b, h, n, r, L, dtype=torch.float32, device=kc.device)
+        denom_cm = lse_cm if dt == torch.float32 else torch.empty(b, h, n, r, L, dtype=dt, device=kc.device)
+        ws_bytes = lib.ua_fwd_workspace_bytes(ctypes.byref(dims), code, flags)
+        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=kc.device) if ws_bytes else None
+        rc = lib.ua_fwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kc), _ptr(vc), _ptr(q), _ptr(ss), _ptr(sd),
+                        _ptr(out_cm), _ptr(lse_cm), _ptr(None if denom_cm is lse_cm else denom_cm),
+                        _ptr(ws), ws_bytes, flags, _stream())
+    _lib.check(rc, "ua_fwd")
+    return out_cm, lse_cm, denom_cm
+
+
+def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0):
+    """Gradients (dkc, dvc, dxq, dstatic_src, dstatic_dest) shaped and typed like the inputs."""
+    _require_cuda(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq.shape[2]
+    L = n * c
+    dt = xq.dtype
+    code = _dtype_code(dt)
+    kcc, vcc = kc.contiguous(), vc.contiguous()
+    q = xq.reshape(b, h, r, L, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest.reshape(b, h, L), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    g_out_cm = g_out_cm.to(dt).contiguous()
+    if g_denom_cm.dtype not in (torch.float32, dt):
+        g_denom_cm = g_denom_cm.float()
+    g_denom_cm = g_denom_cm.contiguous()
+    dims = UaDims(b, h, r, n, c, d)
+    with torch.cuda.device(kc.device):
+        dkc = torch.empty_like(kcc)
+        dvc = torch.empty_like(vcc)
+        dxq = torch.empty_like(q)
+        dss = torch.empty_like(ss)
+        dsd = torch.empty_like(sd)
+        ws_bytes = lib.ua_bwd_workspace_bytes(ctypes.byref(dims), code, flags)
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
+        rc = lib.ua_bwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
+                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype),
+                        _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss), _ptr(dsd), _ptr(ws), ws_bytes, flags, _stream())
+    _lib.check(rc, "ua_bwd")
+    return (dkc.view(kc.shape), dvc.view(vc.shape), dxq.view(xq.shape),
+            dss.to(static_src.dtype).view(static_src.shape), dsd.to(static_dest.dtype).view(static_dest.shape))
+
+
+def as_reference_out(out_cm):
+    """(b,h,n,r,L,d) storage viewed as the reference's out (b,h,r,L,d,n)."""
+    return out_cm.permute(0, 1, 3, 4, 5, 2)
+
+
+def as_reference_denom(denom_cm):
+    """(b,h,n,r,L) storage viewed as the reference's denom (b,h,r,L,n)."""
+    return denom_cm.permute(0, 1, 3, 4, 2)
+
+
+def out_to_chunk_major(t):
+    """Reference-shaped out / g_out (b,h,r,L,d,n), any strides -> contiguous (b,h,n,r,L,d)."""
+    v = t.permute(0, 1, 5, 2, 3, 4)
+    return v if v.is_contiguous() else _relayout(t, inner=t.shape[4], to_reference=False)
+
+
+def denom_to_chunk_major(t):
+    """Reference-shaped denom / g_denom (b,h,r,L,n), any strides -> contiguous (b,h,n,r,L)."""
+    v = t.permute(0, 1, 4, 2, 3)
+    return v if v.is_contiguous() else _relayout(t, inner=1, to_reference=False)
+
+
+def _relayout(t, inner: int, to_reference: bool):
+    _require_cuda(t)
+    lib = _lib.load()
+    if t.element_size() not in (2, 4):
+        raise TypeError("relayout handles 2- and 4-byte elements")
+    if to_reference:      # t is chunk-major (b,h,n,r,L[,d])
+        b, h, n, r, L = t.shape[:5]
+        src = t.contiguous()
+        dst = torch.empty((b, h, r, L) + ((inner,) if t.dim() == 6 else ()) + (n,), dtype=t.dtype, device=t.device)
+    else:                 # t is reference-shaped (b,h,r,L[,d],n)
+        b, h, r, L = t.shape[:4]
+        n = t.shape[-1]
+        src = t.contiguous()
+        dst = torch.empty((b, h, n, r, L) + ((inner,) if t.dim() == 6 else ()), dtype=t.dtype, device=t.device)
+    dims = UaDims(b, h, r, n, 16, 4)      # chunk/head_dim are not used by the converter; only L = n*chunk matters
+    # the converter takes L through dims: encode L as n_chunks*chunk
+    if L % n:
+        raise ValueError("rows must be a multiple of the number of key chunks")
+    dims.chunk = L // n
+    if dims.chunk % 16:
+        raise ValueError("chunk must be a multiple of 16")
+    with torch.cuda.device(t.device):
+        rc = lib.ua_relayout(ctypes.byref(dims), inner, t.element_size(), 1 if to_reference else 0,
+                             _ptr(src), _ptr(dst), _stream())
+    _lib.check(rc, "ua_relayout")
+    return dst
+
+
+def to_reference_layout(out_cm, denom_cm):
+    """Materialise the reference's contiguous (b,h,r,L,d,n) / (b,h,r,L,n) tensors."""
+    return (_relayout(out_cm, inner=out_cm.shape[-1], to_reference=True),
+            _relayout(denom_cm, inner=1, to_reference=True))
+
+
+def merge_fwd_cm(out_cm, lse_cm):
+    """SMVecMatMul forward on chunk-major storage -> merged (b,h,r,L,d)."""
+    _require_cuda(out_cm, lse_cm)
+    lib = _lib.load()
+    b, h, n, r, L, d = out_cm.shape
+    dims = UaDims(b, h, r, n, L // n, d)
+    out_cm = out_cm.contiguous()
+    lse_cm = lse_cm.float().contiguous()
+    merged = torch.empty(b, h, r, L, d, dtype=out_cm.dtype, device=out_cm.device)
+    with torch.cuda.device(out_cm.device):
+        rc = lib.ua_merge_fwd(ctypes.byref(dims), _dtype_code(out_cm.dtype), _ptr(out_cm), _ptr(lse_cm), _ptr(merged), _stream())
+    _lib.check(rc, "ua_merge_fwd")
+    return merged
+
+
+def merge_bwd_cm(out_cm, lse_cm, g_merged):
+    """SMVecMatMul backward on chunk-major storage -> (g_out_cm, g_lse_cm fp32)."""
+    _require_cuda(out_cm, lse_cm, g_merged)
+    lib = _lib.load()
+    b, h, n, r, L, d = out_cm.shape
+    dims = UaDims(b, h, r, n, L // n, d)
+    out_cm = out_cm.contiguous()
+    lse_cm = lse_cm.float().contiguous()
+    g_merged = g_merged.to(out_cm.dtype).contiguous()
+    g_out_cm = torch.empty_like(out_cm)
+    g_lse_cm = torch.empty_like(lse_cm)
+    with torch.cuda.device(out_cm.device):
+        rc = lib.ua_merge_bwd(ctypes.byref(dims), _dtype_code(out_cm.dtype), _ptr(out_cm), _ptr(lse_cm), _ptr(g_merged),
+                              _ptr(g_out_cm), _ptr(g_lse_cm), _stream())
+    _lib.check(rc, "ua_merge_bwd")
+    return g_out_cm, g_lse_cm

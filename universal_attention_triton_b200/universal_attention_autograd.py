@@ -1,0 +1,124 @@
+"""Drop-in autograd entry points of the Universal Attention operator, backed by
+the sm_100a CUDA library.  Same names, argument layout, output shapes/dtypes
+and gradients as the reference module of the same name:
+
+* ``UniversalAttention``   1-D signature   (universal_attention_autograd.py:7-99)
+* ``UniversalAttention2``  2-D signature   (universal_attention_autograd.py:102-276)
+* ``SMVecMatMul``          merge over key chunks (universal_attention_autograd.py:278-297)
+
+    out, denom = UniversalAttention.apply(kc, vc, xq, static_src, static_dest)
+
+``out (b,h,r,L,d,n_)`` and ``denom (b,h,r,L,n_)`` have the reference's shapes and
+dtypes.  By default they are permuted views of chunk-major storage (see
+``ops.py``); ``set_output_layout("reference")`` makes them contiguous in the
+reference's order at the cost of one extra pass over ``out``.
+
+Only the five inputs are saved for backward; everything else is recomputed
+(universal_attention_autograd.py:41-44, :166-169).  Tensors must be CUDA
+tensors: there is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import torch
+from torch.autograd import Function
+
+from . import _lib, ops
+
+_OUTPUT_LAYOUT = "chunk_major"
+_STRICT_MASKED_GRADS = True
+
+
+def set_output_layout(layout: str) -> None:
+    """"chunk_major" (default; permuted views) or "reference" (contiguous (b,h,r,L,d,n_))."""
+    global _OUTPUT_LAYOUT
+    if layout not in ("chunk_major", "reference"):
+        raise ValueError(layout)
+    _OUTPUT_LAYOUT = layout
+
+
+def set_strict_masked_grads(on: bool) -> None:
+    """When off, backward skips the gradient through fully masked blocks (rows
+    before a key chunk).  That gradient is exactly zero when ``SMVecMatMul``
+    consumes ``(out, denom)``; it is not for arbitrary upstream gradients."""
+    global _STRICT_MASKED_GRADS
+    _STRICT_MASKED_GRADS = bool(on)
+
+
+def _forward(kc, vc, xq, static_src, static_dest):
+    out_cm, lse_cm, denom_cm = ops.forward_cm(kc, vc, xq, static_src, static_dest)
+    if _OUTPUT_LAYOUT == "reference":
+        return ops.to_reference_layout(out_cm, denom_cm)
+    return ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm)
+
+
+def _backward(ctx, g_out, g_denom):
+    kc, vc, xq, static_src, static_dest = ctx.saved_tensors
+    flags = 0 if _STRICT_MASKED_GRADS else _lib.FLAG_SKIP_MASKED_GRADS
+    g_out_cm = ops.out_to_chunk_major(g_out)
+    g_denom_cm = ops.denom_to_chunk_major(g_denom)
+    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags)
+
+
+class UniversalAttention(Function):
+    """kc, vc (b,h,n,c,d); xq (b,h,r,l,d); static_src (b,h,n,c); static_dest (b,h,l)."""
+
+    @staticmethod
+    def forward(kc, vc, xq, static_src, static_dest):
+        b, h, r, l, d = xq.shape
+        _, _, n, c, _ = kc.shape
+        assert kc.shape == (b, h, n, c, d) and n * c == l
+        assert vc.shape == (b, h, n, c, d)
+        assert static_src.shape == (b, h, n, c)
+        assert static_dest.shape == (b, h, l)
+        return _forward(kc, vc, xq, static_src, static_dest)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        ctx.save_for_backward(*inputs)
+
+    @staticmethod
+    def backward(ctx, g_out, g_denom):
+        return _backward(ctx, g_out, g_denom)
+
+
+class UniversalAttention2(Function):
+    """kc, vc (b,h,n_,c_,d); xq (b,h,r,_n,_c,d); static_src (b,h,n_,c_); static_dest (b,h,_n,_c).
+    The row chunking (_n,_c) is only a view of the rows; the result does not depend on it."""
+
+    @staticmethod
+    def forward(kc, vc, xq, static_src, static_dest):
+        b, h, r, _n, _c, d = xq.shape
+        _, _, n_, c_, _ = kc.shape
+        assert kc.shape == (b, h, n_, c_, d) and n_ * c_ == _n * _c
+        assert vc.shape == (b, h, n_, c_, d)
+        assert static_src.shape == (b, h, n_, c_)
+        assert static_dest.shape == (b, h, _n, _c)
+        return _forward(kc, vc, xq, static_src, static_dest)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        ctx.save_for_backward(*inputs)
+
+    @staticmethod
+    def backward(ctx, g_out, g_denom):
+        return _backward(ctx, g_out, g_denom)
+
+
+class SMVecMatMul(Function):
+    """``mat (..., d, n)``, ``vec (..., n)`` -> ``sum_n softmax(vec)[n] * mat[..., n]``.
+    Takes the 6-D ``out`` and 5-D ``denom`` of the operator (any strides)."""
+
+    @staticmethod
+    def forward(mat, vec):
+        assert mat.dim() == 6 and vec.dim() == 5 and mat.shape[:4] == vec.shape[:4] and mat.shape[-1] == vec.shape[-1]
+        return ops.merge_fwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec))
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        ctx.save_for_backward(*inputs)
+
+    @staticmethod
+    def backward(ctx, g):
+        mat, vec = ctx.saved_tensors
+        g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g)
+        return ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
