@@ -61,7 +61,8 @@ enum {
   UA_ERR_UNSUPPORTED = 5,    /* no kernel for this shape (tile does not fit shared memory) */
   UA_ERR_CUDA = 6,           /* a CUDA runtime call failed; cudaGetLastError() has the cause */
   UA_ERR_ALIGNMENT = 7,      /* a tensor pointer is not 16-byte aligned */
-  UA_ERR_DEVICE = 8          /* wrong GPU architecture (needs compute capability 10.x) */
+  UA_ERR_DEVICE = 8,         /* wrong GPU architecture (needs compute capability 10.x) */
+  UA_ERR_TIMEOUT = 9         /* a bounded device-side wait ran out; reported by ua_workspace_status() */
 };
 
 /* Flags for ua_fwd / ua_bwd. */
@@ -83,7 +84,8 @@ int ua_version(void);
 const char* ua_error_string(int code);
 
 /* Bytes of scratch ua_fwd / ua_bwd need for these dims (256-byte aligned
- * device memory, contents irrelevant on entry, garbage on exit). */
+ * device memory, contents irrelevant on entry; the first word holds the
+ * status read by ua_workspace_status(), the rest is garbage on exit). */
 size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags);
 size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags);
 
@@ -109,6 +111,14 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype,
            const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype,
            void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
            void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* The kernels never trap and never spin without bound: a device-side wait that
+ * runs out makes the kernel give up and set a status word at the start of the
+ * workspace it was given.  ua_workspace_status() copies that word back and
+ * SYNCHRONISES the stream: 0 = every kernel of the last ua_fwd/ua_bwd call
+ * that used this workspace completed, UA_ERR_TIMEOUT otherwise.  No
+ * counterpart in the reference (its kernels have no device-side waits). */
+int ua_workspace_status(const void* workspace, void* stream);
 
 /* Layout converters between chunk-major storage and the reference's contiguous
  * layouts: out (b,h,r,L,d,n) <-> out_cm (b,h,n,r,L,d), with inner = d; and

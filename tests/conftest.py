@@ -3,6 +3,8 @@ import sys
 
 import pytest
 
+os.environ.setdefault("UA_CHECK_STATUS", "1")   # tests read the kernels' device status word after every call
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

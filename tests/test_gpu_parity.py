@@ -177,3 +177,49 @@ def test_merge_kernels_against_oracle():
     d_mat, d_vec = O.merge_backward(mat, vec, g)
     assert (m.grad.cpu() - d_mat).abs().max() <= 1e-5
     assert (v.grad.cpu() - d_vec).abs().max() <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(1, 2, 4, 1024, 128, 64), (2, 1, 1, 768, 128, 64), (1, 1, 3, 512, 128, 128),
+                                   (1, 2, 1, 384, 128, 128)])
+def test_tensor_core_forward_matches_simt_forward(shape):
+    """The tcgen05 forward against the generic fp32 SIMT forward of the same library, on the device."""
+    from universal_attention_triton_b200 import _lib, ops
+    B, H, R, L, c, D = shape
+    ins, _ = _bf16_case(*shape, seed=21)
+    cu = _cuda(*ins)
+    out_tc, lse_tc, den_tc = ops.forward_cm(*cu)
+    out_sm, lse_sm, den_sm = ops.forward_cm(*cu, flags=_lib.FLAG_FORCE_SIMT)
+    n = L // c
+    valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda()      # (n, L)
+    v5 = valid.view(1, 1, n, 1, L)
+    assert ((lse_tc - lse_sm).abs() * v5).max().item() <= 2e-2
+    assert torch.equal(lse_tc[~v5.expand_as(lse_tc)], lse_sm[~v5.expand_as(lse_sm)])
+    err = (out_tc.float() - out_sm.float()).abs()
+    bound = 2e-2 + out_sm.float().abs() * 2.0 ** -7
+    assert (err <= bound).all(), (err - bound).max().item()
+
+
+def test_tensor_core_forward_config2_shape_slice_against_oracle():
+    """A (b, h) slice of BASELINE config 2 (R=4, L=4096, chunk=128, D=64) against the CPU oracle."""
+    shape = (1, 1, 4, 4096, 128, 64)
+    B, H, R, L, c, D = shape
+    ua = _ua()
+    ins, ins32 = _bf16_case(*shape, seed=0)
+    ref_out, ref_denom, ref_lse = O.ua_forward(*ins32)
+    from universal_attention_triton_b200 import ops
+    out_cm, lse_cm, _ = ops.forward_cm(*_cuda(*ins))
+    out = ops.as_reference_out(out_cm).float().cpu()
+    lse = ops.as_reference_denom(lse_cm).cpu()
+    from tests._util import valid_row_mask
+    valid = valid_row_mask(L, L // c, c)
+    # far chunks are ill-conditioned in fp32 (the decay prefix reaches -2e4, where fp32 spacing is 2e-3
+    # and the reference's own 1-D and 2-D forms differ by 4e-3): compare the log-sum-exp relative to its size
+    dl = (lse - ref_lse).abs()
+    assert ((dl <= 2e-2 + 1e-5 * ref_lse.abs()) | ~valid).all(), (dl * valid).max().item()
+    err = (out - ref_out).abs()
+    bound = 2e-2 + ref_out.abs() * 2.0 ** -8
+    frac_bad = ((err > bound) & valid.view(L, 1, -1)).float().mean().item()
+    assert frac_bad <= 1e-5, frac_bad
+    merged = O.merge_forward(out, lse)
+    merged_ref = O.merge_forward(ref_out, ref_lse)
+    assert (merged - merged_ref).abs().max() <= 2e-2

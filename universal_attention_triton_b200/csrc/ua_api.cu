@@ -7,6 +7,7 @@
 
 #include "ua_aux.cuh"
 #include "ua_simt.cuh"
+#include "ua_sm100_host.cuh"
 
 namespace {
 
@@ -50,7 +51,7 @@ struct BwdWorkspace {
 BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
   BwdWorkspace w;
   const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
-  size_t o = 0;
+  size_t o = 256;   // [0, 256): status word
   w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.off_dv = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
@@ -117,13 +118,14 @@ const char* ua_error_string(int code) {
     case UA_ERR_CUDA: return "CUDA runtime error";
     case UA_ERR_ALIGNMENT: return "tensor pointer not 16-byte aligned";
     case UA_ERR_DEVICE: return "device is not compute capability 10.x";
+    case UA_ERR_TIMEOUT: return "a kernel gave up on a bounded device-side wait (results are invalid)";
     default: return "unknown error code";
   }
 }
 
 size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
   (void)dims; (void)dtype; (void)flags;
-  return 0;
+  return 256;   // status word
 }
 
 size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
@@ -138,14 +140,23 @@ size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
 int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
            const void* static_src, const void* static_dest, void* out_cm, float* lse_cm, void* denom_cm,
            void* workspace, size_t workspace_bytes, int flags, void* stream) {
-  (void)workspace; (void)workspace_bytes;
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
   if (!kc || !vc || !xq || !static_src || !static_dest || !out_cm || !lse_cm) return UA_ERR_NULL_POINTER;
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(out_cm)) return UA_ERR_ALIGNMENT;
+  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ua::Shape s = to_shape(dims);
+  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+
+  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::fwd_supported(s, dtype)) {
+    ua::sm100::FwdParams fp;
+    fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest;
+    fp.out = static_cast<bf16*>(out_cm); fp.lse = lse_cm; fp.denom = static_cast<bf16*>(denom_cm);
+    fp.status = static_cast<int*>(workspace);
+    return ua::sm100::launch_fwd(s, gate_dtype, kc, vc, xq, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
+  }
 
   ua::simt::FwdParams p;
   p.s = s; p.kc = kc; p.vc = vc; p.xq = xq; p.ssrc = static_src; p.sdest = static_dest;
@@ -202,6 +213,15 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
   if ((e = convert_any(gate_dtype, p.acc_ds, dstatic_src, BH * s.L, st))) return e;
   if ((e = convert_any(gate_dtype, p.acc_dt, dstatic_dest, BH * s.L, st))) return e;
   return UA_OK;
+}
+
+int ua_workspace_status(const void* workspace, void* stream) {
+  if (!workspace) return UA_ERR_NULL_POINTER;
+  int host = 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&host, workspace, sizeof(int), cudaMemcpyDeviceToHost, st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaStreamSynchronize(st) != cudaSuccess) return UA_ERR_CUDA;
+  return host == 0 ? UA_OK : UA_ERR_TIMEOUT;
 }
 
 int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference, const void* src, void* dst,

@@ -1,0 +1,448 @@
+// Tensor-core forward of the Universal Attention operator for sm_100a.
+//
+// bf16 inputs, key chunk = 128, head_dim D in {64, 128}.  One thread block owns
+// one key chunk (b, h, i) and sweeps the row tiles j = i .. n-1 (128 rows each)
+// upwards, so the per-key decay prefix is carried in registers.
+//
+//   G    = K_i  K_j^T    tcgen05.mma  M = keys, N = rows   (keys on TMEM lanes)
+//   S_r  = Q_rj K_i^T    tcgen05.mma  M = rows, N = keys   (rows on TMEM lanes)
+//   O_r  = P_r  V_i      tcgen05.mma  A = P (bf16, TMEM), B = V_i (MN-major smem)
+//
+// Warp roles (512 threads):
+//   warp 0      TMA producer: K_i, V_i once; K_j and Q_rj tiles through mbarrier rings
+//   warp 1      MMA issuer (one elected thread issues every tcgen05.mma / commit)
+//   warps 4-7   decay group: thread = key.  Reads G from TMEM, computes the
+//               log-retention, scans it along the rows in registers (carry kept
+//               across tiles), writes the prefix C^T[row][key] to shared memory.
+//   warps 8-15  two softmax groups alternating over (tile, r): thread = row.
+//               S + C, row max / sum in registers (no shuffles), P -> TMEM as
+//               bf16, then the epilogue O / l -> out and m + log l -> lse.
+//
+// The two reductions of the operator run along perpendicular axes of the tile
+// (scan along rows per key, softmax along keys per row); putting keys on lanes
+// for G and rows on lanes for S makes both of them thread-local, at the price
+// of one 64 KB shared-memory transpose of C per tile, shared by the R heads.
+//
+// Every mbarrier wait is bounded; on a timeout the block raises a shared abort
+// flag, every role leaves its loop, TMEM is freed and status[0] is set.
+#pragma once
+#include "ua_common.cuh"
+#include "ua_ptx.cuh"
+
+namespace ua {
+namespace sm100 {
+
+using namespace ua::ptx;
+
+struct FwdParams {
+  Shape s;
+  const void* ssrc;
+  const void* sdest;
+  __nv_bfloat16* out;    // chunk-major (b,h,n,r,L,d)
+  float* lse;            // (b,h,n,r,L)
+  __nv_bfloat16* denom;  // (b,h,n,r,L) or null
+  int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
+};
+
+template <int D>
+struct FwdCfg {
+  static constexpr int kTileBytes = 128 * D * 2;   // one [128][D] bf16 tile
+  static constexpr int kBoxBytes = 128 * 128;      // one TMA box: 128 rows x 64 elements
+  static constexpr int kBoxes = D / 64;
+  static constexpr int kKjStages = (D == 64) ? 2 : 1;
+  static constexpr int kQStages = 2;
+  static constexpr int kOBufs = (D == 64) ? 2 : 1;
+  static constexpr int oKi = 0;
+  static constexpr int oVi = oKi + kTileBytes;
+  static constexpr int oKj = oVi + kTileBytes;
+  static constexpr int oQ = oKj + kKjStages * kTileBytes;
+  static constexpr int oCs = oQ + kQStages * kTileBytes;
+  static constexpr int oT3 = oCs + 65536;
+  static constexpr int oBar = oT3 + 1024;
+  static constexpr int oMisc = oBar + 256;
+  static constexpr int kSmemBytes = oMisc + 64 + 1024;   // + slack to align the base to 1024 B
+  static constexpr uint32_t tG = 0, tS0 = 128, tS1 = 256, tO0 = 384, tO1 = 384 + D;
+};
+
+enum FwdBar {
+  kKvFull = 0, kKjFull = 1, kKjEmpty = 3, kQFull = 5, kQEmpty = 7, kGFull = 9, kGFree = 10, kCReady = 11, kCFree = 12,
+  kSFull = 13, kPReady = 15, kOFull = 17, kOFree = 19, kT3Ready = 21, kNumBars = 22
+};
+
+template <int D>
+struct FwdCtx {
+  uint8_t* smem;
+  uint32_t bars;      // shared address of barrier 0
+  uint32_t tmem;
+  volatile int* abort_flag;
+  int i, bh, ntiles;
+  __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
+  __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
+};
+
+// ------------------------------------------------------------------ producer --
+template <int D>
+__device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams& p, const CUtensorMap* tmK,
+                                             const CUtensorMap* tmV, const CUtensorMap* tmQ) {
+  using Cfg = FwdCfg<D>;
+  const int L = p.s.L, R = p.s.R;
+  const uint32_t sbase = smem_u32(c.smem);
+  const int krow = c.bh * L + c.i * 128;
+  mbar_expect_tx(c.bar(kKvFull), 2 * Cfg::kTileBytes);
+  for (int b = 0; b < Cfg::kBoxes; ++b) {
+    tma_load_2d(sbase + Cfg::oKi + b * Cfg::kBoxBytes, tmK, b * 64, krow, c.bar(kKvFull));
+    tma_load_2d(sbase + Cfg::oVi + b * Cfg::kBoxBytes, tmV, b * 64, krow, c.bar(kKvFull));
+  }
+  auto load_kj = [&](int T) -> bool {
+    const int ks = T % Cfg::kKjStages, u = T / Cfg::kKjStages;
+    if (u >= 1 && !c.wait(kKjEmpty + ks, u - 1)) return false;
+    mbar_expect_tx(c.bar(kKjFull + ks), Cfg::kTileBytes);
+    for (int b = 0; b < Cfg::kBoxes; ++b)
+      tma_load_2d(sbase + Cfg::oKj + ks * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmK, b * 64, c.bh * L + (c.i + T) * 128,
+                  c.bar(kKjFull + ks));
+    return true;
+  };
+  if (!load_kj(0)) return;
+  int t = 0;
+  for (int T = 0; T < c.ntiles; ++T) {
+    for (int r = 0; r < R; ++r, ++t) {
+      const int qs = t & 1, u = t >> 1;
+      if (u >= 1 && !c.wait(kQEmpty + qs, u - 1)) return;
+      mbar_expect_tx(c.bar(kQFull + qs), Cfg::kTileBytes);
+      for (int b = 0; b < Cfg::kBoxes; ++b)
+        tma_load_2d(sbase + Cfg::oQ + qs * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmQ, b * 64,
+                    (c.bh * R + r) * L + (c.i + T) * 128, c.bar(kQFull + qs));
+      if (r == 0 && T + 1 < c.ntiles && !load_kj(T + 1)) return;
+    }
+  }
+}
+
+// ---------------------------------------------------------------- MMA issuer --
+template <int D>
+__device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) {
+  using Cfg = FwdCfg<D>;
+  const int R = p.s.R;
+  const uint32_t sbase = smem_u32(c.smem);
+  constexpr uint32_t idesc_sq = idesc_bf16(128, 128, 0, 0);
+  constexpr uint32_t idesc_pv = idesc_bf16(128, D, 0, 1);
+  const uint32_t tS[2] = {c.tmem + Cfg::tS0, c.tmem + Cfg::tS1};
+  const uint32_t tO[2] = {c.tmem + Cfg::tO0, c.tmem + (Cfg::kOBufs == 2 ? Cfg::tO1 : Cfg::tO0)};
+
+  // D[128 x 128] = A[128][D] * B[128][D]^T, both K-major
+  auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const uint32_t off = (ks >> 2) * Cfg::kBoxBytes + (ks & 3) * 32;
+      mma_ss(d_tmem, smem_desc_sw128(a_addr + off, 16, 1024), smem_desc_sw128(b_addr + off, 16, 1024), idesc_sq, ks > 0);
+    }
+  };
+  auto issue_g = [&](int T) -> bool {
+    const int ks = T % Cfg::kKjStages, u = T / Cfg::kKjStages;
+    if (!c.wait(kKjFull + ks, u)) return false;
+    if (T >= 1 && !c.wait(kGFree, T - 1)) return false;
+    tc_fence_after();
+    issue_kmajor(c.tmem + Cfg::tG, sbase + Cfg::oKi, sbase + Cfg::oKj + ks * Cfg::kTileBytes);
+    tc_commit(c.bar(kGFull));
+    tc_commit(c.bar(kKjEmpty + ks));
+    return true;
+  };
+  auto issue_pv = [&](int tt) -> bool {
+    const int sb = tt & 1, ob = tt % Cfg::kOBufs;
+    if (!c.wait(kPReady + sb, tt >> 1)) return false;
+    // the O buffer must have been drained by the epilogue that used it last
+    // (barriers are per softmax group so that each waiter sees consecutive phases)
+    if (Cfg::kOBufs == 2) {
+      if (tt >= 2 && !c.wait(kOFree + sb, (tt >> 1) - 1)) return false;
+    } else {
+      if (tt >= 1 && !c.wait(kOFree + ((tt - 1) & 1), (tt - 1) >> 1)) return false;
+    }
+    tc_fence_after();
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks)
+      mma_ts(tO[ob], tS[sb] + ks * 8, smem_desc_sw128(sbase + Cfg::oVi + ks * 2048, Cfg::kBoxBytes, 1024), idesc_pv, ks > 0);
+    tc_commit(c.bar(kOFull + sb));
+    return true;
+  };
+
+  if (!c.wait(kKvFull, 0)) return;
+  if (!issue_g(0)) return;
+  int t = 0;
+  for (int T = 0; T < c.ntiles; ++T) {
+    for (int r = 0; r < R; ++r, ++t) {
+      const int qs = t & 1;
+      if (!c.wait(kQFull + qs, t >> 1)) return;
+      tc_fence_after();
+      issue_kmajor(tS[t & 1], sbase + Cfg::oQ + qs * Cfg::kTileBytes, sbase + Cfg::oKi);
+      tc_commit(c.bar(kSFull + (t & 1)));
+      tc_commit(c.bar(kQEmpty + qs));
+      if (t >= 1 && !issue_pv(t - 1)) return;
+      if (r == 0 && T + 1 < c.ntiles && !issue_g(T + 1)) return;
+    }
+  }
+  if (t >= 1) issue_pv(t - 1);
+}
+
+// --------------------------------------------------------------- decay group --
+template <int D, typename TG>
+__device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p) {
+  using Cfg = FwdCfg<D>;
+  const int L = p.s.L;
+  const int k = threadIdx.x & 127;
+  const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
+  const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
+  const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + k));
+  float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
+  uint8_t* sCs = c.smem + Cfg::oCs;
+  const float hi = clamp_hi();
+  const float kLn2 = 0.6931471805599453f;
+  float carry = 0.f;
+  for (int T = 0; T < c.ntiles; ++T) {
+    const int j = c.i + T;
+    float* t3buf = sT3 + (T & 1) * 128;
+    t3buf[k] = cbrtf(Num<TG>::ld(sd + j * 128 + k));
+    mbar_arrive(c.bar(kT3Ready));
+    if (!c.wait(kT3Ready, T)) return;
+    if (!c.wait(kGFull, T)) return;
+    tc_fence_after();
+    const bool diag = (T == 0);
+    float local = 0.f, cval = carry;
+#pragma unroll 1
+    for (int cb = 0; cb < 4; ++cb) {
+      uint32_t g[32];
+      tmem_ld32(c.tmem + Cfg::tG + lane_base + cb * 32, g);
+      tc_wait_ld();
+      if (cb == 3) {
+        tc_fence_before();
+        mbar_arrive(c.bar(kGFree));
+      }
+      float v[32];
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        const int q = cb * 32 + x;
+        const float gv = __uint_as_float(g[x]);
+        float a = gv > 0.f ? ex2(lg2(gv) * (2.0f / 3.0f)) * s3 * t3buf[q] : 0.f;
+        a = fminf(a, hi);
+        float ell = lg2(1.0f - a) * kLn2;
+        if (diag && q <= k) ell = 0.f;
+        local += ell;
+        cval = local + carry;
+        v[x] = (diag && q < k) ? mask_value() : cval;
+      }
+      if (cb == 0 && T >= 1 && !c.wait(kCFree, T - 1)) return;
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        const int q = cb * 32 + x;
+        *reinterpret_cast<float*>(sCs + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v[x];
+      }
+    }
+    carry = cval;
+    mbar_arrive(c.bar(kCReady));
+  }
+}
+
+// ------------------------------------------------------------ softmax groups --
+template <int D>
+__device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams& p, int me) {
+  using Cfg = FwdCfg<D>;
+  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int row = threadIdx.x & 127;
+  const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
+  const uint8_t* sCrow = c.smem + Cfg::oCs + row * 512;
+  const size_t chunk_id = (size_t)c.bh * N + c.i;
+  const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
+  int t = 0;
+  for (int T = 0; T < c.ntiles; ++T) {
+    // Every softmax thread observes every phase of c_ready and arrives on c_free exactly
+    // once per tile (after its last read of C in that tile), whether or not its group has
+    // a head to process in this tile; parity waits stay within one phase of the barrier.
+    if (!c.wait(kCReady, T)) return;
+    int last_r = -1;
+    for (int r = R - 1; r >= 0; --r)
+      if (((T * R + r) & 1) == me) { last_r = r; break; }
+    if (last_r < 0) mbar_arrive(c.bar(kCFree));
+    for (int r = 0; r < R; ++r, ++t) {
+      if ((t & 1) != me) continue;
+      const int sb = t & 1, ob = t % Cfg::kOBufs;
+      const uint32_t tS = c.tmem + (sb ? Cfg::tS1 : Cfg::tS0) + lane_base;
+      const uint32_t tO = c.tmem + ((Cfg::kOBufs == 2 && ob) ? Cfg::tO1 : Cfg::tO0) + lane_base;
+      if (!c.wait(kSFull + sb, t >> 1)) return;
+      tc_fence_after();
+      // pass 1: s = S + C (written back to TMEM), row max
+      float m = -INFINITY;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t s[32];
+        tmem_ld32(tS + cb * 32, s);
+        tc_wait_ld();
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int chunk = cb * 8 + u;
+          const float4 cv = *reinterpret_cast<const float4*>(sCrow + (((chunk ^ (row & 7)) & 31) << 4));
+          float a0 = __uint_as_float(s[u * 4 + 0]) + cv.x, a1 = __uint_as_float(s[u * 4 + 1]) + cv.y;
+          float a2 = __uint_as_float(s[u * 4 + 2]) + cv.z, a3 = __uint_as_float(s[u * 4 + 3]) + cv.w;
+          m = fmaxf(m, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
+          s[u * 4 + 0] = __float_as_uint(a0); s[u * 4 + 1] = __float_as_uint(a1);
+          s[u * 4 + 2] = __float_as_uint(a2); s[u * 4 + 3] = __float_as_uint(a3);
+        }
+        tmem_st32(tS + cb * 32, s);
+      }
+      tc_wait_st();
+      if (r == last_r) mbar_arrive(c.bar(kCFree));
+      // pass 2: P = exp(s - m) as bf16 into the first 64 columns of the S buffer
+      const float mb = m * kLog2e;
+      float l = 0.f;
+#pragma unroll 1
+      for (int cb = 0; cb < 4; ++cb) {
+        uint32_t s[32];
+        tmem_ld32(tS + cb * 32, s);
+        tc_wait_ld();
+        uint32_t pk[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float p0 = ex2(fmaf(__uint_as_float(s[2 * u]), kLog2e, -mb));
+          const float p1 = ex2(fmaf(__uint_as_float(s[2 * u + 1]), kLog2e, -mb));
+          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          // the row sum uses the rounded probabilities, the values the tensor core multiplies
+          l += __bfloat162float(h.x) + __bfloat162float(h.y);
+          pk[u] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        tmem_st16(tS + cb * 16, pk);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(c.bar(kPReady + sb));
+      const int qg = (c.i + T) * 128 + row;
+      const float lse = m + lg2(l) * kLn2;
+      const size_t orow = (chunk_id * R + r) * L + qg;
+      p.lse[orow] = lse;
+      if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
+      const float linv = 1.0f / l;
+      if (!c.wait(kOFull + sb, t >> 1)) return;
+      tc_fence_after();
+      __nv_bfloat16* orow_ptr = p.out + orow * D;
+#pragma unroll 1
+      for (int cb = 0; cb < D / 32; ++cb) {
+        uint32_t o[32];
+        tmem_ld32(tO + cb * 32, o);
+        tc_wait_ld();
+        if (cb == D / 32 - 1) {
+          tc_fence_before();
+          mbar_arrive(c.bar(kOFree + sb));
+        }
+        uint32_t pk[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]) * linv, __uint_as_float(o[2 * u + 1]) * linv);
+          pk[u] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(orow_ptr + cb * 32);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        dst[2] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
+        dst[3] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
+      }
+    }
+  }
+}
+
+template <int D, typename TG>
+__global__ void __launch_bounds__(512, 1)
+fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+           const __grid_constant__ CUtensorMap tmQ, FwdParams p) {
+  using Cfg = FwdCfg<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint32_t* misc = reinterpret_cast<uint32_t*>(smem + Cfg::oMisc);   // [0] tmem base, [1] abort flag
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int BH = p.s.B * p.s.H;
+
+  FwdCtx<D> c;
+  c.smem = smem;
+  c.bars = smem_u32(smem + Cfg::oBar);
+  c.abort_flag = reinterpret_cast<volatile int*>(misc + 1);
+  c.i = blockIdx.x / BH;                 // heavy chunks (small i: most row tiles) first
+  c.bh = blockIdx.x - c.i * BH;
+  c.ntiles = p.s.N - c.i;
+
+  if (threadIdx.x == 0) {
+    misc[1] = 0;
+    for (int b = 0; b < kNumBars; ++b) {
+      uint32_t count = 1;
+      if (b == kGFree || b == kCReady || b == kT3Ready) count = 128;
+      if (b == kCFree) count = 256;
+      if (b == kPReady || b == kPReady + 1 || b == kOFree || b == kOFree + 1) count = 128;
+      mbar_init(c.bar(b), count);
+    }
+    mbar_init_fence();
+    prefetch_tmap(&tmK);
+    prefetch_tmap(&tmV);
+    prefetch_tmap(&tmQ);
+  }
+  if (warp == 0) {
+    tmem_alloc(smem_u32(misc), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  c.tmem = misc[0];
+
+  if (warp == 0) {
+    if (lane == 0) fwd_producer<D>(c, p, &tmK, &tmV, &tmQ);
+  } else if (warp == 1) {
+    if (lane == 0) fwd_mma<D>(c, p);
+  } else if (warp >= 4 && warp < 8) {
+    fwd_decay<D, TG>(c, p);
+  } else if (warp >= 8) {
+    fwd_softmax<D>(c, p, (warp - 8) >> 2);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*c.abort_flag) {
+    if (threadIdx.x == 0) atomicExch(p.status, 1);
+    // let copies and MMAs that are still in flight drain before shared memory and TMEM are released
+    for (int it = 0; it < 64; ++it) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(c.tmem, 512);
+}
+
+// Rows before the key chunk: every score is -1e12 (fp32 absorbs k.q), the softmax
+// is uniform, so out = sum_k bf16(1/128) V_k and lse = -1e12
+// (universal_attention_autograd.py:28, :154).  HBM-write bound.
+__global__ void __launch_bounds__(256) fwd_fill_masked_kernel(const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
+                                                              float* __restrict__ lse, __nv_bfloat16* __restrict__ denom, Shape s) {
+  __shared__ __align__(16) __nv_bfloat16 vmean[256];
+  const int BH = s.B * s.H;
+  const int i = s.N - 1 - blockIdx.x / BH;          // largest fill first
+  const int bh = blockIdx.x % BH;
+  if (i == 0) return;
+  const int D = s.D, L = s.L, R = s.R, C = s.C;
+  const __nv_bfloat16* v = vc + ((size_t)bh * L + (size_t)i * C) * D;
+  const float w = __bfloat162float(__float2bfloat16_rn(1.0f / (float)C));
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < C; ++k) acc = fmaf(w, __bfloat162float(v[(size_t)k * D + d]), acc);
+    vmean[d] = __float2bfloat16_rn(acc);
+  }
+  __syncthreads();
+  const size_t chunk_id = (size_t)bh * s.N + i;
+  const int rows = i * C;
+  const int vec_per_row = D / 8;                       // 16-byte vectors
+  const uint4* vm = reinterpret_cast<const uint4*>(vmean);
+  for (int r = 0; r < R; ++r) {
+    uint4* o = reinterpret_cast<uint4*>(out + ((chunk_id * R + r) * L) * D);
+    const size_t nvec = (size_t)rows * vec_per_row;
+    for (size_t e = threadIdx.x; e < nvec; e += blockDim.x) o[e] = vm[e % vec_per_row];
+    float* lr = lse + (chunk_id * R + r) * L;
+    for (int q = threadIdx.x; q < rows; q += blockDim.x) {
+      lr[q] = mask_value();
+      if (denom) denom[(chunk_id * R + r) * L + q] = __float2bfloat16_rn(mask_value());
+    }
+  }
+}
+
+}  // namespace sm100
+}  // namespace ua

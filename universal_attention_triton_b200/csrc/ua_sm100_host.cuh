@@ -1,0 +1,76 @@
+// Host-side launchers of the sm_100a tensor-core kernels: TMA descriptor
+// construction and launch configuration.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/ua_b200.h"
+#include "ua_fwd_sm100.cuh"
+
+namespace ua {
+namespace sm100 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess) return nullptr;
+    if (q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// 2-D bf16 tensor [rows][D] row-major, boxes of 128 rows x 64 elements, 128-byte swizzle.
+inline bool make_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int D) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdim[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)D * 2};
+  cuuint32_t box[2] = {64, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+inline bool fwd_supported(const Shape& s, int dtype) {
+  return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128);
+}
+
+template <int D, typename TG>
+int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const FwdParams& p, bool fill_masked,
+                 cudaStream_t st) {
+  using Cfg = FwdCfg<D>;
+  CUtensorMap tmK, tmV, tmQ;
+  const uint64_t BH = (uint64_t)s.B * s.H;
+  if (!make_rows_map(&tmK, kc, BH * s.L, D) || !make_rows_map(&tmV, vc, BH * s.L, D) ||
+      !make_rows_map(&tmQ, xq, BH * s.R * s.L, D))
+    return UA_ERR_CUDA;
+  auto kern = fwd_kernel<D, TG>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
+  if (fill_masked && s.N > 1) {
+    fwd_fill_masked_kernel<<<(unsigned)(BH * s.N), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(vc), p.out, p.lse, p.denom, s);
+    if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+  }
+  kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+inline int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const FwdParams& p,
+                      bool fill_masked, cudaStream_t st) {
+  if (s.D == 64) {
+    return gate_dtype == UA_F32 ? launch_fwd_t<64, float>(s, kc, vc, xq, p, fill_masked, st)
+                                : launch_fwd_t<64, __nv_bfloat16>(s, kc, vc, xq, p, fill_masked, st);
+  }
+  return gate_dtype == UA_F32 ? launch_fwd_t<128, float>(s, kc, vc, xq, p, fill_masked, st)
+                              : launch_fwd_t<128, __nv_bfloat16>(s, kc, vc, xq, p, fill_masked, st);
+}
+
+}  // namespace sm100
+}  // namespace ua

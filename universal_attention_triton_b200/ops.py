@@ -10,6 +10,7 @@ different strides, so that every kernel reads and writes whole contiguous
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -37,6 +38,13 @@ def _require_cuda(*tensors):
     for t in tensors:
         if not t.is_cuda:
             raise RuntimeError("Universal Attention has no CPU path: tensors must live on a CUDA device")
+
+
+def _check_status(lib, ws, what):
+    """With UA_CHECK_STATUS=1 every call synchronises and reads the kernels' status word
+    (a bounded device-side wait that ran out) -- for tests and debugging."""
+    if os.environ.get("UA_CHECK_STATUS") == "1":
+        _lib.check(lib.ua_workspace_status(_ptr(ws), _stream()), what + " (device status)")
 
 
 def make_dims(kc, xq):
@@ -73,11 +81,12 @@ def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0):
         lse_cm = torch.empty(b, h, n, r, L, dtype=torch.float32, device=kc.device)
         denom_cm = lse_cm if dt == torch.float32 else torch.empty(b, h, n, r, L, dtype=dt, device=kc.device)
         ws_bytes = lib.ua_fwd_workspace_bytes(ctypes.byref(dims), code, flags)
-        ws = torch.empty(max(ws_bytes, 1), dtype=torch.uint8, device=kc.device) if ws_bytes else None
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
         rc = lib.ua_fwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kc), _ptr(vc), _ptr(q), _ptr(ss), _ptr(sd),
                         _ptr(out_cm), _ptr(lse_cm), _ptr(None if denom_cm is lse_cm else denom_cm),
                         _ptr(ws), ws_bytes, flags, _stream())
-    _lib.check(rc, "ua_fwd")
+        _lib.check(rc, "ua_fwd")
+        _check_status(lib, ws, "ua_fwd")
     return out_cm, lse_cm, denom_cm
 
 
@@ -112,7 +121,8 @@ def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags
         rc = lib.ua_bwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
                         _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype),
                         _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss), _ptr(dsd), _ptr(ws), ws_bytes, flags, _stream())
-    _lib.check(rc, "ua_bwd")
+        _lib.check(rc, "ua_bwd")
+        _check_status(lib, ws, "ua_bwd")
     return (dkc.view(kc.shape), dvc.view(vc.shape), dxq.view(xq.shape),
             dss.to(static_src.dtype).view(static_src.shape), dsd.to(static_dest.dtype).view(static_dest.shape))
 
