@@ -223,3 +223,28 @@ def test_tensor_core_forward_config2_shape_slice_against_oracle():
     merged = O.merge_forward(out, lse)
     merged_ref = O.merge_forward(ref_out, ref_lse)
     assert (merged - merged_ref).abs().max() <= 2e-2
+
+
+@pytest.mark.parametrize("shape,skip", [((1, 2, 4, 1024, 128, 64), False), ((2, 1, 1, 768, 128, 64), False),
+                                         ((1, 1, 2, 1024, 128, 64), True)])
+def test_tensor_core_backward_matches_simt_backward(shape, skip):
+    """The tcgen05 backward against the generic fp32 SIMT backward of the same library, on the device,
+    with random upstream gradients (masked-block gradients included unless skipped)."""
+    from universal_attention_triton_b200 import _lib, ops
+    B, H, R, L, c, D = shape
+    n = L // c
+    ins, _ = _bf16_case(*shape, seed=31)
+    cu = _cuda(*ins)
+    gen = torch.Generator(device="cuda").manual_seed(7)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    if skip:        # zero the masked-block upstream gradient so that both modes must agree with the full computation
+        valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda().view(1, 1, n, 1, L)
+        g_out = g_out * valid.unsqueeze(-1)
+        g_lse = g_lse * valid
+    flags = _lib.FLAG_SKIP_MASKED_GRADS if skip else 0
+    tc = ops.backward_cm(*cu, g_out, g_lse, flags=flags)
+    sm = ops.backward_cm(*cu, g_out, g_lse, flags=_lib.FLAG_FORCE_SIMT)
+    for a, b, key in zip(tc, sm, GRADS):
+        assert torch.isfinite(a.float()).all(), key
+        assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, rel_fro(a.float().cpu(), b.float().cpu()))

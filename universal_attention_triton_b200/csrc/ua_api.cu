@@ -63,6 +63,23 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
   return w;
 }
 
+struct BwdWorkspaceTc {
+  size_t off_dk, off_dq, off_dt, off_carry, acc_bytes, total;
+};
+
+BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
+  BwdWorkspaceTc w;
+  const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
+  size_t o = 256;   // [0, 256): status word
+  w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
+  w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
+  w.off_dt = o; o = align_up(o + BH * s.L * f, 256);
+  w.acc_bytes = o;
+  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 128 * f, 256);
+  w.total = o;
+  return w;
+}
+
 template <typename T, typename TG>
 int launch_simt_fwd(const ua::simt::FwdParams& p, cudaStream_t st) {
   size_t smem = ua::simt::fwd_smem_bytes(p.s.C, p.s.D, p.rt);
@@ -129,9 +146,9 @@ size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
 }
 
 size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
-  (void)dtype; (void)flags;
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
+  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd_supported(s, dtype)) return bwd_layout_tc(s).total;
   int rt = simt_rows(s.C, s.D, true);
   if (!rt) return 0;
   return bwd_layout(s, rt).total;
@@ -155,6 +172,7 @@ int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
     fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest;
     fp.out = static_cast<bf16*>(out_cm); fp.lse = lse_cm; fp.denom = static_cast<bf16*>(denom_cm);
     fp.status = static_cast<int*>(workspace);
+    fp.carry = nullptr;
     return ua::sm100::launch_fwd(s, gate_dtype, kc, vc, xq, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
   }
 
@@ -183,6 +201,33 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(g_out_cm)) return UA_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ua::Shape s = to_shape(dims);
+
+  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd_supported(s, dtype)) {
+    if (!aligned16(dvc) || !aligned16(dkc) || !aligned16(dxq)) return UA_ERR_ALIGNMENT;
+    BwdWorkspaceTc w = bwd_layout_tc(s);
+    if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
+    ua::sm100::BwdParams bp;
+    bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
+    bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+    bp.carry = reinterpret_cast<float*>(ws + w.off_carry);
+    bp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
+    bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
+    bp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+    bp.dvc = static_cast<bf16*>(dvc);
+    bp.dss = dstatic_src;
+    bp.status = reinterpret_cast<int*>(ws);
+    bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
+    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, reinterpret_cast<float*>(ws + w.off_carry), st);
+    if (e) return e;
+    const size_t BHs = (size_t)s.B * s.H;
+    if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;
+    if ((e = convert_any(dtype, bp.acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
+    if ((e = convert_any(gate_dtype, bp.acc_dt, dstatic_dest, BHs * s.L, st))) return e;
+    return UA_OK;
+  }
+
   const int rt = simt_rows(s.C, s.D, true);
   if (!rt) return UA_ERR_UNSUPPORTED;
   BwdWorkspace w = bwd_layout(s, rt);

@@ -42,7 +42,18 @@ struct FwdParams {
   float* lse;            // (b,h,n,r,L)
   __nv_bfloat16* denom;  // (b,h,n,r,L) or null
   int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
+  float* carry;          // carry-only mode: (b*h*n, n, 128) decay prefix of key k at the start of row tile j
 };
+
+// Gated affinity and log-retention of one (key, row) pair from the Gram value
+// (universal_attention_autograd.py:148-150), with hardware ex2/lg2.  Shared by
+// the forward, the carry pre-pass and the backward so that recomputation is
+// bit-identical.
+__device__ __forceinline__ float gram_pow23(float gv) { return gv > 0.f ? ex2(lg2(gv) * (2.0f / 3.0f)) : 0.f; }
+__device__ __forceinline__ float gated_affinity(float pw, float s3, float t3) { return pw * s3 * t3; }
+__device__ __forceinline__ float log_retention(float a) {
+  return lg2(1.0f - fminf(a, clamp_hi())) * 0.6931471805599453f;
+}
 
 template <int D>
 struct FwdCfg {
@@ -81,17 +92,17 @@ struct FwdCtx {
 };
 
 // ------------------------------------------------------------------ producer --
-template <int D>
+template <int D, bool kCarryOnly>
 __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams& p, const CUtensorMap* tmK,
                                              const CUtensorMap* tmV, const CUtensorMap* tmQ) {
   using Cfg = FwdCfg<D>;
   const int L = p.s.L, R = p.s.R;
   const uint32_t sbase = smem_u32(c.smem);
   const int krow = c.bh * L + c.i * 128;
-  mbar_expect_tx(c.bar(kKvFull), 2 * Cfg::kTileBytes);
+  mbar_expect_tx(c.bar(kKvFull), (kCarryOnly ? 1 : 2) * Cfg::kTileBytes);
   for (int b = 0; b < Cfg::kBoxes; ++b) {
     tma_load_2d(sbase + Cfg::oKi + b * Cfg::kBoxBytes, tmK, b * 64, krow, c.bar(kKvFull));
-    tma_load_2d(sbase + Cfg::oVi + b * Cfg::kBoxBytes, tmV, b * 64, krow, c.bar(kKvFull));
+    if (!kCarryOnly) tma_load_2d(sbase + Cfg::oVi + b * Cfg::kBoxBytes, tmV, b * 64, krow, c.bar(kKvFull));
   }
   auto load_kj = [&](int T) -> bool {
     const int ks = T % Cfg::kKjStages, u = T / Cfg::kKjStages;
@@ -103,6 +114,11 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
     return true;
   };
   if (!load_kj(0)) return;
+  if (kCarryOnly) {
+    for (int T = 1; T < c.ntiles; ++T)
+      if (!load_kj(T)) return;
+    return;
+  }
   int t = 0;
   for (int T = 0; T < c.ntiles; ++T) {
     for (int r = 0; r < R; ++r, ++t) {
@@ -118,7 +134,7 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
 }
 
 // ---------------------------------------------------------------- MMA issuer --
-template <int D>
+template <int D, bool kCarryOnly>
 __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) {
   using Cfg = FwdCfg<D>;
   const int R = p.s.R;
@@ -166,6 +182,11 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
 
   if (!c.wait(kKvFull, 0)) return;
   if (!issue_g(0)) return;
+  if (kCarryOnly) {
+    for (int T = 1; T < c.ntiles; ++T)
+      if (!issue_g(T)) return;
+    return;
+  }
   int t = 0;
   for (int T = 0; T < c.ntiles; ++T) {
     for (int r = 0; r < R; ++r, ++t) {
@@ -183,7 +204,7 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
 }
 
 // --------------------------------------------------------------- decay group --
-template <int D, typename TG>
+template <int D, typename TG, bool kCarryOnly>
 __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p) {
   using Cfg = FwdCfg<D>;
   const int L = p.s.L;
@@ -194,8 +215,6 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + k));
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   uint8_t* sCs = c.smem + Cfg::oCs;
-  const float hi = clamp_hi();
-  const float kLn2 = 0.6931471805599453f;
   float carry = 0.f;
   for (int T = 0; T < c.ntiles; ++T) {
     const int j = c.i + T;
@@ -206,6 +225,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
     if (!c.wait(kGFull, T)) return;
     tc_fence_after();
     const bool diag = (T == 0);
+    if (kCarryOnly) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
     float local = 0.f, cval = carry;
 #pragma unroll 1
     for (int cb = 0; cb < 4; ++cb) {
@@ -221,23 +241,23 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
       for (int x = 0; x < 32; ++x) {
         const int q = cb * 32 + x;
         const float gv = __uint_as_float(g[x]);
-        float a = gv > 0.f ? ex2(lg2(gv) * (2.0f / 3.0f)) * s3 * t3buf[q] : 0.f;
-        a = fminf(a, hi);
-        float ell = lg2(1.0f - a) * kLn2;
+        float ell = log_retention(gated_affinity(gram_pow23(gv), s3, t3buf[q]));
         if (diag && q <= k) ell = 0.f;
         local += ell;
         cval = local + carry;
         v[x] = (diag && q < k) ? mask_value() : cval;
       }
-      if (cb == 0 && T >= 1 && !c.wait(kCFree, T - 1)) return;
+      if (!kCarryOnly) {
+        if (cb == 0 && T >= 1 && !c.wait(kCFree, T - 1)) return;
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        const int q = cb * 32 + x;
-        *reinterpret_cast<float*>(sCs + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v[x];
+        for (int x = 0; x < 32; ++x) {
+          const int q = cb * 32 + x;
+          *reinterpret_cast<float*>(sCs + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v[x];
+        }
       }
     }
     carry = cval;
-    mbar_arrive(c.bar(kCReady));
+    if (!kCarryOnly) mbar_arrive(c.bar(kCReady));
   }
 }
 
@@ -346,7 +366,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
   }
 }
 
-template <int D, typename TG>
+template <int D, typename TG, bool kCarryOnly>
 __global__ void __launch_bounds__(512, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, FwdParams p) {
@@ -389,12 +409,12 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   c.tmem = misc[0];
 
   if (warp == 0) {
-    if (lane == 0) fwd_producer<D>(c, p, &tmK, &tmV, &tmQ);
+    if (lane == 0) fwd_producer<D, kCarryOnly>(c, p, &tmK, &tmV, &tmQ);
   } else if (warp == 1) {
-    if (lane == 0) fwd_mma<D>(c, p);
+    if (lane == 0) fwd_mma<D, kCarryOnly>(c, p);
   } else if (warp >= 4 && warp < 8) {
-    fwd_decay<D, TG>(c, p);
-  } else if (warp >= 8) {
+    fwd_decay<D, TG, kCarryOnly>(c, p);
+  } else if (warp >= 8 && !kCarryOnly) {
     fwd_softmax<D>(c, p, (warp - 8) >> 2);
   }
 

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/ua_b200.h"
+#include "ua_bwd_sm100.cuh"
 #include "ua_fwd_sm100.cuh"
 
 namespace ua {
@@ -52,7 +53,7 @@ int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
   if (!make_rows_map(&tmK, kc, BH * s.L, D) || !make_rows_map(&tmV, vc, BH * s.L, D) ||
       !make_rows_map(&tmQ, xq, BH * s.R * s.L, D))
     return UA_ERR_CUDA;
-  auto kern = fwd_kernel<D, TG>;
+  auto kern = fwd_kernel<D, TG, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   if (fill_masked && s.N > 1) {
     fwd_fill_masked_kernel<<<(unsigned)(BH * s.N), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(vc), p.out, p.lse, p.denom, s);
@@ -70,6 +71,40 @@ inline int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void
   }
   return gate_dtype == UA_F32 ? launch_fwd_t<128, float>(s, kc, vc, xq, p, fill_masked, st)
                               : launch_fwd_t<128, __nv_bfloat16>(s, kc, vc, xq, p, fill_masked, st);
+}
+
+inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && s.D == 64; }
+
+// Backward: (1) carry-only run of the forward kernel fills the decay-prefix table,
+// (2) the backward kernel proper.  The caller zeroes the fp32 accumulators.
+template <typename TG>
+int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const BwdParams& p,
+                 float* carry, cudaStream_t st) {
+  CUtensorMap tmK, tmV, tmQ, tmG;
+  const uint64_t BH = (uint64_t)s.B * s.H;
+  if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64) ||
+      !make_rows_map(&tmQ, xq, BH * s.R * s.L, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, 64))
+    return UA_ERR_CUDA;
+  {
+    using Cfg = FwdCfg<64>;
+    FwdParams fp;
+    fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
+    fp.status = p.status; fp.carry = carry;
+    auto kern = fwd_kernel<64, TG, true>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
+    kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, fp);
+    if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+  }
+  auto kern = bwd_kernel<TG>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
+  kern<<<(unsigned)(BH * s.N), 384, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const void* g_out,
+                      const BwdParams& p, float* carry, cudaStream_t st) {
+  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, st)
+                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, st);
 }
 
 }  // namespace sm100
