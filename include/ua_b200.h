@@ -62,7 +62,8 @@ enum {
   UA_ERR_CUDA = 6,           /* a CUDA runtime call failed; cudaGetLastError() has the cause */
   UA_ERR_ALIGNMENT = 7,      /* a tensor pointer is not 16-byte aligned */
   UA_ERR_DEVICE = 8,         /* wrong GPU architecture (needs compute capability 10.x) */
-  UA_ERR_TIMEOUT = 9         /* a bounded device-side wait ran out; reported by ua_workspace_status() */
+  UA_ERR_TIMEOUT = 9,        /* a bounded device-side wait ran out; reported by ua_workspace_status() */
+  UA_ERR_STATIC_LIMIT = 10   /* ua_bwd_static: the problem needs more scratch than UA_STATIC_SCRATCH_BYTES */
 };
 
 /* Flags for ua_fwd / ua_bwd. */
@@ -111,6 +112,38 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype,
            const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype,
            void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
            void* workspace, size_t workspace_bytes, int flags, void* stream);
+
+/* Backward for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Some hosts of this library cannot hand it a workspace: an inference or
+ * training runtime that has frozen its memory plan, a plugin slot that only
+ * passes the operator's inputs and outputs, code running under a memory pool
+ * whose owner forbids cudaMalloc after start-up.  ua_bwd_static() is ua_bwd()
+ * with the scratch taken from a fixed buffer of UA_STATIC_SCRATCH_BYTES that is
+ * part of the library image on the device (every GPU context that loads the
+ * library carries it from load until exit, used or not).  The call allocates
+ * nothing, neither directly nor through a library.
+ *
+ *  - Limit: ua_bwd_workspace_bytes(dims, dtype, flags) must not exceed
+ *    UA_STATIC_SCRATCH_BYTES (ua_static_scratch_bytes() returns it at run time);
+ *    larger problems are refused with UA_ERR_STATIC_LIMIT and nothing is launched.
+ *  - The first call on each device looks up the buffer's device address (with that
+ *    device current).  Make that first call outside any stream capture.
+ *  - There is one buffer per device and every call uses it, so two calls whose
+ *    kernels can overlap on the GPU (different streams, no dependency) race; keep
+ *    the calls of one device in stream order.  The buffer keeps what the previous
+ *    call left; each call first clears the part that has to start at zero.
+ *  - ua_static_status() is ua_workspace_status() for this buffer (it synchronises).
+ * Inputs, outputs, flags and results are those of ua_bwd(). */
+#define UA_STATIC_SCRATCH_BYTES (16u * 1024u * 1024u)
+size_t ua_static_scratch_bytes(void);
+int ua_bwd_static(const UaDims* dims, int dtype, int gate_dtype,
+                  const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest,
+                  const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype,
+                  void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+                  int flags, void* stream);
+int ua_static_status(void* stream);
 
 /* The kernels never trap and never spin without bound: a device-side wait that
  * runs out makes the kernel give up and set a status word at the start of the

@@ -5,6 +5,8 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "ua_aux.cuh"
 #include "ua_simt.cuh"
 #include "ua_sm100_host.cuh"
@@ -118,6 +120,32 @@ bool dtype_ok(int dtype, int gate_dtype) {
   return true;
 }
 
+// ---- scratch for ua_bwd_static -------------------------------------------------
+// Lives in every CUDA context that loads this library, from load to exit.
+constexpr size_t kStaticScratchBytes = UA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_ptr[kMaxDevices] = {};      // device address of g_static_scratch, per device ordinal
+
+// In host code `g_static_scratch` is only a handle for the runtime, not an address a
+// kernel can use; the device address has to be asked for, once per device, with that
+// device current.
+int static_scratch_for_current_device(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) return UA_ERR_CUDA;
+  if (dev < 0 || dev >= kMaxDevices) return UA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (!g_static_ptr[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return UA_ERR_CUDA;
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return UA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -135,6 +163,7 @@ const char* ua_error_string(int code) {
     case UA_ERR_CUDA: return "CUDA runtime error";
     case UA_ERR_ALIGNMENT: return "tensor pointer not 16-byte aligned";
     case UA_ERR_DEVICE: return "device is not compute capability 10.x";
+    case UA_ERR_STATIC_LIMIT: return "problem needs more scratch than the built-in static buffer of ua_bwd_static holds";
     case UA_ERR_TIMEOUT: return "a kernel gave up on a bounded device-side wait (results are invalid)";
     default: return "unknown error code";
   }
@@ -258,6 +287,31 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
   if ((e = convert_any(gate_dtype, p.acc_ds, dstatic_src, BH * s.L, st))) return e;
   if ((e = convert_any(gate_dtype, p.acc_dt, dstatic_dest, BH * s.L, st))) return e;
   return UA_OK;
+}
+
+size_t ua_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+int ua_bwd_static(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
+                  int g_denom_dtype, void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest, int flags,
+                  void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  const size_t need = ua_bwd_workspace_bytes(dims, dtype, flags);
+  if (need == 0) return UA_ERR_UNSUPPORTED;
+  if (need > kStaticScratchBytes) return UA_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  if ((e = static_scratch_for_current_device(&scratch))) return e;
+  // ua_bwd clears the part of the scratch that must start at zero (accumulators, status word)
+  return ua_bwd(dims, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, g_denom_dtype, dkc, dvc,
+                dxq, dstatic_src, dstatic_dest, scratch, kStaticScratchBytes, flags, stream);
+}
+
+int ua_static_status(void* stream) {
+  void* scratch = nullptr;
+  int e = static_scratch_for_current_device(&scratch);
+  if (e) return e;
+  return ua_workspace_status(scratch, stream);
 }
 
 int ua_workspace_status(const void* workspace, void* stream) {
