@@ -194,6 +194,8 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--skip-masked-grads", action="store_true",
+                    help="device-resident step without the gradient through fully masked blocks (valid when SMVecMatMul is upstream)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture run: honour --warmup below 3; the printed numbers are not bench values")
     args = ap.parse_args()
@@ -237,6 +239,7 @@ def main():
     g_out_cm = None if w["fwd_only"] else torch.randn(B, H, n, R, L, D, generator=gen, device=device, dtype=dt)
     g_lse_cm = None if w["fwd_only"] else torch.randn(B, H, n, R, L, generator=gen, device=device, dtype=torch.float32)
 
+    bwd_flags = _lib.FLAG_SKIP_MASKED_GRADS if args.skip_masked_grads else 0
     ev = lambda: torch.cuda.Event(enable_timing=True)
     fwd_ms, bwd_ms = [], []
 
@@ -246,7 +249,7 @@ def main():
         out_cm, lse_cm, denom_cm = ops.forward_cm(kc, vc, xq, ss, sd)
         e1.record()
         if not w["fwd_only"]:
-            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm)
+            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags)
         e2.record()
         if record:
             fwd_ms.append((e0, e1)); bwd_ms.append((e1, e2))
@@ -337,7 +340,7 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": w["dtype"], "data": "synthetic",
             "config": {"workload": f"{args.workload}: B={B} (per GPU) H_kv={H} R={R} L={L} chunk={c} D={D} {w['dtype']} "
-                                   f"fwd{'' if w['fwd_only'] else '+bwd'}, random upstream grads, masked-block grads included",
+                                   f"fwd{'' if w['fwd_only'] else '+bwd'}, random upstream grads, masked-block grads {'skipped' if args.skip_masked_grads else 'included'}",
                        "global_batch": B * world, "seq_len": L, "parallelism": f"batch-shard x{world}, no collective",
                        "l2_policy": "working set (out + g_out > 4 GB) exceeds the 126 MB L2; no explicit flush"},
             "tflops": (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12,

@@ -56,7 +56,8 @@ struct BwdCfg {
   static constexpr int odS = 180224;          // 32 KB bf16 dS[row][key]
   static constexpr int oI = 212992;           // 2 KB: 16 x 64 bf16, identity in the first 16 columns
   static constexpr int oT3 = 215040;          // 2 x 128 floats
-  static constexpr int oBar = 216064;
+  static constexpr int oXch = 216064;          // 2 slots x 4 groups x 3 x 128 floats mailbox (12 KB)
+  static constexpr int oBar = 228352;
   static constexpr int oMisc = oBar + 256;
   static constexpr int kSmemBytes = oMisc + 64 + 1024;
   static constexpr uint32_t tX0 = 0, tX1 = 128, tXC = 256, tDV = 384, tDK = 448;
@@ -64,7 +65,7 @@ struct BwdCfg {
 
 enum BwdBar {
   bKvFull = 0, bKjFull, bInFull, bGFull, bX0Free, bSdpFull, bX1Free, bCReady, bCsFree, bPdsReady, bRDone, bG2Full,
-  bDgReady, bDkjFull, bT3Ready, bFinal, bNumBars
+  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bNumBars
 };
 
 struct BwdCtx {
@@ -75,6 +76,9 @@ struct BwdCtx {
   int i, bh, nvalid, ntiles;
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
   __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
+  // warp-collective forms for the worker groups
+  __device__ __forceinline__ bool wait_w(int idx, uint32_t parity) const { return mbar_wait_warp(bar(idx), parity & 1u, abort_flag); }
+  __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
   // row tile index of sweep step T: valid tiles n-1 .. i first, then the masked ones i-1 .. 0
   __device__ __forceinline__ int tile_j(int T, int N) const { return T < nvalid ? N - 1 - T : i - 1 - (T - nvalid); }
 };
@@ -118,7 +122,7 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
       tma_load_2d(sbase + BwdCfg::oKj, tmK, 0, c.bh * L + j * 128, c.bar(bKjFull));
     }
     for (int r = 0; r < R; ++r, ++rc) {
-      if (rc >= 1 && !c.wait(bRDone, rc - 1)) return;
+      if (rc >= 1 && !c.wait(bInFree, rc - 1)) return;
       mbar_expect_tx(c.bar(bInFull), 2 * BwdCfg::kTileBytes);
       tma_load_2d(sbase + BwdCfg::oQ, tmQ, 0, (c.bh * R + r) * L + j * 128, c.bar(bInFull));
       tma_load_2d(sbase + BwdCfg::oGo, tmG, 0, (int)((chunk_id * R + r) * L + (size_t)j * 128), c.bar(bInFull));
@@ -190,6 +194,7 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p) {
       mma_tt(DV, sb + BwdCfg::oP, sb + BwdCfg::oGo, have_acc);        // dV_i += P^T dO
       mma_tt(DK, sb + BwdCfg::odS, sb + BwdCfg::oQ, have_acc);        // dK_i += dS^T Q
       have_acc = true;
+      tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
       mma_nn(X1, sb + BwdCfg::odS, sb + BwdCfg::oKi, false);          // dQ = dS K_i  (dP has been consumed)
       if (valid) {
 #pragma unroll
@@ -217,303 +222,385 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p) {
   tc_commit(c.bar(bFinal));
 }
 
-// --------------------------------------------------------------- decay group --
+// ------------------------------------------------------------ worker groups --
+// Four groups of 128 threads share every elementwise phase: thread t of group
+// `part` owns row/key t and the 32 tile columns [32*part, 32*part+32), which it
+// keeps in registers across the passes of a phase.  Partial row/key statistics
+// cross between the groups through a shared-memory mailbox and an mbarrier
+// rendezvous in which all 512 threads take part, in the same order, every time.
+constexpr int kParts = 4;
+
+struct Mailbox {
+  const BwdCtx* c;
+  float* box;       // [2 slots][kParts][3][128]
+  int part, tid, n;
+  bool ok;
+  // publish (x, y, z), wait for everybody, return all four triples (index = part; w unused)
+  __device__ __forceinline__ void gather(float4 mine, float4* all) {
+    float* slot = box + (n & 1) * kParts * 3 * 128;
+    slot[(part * 3 + 0) * 128 + tid] = mine.x;
+    slot[(part * 3 + 1) * 128 + tid] = mine.y;
+    slot[(part * 3 + 2) * 128 + tid] = mine.z;
+    c->arrive_w(bXchg);
+    if (!c->wait_w(bXchg, n)) ok = false;
+#pragma unroll
+    for (int q = 0; q < kParts; ++q)
+      all[q] = make_float4(slot[(q * 3 + 0) * 128 + tid], slot[(q * 3 + 1) * 128 + tid], slot[(q * 3 + 2) * 128 + tid], 0.f);
+    ++n;
+  }
+  __device__ __forceinline__ void sync() {
+    c->arrive_w(bXchg);
+    if (!c->wait_w(bXchg, n)) ok = false;
+    ++n;
+  }
+};
+
+// Optional phase timing (compile with -DUA_PROFILE_PHASES): thread 0 of worker group 0 of block 0
+// accumulates clock64() deltas per phase and stores them after the status word.
+#ifdef UA_PROFILE_PHASES
+#define UA_PH_DECL long long ph_t = clock64(), ph_acc[20] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#define UA_PH(idx) { long long now_ = clock64(); ph_acc[idx] += now_ - ph_t; ph_t = now_; }
+#define UA_PH_STORE if (blockIdx.x == 0 && part == 0 && tid == 0) { for (int z = 0; z < 20; ++z) reinterpret_cast<long long*>(p.status)[2 + z] = ph_acc[z]; }
+#else
+#define UA_PH_DECL
+#define UA_PH(idx)
+#define UA_PH_STORE
+#endif
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
 template <typename TG>
-__device__ __forceinline__ void bwd_decay(const BwdCtx& c, const BwdParams& p) {
-  const int L = p.s.L, N = p.s.N;
-  const int k = threadIdx.x & 127, lane = threadIdx.x & 31;
+__device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part) {
+  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int tid = threadIdx.x & 127, lane = threadIdx.x & 31;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
   const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
-  const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + k));
+  const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + tid));
   float* sT3 = reinterpret_cast<float*>(c.smem + BwdCfg::oT3);
   uint8_t* sCs = c.smem + BwdCfg::oCs;
-  uint8_t* sdG = c.smem + BwdCfg::oP;
-  const size_t chunk_id = (size_t)c.bh * N + c.i;
-  const uint32_t X0 = c.tmem + BwdCfg::tX0 + lane_base, XC = c.tmem + BwdCfg::tXC + lane_base;
-  float suffix = 0.f, ds_acc = 0.f;
-
-  for (int T = 0; T < c.nvalid; ++T) {
-    const int j = N - 1 - T;
-    const bool diag = (j == c.i);
-    float* t3buf = sT3 + (T & 1) * 128;
-    t3buf[k] = cbrtf(Num<TG>::ld(sd + j * 128 + k));
-    mbar_arrive(c.bar(bT3Ready));
-    if (!c.wait(bT3Ready, T)) return;
-    const float carry = p.carry[(chunk_id * N + j) * 128 + k];
-    if (!c.wait(bGFull, T)) return;
-    tc_fence_after();
-    if (T >= 1 && !c.wait(bCsFree, T - 1)) return;
-    // ---- forward recomputation: decay prefix C^T[row][key] ------------------
-    float local = 0.f;
-#pragma unroll 1
-    for (int cb = 0; cb < 4; ++cb) {
-      uint32_t g[32];
-      tmem_ld32(X0 + cb * 32, g);
-      tc_wait_ld();
-#pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        const int q = cb * 32 + x;
-        float ell = log_retention(gated_affinity(gram_pow23(__uint_as_float(g[x])), s3, t3buf[q]));
-        if (diag && q <= k) ell = 0.f;
-        local += ell;
-        const float v = (diag && q < k) ? mask_value() : (local + carry);
-        *reinterpret_cast<float*>(sCs + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v;
-      }
-    }
-    tc_fence_before();
-    mbar_arrive(c.bar(bX0Free));
-    mbar_arrive(c.bar(bCReady));
-
-    // ---- backward: reverse scan of dC, gradients of the decay term -----------
-    if (!c.wait(bG2Full, T)) return;
-    tc_fence_after();
-    float run = 0.f, first = 0.f;
-#pragma unroll 1
-    for (int cb = 3; cb >= 0; --cb) {
-      uint32_t g[32], dc[32];
-      tmem_ld32(X0 + cb * 32, g);
-      tmem_ld32(XC + cb * 32, dc);
-      tc_wait_ld();
-      float xs[32];
-      uint32_t pk[16];
-      float dg_hold = 0.f;
-#pragma unroll
-      for (int x = 31; x >= 0; --x) {
-        const int q = cb * 32 + x;
-        run += __uint_as_float(dc[x]);
-        float dl = run + suffix;
-        if (diag && q <= k) dl = 0.f;
-        if (q == 0) first = dl;
-        const float gv = __uint_as_float(g[x]);
-        const float t3 = t3buf[q];
-        const float lg = lg2(gv);                                  // NaN for gv < 0: guarded below
-        const float pw = gv > 0.f ? ex2(lg * (2.0f / 3.0f)) : 0.f;
-        const float a = gated_affinity(pw, s3, t3);
-        float da = __fdividef(dl, fminf(fmaxf(a, clamp_lo_bwd()), clamp_hi()) - 1.0f);
-        if (!(a <= clamp_hi())) da = 0.f;
-        const float dstat = da * pw;
-        ds_acc = fmaf(dstat, t3, ds_acc);
-        xs[x] = dstat * s3;
-        float dg = __bfloat162float(__float2bfloat16_rn(da * s3 * t3));
-        dg = gv > 0.f ? dg * (2.0f / 3.0f) * ex2(lg * (-1.0f / 3.0f)) : 0.f;
-        if (x & 1) {
-          dg_hold = dg;
-        } else {
-          __nv_bfloat162 h = __floats2bfloat162_rn(dg, dg_hold);
-          pk[x >> 1] = *reinterpret_cast<uint32_t*>(&h);
-        }
-      }
-      // dG[key][row] bf16, 128-byte swizzled, rows = keys, two boxes of 64 rows-of-the-tile
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int ch = cb * 4 + u;
-        *reinterpret_cast<uint4*>(sdG + (ch >> 3) * 16384 + k * 128 + ((((ch & 7) ^ (k & 7)) & 7) << 4)) =
-            make_uint4(pk[u * 4 + 0], pk[u * 4 + 1], pk[u * 4 + 2], pk[u * 4 + 3]);
-      }
-      // d static_dest: sum over the 128 keys of dstat * src^(1/3)
-      const float colsum = warp_transpose_reduce(xs, lane);
-      const float t3l = t3buf[cb * 32 + lane];
-      if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + j * 128 + cb * 32 + lane, colsum / (3.0f * t3l * t3l));
-    }
-    suffix = first;
-    fence_proxy_async();
-    tc_fence_before();
-    mbar_arrive(c.bar(bX0Free));
-    mbar_arrive(c.bar(bDgReady));
-  }
-
-  // ---- end of the sweep: dV_i, dK_i, d static_src ----------------------------
-  if (!c.wait(bFinal, 0)) return;
-  tc_fence_after();
-  const size_t krow = (size_t)c.bh * L + c.i * 128 + k;
-#pragma unroll 1
-  for (int cb = 0; cb < 2; ++cb) {
-    uint32_t o[32];
-    tmem_ld32(c.tmem + BwdCfg::tDV + lane_base + cb * 32, o);
-    tc_wait_ld();
-    uint32_t pk[16];
-#pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]), __uint_as_float(o[2 * u + 1]));
-      pk[u] = *reinterpret_cast<uint32_t*>(&h);
-    }
-    uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * 64 + cb * 32);
-    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
-    dst[2] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
-    dst[3] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
-    tmem_ld32(c.tmem + BwdCfg::tDK + lane_base + cb * 32, o);
-    tc_wait_ld();
-    float* dk = p.acc_dk + krow * 64 + cb * 32;
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      red_add_v4(dk + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]), __uint_as_float(o[u * 4 + 2]),
-                 __uint_as_float(o[u * 4 + 3]));
-  }
-  Num<TG>::st(static_cast<TG*>(p.dss) + krow, ds_acc / (3.0f * s3 * s3));
-}
-
-// ------------------------------------------------------------- softmax group --
-__device__ __forceinline__ void bwd_softmax(const BwdCtx& c, const BwdParams& p) {
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
-  const int row = threadIdx.x & 127;
-  const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
-  const uint8_t* sCrow = c.smem + BwdCfg::oCs + row * 512;
   uint8_t* sP = c.smem + BwdCfg::oP;
   uint8_t* sdS = c.smem + BwdCfg::odS;
   const size_t chunk_id = (size_t)c.bh * N + c.i;
-  const uint32_t X0 = c.tmem + BwdCfg::tX0 + lane_base, X1 = c.tmem + BwdCfg::tX1 + lane_base;
+  const int col0 = 32 * part;
+  const uint32_t X0 = c.tmem + BwdCfg::tX0 + lane_base + col0;
+  const uint32_t X1 = c.tmem + BwdCfg::tX1 + lane_base;
+  const uint32_t XC = c.tmem + BwdCfg::tXC + lane_base + col0;
   const float kLog2e = 1.4426950408889634f;
-  const uint32_t swz = (uint32_t)(row & 7);
+  const uint32_t swz = (uint32_t)(tid & 7);
+  Mailbox mb{&c, reinterpret_cast<float*>(c.smem + BwdCfg::oXch), part, tid, 0, true};
+  float suffix = 0.f, ds_acc = 0.f;
+  UA_PH_DECL
 
-  auto store_rows = [&](int cb, const uint32_t* pp, const uint32_t* dd) {
+  // this thread's 32 columns of row `tid` of a [row][key] bf16 tile: 4 chunks of box part/2
+  auto store_row = [&](uint8_t* base, const uint32_t* v) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int ch = cb * 4 + u;
-      const uint32_t off = (ch >> 3) * 16384 + row * 128 + ((((uint32_t)(ch & 7) ^ swz) & 7) << 4);
-      *reinterpret_cast<uint4*>(sP + off) = make_uint4(pp[u * 4], pp[u * 4 + 1], pp[u * 4 + 2], pp[u * 4 + 3]);
-      *reinterpret_cast<uint4*>(sdS + off) = make_uint4(dd[u * 4], dd[u * 4 + 1], dd[u * 4 + 2], dd[u * 4 + 3]);
+      const uint32_t ch = (uint32_t)((part & 1) * 4 + u);
+      *reinterpret_cast<uint4*>(base + (part >> 1) * 16384 + tid * 128 + (((ch ^ swz) & 7) << 4)) =
+          make_uint4(v[u * 4], v[u * 4 + 1], v[u * 4 + 2], v[u * 4 + 3]);
     }
   };
+  // 16 of the 64 accumulator columns of X1 (dQ_rj or dK_j), row `tid`, added to global fp32 rows
   auto drain_x1 = [&](float* dst_row) {
-#pragma unroll 1
-    for (int cb = 0; cb < 2; ++cb) {
-      uint32_t o[32];
-      tmem_ld32(X1 + cb * 32, o);
-      tc_wait_ld();
-#pragma unroll
-      for (int u = 0; u < 8; ++u)
-        red_add_v4(dst_row + cb * 32 + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]),
-                   __uint_as_float(o[u * 4 + 2]), __uint_as_float(o[u * 4 + 3]));
-    }
+    uint32_t o[16];
+    tmem_ld16(X1 + 16 * part, o);
+    tc_wait_ld();
     tc_fence_before();
-    mbar_arrive(c.bar(bX1Free));
+    c.arrive_w(bX1Free);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      red_add_v4(dst_row + 16 * part + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]),
+                 __uint_as_float(o[u * 4 + 2]), __uint_as_float(o[u * 4 + 3]));
   };
 
   int rc = 0;
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
     const int j = c.tile_j(T, N);
+    const bool diag = (j == c.i);
+    float* t3buf = sT3 + (T & 1) * 128;
+
+    if (valid) {
+      // ---- decay prefix (forward recomputation): thread = key, C^T[row][key] to shared memory ----
+      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + j * 128 + tid));
+      const float carry = p.carry[(chunk_id * N + j) * 128 + tid];
+      mb.sync();                                  // t3 visible; every reader of the previous tile's C^T is done
+      UA_PH(0)
+      if (!mb.ok || !c.wait_w(bGFull, T)) return;
+      UA_PH(1)
+      tc_fence_after();
+      float ell[32];
+      {
+        uint32_t g[32];
+        tmem_ld32(X0, g);
+        tc_wait_ld();
+        tc_fence_before();
+        c.arrive_w(bX0Free);
+#pragma unroll
+        for (int x = 0; x < 32; ++x) {
+          const int q = col0 + x;
+          float e = log_retention(gated_affinity(gram_pow23(__uint_as_float(g[x])), s3, t3buf[q]));
+          if (diag && q <= tid) e = 0.f;
+          ell[x] = e;
+        }
+      }
+      // block-local scan; the totals of the earlier blocks are added in the forward kernel's order
+      float local = 0.f;
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        local += ell[x];
+        ell[x] = local;
+      }
+      float4 tots[kParts];
+      mb.gather(make_float4(local, 0.f, 0.f, 0.f), tots);
+      if (!mb.ok) return;
+      float tprev = 0.f;
+#pragma unroll
+      for (int q = 0; q < kParts; ++q)
+        if (q < part) tprev += tots[q].x;
+#pragma unroll
+      for (int x = 0; x < 32; ++x) {
+        const int q = col0 + x;
+        const float v = (diag && q < tid) ? mask_value() : (carry + (tprev + ell[x]));
+        *reinterpret_cast<float*>(sCs + q * 512 + ((((tid >> 2) ^ (q & 7)) & 31) << 4) + (tid & 3) * 4) = v;
+      }
+      mb.sync();                                  // C^T complete
+      if (!mb.ok) return;
+      UA_PH(2)
+    }
+
     for (int r = 0; r < R; ++r, ++rc) {
-      const size_t grow = (chunk_id * R + r) * L + (size_t)j * 128 + row;
+      const size_t grow = (chunk_id * R + r) * L + (size_t)j * 128 + tid;
       const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
-      if (!c.wait(bSdpFull, rc)) return;
+      if (!c.wait_w(bSdpFull, rc)) return;
+      UA_PH(3)
       tc_fence_after();
+      uint32_t pp[16], dd[16];
       if (valid) {
-        if (r == 0 && !c.wait(bCReady, T)) return;
-        // pass 1: s = S + C, row max
-        float m = -INFINITY;
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t s[32];
-          tmem_ld32(X0 + cb * 32, s);
+        // ---- thread = row: s = S + C on 32 columns held in registers ------------------------
+        float sv[32];
+        {
+          uint32_t t[32];
+          tmem_ld32(X0, t);
           tc_wait_ld();
+          tc_fence_before();
+          c.arrive_w(bX0Free);
 #pragma unroll
           for (int u = 0; u < 8; ++u) {
-            const int chunk = cb * 8 + u;
-            const float4 cv = *reinterpret_cast<const float4*>(sCrow + ((((uint32_t)chunk ^ swz) & 31) << 4));
-            const float a0 = __uint_as_float(s[u * 4 + 0]) + cv.x, a1 = __uint_as_float(s[u * 4 + 1]) + cv.y;
-            const float a2 = __uint_as_float(s[u * 4 + 2]) + cv.z, a3 = __uint_as_float(s[u * 4 + 3]) + cv.w;
-            m = fmaxf(m, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
-            s[u * 4 + 0] = __float_as_uint(a0); s[u * 4 + 1] = __float_as_uint(a1);
-            s[u * 4 + 2] = __float_as_uint(a2); s[u * 4 + 3] = __float_as_uint(a3);
+            const uint32_t chunk = (uint32_t)(8 * part + u);
+            const float4 cv = *reinterpret_cast<const float4*>(sCs + tid * 512 + (((chunk ^ swz) & 31) << 4));
+            sv[4 * u + 0] = __uint_as_float(t[4 * u + 0]) + cv.x;
+            sv[4 * u + 1] = __uint_as_float(t[4 * u + 1]) + cv.y;
+            sv[4 * u + 2] = __uint_as_float(t[4 * u + 2]) + cv.z;
+            sv[4 * u + 3] = __uint_as_float(t[4 * u + 3]) + cv.w;
           }
-          tmem_st32(X0 + cb * 32, s);
         }
-        tc_wait_st();
-        if (r == R - 1) mbar_arrive(c.bar(bCsFree));
-        // pass 2: e = exp(s - m), l = sum e, sum e dP
-        const float mb = m * kLog2e;
+        // every group stabilises its 32 columns with its own maximum; one rendezvous then
+        // combines (max, sum e, sum e dP) of the four groups
+        float m = sv[0];
+#pragma unroll
+        for (int x = 1; x < 32; ++x) m = fmaxf(m, sv[x]);
+        UA_PH(11)
+        const float mbias = m * kLog2e;
+        uint32_t dp[32];
+        tmem_ld32(X1 + col0, dp);
+        tc_wait_ld();
         float l = 0.f, edp = 0.f;
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t s[32], dp[32];
-          tmem_ld32(X0 + cb * 32, s);
-          tmem_ld32(X1 + cb * 32, dp);
-          tc_wait_ld();
 #pragma unroll
-          for (int x = 0; x < 32; ++x) {
-            const float e = ex2(fmaf(__uint_as_float(s[x]), kLog2e, -mb));
-            l += e;
-            edp = fmaf(e, __uint_as_float(dp[x]), edp);
-            s[x] = __float_as_uint(e);
-          }
-          tmem_st32(X0 + cb * 32, s);
+        for (int x = 0; x < 32; ++x) {
+          const float e = ex2(fmaf(sv[x], kLog2e, -mbias));
+          sv[x] = e;
+          l += e;
+          edp = fmaf(e, __uint_as_float(dp[x]), edp);
         }
-        tc_wait_st();
-        const float linv = 1.0f / l;
-        const float corr = gd - edp * linv;          // g_denom - sum_k P dP
-        // pass 3: P = e / l, dS = P (dP + corr)
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t s[32], dp[32];
-          tmem_ld32(X0 + cb * 32, s);
-          tmem_ld32(X1 + cb * 32, dp);
-          tc_wait_ld();
-          uint32_t pp[16], dd[16];
+        UA_PH(13)
+        float4 all[kParts];
+        mb.gather(make_float4(m, l, edp, 0.f), all);
+        if (!mb.ok) return;
+        UA_PH(14)
+        const float mrow = fmaxf(fmaxf(all[0].x, all[1].x), fmaxf(all[2].x, all[3].x));
+        float lrow = 0.f, edprow = 0.f;
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            const float p0 = __uint_as_float(s[2 * u]) * linv, p1 = __uint_as_float(s[2 * u + 1]) * linv;
-            const float d0 = p0 * (__uint_as_float(dp[2 * u]) + corr), d1 = p1 * (__uint_as_float(dp[2 * u + 1]) + corr);
-            __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
-            pp[u] = *reinterpret_cast<uint32_t*>(&hp);
-            dd[u] = *reinterpret_cast<uint32_t*>(&hd);
-          }
-          store_rows(cb, pp, dd);
+        for (int q = 0; q < kParts; ++q) {
+          const float f = ex2((all[q].x - mrow) * kLog2e);
+          lrow = fmaf(all[q].y, f, lrow);
+          edprow = fmaf(all[q].z, f, edprow);
         }
-        tc_fence_before();
-        mbar_arrive(c.bar(bX0Free));
+        const float linv = ex2((m - mrow) * kLog2e) / lrow;          // own rescale folded into 1/l
+        const float corr = gd - edprow / lrow;                       // g_denom - sum_k P dP
+#pragma unroll
+        for (int u = 0; u < 16; ++u) {
+          const float p0 = sv[2 * u] * linv, p1 = sv[2 * u + 1] * linv;
+          const float d0 = p0 * (__uint_as_float(dp[2 * u]) + corr), d1 = p1 * (__uint_as_float(dp[2 * u + 1]) + corr);
+          __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
+          pp[u] = *reinterpret_cast<uint32_t*>(&hp);
+          dd[u] = *reinterpret_cast<uint32_t*>(&hd);
+        }
       } else {
-        // rows before the chunk: uniform softmax P = 1/128 (universal_attention_autograd.py:154)
+        // ---- rows before the chunk: uniform softmax P = 1/128 (universal_attention_autograd.py:154) ----
+        uint32_t dp[32];
+        tmem_ld32(X1 + col0, dp);
+        tc_wait_ld();
         float sum = 0.f;
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t dp[32];
-          tmem_ld32(X1 + cb * 32, dp);
-          tc_wait_ld();
 #pragma unroll
-          for (int x = 0; x < 32; ++x) sum += __uint_as_float(dp[x]);
-        }
+        for (int x = 0; x < 32; ++x) sum += __uint_as_float(dp[x]);
+        float4 all[kParts];
+        mb.gather(make_float4(sum, 0.f, 0.f, 0.f), all);
+        if (!mb.ok) return;
+        sum = (all[0].x + all[1].x) + (all[2].x + all[3].x);
         const float pu = 1.0f / 128.0f;
         const float corr = gd - sum * pu;
         __nv_bfloat162 hp = __floats2bfloat162_rn(pu, pu);
         const uint32_t pconst = *reinterpret_cast<uint32_t*>(&hp);
-#pragma unroll 1
-        for (int cb = 0; cb < 4; ++cb) {
-          uint32_t dp[32];
-          tmem_ld32(X1 + cb * 32, dp);
-          tc_wait_ld();
-          uint32_t pp[16], dd[16];
 #pragma unroll
-          for (int u = 0; u < 16; ++u) {
-            __nv_bfloat162 hd = __floats2bfloat162_rn(pu * (__uint_as_float(dp[2 * u]) + corr),
-                                                      pu * (__uint_as_float(dp[2 * u + 1]) + corr));
-            pp[u] = pconst;
-            dd[u] = *reinterpret_cast<uint32_t*>(&hd);
-          }
-          store_rows(cb, pp, dd);
+        for (int u = 0; u < 16; ++u) {
+          __nv_bfloat162 hd = __floats2bfloat162_rn(pu * (__uint_as_float(dp[2 * u]) + corr), pu * (__uint_as_float(dp[2 * u + 1]) + corr));
+          pp[u] = pconst;
+          dd[u] = *reinterpret_cast<uint32_t*>(&hd);
         }
+      }
+      UA_PH(15)
+      store_row(sP, pp);
+      store_row(sdS, dd);
+      UA_PH(16)
+      fence_proxy_async();
+      tc_fence_before();
+      c.arrive_w(bPdsReady);
+      UA_PH(4)
+      // dQ_rj leaves through fp32 atomics: other key chunks add to the same rows
+      if (!c.wait_w(bRDone, rc)) return;
+      UA_PH(5)
+      tc_fence_after();
+      drain_x1(p.acc_dq + (((size_t)c.bh * R + r) * L + (size_t)j * 128 + tid) * 64);
+      UA_PH(6)
+    }
+
+    if (valid) {
+      // ---- decay backward: thread = key; reverse scan of dC, then d affinity -> dG, d src, d dest ----
+      if (!c.wait_w(bG2Full, T)) return;
+      UA_PH(7)
+      tc_fence_after();
+      float dcs[32];
+      {
+        uint32_t t[32];
+        tmem_ld32(XC, t);
+        tc_wait_ld();
+        float run = 0.f;
+#pragma unroll
+        for (int x = 31; x >= 0; --x) {
+          run += __uint_as_float(t[x]);
+          dcs[x] = run;
+        }
+        float4 tots[kParts];
+        mb.gather(make_float4(run, 0.f, 0.f, 0.f), tots);
+        if (!mb.ok) return;
+        // rows after this thread's block: the carried suffix plus the totals of the later blocks
+#pragma unroll
+        for (int q = kParts - 1; q >= 0; --q)
+          if (q > part) suffix += tots[q].x;
+      }
+      float first = 0.f;
+      {
+        uint32_t g[32];
+        tmem_ld32(X0, g);
+        tc_wait_ld();
+        tc_fence_before();
+        c.arrive_w(bX0Free);
+        uint32_t pk[16];
+        float dg_hold = 0.f;
+#pragma unroll
+        for (int x = 31; x >= 0; --x) {
+          const int q = col0 + x;
+          float dl = dcs[x] + suffix;
+          if (diag && q <= tid) dl = 0.f;
+          if (q == 0) first = dl;
+          const float gv = __uint_as_float(g[x]);
+          const float t3 = t3buf[q];
+          const float lg = lg2(gv);                                  // NaN for gv < 0: guarded below
+          const float pw = gv > 0.f ? ex2(lg * (2.0f / 3.0f)) : 0.f;
+          const float a = gated_affinity(pw, s3, t3);
+          float da = __fdividef(dl, fminf(fmaxf(a, clamp_lo_bwd()), clamp_hi()) - 1.0f);
+          if (!(a <= clamp_hi())) da = 0.f;
+          const float dstat = da * pw;
+          ds_acc = fmaf(dstat, t3, ds_acc);
+          dcs[x] = dstat * s3;                                       // reuse: per-(key,row) term of d static_dest
+          float dg = __bfloat162float(__float2bfloat16_rn(da * s3 * t3));
+          dg = gv > 0.f ? dg * (2.0f / 3.0f) * ex2(lg * (-1.0f / 3.0f)) : 0.f;
+          if (x & 1) {
+            dg_hold = dg;
+          } else {
+            __nv_bfloat162 h = __floats2bfloat162_rn(dg, dg_hold);
+            pk[x >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        store_row(sP, pk);                     // dG[key][row] reuses the P buffer (rows = keys here)
       }
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(c.bar(bPdsReady));
-      // dQ_rj leaves through fp32 atomics: other key chunks add to the same rows
-      if (!c.wait(bRDone, rc)) return;
+      c.arrive_w(bDgReady);
+      // d static_dest: sum over the 128 keys of dstat * src^(1/3)
+      {
+        const float colsum = warp_transpose_reduce(dcs, lane);
+        const float t3l = t3buf[col0 + lane];
+        if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + j * 128 + col0 + lane, colsum / (3.0f * t3l * t3l));
+      }
+      // the suffix carried to the next (lower) tile is d ell at the tile's first row
+      float4 f[kParts];
+      mb.gather(make_float4(first, 0.f, 0.f, 0.f), f);
+      if (!mb.ok) return;
+      suffix = f[0].x;
+      UA_PH(8)
+      if (!c.wait_w(bDkjFull, T)) return;
+      UA_PH(9)
       tc_fence_after();
-      drain_x1(p.acc_dq + (((size_t)c.bh * R + r) * L + (size_t)j * 128 + row) * 64);
-    }
-    if (valid) {
-      if (!c.wait(bDkjFull, T)) return;
-      tc_fence_after();
-      drain_x1(p.acc_dk + ((size_t)c.bh * L + (size_t)j * 128 + row) * 64);      // dK_j
+      drain_x1(p.acc_dk + ((size_t)c.bh * L + (size_t)j * 128 + tid) * 64);      // dK_j
+      UA_PH(10)
     }
   }
+  UA_PH_STORE
+
+  // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, 16 of the 64 columns each) ----
+  if (!c.wait_w(bFinal, 0)) return;
+  tc_fence_after();
+  const size_t krow = (size_t)c.bh * L + c.i * 128 + tid;
+  {
+    uint32_t o[16];
+    tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
+    tc_wait_ld();
+    uint32_t pk[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]), __uint_as_float(o[2 * u + 1]));
+      pk[u] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * 64 + 16 * part);
+    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    tmem_ld16(c.tmem + BwdCfg::tDK + lane_base + 16 * part, o);
+    tc_wait_ld();
+    float* dk = p.acc_dk + krow * 64 + 16 * part;
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      red_add_v4(dk + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]), __uint_as_float(o[u * 4 + 2]),
+                 __uint_as_float(o[u * 4 + 3]));
+  }
+  float4 od[kParts];
+  mb.gather(make_float4(ds_acc, 0.f, 0.f, 0.f), od);
+  if (mb.ok && part == 0)
+    Num<TG>::st(static_cast<TG*>(p.dss) + krow, ((od[0].x + od[1].x) + (od[2].x + od[3].x)) / (3.0f * s3 * s3));
 }
 
 template <typename TG>
-__global__ void __launch_bounds__(384, 1)
+__global__ void __launch_bounds__(640, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG, BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -535,8 +622,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     misc[1] = 0;
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
-      if (b == bX0Free || b == bX1Free || b == bCReady || b == bCsFree || b == bPdsReady || b == bDgReady || b == bT3Ready)
-        count = 128;
+      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg) count = 16;   // one arrival per worker warp
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
@@ -564,10 +650,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     if (lane == 0) bwd_producer(c, p, &tmK, &tmV, &tmQ, &tmG);
   } else if (warp == 1) {
     if (lane == 0) bwd_mma(c, p);
-  } else if (warp >= 4 && warp < 8) {
-    bwd_decay<TG>(c, p);
-  } else if (warp >= 8) {
-    bwd_softmax(c, p);
+  } else if (warp >= 4) {
+    bwd_worker<TG>(c, p, (warp - 4) >> 2);
   }
 
   tc_fence_before();

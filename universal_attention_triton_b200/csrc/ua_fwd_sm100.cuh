@@ -89,6 +89,9 @@ struct FwdCtx {
   int i, bh, ntiles;
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
   __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
+  // warp-collective forms for the decay and softmax groups
+  __device__ __forceinline__ bool wait_w(int idx, uint32_t parity) const { return mbar_wait_warp(bar(idx), parity & 1u, abort_flag); }
+  __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
 };
 
 // ------------------------------------------------------------------ producer --
@@ -220,13 +223,15 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
     const int j = c.i + T;
     float* t3buf = sT3 + (T & 1) * 128;
     t3buf[k] = cbrtf(Num<TG>::ld(sd + j * 128 + k));
-    mbar_arrive(c.bar(kT3Ready));
-    if (!c.wait(kT3Ready, T)) return;
-    if (!c.wait(kGFull, T)) return;
+    c.arrive_w(kT3Ready);
+    if (!c.wait_w(kT3Ready, T)) return;
+    if (!c.wait_w(kGFull, T)) return;
     tc_fence_after();
     const bool diag = (T == 0);
     if (kCarryOnly) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
-    float local = 0.f, cval = carry;
+    // The prefix inside a tile is  carry + (sum of the totals of earlier 32-row blocks + scan inside the block):
+    // the backward recomputes it with four threads per key, one per block, and must get the same bits.
+    float tprev = 0.f, cval = carry;
 #pragma unroll 1
     for (int cb = 0; cb < 4; ++cb) {
       uint32_t g[32];
@@ -234,9 +239,10 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
       tc_wait_ld();
       if (cb == 3) {
         tc_fence_before();
-        mbar_arrive(c.bar(kGFree));
+        c.arrive_w(kGFree);
       }
       float v[32];
+      float local = 0.f;
 #pragma unroll
       for (int x = 0; x < 32; ++x) {
         const int q = cb * 32 + x;
@@ -244,11 +250,12 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
         float ell = log_retention(gated_affinity(gram_pow23(gv), s3, t3buf[q]));
         if (diag && q <= k) ell = 0.f;
         local += ell;
-        cval = local + carry;
+        cval = carry + (tprev + local);
         v[x] = (diag && q < k) ? mask_value() : cval;
       }
+      tprev += local;
       if (!kCarryOnly) {
-        if (cb == 0 && T >= 1 && !c.wait(kCFree, T - 1)) return;
+        if (cb == 0 && T >= 1 && !c.wait_w(kCFree, T - 1)) return;
 #pragma unroll
         for (int x = 0; x < 32; ++x) {
           const int q = cb * 32 + x;
@@ -257,7 +264,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
       }
     }
     carry = cval;
-    if (!kCarryOnly) mbar_arrive(c.bar(kCReady));
+    if (!kCarryOnly) c.arrive_w(kCReady);
   }
 }
 
@@ -276,17 +283,17 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
     // Every softmax thread observes every phase of c_ready and arrives on c_free exactly
     // once per tile (after its last read of C in that tile), whether or not its group has
     // a head to process in this tile; parity waits stay within one phase of the barrier.
-    if (!c.wait(kCReady, T)) return;
+    if (!c.wait_w(kCReady, T)) return;
     int last_r = -1;
     for (int r = R - 1; r >= 0; --r)
       if (((T * R + r) & 1) == me) { last_r = r; break; }
-    if (last_r < 0) mbar_arrive(c.bar(kCFree));
+    if (last_r < 0) c.arrive_w(kCFree);
     for (int r = 0; r < R; ++r, ++t) {
       if ((t & 1) != me) continue;
       const int sb = t & 1, ob = t % Cfg::kOBufs;
       const uint32_t tS = c.tmem + (sb ? Cfg::tS1 : Cfg::tS0) + lane_base;
       const uint32_t tO = c.tmem + ((Cfg::kOBufs == 2 && ob) ? Cfg::tO1 : Cfg::tO0) + lane_base;
-      if (!c.wait(kSFull + sb, t >> 1)) return;
+      if (!c.wait_w(kSFull + sb, t >> 1)) return;
       tc_fence_after();
       // pass 1: s = S + C (written back to TMEM), row max
       float m = -INFINITY;
@@ -308,7 +315,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         tmem_st32(tS + cb * 32, s);
       }
       tc_wait_st();
-      if (r == last_r) mbar_arrive(c.bar(kCFree));
+      if (r == last_r) c.arrive_w(kCFree);
       // pass 2: P = exp(s - m) as bf16 into the first 64 columns of the S buffer
       const float mb = m * kLog2e;
       float l = 0.f;
@@ -331,14 +338,14 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       }
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(c.bar(kPReady + sb));
+      c.arrive_w(kPReady + sb);
       const int qg = (c.i + T) * 128 + row;
       const float lse = m + lg2(l) * kLn2;
       const size_t orow = (chunk_id * R + r) * L + qg;
       p.lse[orow] = lse;
       if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
       const float linv = 1.0f / l;
-      if (!c.wait(kOFull + sb, t >> 1)) return;
+      if (!c.wait_w(kOFull + sb, t >> 1)) return;
       tc_fence_after();
       __nv_bfloat16* orow_ptr = p.out + orow * D;
 #pragma unroll 1
@@ -348,7 +355,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         tc_wait_ld();
         if (cb == D / 32 - 1) {
           tc_fence_before();
-          mbar_arrive(c.bar(kOFree + sb));
+          c.arrive_w(kOFree + sb);
         }
         uint32_t pk[16];
 #pragma unroll
@@ -389,9 +396,10 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     misc[1] = 0;
     for (int b = 0; b < kNumBars; ++b) {
       uint32_t count = 1;
-      if (b == kGFree || b == kCReady || b == kT3Ready) count = 128;
-      if (b == kCFree) count = 256;
-      if (b == kPReady || b == kPReady + 1 || b == kOFree || b == kOFree + 1) count = 128;
+      // one arrival per warp of the group that signals
+      if (b == kGFree || b == kCReady || b == kT3Ready) count = 4;
+      if (b == kCFree) count = 8;
+      if (b == kPReady || b == kPReady + 1 || b == kOFree || b == kOFree + 1) count = 4;
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();

@@ -59,6 +59,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Warp-collective variants (all 32 lanes must call them).  One arrival per warp instead
+// of 32 (mbarrier arrivals on one shared-memory word are serialised), and a wait whose
+// outcome is agreed by vote so that a warp never splits on a timeout.
+__device__ __forceinline__ void mbar_arrive_warp(uint32_t bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               uint64_t limit_ns = 2000000000ull) {
+  if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+  const uint64_t t0 = globaltimer_ns();
+  for (uint32_t it = 1;; ++it) {
+    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    if ((it & 63u) == 0u) {
+      const bool give_up = (*abort_flag != 0) || (globaltimer_ns() - t0 > limit_ns);
+      if (__any_sync(0xffffffffu, give_up)) break;
+    }
+  }
+  *abort_flag = 1;
+  return false;
+}
+
 // --------------------------------------------------------------------- TMA ----
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(

@@ -97,7 +97,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
   }
   auto kern = bwd_kernel<TG>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 384, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, p);
+  kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
