@@ -112,6 +112,14 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
   mbar_expect_tx(c.bar(bKvFull), 2 * BwdCfg::kTileBytes);
   tma_load_2d(sbase + BwdCfg::oKi, tmK, 0, krow, c.bar(bKvFull));
   tma_load_2d(sbase + BwdCfg::oVi, tmV, 0, krow, c.bar(bKvFull));
+  // dO tiles stream from HBM (g_out is far larger than L2): the tiles of the next head / next
+  // row tile are prefetched into L2 one phase ahead, so that the load issued when the single
+  // shared-memory slot frees up only pays L2 latency.
+  auto coords = [&](int T, int r, int& qrow, int& grow) {
+    const int j = c.tile_j(T, N);
+    qrow = (c.bh * R + r) * L + j * 128;
+    grow = (int)((chunk_id * R + r) * L + (size_t)j * 128);
+  };
   int rc = 0;
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
@@ -122,10 +130,21 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
       tma_load_2d(sbase + BwdCfg::oKj, tmK, 0, c.bh * L + j * 128, c.bar(bKjFull));
     }
     for (int r = 0; r < R; ++r, ++rc) {
+      int qrow, grow;
+      {
+        int Tn = T, rn = r + 1;
+        if (rn == R) { rn = 0; ++Tn; }
+        if (Tn < c.ntiles) {
+          coords(Tn, rn, qrow, grow);
+          tma_prefetch_2d(tmG, 0, grow);
+          tma_prefetch_2d(tmQ, 0, qrow);
+        }
+      }
+      coords(T, r, qrow, grow);
       if (rc >= 1 && !c.wait(bInFree, rc - 1)) return;
       mbar_expect_tx(c.bar(bInFull), 2 * BwdCfg::kTileBytes);
-      tma_load_2d(sbase + BwdCfg::oQ, tmQ, 0, (c.bh * R + r) * L + j * 128, c.bar(bInFull));
-      tma_load_2d(sbase + BwdCfg::oGo, tmG, 0, (int)((chunk_id * R + r) * L + (size_t)j * 128), c.bar(bInFull));
+      tma_load_2d(sbase + BwdCfg::oQ, tmQ, 0, qrow, c.bar(bInFull));
+      tma_load_2d(sbase + BwdCfg::oGo, tmG, 0, grow, c.bar(bInFull));
     }
   }
 }
@@ -142,84 +161,120 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p) {
   const uint32_t X0 = c.tmem + BwdCfg::tX0, X1 = c.tmem + BwdCfg::tX1, XC = c.tmem + BwdCfg::tXC;
   const uint32_t DV = c.tmem + BwdCfg::tDV, DK = c.tmem + BwdCfg::tDK;
 
+  // Descriptor low words of every operand, built once (shared-memory addresses never change);
+  // a k-step is then one 32-bit add per operand.  K-major: +32 B per 16 elements of K (>>4 = 2);
+  // MN-major: +2048 B per 16 rows of K (>>4 = 128); second 64-wide box of a K-major tile: +16384 B (>>4 = 1024).
+  const uint32_t kKi = desc_lo(sb + BwdCfg::oKi, 16), kKj = desc_lo(sb + BwdCfg::oKj, 16), kQ = desc_lo(sb + BwdCfg::oQ, 16);
+  const uint32_t kGo = desc_lo(sb + BwdCfg::oGo, 16), kVi = desc_lo(sb + BwdCfg::oVi, 16), kI = desc_lo(sb + BwdCfg::oI, 16);
+  const uint32_t kdS = desc_lo(sb + BwdCfg::odS, 16), kdG = desc_lo(sb + BwdCfg::oP, 16);
+  const uint32_t mP = desc_lo(sb + BwdCfg::oP, 16384), mdS = desc_lo(sb + BwdCfg::odS, 16384);
+  const uint32_t mGo = desc_lo(sb + BwdCfg::oGo, 16384), mQ = desc_lo(sb + BwdCfg::oQ, 16384);
+  const uint32_t mKi = desc_lo(sb + BwdCfg::oKi, 16384), mKj = desc_lo(sb + BwdCfg::oKj, 16384);
+
   // D[128x128] = A[128][64] B[128][64]^T (both K-major, one 64-element box)
   auto mma_nt = [&](uint32_t d, uint32_t a, uint32_t b) {
+    mma_ss_c<false>(d, desc_from_lo(a), desc_from_lo(b), id_nt);
 #pragma unroll
-    for (int ks = 0; ks < 4; ++ks)
-      mma_ss(d, smem_desc_sw128(a + ks * 32, 16, 1024), smem_desc_sw128(b + ks * 32, 16, 1024), id_nt, ks > 0);
+    for (int ks = 1; ks < 4; ++ks) mma_ss_c<true>(d, desc_from_lo(a + ks * 2), desc_from_lo(b + ks * 2), id_nt);
   };
   // D[128x64] (+)= A^T B : A stored [K=128 rows][M=128] (two 64-wide boxes), B stored [K=128 rows][N=64]
   auto mma_tt = [&](uint32_t d, uint32_t a, uint32_t b, bool acc) {
+    if (acc) mma_ss_c<true>(d, desc_from_lo(a), desc_from_lo(b), id_tt);
+    else mma_ss_c<false>(d, desc_from_lo(a), desc_from_lo(b), id_tt);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      mma_ss(d, smem_desc_sw128(a + ks * 2048, 16384, 1024), smem_desc_sw128(b + ks * 2048, 16384, 1024), id_tt,
-             (acc || ks > 0) ? 1u : 0u);
+    for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(d, desc_from_lo(a + ks * 128), desc_from_lo(b + ks * 128), id_tt);
   };
   // D[128x64] (+)= A B : A stored [M=128 rows][K=128] (two boxes), B stored [K=128 rows][N=64]
   auto mma_nn = [&](uint32_t d, uint32_t a, uint32_t b, bool acc) {
+    if (acc) mma_ss_c<true>(d, desc_from_lo(a), desc_from_lo(b), id_nt64);
+    else mma_ss_c<false>(d, desc_from_lo(a), desc_from_lo(b), id_nt64);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      mma_ss(d, smem_desc_sw128(a + (ks >> 2) * 16384 + (ks & 3) * 32, 16, 1024), smem_desc_sw128(b + ks * 2048, 16384, 1024),
-             id_nt64, (acc || ks > 0) ? 1u : 0u);
+    for (int ks = 1; ks < 8; ++ks)
+      mma_ss_c<true>(d, desc_from_lo(a + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(b + ks * 128), id_nt64);
   };
 
+#ifdef UA_PROFILE_PHASES
+  long long mt = clock64(), macc[12] = {0,0,0,0,0,0,0,0,0,0,0,0};
+#define UA_MPH(i) { long long n_ = clock64(); macc[i] += n_ - mt; mt = n_; }
+#else
+#define UA_MPH(i)
+#endif
   if (!c.wait(bKvFull, 0)) return;
   int x0_uses = 0, x1_uses = 0, rc = 0;
   bool have_acc = false;     // dV / dK_i accumulators hold something
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
     if (valid) {
+      UA_MPH(0)
       if (!c.wait(bKjFull, T)) return;
+      UA_MPH(1)
       if (x0_uses >= 1 && !c.wait(bX0Free, x0_uses - 1)) return;
+      UA_MPH(2)
       tc_fence_after();
-      mma_nt(X0, sb + BwdCfg::oKi, sb + BwdCfg::oKj);                 // G = K_i K_j^T
+      mma_nt(X0, kKi, kKj);                                           // G = K_i K_j^T
       tc_commit(c.bar(bGFull));
       ++x0_uses;
     }
     for (int r = 0; r < R; ++r, ++rc) {
+      UA_MPH(0)
       if (!c.wait(bInFull, rc)) return;
+      UA_MPH(3)
       if (valid) {
         if (!c.wait(bX0Free, x0_uses - 1)) return;
+        UA_MPH(4)
         tc_fence_after();
-        mma_nt(X0, sb + BwdCfg::oQ, sb + BwdCfg::oKi);                // S = Q K_i^T
+        mma_nt(X0, kQ, kKi);                                          // S = Q K_i^T
         ++x0_uses;
       }
+      UA_MPH(0)
       if (x1_uses >= 1 && !c.wait(bX1Free, x1_uses - 1)) return;
+      UA_MPH(5)
       tc_fence_after();
-      mma_nt(X1, sb + BwdCfg::oGo, sb + BwdCfg::oVi);                 // dP = dO V_i^T
+      mma_nt(X1, kGo, kVi);                                           // dP = dO V_i^T
       ++x1_uses;
       tc_commit(c.bar(bSdpFull));
+      UA_MPH(0)
       if (!c.wait(bPdsReady, rc)) return;
+      UA_MPH(6)
       tc_fence_after();
-      mma_tt(DV, sb + BwdCfg::oP, sb + BwdCfg::oGo, have_acc);        // dV_i += P^T dO
-      mma_tt(DK, sb + BwdCfg::odS, sb + BwdCfg::oQ, have_acc);        // dK_i += dS^T Q
+      mma_tt(DV, mP, mGo, have_acc);                                  // dV_i += P^T dO
+      mma_tt(DK, mdS, mQ, have_acc);                                  // dK_i += dS^T Q
       have_acc = true;
       tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
-      mma_nn(X1, sb + BwdCfg::odS, sb + BwdCfg::oKi, false);          // dQ = dS K_i  (dP has been consumed)
+      mma_nn(X1, kdS, mKi, false);                                    // dQ = dS K_i  (dP has been consumed)
       if (valid) {
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb)                                 // dC[key][row] (+)= dS^T I
-          mma_ss(XC + nb * 16, smem_desc_sw128(sb + BwdCfg::odS + nb * 2048, 16384, 1024),
-                 smem_desc_sw128(sb + BwdCfg::oI, 16, 1024), id_dc, r > 0 ? 1u : 0u);
+          if (r > 0) mma_ss_c<true>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
+          else mma_ss_c<false>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
       }
       tc_commit(c.bar(bRDone));
     }
     if (valid) {
+      UA_MPH(0)
       if (!c.wait(bX0Free, x0_uses - 1)) return;
+      UA_MPH(7)
       tc_fence_after();
-      mma_nt(X0, sb + BwdCfg::oKi, sb + BwdCfg::oKj);                 // G again for the decay backward
+      mma_nt(X0, kKi, kKj);                                           // G again for the decay backward
       tc_commit(c.bar(bG2Full));
       ++x0_uses;
+      UA_MPH(0)
       if (!c.wait(bDgReady, T)) return;
+      UA_MPH(8)
       if (!c.wait(bX1Free, x1_uses - 1)) return;
+      UA_MPH(9)
       tc_fence_after();
-      mma_tt(X1, sb + BwdCfg::oP, sb + BwdCfg::oKi, false);           // dK_j = dG^T K_i
+      mma_tt(X1, mP, mKi, false);                                     // dK_j = dG^T K_i
       ++x1_uses;
-      mma_nn(DK, sb + BwdCfg::oP, sb + BwdCfg::oKj, true);            // dK_i += dG K_j
+      mma_nn(DK, kdG, mKj, true);                                     // dK_i += dG K_j
       tc_commit(c.bar(bDkjFull));
     }
   }
   tc_commit(c.bar(bFinal));
+#ifdef UA_PROFILE_PHASES
+  UA_MPH(0)
+  if (blockIdx.x == 0) for (int z = 0; z < 10; ++z) reinterpret_cast<long long*>(p.status)[24 + z] = macc[z];
+#endif
 }
 
 // ------------------------------------------------------------ worker groups --

@@ -147,20 +147,25 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
   const uint32_t tS[2] = {c.tmem + Cfg::tS0, c.tmem + Cfg::tS1};
   const uint32_t tO[2] = {c.tmem + Cfg::tO0, c.tmem + (Cfg::kOBufs == 2 ? Cfg::tO1 : Cfg::tO0)};
 
-  // D[128 x 128] = A[128][D] * B[128][D]^T, both K-major
-  auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_addr, uint32_t b_addr) {
+  // D[128 x 128] = A[128][D] * B[128][D]^T, both K-major.  Operands are passed as descriptor low words
+  // (built once: shared-memory addresses never change); a k-step of 16 elements is +32 B (>>4 = 2), the
+  // second 64-element box of a tile +16384 B (>>4 = 1024).
+  auto issue_kmajor = [&](uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo) {
+    mma_ss_c<false>(d_tmem, desc_from_lo(a_lo), desc_from_lo(b_lo), idesc_sq);
 #pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks) {
-      const uint32_t off = (ks >> 2) * Cfg::kBoxBytes + (ks & 3) * 32;
-      mma_ss(d_tmem, smem_desc_sw128(a_addr + off, 16, 1024), smem_desc_sw128(b_addr + off, 16, 1024), idesc_sq, ks > 0);
+    for (int ks = 1; ks < D / 16; ++ks) {
+      const uint32_t off = (ks >> 2) * 1024 + (ks & 3) * 2;
+      mma_ss_c<true>(d_tmem, desc_from_lo(a_lo + off), desc_from_lo(b_lo + off), idesc_sq);
     }
   };
+  const uint32_t kKi = desc_lo(sbase + Cfg::oKi, 16);
+  const uint32_t mVi = desc_lo(sbase + Cfg::oVi, Cfg::kBoxBytes);
   auto issue_g = [&](int T) -> bool {
     const int ks = T % Cfg::kKjStages, u = T / Cfg::kKjStages;
     if (!c.wait(kKjFull + ks, u)) return false;
     if (T >= 1 && !c.wait(kGFree, T - 1)) return false;
     tc_fence_after();
-    issue_kmajor(c.tmem + Cfg::tG, sbase + Cfg::oKi, sbase + Cfg::oKj + ks * Cfg::kTileBytes);
+    issue_kmajor(c.tmem + Cfg::tG, kKi, desc_lo(sbase + Cfg::oKj + ks * Cfg::kTileBytes, 16));
     tc_commit(c.bar(kGFull));
     tc_commit(c.bar(kKjEmpty + ks));
     return true;
@@ -176,9 +181,9 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
       if (tt >= 1 && !c.wait(kOFree + ((tt - 1) & 1), (tt - 1) >> 1)) return false;
     }
     tc_fence_after();
+    mma_ts_c<false>(tO[ob], tS[sb], desc_from_lo(mVi), idesc_pv);
 #pragma unroll
-    for (int ks = 0; ks < 8; ++ks)
-      mma_ts(tO[ob], tS[sb] + ks * 8, smem_desc_sw128(sbase + Cfg::oVi + ks * 2048, Cfg::kBoxBytes, 1024), idesc_pv, ks > 0);
+    for (int ks = 1; ks < 8; ++ks) mma_ts_c<true>(tO[ob], tS[sb] + ks * 8, desc_from_lo(mVi + ks * 128), idesc_pv);
     tc_commit(c.bar(kOFull + sb));
     return true;
   };
@@ -196,7 +201,7 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
       const int qs = t & 1;
       if (!c.wait(kQFull + qs, t >> 1)) return;
       tc_fence_after();
-      issue_kmajor(tS[t & 1], sbase + Cfg::oQ + qs * Cfg::kTileBytes, sbase + Cfg::oKi);
+      issue_kmajor(tS[t & 1], desc_lo(sbase + Cfg::oQ + qs * Cfg::kTileBytes, 16), kKi);
       tc_commit(c.bar(kSFull + (t & 1)));
       tc_commit(c.bar(kQEmpty + qs));
       if (t >= 1 && !issue_pv(t - 1)) return;
