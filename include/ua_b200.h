@@ -113,6 +113,29 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype,
            void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
            void* workspace, size_t workspace_bytes, int flags, void* stream);
 
+/* Optional hand-over of the decay-prefix table from forward to backward.  The
+ * backward sweeps the rows downwards and needs, per key and row tile, the decay
+ * prefix at the start of the tile; by default ua_bwd recomputes that table with a
+ * pre-pass.  ua_fwd_keep() is ua_fwd() that also stores the table it has in
+ * registers anyway into carry_out (ua_carry_bytes() bytes, fp32; 0 bytes means
+ * this shape has no table and carry_out is ignored), and ua_bwd_kept() is ua_bwd()
+ * that reads it from carry_in instead of running the pre-pass (carry_in may be
+ * NULL: then it is ua_bwd()).  Same inputs must be given to both calls.  The
+ * reference keeps nothing but the five inputs (universal_attention_autograd.py:
+ * 166-169); this is the "tiny extra saved tensor" variant of the same recompute. */
+size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags);
+int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype,
+                const void* kc, const void* vc, const void* xq,
+                const void* static_src, const void* static_dest,
+                void* out_cm, float* lse_cm, void* denom_cm, void* carry_out,
+                void* workspace, size_t workspace_bytes, int flags, void* stream);
+int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
+                const void* kc, const void* vc, const void* xq,
+                const void* static_src, const void* static_dest,
+                const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype, const void* carry_in,
+                void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+                void* workspace, size_t workspace_bytes, int flags, void* stream);
+
 /* Backward for callers that must not allocate.  No counterpart in the reference.
  *
  * Some hosts of this library cannot hand it a workspace: an inference or

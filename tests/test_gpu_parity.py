@@ -248,3 +248,25 @@ def test_tensor_core_backward_matches_simt_backward(shape, skip):
     for a, b, key in zip(tc, sm, GRADS):
         assert torch.isfinite(a.float()).all(), key
         assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, rel_fro(a.float().cpu(), b.float().cpu()))
+
+
+def test_backward_with_kept_decay_table_matches_prepass():
+    """ua_fwd_keep / ua_bwd_kept: the decay-prefix table handed over by the forward gives the same
+    gradients as the backward's own pre-pass (same kernels; only fp32 atomic order differs)."""
+    from universal_attention_triton_b200 import ops
+    shape = (1, 2, 2, 768, 128, 64)
+    B, H, R, L, c, D = shape
+    n = L // c
+    ins, _ = _bf16_case(*shape, seed=41)
+    cu = _cuda(*ins)
+    gen = torch.Generator(device="cuda").manual_seed(8)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    out_cm, lse_cm, den_cm, carry = ops.forward_cm(*cu, keep_carry=True)
+    assert carry is not None and carry.numel() == B * H * n * n * 128
+    out2, lse2, _ = ops.forward_cm(*cu)
+    assert torch.equal(out_cm, out2) and torch.equal(lse_cm, lse2)
+    a = ops.backward_cm(*cu, g_out, g_lse, carry=carry)
+    b = ops.backward_cm(*cu, g_out, g_lse)
+    for x, y, key in zip(a, b, GRADS):
+        assert rel_fro(x.float().cpu(), y.float().cpu()) <= 1e-3, key

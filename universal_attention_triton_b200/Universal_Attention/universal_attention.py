@@ -11,18 +11,14 @@ from .. import universal_attention_autograd as _ua
 
 class UniversalAttention(Function):
     @staticmethod
-    def forward(kc, vc, xq, static_src, static_dest):
+    def forward(ctx, kc, vc, xq, static_src, static_dest):
         b, h, r, _n, _c, d = xq.shape
         _, _, n_, c_, _ = kc.shape
         assert kc.shape == (b, h, n_, c_, d)
         assert vc.shape == (b, h, n_, c_, d)
         assert static_src.shape == (b, h, n_, c_)
         assert static_dest.shape == (b, h, _n, _c)
-        return _ua._forward(kc, vc, xq, static_src, static_dest)
-
-    @staticmethod
-    def setup_context(ctx, inputs, outputs):
-        ctx.save_for_backward(*inputs)
+        return _ua._forward(ctx, kc, vc, xq, static_src, static_dest)
 
     @staticmethod
     def backward(ctx, dout, ddenom):

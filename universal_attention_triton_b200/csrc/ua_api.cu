@@ -183,9 +183,23 @@ size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
   return bwd_layout(s, rt).total;
 }
 
+size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags) {
+  if (check_dims(dims) != UA_OK) return 0;
+  ua::Shape s = to_shape(dims);
+  if ((flags & UA_FLAG_FORCE_SIMT) || !ua::sm100::bwd_supported(s, dtype)) return 0;
+  return (size_t)s.B * s.H * s.N * s.N * 128 * sizeof(float);
+}
+
 int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
            const void* static_src, const void* static_dest, void* out_cm, float* lse_cm, void* denom_cm,
            void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  return ua_fwd_keep(dims, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, out_cm, lse_cm, denom_cm, nullptr,
+                     workspace, workspace_bytes, flags, stream);
+}
+
+int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                const void* static_src, const void* static_dest, void* out_cm, float* lse_cm, void* denom_cm,
+                void* carry_out, void* workspace, size_t workspace_bytes, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -201,7 +215,7 @@ int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
     fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest;
     fp.out = static_cast<bf16*>(out_cm); fp.lse = lse_cm; fp.denom = static_cast<bf16*>(denom_cm);
     fp.status = static_cast<int*>(workspace);
-    fp.carry = nullptr;
+    fp.carry = ua_carry_bytes(dims, dtype, flags) ? static_cast<float*>(carry_out) : nullptr;
     return ua::sm100::launch_fwd(s, gate_dtype, kc, vc, xq, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
   }
 
@@ -220,6 +234,14 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
            const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
            int g_denom_dtype, void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
            void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  return ua_bwd_kept(dims, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, g_denom_dtype,
+                     nullptr, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, workspace_bytes, flags, stream);
+}
+
+int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
+                int g_denom_dtype, const void* carry_in, void* dkc, void* dvc, void* dxq, void* dstatic_src,
+                void* dstatic_dest, void* workspace, size_t workspace_bytes, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -240,7 +262,8 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
     ua::sm100::BwdParams bp;
     bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
     bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-    bp.carry = reinterpret_cast<float*>(ws + w.off_carry);
+    float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
+    bp.carry = carry_tab;
     bp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
     bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
     bp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
@@ -248,7 +271,7 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
     bp.dss = dstatic_src;
     bp.status = reinterpret_cast<int*>(ws);
     bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, reinterpret_cast<float*>(ws + w.off_carry), st);
+    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, carry_tab, carry_in == nullptr, st);
     if (e) return e;
     const size_t BHs = (size_t)s.B * s.H;
     if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;

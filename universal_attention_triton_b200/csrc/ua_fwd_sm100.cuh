@@ -42,7 +42,7 @@ struct FwdParams {
   float* lse;            // (b,h,n,r,L)
   __nv_bfloat16* denom;  // (b,h,n,r,L) or null
   int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
-  float* carry;          // carry-only mode: (b*h*n, n, 128) decay prefix of key k at the start of row tile j
+  float* carry;          // optional (required in carry-only mode): (b*h*n, n, 128) decay prefix of key k at the start of row tile j
 };
 
 // Gated affinity and log-retention of one (key, row) pair from the Gram value
@@ -233,7 +233,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
     if (!c.wait_w(kGFull, T)) return;
     tc_fence_after();
     const bool diag = (T == 0);
-    if (kCarryOnly) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
+    if (kCarryOnly || p.carry) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
     // The prefix inside a tile is  carry + (sum of the totals of earlier 32-row blocks + scan inside the block):
     // the backward recomputes it with four threads per key, one per block, and must get the same bits.
     float tprev = 0.f, cval = carry;

@@ -79,13 +79,13 @@ inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 &
 // (2) the backward kernel proper.  The caller zeroes the fp32 accumulators.
 template <typename TG>
 int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const BwdParams& p,
-                 float* carry, cudaStream_t st) {
+                 float* carry, bool run_prepass, cudaStream_t st) {
   CUtensorMap tmK, tmV, tmQ, tmG;
   const uint64_t BH = (uint64_t)s.B * s.H;
   if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64) ||
       !make_rows_map(&tmQ, xq, BH * s.R * s.L, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, 64))
     return UA_ERR_CUDA;
-  {
+  if (run_prepass) {
     using Cfg = FwdCfg<64>;
     FwdParams fp;
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
@@ -102,9 +102,9 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
 }
 
 inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const void* g_out,
-                      const BwdParams& p, float* carry, cudaStream_t st) {
-  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, st)
-                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, st);
+                      const BwdParams& p, float* carry, bool run_prepass, cudaStream_t st) {
+  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, run_prepass, st)
+                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, run_prepass, st);
 }
 
 }  // namespace sm100

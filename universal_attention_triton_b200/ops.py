@@ -60,8 +60,10 @@ def _gate_cast(g, dtype):
     return g.float().contiguous()
 
 
-def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0):
-    """Returns (out_cm, lse_cm fp32, denom_cm).  ``denom_cm`` is ``lse_cm`` itself in fp32 mode."""
+def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0, keep_carry: bool = False):
+    """Returns (out_cm, lse_cm fp32, denom_cm).  ``denom_cm`` is ``lse_cm`` itself in fp32 mode.
+    With ``keep_carry`` a fourth value is returned: the decay-prefix table for ``backward_cm(carry=...)``
+    (``None`` for shapes whose backward does not use one)."""
     _require_cuda(kc, vc, xq, static_src, static_dest)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
@@ -82,16 +84,24 @@ def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0):
         denom_cm = lse_cm if dt == torch.float32 else torch.empty(b, h, n, r, L, dtype=dt, device=kc.device)
         ws_bytes = lib.ua_fwd_workspace_bytes(ctypes.byref(dims), code, flags)
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
-        rc = lib.ua_fwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kc), _ptr(vc), _ptr(q), _ptr(ss), _ptr(sd),
-                        _ptr(out_cm), _ptr(lse_cm), _ptr(None if denom_cm is lse_cm else denom_cm),
-                        _ptr(ws), ws_bytes, flags, _stream())
+        carry = None
+        if keep_carry:
+            cbytes = lib.ua_carry_bytes(ctypes.byref(dims), code, flags)
+            if cbytes:
+                carry = torch.empty(cbytes // 4, dtype=torch.float32, device=kc.device)
+        rc = lib.ua_fwd_keep(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kc), _ptr(vc), _ptr(q), _ptr(ss), _ptr(sd),
+                             _ptr(out_cm), _ptr(lse_cm), _ptr(None if denom_cm is lse_cm else denom_cm), _ptr(carry),
+                             _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_fwd")
         _check_status(lib, ws, "ua_fwd")
+    if keep_carry:
+        return out_cm, lse_cm, denom_cm, carry
     return out_cm, lse_cm, denom_cm
 
 
-def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0):
-    """Gradients (dkc, dvc, dxq, dstatic_src, dstatic_dest) shaped and typed like the inputs."""
+def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0, carry=None):
+    """Gradients (dkc, dvc, dxq, dstatic_src, dstatic_dest) shaped and typed like the inputs.
+    ``carry``: the table ``forward_cm(keep_carry=True)`` returned for the same inputs (skips the pre-pass)."""
     _require_cuda(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
@@ -118,8 +128,10 @@ def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags
         dsd = torch.empty_like(sd)
         ws_bytes = lib.ua_bwd_workspace_bytes(ctypes.byref(dims), code, flags)
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
-        rc = lib.ua_bwd(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
-                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype),
+        if carry is not None and carry.numel() * 4 != lib.ua_carry_bytes(ctypes.byref(dims), code, flags):
+            carry = None
+        rc = lib.ua_bwd_kept(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
+                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype), _ptr(carry),
                         _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss), _ptr(dsd), _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_bwd")
         _check_status(lib, ws, "ua_bwd")

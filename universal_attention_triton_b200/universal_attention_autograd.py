@@ -13,8 +13,10 @@ dtypes.  By default they are permuted views of chunk-major storage (see
 ``ops.py``); ``set_output_layout("reference")`` makes them contiguous in the
 reference's order at the cost of one extra pass over ``out``.
 
-Only the five inputs are saved for backward; everything else is recomputed
-(universal_attention_autograd.py:41-44, :166-169).  Tensors must be CUDA
+The five inputs are saved for backward and everything is recomputed from them
+(universal_attention_autograd.py:41-44, :166-169); the only extra is the small
+fp32 decay-prefix table the forward kernel has in registers anyway (16.8 MB at
+B4 H8 L4096), which spares the backward its pre-pass.  Tensors must be CUDA
 tensors: there is no CPU or PyTorch fallback.
 """
 from __future__ import annotations
@@ -44,8 +46,10 @@ def set_strict_masked_grads(on: bool) -> None:
     _STRICT_MASKED_GRADS = bool(on)
 
 
-def _forward(kc, vc, xq, static_src, static_dest):
-    out_cm, lse_cm, denom_cm = ops.forward_cm(kc, vc, xq, static_src, static_dest)
+def _forward(ctx, kc, vc, xq, static_src, static_dest):
+    out_cm, lse_cm, denom_cm, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, keep_carry=True)
+    ctx.save_for_backward(kc, vc, xq, static_src, static_dest)
+    ctx.ua_carry = carry
     if _OUTPUT_LAYOUT == "reference":
         return ops.to_reference_layout(out_cm, denom_cm)
     return ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm)
@@ -56,25 +60,22 @@ def _backward(ctx, g_out, g_denom):
     flags = 0 if _STRICT_MASKED_GRADS else _lib.FLAG_SKIP_MASKED_GRADS
     g_out_cm = ops.out_to_chunk_major(g_out)
     g_denom_cm = ops.denom_to_chunk_major(g_denom)
-    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags)
+    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags,
+                           carry=getattr(ctx, "ua_carry", None))
 
 
 class UniversalAttention(Function):
     """kc, vc (b,h,n,c,d); xq (b,h,r,l,d); static_src (b,h,n,c); static_dest (b,h,l)."""
 
     @staticmethod
-    def forward(kc, vc, xq, static_src, static_dest):
+    def forward(ctx, kc, vc, xq, static_src, static_dest):
         b, h, r, l, d = xq.shape
         _, _, n, c, _ = kc.shape
         assert kc.shape == (b, h, n, c, d) and n * c == l
         assert vc.shape == (b, h, n, c, d)
         assert static_src.shape == (b, h, n, c)
         assert static_dest.shape == (b, h, l)
-        return _forward(kc, vc, xq, static_src, static_dest)
-
-    @staticmethod
-    def setup_context(ctx, inputs, outputs):
-        ctx.save_for_backward(*inputs)
+        return _forward(ctx, kc, vc, xq, static_src, static_dest)
 
     @staticmethod
     def backward(ctx, g_out, g_denom):
@@ -86,18 +87,14 @@ class UniversalAttention2(Function):
     The row chunking (_n,_c) is only a view of the rows; the result does not depend on it."""
 
     @staticmethod
-    def forward(kc, vc, xq, static_src, static_dest):
+    def forward(ctx, kc, vc, xq, static_src, static_dest):
         b, h, r, _n, _c, d = xq.shape
         _, _, n_, c_, _ = kc.shape
         assert kc.shape == (b, h, n_, c_, d) and n_ * c_ == _n * _c
         assert vc.shape == (b, h, n_, c_, d)
         assert static_src.shape == (b, h, n_, c_)
         assert static_dest.shape == (b, h, _n, _c)
-        return _forward(kc, vc, xq, static_src, static_dest)
-
-    @staticmethod
-    def setup_context(ctx, inputs, outputs):
-        ctx.save_for_backward(*inputs)
+        return _forward(ctx, kc, vc, xq, static_src, static_dest)
 
     @staticmethod
     def backward(ctx, g_out, g_denom):
