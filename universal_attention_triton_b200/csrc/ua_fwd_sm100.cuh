@@ -38,10 +38,12 @@ struct FwdParams {
   Shape s;
   const void* ssrc;
   const void* sdest;
+  const void* vc;        // values, for the masked-row fill
   __nv_bfloat16* out;    // chunk-major (b,h,n,r,L,d)
   float* lse;            // (b,h,n,r,L)
   __nv_bfloat16* denom;  // (b,h,n,r,L) or null
   int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
+  int fill_masked;       // write the rows before the key chunk (uniform softmax) from the two otherwise idle warps
   float* carry;          // optional (required in carry-only mode): (b*h*n, n, 128) decay prefix of key k at the start of row tile j
 };
 
@@ -71,7 +73,8 @@ struct FwdCfg {
   static constexpr int oT3 = oCs + 65536;
   static constexpr int oBar = oT3 + 1024;
   static constexpr int oMisc = oBar + 256;
-  static constexpr int kSmemBytes = oMisc + 64 + 1024;   // + slack to align the base to 1024 B
+  static constexpr int oFill = oMisc + 64;                // bf16[D]: value of a fully masked output row
+  static constexpr int kSmemBytes = oFill + 256 + 1024;  // + slack to align the base to 1024 B
   static constexpr uint32_t tG = 0, tS0 = 128, tS1 = 256, tO0 = 384, tO1 = 384 + D;
 };
 
@@ -378,6 +381,38 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
   }
 }
 
+// Rows before the key chunk (j < i): every score is -1e12 (fp32 absorbs k.q), the softmax is
+// uniform, so out = sum_k bf16(1/128) V_k and lse = -1e12 (universal_attention_autograd.py:28,
+// :154).  Pure HBM writes (i * 128 * R rows), done by warps 2-3 while the others compute the
+// n - i valid tiles: chunks with many masked rows have few tiles to compute.
+template <int D>
+__device__ __forceinline__ void fwd_fill_rows(const FwdCtx<D>& c, const FwdParams& p, __nv_bfloat16* vmean) {
+  const int t = threadIdx.x - 64;                      // 0..63
+  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const __nv_bfloat16* v = static_cast<const __nv_bfloat16*>(p.vc) + ((size_t)c.bh * L + (size_t)c.i * 128) * D;
+  const float w = 1.0f / 128.0f;
+  for (int d = t; d < D; d += 64) {
+    float acc = 0.f;
+    for (int k = 0; k < 128; ++k) acc = fmaf(w, __bfloat162float(v[(size_t)k * D + d]), acc);
+    vmean[d] = __float2bfloat16_rn(acc);
+  }
+  named_bar_sync(2, 64);
+  const size_t chunk_id = (size_t)c.bh * N + c.i;
+  const int rows = c.i * 128;
+  constexpr int kVecPerRow = D / 8;                    // 16-byte vectors
+  const uint4 mine = reinterpret_cast<const uint4*>(vmean)[t % kVecPerRow];   // 64 % kVecPerRow == 0: fixed per thread
+  for (int r = 0; r < R; ++r) {
+    uint4* o = reinterpret_cast<uint4*>(p.out + ((chunk_id * R + r) * L) * D);
+    const size_t nvec = (size_t)rows * kVecPerRow;
+    for (size_t e = t; e < nvec; e += 64) o[e] = mine;
+    float* lr = p.lse + (chunk_id * R + r) * L;
+    for (int q = t; q < rows; q += 64) {
+      lr[q] = mask_value();
+      if (p.denom) p.denom[(chunk_id * R + r) * L + q] = __float2bfloat16_rn(mask_value());
+    }
+  }
+}
+
 template <int D, typename TG, bool kCarryOnly>
 __global__ void __launch_bounds__(512, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -429,6 +464,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     fwd_decay<D, TG, kCarryOnly>(c, p);
   } else if (warp >= 8 && !kCarryOnly) {
     fwd_softmax<D>(c, p, (warp - 8) >> 2);
+  } else if ((warp == 2 || warp == 3) && !kCarryOnly && p.fill_masked && c.i > 0) {
+    fwd_fill_rows<D>(c, p, reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oFill));
   }
 
   tc_fence_before();
@@ -440,41 +477,6 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     __syncthreads();
   }
   if (warp == 0) tmem_dealloc(c.tmem, 512);
-}
-
-// Rows before the key chunk: every score is -1e12 (fp32 absorbs k.q), the softmax
-// is uniform, so out = sum_k bf16(1/128) V_k and lse = -1e12
-// (universal_attention_autograd.py:28, :154).  HBM-write bound.
-__global__ void __launch_bounds__(256) fwd_fill_masked_kernel(const __nv_bfloat16* __restrict__ vc, __nv_bfloat16* __restrict__ out,
-                                                              float* __restrict__ lse, __nv_bfloat16* __restrict__ denom, Shape s) {
-  __shared__ __align__(16) __nv_bfloat16 vmean[256];
-  const int BH = s.B * s.H;
-  const int i = s.N - 1 - blockIdx.x / BH;          // largest fill first
-  const int bh = blockIdx.x % BH;
-  if (i == 0) return;
-  const int D = s.D, L = s.L, R = s.R, C = s.C;
-  const __nv_bfloat16* v = vc + ((size_t)bh * L + (size_t)i * C) * D;
-  const float w = __bfloat162float(__float2bfloat16_rn(1.0f / (float)C));
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int k = 0; k < C; ++k) acc = fmaf(w, __bfloat162float(v[(size_t)k * D + d]), acc);
-    vmean[d] = __float2bfloat16_rn(acc);
-  }
-  __syncthreads();
-  const size_t chunk_id = (size_t)bh * s.N + i;
-  const int rows = i * C;
-  const int vec_per_row = D / 8;                       // 16-byte vectors
-  const uint4* vm = reinterpret_cast<const uint4*>(vmean);
-  for (int r = 0; r < R; ++r) {
-    uint4* o = reinterpret_cast<uint4*>(out + ((chunk_id * R + r) * L) * D);
-    const size_t nvec = (size_t)rows * vec_per_row;
-    for (size_t e = threadIdx.x; e < nvec; e += blockDim.x) o[e] = vm[e % vec_per_row];
-    float* lr = lse + (chunk_id * R + r) * L;
-    for (int q = threadIdx.x; q < rows; q += blockDim.x) {
-      lr[q] = mask_value();
-      if (denom) denom[(chunk_id * R + r) * L + q] = __float2bfloat16_rn(mask_value());
-    }
-  }
 }
 
 }  // namespace sm100

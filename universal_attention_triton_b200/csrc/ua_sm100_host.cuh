@@ -55,11 +55,10 @@ int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     return UA_ERR_CUDA;
   auto kern = fwd_kernel<D, TG, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  if (fill_masked && s.N > 1) {
-    fwd_fill_masked_kernel<<<(unsigned)(BH * s.N), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(vc), p.out, p.lse, p.denom, s);
-    if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
-  }
-  kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, p);
+  FwdParams q = p;
+  q.vc = vc;
+  q.fill_masked = fill_masked ? 1 : 0;
+  kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, q);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
@@ -89,7 +88,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     using Cfg = FwdCfg<64>;
     FwdParams fp;
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
-    fp.status = p.status; fp.carry = carry;
+    fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
     auto kern = fwd_kernel<64, TG, true>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
     kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, fp);
