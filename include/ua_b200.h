@@ -190,9 +190,13 @@ int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float*
                  void* merged, void* stream);
 
 /* SMVecMatMul.backward (universal_attention_autograd.py:291-297) producing
- * chunk-major gradients: g_out_cm (dtype) and g_lse_cm (fp32). */
+ * chunk-major gradients: g_out_cm (dtype) and g_lse_cm (fp32).  head_dim must be a
+ * power of two between 8 (bf16) / 4 (fp32) and 128.  With UA_FLAG_SKIP_MASKED_FILL the
+ * (row, chunk) blocks with row < chunk index * chunk size -- the rows before a key
+ * chunk, whose merge weight is exactly zero -- are left unwritten: valid when the consumer is ua_bwd with
+ * UA_FLAG_SKIP_MASKED_GRADS, which never reads them. */
 int ua_merge_bwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
-                 const void* g_merged, void* g_out_cm, float* g_lse_cm, void* stream);
+                 const void* g_merged, void* g_out_cm, float* g_lse_cm, int flags, void* stream);
 
 #ifdef __cplusplus
 }

@@ -45,7 +45,7 @@ SIGNATURES = {
     "ua_workspace_status": (_i, [_vp, _vp]),
     "ua_relayout": (_i, [_dp, _i, _i, _i, _vp, _vp, _vp]),
     "ua_merge_fwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp]),
-    "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
 }
 
 _lib = None

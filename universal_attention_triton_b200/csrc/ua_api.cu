@@ -373,41 +373,61 @@ int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float*
   if (e) return e;
   if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
   if (!out_cm || !lse_cm || !merged) return UA_ERR_NULL_POINTER;
+  if (!aligned16(out_cm) || !aligned16(merged)) return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
   const long long rows = (long long)s.B * s.H * s.R * s.L;
-  long long blocks = (rows + ua::aux::kMergeWarps - 1) / ua::aux::kMergeWarps;
-  if (blocks > 148 * 32) blocks = 148 * 32;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == UA_F32)
-    ua::aux::merge_fwd_kernel<float><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, 0, st>>>(
-        static_cast<const float*>(out_cm), lse_cm, static_cast<float*>(merged), s.B * s.H, s.N, s.R, s.L, s.D);
-  else
-    ua::aux::merge_fwd_kernel<bf16><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, 0, st>>>(
-        static_cast<const bf16*>(out_cm), lse_cm, static_cast<bf16*>(merged), s.B * s.H, s.N, s.R, s.L, s.D);
+  const int tpr = s.D * (dtype == UA_F32 ? 4 : 2) / 16;
+  const unsigned blocks = (unsigned)((rows * tpr + ua::aux::kMergeThreads - 1) / ua::aux::kMergeThreads);
+#define UA_MERGE_FWD(T, TPR)                                                                                         \
+  ua::aux::merge_fwd_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(static_cast<const T*>(out_cm), lse_cm, \
+                                                                                static_cast<T*>(merged), rows, s.N, s.R, s.L)
+  if (dtype == UA_BF16 && s.D == 64) UA_MERGE_FWD(bf16, 8);
+  else if (dtype == UA_BF16 && s.D == 128) UA_MERGE_FWD(bf16, 16);
+  else if (dtype == UA_BF16 && s.D == 32) UA_MERGE_FWD(bf16, 4);
+  else if (dtype == UA_BF16 && s.D == 16) UA_MERGE_FWD(bf16, 2);
+  else if (dtype == UA_BF16 && s.D == 8) UA_MERGE_FWD(bf16, 1);
+  else if (dtype == UA_F32 && s.D == 128) UA_MERGE_FWD(float, 32);
+  else if (dtype == UA_F32 && s.D == 64) UA_MERGE_FWD(float, 16);
+  else if (dtype == UA_F32 && s.D == 32) UA_MERGE_FWD(float, 8);
+  else if (dtype == UA_F32 && s.D == 16) UA_MERGE_FWD(float, 4);
+  else if (dtype == UA_F32 && s.D == 8) UA_MERGE_FWD(float, 2);
+  else if (dtype == UA_F32 && s.D == 4) UA_MERGE_FWD(float, 1);
+  else return UA_ERR_UNSUPPORTED;
+#undef UA_MERGE_FWD
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
 int ua_merge_bwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, const void* g_merged,
-                 void* g_out_cm, float* g_lse_cm, void* stream) {
+                 void* g_out_cm, float* g_lse_cm, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
   if (!out_cm || !lse_cm || !g_merged || !g_out_cm || !g_lse_cm) return UA_ERR_NULL_POINTER;
+  if (!aligned16(out_cm) || !aligned16(g_merged) || !aligned16(g_out_cm)) return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
   const long long rows = (long long)s.B * s.H * s.R * s.L;
-  long long blocks = (rows + ua::aux::kMergeWarps - 1) / ua::aux::kMergeWarps;
-  if (blocks > 148 * 32) blocks = 148 * 32;
-  const size_t smem = sizeof(float) * ua::aux::kMergeWarps * 2 * s.N;
-  if (smem > 48 * 1024) return UA_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (dtype == UA_F32)
-    ua::aux::merge_bwd_kernel<float><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, smem, st>>>(
-        static_cast<const float*>(out_cm), lse_cm, static_cast<const float*>(g_merged), static_cast<float*>(g_out_cm),
-        g_lse_cm, s.B * s.H, s.N, s.R, s.L, s.D);
-  else
-    ua::aux::merge_bwd_kernel<bf16><<<(unsigned)blocks, ua::aux::kMergeWarps * 32, smem, st>>>(
-        static_cast<const bf16*>(out_cm), lse_cm, static_cast<const bf16*>(g_merged), static_cast<bf16*>(g_out_cm),
-        g_lse_cm, s.B * s.H, s.N, s.R, s.L, s.D);
+  const int tpr = s.D * (dtype == UA_F32 ? 4 : 2) / 16;
+  const unsigned blocks = (unsigned)((rows * tpr + ua::aux::kMergeThreads - 1) / ua::aux::kMergeThreads);
+  const int skip = (flags & UA_FLAG_SKIP_MASKED_FILL) ? 1 : 0;
+#define UA_MERGE_BWD(T, TPR)                                                                                          \
+  ua::aux::merge_bwd_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(                                       \
+      static_cast<const T*>(out_cm), lse_cm, static_cast<const T*>(g_merged), static_cast<T*>(g_out_cm), g_lse_cm, rows, \
+      s.N, s.R, s.L, skip)
+  if (dtype == UA_BF16 && s.D == 64) UA_MERGE_BWD(bf16, 8);
+  else if (dtype == UA_BF16 && s.D == 128) UA_MERGE_BWD(bf16, 16);
+  else if (dtype == UA_BF16 && s.D == 32) UA_MERGE_BWD(bf16, 4);
+  else if (dtype == UA_BF16 && s.D == 16) UA_MERGE_BWD(bf16, 2);
+  else if (dtype == UA_BF16 && s.D == 8) UA_MERGE_BWD(bf16, 1);
+  else if (dtype == UA_F32 && s.D == 128) UA_MERGE_BWD(float, 32);
+  else if (dtype == UA_F32 && s.D == 64) UA_MERGE_BWD(float, 16);
+  else if (dtype == UA_F32 && s.D == 32) UA_MERGE_BWD(float, 8);
+  else if (dtype == UA_F32 && s.D == 16) UA_MERGE_BWD(float, 4);
+  else if (dtype == UA_F32 && s.D == 8) UA_MERGE_BWD(float, 2);
+  else if (dtype == UA_F32 && s.D == 4) UA_MERGE_BWD(float, 1);
+  else return UA_ERR_UNSUPPORTED;
+#undef UA_MERGE_BWD
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 

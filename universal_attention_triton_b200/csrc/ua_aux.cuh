@@ -47,89 +47,159 @@ __global__ void __launch_bounds__(256) relayout_kernel(const E* __restrict__ src
   }
 }
 
-constexpr int kMergeWarps = 4;
+// ---- merge over key chunks (SMVecMatMul) -----------------------------------------
+// One group of TPR = D * sizeof(T) / 16 threads per output row (b,h,r,l); every thread owns
+// one 16-byte slice of the row (8 bf16 or 4 floats), so a warp reads whole contiguous rows of
+// out_cm.  Chunks whose softmax weight is exactly zero (rows before a key chunk have
+// lse = -1e12) are never read; on B4 H8 L4096 that halves the traffic.
+constexpr int kMergeThreads = 256;
 
-// merged[row][d] = sum_n softmax_n(lse[n][row]) * out_cm[n][row][d]; one warp per row.
-template <typename T>
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_fwd_kernel(const T* __restrict__ out_cm,
-                                                                     const float* __restrict__ lse_cm,
-                                                                     T* __restrict__ merged, int BH, int N, int R,
-                                                                     int L, int D) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const long long rows = (long long)BH * R * L;
-  for (long long row = (long long)blockIdx.x * kMergeWarps + warp; row < rows; row += (long long)gridDim.x * kMergeWarps) {
-    const int l = (int)(row % L);
-    const long long gr = row / L;
-    const int r = (int)(gr % R);
-    const long long bh = gr / R;
-    const size_t base = ((size_t)bh * N * R + r) * L + l;      // + n*R*L
-    float m = -INFINITY;
-    for (int n = 0; n < N; ++n) m = fmaxf(m, lse_cm[base + (size_t)n * R * L]);
-    float z = 0.f;
-    for (int n = 0; n < N; ++n) z += expf(lse_cm[base + (size_t)n * R * L] - m);
-    const float zinv = 1.0f / z;
-    for (int d = lane; d < D; d += 32) {
-      float acc = 0.f;
-      for (int n = 0; n < N; ++n) {
-        const float w = expf(lse_cm[base + (size_t)n * R * L] - m) * zinv;
-        if (w != 0.f) acc = fmaf(w, Num<T>::ld(out_cm + (base + (size_t)n * R * L) * D + d), acc);
-      }
-      Num<T>::st(merged + (size_t)row * D + d, acc);
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int kN = 4;
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int kN = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+      v[2 * i] = __bfloat162float(h.x);
+      v[2 * i + 1] = __bfloat162float(h.y);
     }
   }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+
+template <int TPR>
+__device__ __forceinline__ float group_max(float v) {
+#pragma unroll
+  for (int o = TPR / 2; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v) {
+#pragma unroll
+  for (int o = TPR / 2; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
 
-// Backward of the merge; one warp per row.  Dynamic shared memory: kMergeWarps * 2 * N floats.
-template <typename T>
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_bwd_kernel(const T* __restrict__ out_cm,
-                                                                     const float* __restrict__ lse_cm,
-                                                                     const T* __restrict__ g_merged,
-                                                                     T* __restrict__ g_out_cm,
-                                                                     float* __restrict__ g_lse_cm, int BH, int N,
-                                                                     int R, int L, int D) {
-  extern __shared__ float sm[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* w = sm + (size_t)warp * 2 * N;
-  float* s = w + N;
-  const long long rows = (long long)BH * R * L;
-  for (long long row = (long long)blockIdx.x * kMergeWarps + warp; row < rows; row += (long long)gridDim.x * kMergeWarps) {
-    const int l = (int)(row % L);
-    const long long gr = row / L;
-    const int r = (int)(gr % R);
-    const long long bh = gr / R;
-    const size_t base = ((size_t)bh * N * R + r) * L + l;
-    float m = -INFINITY;
-    for (int n = lane; n < N; n += 32) m = fmaxf(m, lse_cm[base + (size_t)n * R * L]);
-    for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float z = 0.f;
-    for (int n = lane; n < N; n += 32) {
-      float e = expf(lse_cm[base + (size_t)n * R * L] - m);
-      w[n] = e;
-      z += e;
+// row statistics of the softmax over chunks: max and 1 / sum exp
+template <int TPR>
+__device__ __forceinline__ void merge_row_stats(const float* lse_row, size_t nstride, int N, int sub, float& m, float& zinv) {
+  float mm = -INFINITY;
+  for (int n = sub; n < N; n += TPR) mm = fmaxf(mm, lse_row[(size_t)n * nstride]);
+  m = group_max<TPR>(mm);
+  float z = 0.f;
+  for (int n = sub; n < N; n += TPR) z += expf(lse_row[(size_t)n * nstride] - m);
+  zinv = 1.0f / group_sum<TPR>(z);
+}
+
+// merged[row][d] = sum_n softmax_n(lse[n][row]) * out_cm[n][row][d]
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kMergeThreads) merge_fwd_kernel(const T* __restrict__ out_cm, const float* __restrict__ lse_cm,
+                                                                  T* __restrict__ merged, long long rows, int N, int R, int L) {
+  constexpr int kN = Vec16<T>::kN;
+  constexpr int D = TPR * kN;
+  const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
+  const int sub = threadIdx.x % TPR;
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;          // keep whole warps in the shuffles
+  const int l = (int)(rr % L);
+  const long long gr = rr / L;
+  const int r = (int)(gr % R);
+  const long long bh = gr / R;
+  const size_t nstride = (size_t)R * L;
+  const size_t base = ((size_t)bh * N * R + r) * L + l;
+  float m, zinv;
+  merge_row_stats<TPR>(lse_cm + base, nstride, N, sub, m, zinv);
+  float acc[kN];
+#pragma unroll
+  for (int i = 0; i < kN; ++i) acc[i] = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const float w = expf(lse_cm[base + (size_t)n * nstride] - m) * zinv;
+    if (w != 0.f) {
+      float v[kN];
+      Vec16<T>::load(out_cm + (base + (size_t)n * nstride) * D + sub * kN, v);
+#pragma unroll
+      for (int i = 0; i < kN; ++i) acc[i] = fmaf(w, v[i], acc[i]);
     }
-    for (int o = 16; o; o >>= 1) z += __shfl_xor_sync(0xffffffffu, z, o);
-    __syncwarp();
-    const float zinv = 1.0f / z;
-    float t = 0.f;                                            // sum_n s_n w_n
-    for (int n = 0; n < N; ++n) {
-      const float wn = w[n] * zinv;
-      float part = 0.f;
-      const size_t o = (base + (size_t)n * R * L) * D;
-      for (int d = lane; d < D; d += 32) {
-        const float g = Num<T>::ld(g_merged + (size_t)row * D + d);
-        Num<T>::st(g_out_cm + o + d, g * wn);
-        if (wn != 0.f) part = fmaf(g, Num<T>::ld(out_cm + o + d), part);
+  }
+  if (live) Vec16<T>::store(merged + (size_t)row * D + sub * kN, acc);
+}
+
+// Backward of the merge: g_out_cm[n][row][:] = g[row][:] w_n ; g_lse[n][row] = (s_n - sum_m s_m w_m) w_n,
+// s_n = g[row] . out_cm[n][row].  With skip_masked, the (row, chunk) blocks with row < n * chunk (rows before
+// the key chunk, whose weight is exactly zero) are not written: the caller promises not to read them.
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kMergeThreads) merge_bwd_kernel(const T* __restrict__ out_cm, const float* __restrict__ lse_cm,
+                                                                  const T* __restrict__ g_merged, T* __restrict__ g_out_cm,
+                                                                  float* __restrict__ g_lse_cm, long long rows, int N, int R,
+                                                                  int L, int skip_masked) {
+  constexpr int kN = Vec16<T>::kN;
+  constexpr int D = TPR * kN;
+  const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
+  const int sub = threadIdx.x % TPR;
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
+  const int l = (int)(rr % L);
+  const long long gr = rr / L;
+  const int r = (int)(gr % R);
+  const long long bh = gr / R;
+  const size_t nstride = (size_t)R * L;
+  const size_t base = ((size_t)bh * N * R + r) * L + l;
+  const int chunk = L / N;
+  float m, zinv;
+  merge_row_stats<TPR>(lse_cm + base, nstride, N, sub, m, zinv);
+  float g[kN];
+  Vec16<T>::load(g_merged + (size_t)rr * D + sub * kN, g);
+  float t = 0.f;
+  for (int n = 0; n < N; ++n) {
+    const size_t idx = base + (size_t)n * nstride;
+    const float w = expf(lse_cm[idx] - m) * zinv;
+    float s = 0.f;
+    if (w != 0.f) {
+      float v[kN], o[kN];
+      Vec16<T>::load(out_cm + idx * D + sub * kN, v);
+#pragma unroll
+      for (int i = 0; i < kN; ++i) {
+        s = fmaf(g[i], v[i], s);
+        o[i] = g[i] * w;
       }
-      for (int oo = 16; oo; oo >>= 1) part += __shfl_xor_sync(0xffffffffu, part, oo);
-      if (lane == 0) s[n] = part;
-      t = fmaf(part, wn, t);
+      if (live) Vec16<T>::store(g_out_cm + idx * D + sub * kN, o);
+    } else if (!(skip_masked && l < n * chunk) && live) {
+      float o[kN];
+#pragma unroll
+      for (int i = 0; i < kN; ++i) o[i] = 0.f;
+      Vec16<T>::store(g_out_cm + idx * D + sub * kN, o);
     }
-    __syncwarp();
-    for (int n = lane; n < N; n += 32) {
-      const float wn = w[n] * zinv;
-      g_lse_cm[base + (size_t)n * R * L] = (s[n] - t) * wn;
+    s = group_sum<TPR>(s);
+    t = fmaf(s, w, t);
+    if (live && sub == 0 && !(skip_masked && l < n * chunk)) g_lse_cm[idx] = s;     // parked; finished below by the same thread
+  }
+  if (live && sub == 0) {
+    for (int n = 0; n < N; ++n) {
+      const size_t idx = base + (size_t)n * nstride;
+      const float w = expf(lse_cm[idx] - m) * zinv;
+      if (!(skip_masked && l < n * chunk)) g_lse_cm[idx] = (g_lse_cm[idx] - t) * w;
     }
-    __syncwarp();
   }
 }
 

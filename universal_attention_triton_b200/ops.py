@@ -210,8 +210,10 @@ def merge_fwd_cm(out_cm, lse_cm):
     return merged
 
 
-def merge_bwd_cm(out_cm, lse_cm, g_merged):
-    """SMVecMatMul backward on chunk-major storage -> (g_out_cm, g_lse_cm fp32)."""
+def merge_bwd_cm(out_cm, lse_cm, g_merged, skip_zero_weight_blocks: bool = False):
+    """SMVecMatMul backward on chunk-major storage -> (g_out_cm, g_lse_cm fp32).
+    ``skip_zero_weight_blocks``: leave the blocks whose merge weight is exactly zero unwritten
+    (only valid when the consumer never reads them: backward with masked-block gradients skipped)."""
     _require_cuda(out_cm, lse_cm, g_merged)
     lib = _lib.load()
     b, h, n, r, L, d = out_cm.shape
@@ -223,6 +225,7 @@ def merge_bwd_cm(out_cm, lse_cm, g_merged):
     g_lse_cm = torch.empty_like(lse_cm)
     with torch.cuda.device(out_cm.device):
         rc = lib.ua_merge_bwd(ctypes.byref(dims), _dtype_code(out_cm.dtype), _ptr(out_cm), _ptr(lse_cm), _ptr(g_merged),
-                              _ptr(g_out_cm), _ptr(g_lse_cm), _stream())
+                              _ptr(g_out_cm), _ptr(g_lse_cm),
+                              _lib.FLAG_SKIP_MASKED_FILL if skip_zero_weight_blocks else 0, _stream())
     _lib.check(rc, "ua_merge_bwd")
     return g_out_cm, g_lse_cm

@@ -117,5 +117,6 @@ class SMVecMatMul(Function):
     @staticmethod
     def backward(ctx, g):
         mat, vec = ctx.saved_tensors
-        g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g)
+        g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g,
+                                              skip_zero_weight_blocks=not _STRICT_MASKED_GRADS)
         return ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
