@@ -149,10 +149,15 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
   }
 }
 
-// ---------------------------------------------------------------- MMA issuer --
-__device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p) {
-  const int R = p.s.R, N = p.s.N;
-  (void)N;
+// --------------------------------------------------------------- MMA issuers --
+// tcgen05.mma is issued by single threads, and what limits the tensor pipe here is the
+// number of instructions (every one covers only K = 16), not their size: one thread
+// sustains one MMA per ~100 cycles, two threads together close to the pipe's ~50.  So
+// two issuers (lane 0 of warps 1 and 2) split the accumulators between them:
+//   issuer A: X0 (G, S_r, G again), dV_i, dK_i          issuer B: X1 (dP_r, dQ_r, dK_j), dC
+// MMAs into one accumulator always come from the same issuer, so their order is kept.
+__device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, const int which) {
+  const int R = p.s.R;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_nt = idesc_bf16(128, 128, 0, 0);   // A K-major, B K-major, N = 128
   constexpr uint32_t id_tt = idesc_bf16(128, 64, 1, 1);    // A MN-major, B MN-major, N = 64
@@ -193,88 +198,81 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p) {
       mma_ss_c<true>(d, desc_from_lo(a + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(b + ks * 128), id_nt64);
   };
 
-#ifdef UA_PROFILE_PHASES
-  long long mt = clock64(), macc[12] = {0,0,0,0,0,0,0,0,0,0,0,0};
-#define UA_MPH(i) { long long n_ = clock64(); macc[i] += n_ - mt; mt = n_; }
-#else
-#define UA_MPH(i)
-#endif
   if (!c.wait(bKvFull, 0)) return;
-  int x0_uses = 0, x1_uses = 0, rc = 0;
+  int x_uses = 0, rc = 0;    // writes so far into the issuer's own scratch region (X0 for A, X1 for B)
   bool have_acc = false;     // dV / dK_i accumulators hold something
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
-    if (valid) {
-      UA_MPH(0)
-      if (!c.wait(bKjFull, T)) return;
-      UA_MPH(1)
-      if (x0_uses >= 1 && !c.wait(bX0Free, x0_uses - 1)) return;
-      UA_MPH(2)
-      tc_fence_after();
-      mma_nt(X0, kKi, kKj);                                           // G = K_i K_j^T
-      tc_commit(c.bar(bGFull));
-      ++x0_uses;
-    }
-    for (int r = 0; r < R; ++r, ++rc) {
-      UA_MPH(0)
-      if (!c.wait(bInFull, rc)) return;
-      UA_MPH(3)
+    if (which == 0) {
+      // ------------------------------------------------------------- issuer A
       if (valid) {
-        if (!c.wait(bX0Free, x0_uses - 1)) return;
-        UA_MPH(4)
+        if (!c.wait(bKjFull, T)) return;
+        if (x_uses >= 1 && !c.wait(bX0Free, x_uses - 1)) return;
         tc_fence_after();
-        mma_nt(X0, kQ, kKi);                                          // S = Q K_i^T
-        ++x0_uses;
+        mma_nt(X0, kKi, kKj);                                           // G = K_i K_j^T
+        tc_commit(c.bar(bGFull));
+        ++x_uses;
       }
-      UA_MPH(0)
-      if (x1_uses >= 1 && !c.wait(bX1Free, x1_uses - 1)) return;
-      UA_MPH(5)
-      tc_fence_after();
-      mma_nt(X1, kGo, kVi);                                           // dP = dO V_i^T
-      ++x1_uses;
-      tc_commit(c.bar(bSdpFull));
-      UA_MPH(0)
-      if (!c.wait(bPdsReady, rc)) return;
-      UA_MPH(6)
-      tc_fence_after();
-      mma_tt(DV, mP, mGo, have_acc);                                  // dV_i += P^T dO
-      mma_tt(DK, mdS, mQ, have_acc);                                  // dK_i += dS^T Q
-      have_acc = true;
-      tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
-      mma_nn(X1, kdS, mKi, false);                                    // dQ = dS K_i  (dP has been consumed)
+      for (int r = 0; r < R; ++r, ++rc) {
+        if (!c.wait(bInFull, rc)) return;
+        if (valid) {
+          if (!c.wait(bX0Free, x_uses - 1)) return;
+          tc_fence_after();
+          mma_nt(X0, kQ, kKi);                                          // S = Q K_i^T
+          ++x_uses;
+        }
+        tc_commit(c.bar(bSdpFull));
+        if (!c.wait(bPdsReady, rc)) return;
+        tc_fence_after();
+        mma_tt(DV, mP, mGo, have_acc);                                  // dV_i += P^T dO
+        mma_tt(DK, mdS, mQ, have_acc);                                  // dK_i += dS^T Q
+        have_acc = true;
+        tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
+        tc_commit(c.bar(bRDone));
+      }
       if (valid) {
-#pragma unroll
-        for (int nb = 0; nb < 8; ++nb)                                 // dC[key][row] (+)= dS^T I
-          if (r > 0) mma_ss_c<true>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
-          else mma_ss_c<false>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
+        if (!c.wait(bX0Free, x_uses - 1)) return;
+        tc_fence_after();
+        mma_nt(X0, kKi, kKj);                                           // G again for the decay backward
+        tc_commit(c.bar(bG2Full));
+        ++x_uses;
+        if (!c.wait(bDgReady, T)) return;
+        tc_fence_after();
+        mma_nn(DK, kdG, mKj, true);                                     // dK_i += dG K_j
+        tc_commit(c.bar(bDkjFull));
       }
-      tc_commit(c.bar(bRDone));
-    }
-    if (valid) {
-      UA_MPH(0)
-      if (!c.wait(bX0Free, x0_uses - 1)) return;
-      UA_MPH(7)
-      tc_fence_after();
-      mma_nt(X0, kKi, kKj);                                           // G again for the decay backward
-      tc_commit(c.bar(bG2Full));
-      ++x0_uses;
-      UA_MPH(0)
-      if (!c.wait(bDgReady, T)) return;
-      UA_MPH(8)
-      if (!c.wait(bX1Free, x1_uses - 1)) return;
-      UA_MPH(9)
-      tc_fence_after();
-      mma_tt(X1, mP, mKi, false);                                     // dK_j = dG^T K_i
-      ++x1_uses;
-      mma_nn(DK, kdG, mKj, true);                                     // dK_i += dG K_j
-      tc_commit(c.bar(bDkjFull));
+    } else {
+      // ------------------------------------------------------------- issuer B
+      for (int r = 0; r < R; ++r, ++rc) {
+        if (!c.wait(bInFull, rc)) return;
+        if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
+        tc_fence_after();
+        mma_nt(X1, kGo, kVi);                                           // dP = dO V_i^T
+        ++x_uses;
+        tc_commit(c.bar(bSdpFull));
+        if (!c.wait(bPdsReady, rc)) return;
+        tc_fence_after();
+        mma_nn(X1, kdS, mKi, false);                                    // dQ = dS K_i  (dP has been consumed)
+        if (valid) {
+#pragma unroll
+          for (int nb = 0; nb < 8; ++nb) {                              // dC[key][row] (+)= dS^T I
+            if (r > 0) mma_ss_c<true>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
+            else mma_ss_c<false>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
+          }
+        }
+        tc_commit(c.bar(bRDone));
+      }
+      if (valid) {
+        if (!c.wait(bDgReady, T)) return;
+        if (!c.wait(bX1Free, x_uses - 1)) return;
+        tc_fence_after();
+        mma_tt(X1, mP, mKi, false);                                     // dK_j = dG^T K_i
+        ++x_uses;
+        tc_commit(c.bar(bDkjFull));
+      }
     }
   }
   tc_commit(c.bar(bFinal));
-#ifdef UA_PROFILE_PHASES
-  UA_MPH(0)
-  if (blockIdx.x == 0) for (int z = 0; z < 10; ++z) reinterpret_cast<long long*>(p.status)[24 + z] = macc[z];
-#endif
 }
 
 // ------------------------------------------------------------ worker groups --
@@ -678,6 +676,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
       if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg) count = 16;   // one arrival per worker warp
+      if (b == bSdpFull || b == bRDone || b == bDkjFull || b == bFinal) count = 2;                       // one commit per MMA issuer
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
@@ -703,8 +702,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
 
   if (warp == 0) {
     if (lane == 0) bwd_producer(c, p, &tmK, &tmV, &tmQ, &tmG);
-  } else if (warp == 1) {
-    if (lane == 0) bwd_mma(c, p);
+  } else if (warp == 1 || warp == 2) {
+    if (lane == 0) bwd_mma(c, p, warp - 1);
   } else if (warp >= 4) {
     bwd_worker<TG>(c, p, (warp - 4) >> 2);
   }
