@@ -35,15 +35,24 @@ ua::Shape to_shape(const UaDims* d) {
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// rows per tile of the SIMT kernels: the largest of {32, 16} that divides the chunk and fits shared memory
-int simt_rows(int C, int D, bool bwd) {
-  const int cands[2] = {32, 16};
-  for (int rt : cands) {
-    if (C % rt) continue;
-    size_t need = bwd ? ua::simt::bwd_smem_bytes(C, D, rt) : ua::simt::fwd_smem_bytes(C, D, rt);
-    if (need <= kMaxDynSmem) return rt;
+// Tiling of the SIMT kernels: rows per tile and whether K_i / V_i sit in shared memory as fp32 or (bf16 inputs only)
+// as bf16; the first choice that divides the chunk and fits shared memory.
+struct SimtCfg {
+  int rt;        // 0: nothing fits
+  bool compact;  // K_i, V_i kept as bf16
+};
+
+SimtCfg simt_cfg(int C, int D, int dtype, bool bwd) {
+  const int rts[4] = {32, 16, 16, 8};
+  const bool compact[4] = {false, false, true, true};
+  for (int t = 0; t < 4; ++t) {
+    if (C % rts[t]) continue;
+    if (compact[t] && dtype != UA_BF16) continue;
+    const int elem = compact[t] ? 2 : 4;
+    size_t need = bwd ? ua::simt::bwd_smem_bytes(C, D, rts[t], elem) : ua::simt::fwd_smem_bytes(C, D, rts[t], elem);
+    if (need <= kMaxDynSmem) return SimtCfg{rts[t], compact[t]};
   }
-  return 0;
+  return SimtCfg{0, false};
 }
 
 struct BwdWorkspace {
@@ -82,19 +91,19 @@ BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   return w;
 }
 
-template <typename T, typename TG>
+template <typename T, typename TG, typename S>
 int launch_simt_fwd(const ua::simt::FwdParams& p, cudaStream_t st) {
-  size_t smem = ua::simt::fwd_smem_bytes(p.s.C, p.s.D, p.rt);
-  auto kern = ua::simt::fwd_kernel<T, TG>;
+  size_t smem = ua::simt::fwd_smem_bytes(p.s.C, p.s.D, p.rt, (int)sizeof(S));
+  auto kern = ua::simt::fwd_kernel<T, TG, S>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<p.s.B * p.s.H * p.s.N, ua::simt::kThreads, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
-template <typename T, typename TG>
+template <typename T, typename TG, typename S>
 int launch_simt_bwd(const ua::simt::BwdParams& p, cudaStream_t st) {
-  size_t smem = ua::simt::bwd_smem_bytes(p.s.C, p.s.D, p.rt);
-  auto kern = ua::simt::bwd_kernel<T, TG>;
+  size_t smem = ua::simt::bwd_smem_bytes(p.s.C, p.s.D, p.rt, (int)sizeof(S));
+  auto kern = ua::simt::bwd_kernel<T, TG, S>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<p.s.B * p.s.H * p.s.N, ua::simt::kThreads, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
@@ -178,9 +187,9 @@ size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
   if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd_supported(s, dtype)) return bwd_layout_tc(s).total;
-  int rt = simt_rows(s.C, s.D, true);
-  if (!rt) return 0;
-  return bwd_layout(s, rt).total;
+  const SimtCfg cfg = simt_cfg(s.C, s.D, dtype, true);
+  if (!cfg.rt) return 0;
+  return bwd_layout(s, cfg.rt).total;
 }
 
 size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags) {
@@ -223,11 +232,13 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   p.s = s; p.kc = kc; p.vc = vc; p.xq = xq; p.ssrc = static_src; p.sdest = static_dest;
   p.out = out_cm; p.lse = lse_cm; p.denom = denom_cm;
   p.skip_masked_fill = (flags & UA_FLAG_SKIP_MASKED_FILL) ? 1 : 0;
-  p.rt = simt_rows(s.C, s.D, false);
+  const SimtCfg cfg = simt_cfg(s.C, s.D, dtype, false);
+  p.rt = cfg.rt;
   if (!p.rt) return UA_ERR_UNSUPPORTED;
-  if (dtype == UA_F32) return launch_simt_fwd<float, float>(p, st);
-  if (gate_dtype == UA_F32) return launch_simt_fwd<bf16, float>(p, st);
-  return launch_simt_fwd<bf16, bf16>(p, st);
+  if (dtype == UA_F32) return launch_simt_fwd<float, float, float>(p, st);
+  if (cfg.compact) return gate_dtype == UA_F32 ? launch_simt_fwd<bf16, float, bf16>(p, st) : launch_simt_fwd<bf16, bf16, bf16>(p, st);
+  if (gate_dtype == UA_F32) return launch_simt_fwd<bf16, float, float>(p, st);
+  return launch_simt_fwd<bf16, bf16, float>(p, st);
 }
 
 int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
@@ -280,7 +291,8 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     return UA_OK;
   }
 
-  const int rt = simt_rows(s.C, s.D, true);
+  const SimtCfg cfg = simt_cfg(s.C, s.D, dtype, true);
+  const int rt = cfg.rt;
   if (!rt) return UA_ERR_UNSUPPORTED;
   BwdWorkspace w = bwd_layout(s, rt);
   if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
@@ -298,9 +310,10 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   p.carry = reinterpret_cast<float*>(ws + w.off_carry);
   p.rt = rt;
   p.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-  if (dtype == UA_F32) e = launch_simt_bwd<float, float>(p, st);
-  else if (gate_dtype == UA_F32) e = launch_simt_bwd<bf16, float>(p, st);
-  else e = launch_simt_bwd<bf16, bf16>(p, st);
+  if (dtype == UA_F32) e = launch_simt_bwd<float, float, float>(p, st);
+  else if (cfg.compact) e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, bf16>(p, st) : launch_simt_bwd<bf16, bf16, bf16>(p, st);
+  else if (gate_dtype == UA_F32) e = launch_simt_bwd<bf16, float, float>(p, st);
+  else e = launch_simt_bwd<bf16, bf16, float>(p, st);
   if (e) return e;
 
   const size_t BH = (size_t)s.B * s.H;

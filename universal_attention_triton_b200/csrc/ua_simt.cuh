@@ -58,6 +58,48 @@ __device__ __forceinline__ float dot4(const float* a, const float* b, int D) {
   return acc;
 }
 
+// Storage of the chunk's own K_i / V_i tiles in shared memory: fp32 (default) or, for shapes whose
+// fp32 tiles would not fit (chunk 256 x head_dim 128), the input's bf16.
+template <typename S> struct KVS;
+template <> struct KVS<float> {
+  static constexpr int kPad = 4;
+  static __device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ float ld1(const float* p) { return *p; }
+  static __device__ __forceinline__ void st(float* p, float v) { *p = v; }
+};
+template <> struct KVS<__nv_bfloat16> {
+  static constexpr int kPad = 8;
+  static __device__ __forceinline__ float4 ld4(const __nv_bfloat16* p) {
+    const uint2 x = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&x.x), b = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+    return make_float4(__bfloat162float(a.x), __bfloat162float(a.y), __bfloat162float(b.x), __bfloat162float(b.y));
+  }
+  static __device__ __forceinline__ float ld1(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+template <typename S>
+__device__ __forceinline__ float dotk(const S* a, const float* b, int D) {
+  float acc = 0.f;
+  for (int d = 0; d < D; d += 4) {
+    const float4 x = KVS<S>::ld4(a + d);
+    const float4 y = *reinterpret_cast<const float4*>(b + d);
+    acc = fmaf(x.x, y.x, acc);
+    acc = fmaf(x.y, y.y, acc);
+    acc = fmaf(x.z, y.z, acc);
+    acc = fmaf(x.w, y.w, acc);
+  }
+  return acc;
+}
+
+template <typename T, typename S>
+__device__ __forceinline__ void load_tile_k(S* dst, const T* src, int rows, int D, int DPK) {
+  for (int e = threadIdx.x; e < rows * D; e += kThreads) {
+    int rr = e / D, dd = e - rr * D;
+    KVS<S>::st(dst + rr * DPK + dd, Num<T>::ld(src + e));
+  }
+}
+
 __device__ __forceinline__ float pow23(float g) { return g > 0.f ? powf(g, 2.0f / 3.0f) : 0.f; }
 
 __device__ __forceinline__ float log_retention(float a) {
@@ -88,19 +130,23 @@ __device__ __forceinline__ void column_stats(const float* sS, float* sM, float* 
   }
 }
 
-inline size_t fwd_smem_bytes(int C, int D, int RT) {
+inline size_t kv_bytes(int C, int D, int elem) {      // the two [C][D + pad] tiles K_i, V_i, 16-byte aligned
+  size_t b = (size_t)2 * C * (D + 16 / elem) * elem;
+  return (b + 15) / 16 * 16;
+}
+inline size_t fwd_smem_bytes(int C, int D, int RT, int kv_elem = 4) {
   size_t DP = D + 4, RTP = RT + 1;
-  return sizeof(float) * (2 * C * DP + 2 * RT * DP + 2 * C * RTP + 2 * C + 3 * RT + D);
+  return kv_bytes(C, D, kv_elem) + sizeof(float) * (2 * RT * DP + 2 * C * RTP + 2 * C + 3 * RT + D);
 }
 
-template <typename T, typename TG>
+template <typename T, typename TG, typename S>
 __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int C = p.s.C, D = p.s.D, L = p.s.L, N = p.s.N, R = p.s.R, RT = p.rt;
-  const int DP = D + 4, RTP = RT + 1;
-  float* sKi = smem;
-  float* sVi = sKi + C * DP;
-  float* sKj = sVi + C * DP;
+  const int DP = D + 4, RTP = RT + 1, DPK = D + KVS<S>::kPad;
+  S* sKi = reinterpret_cast<S*>(smem);
+  S* sVi = sKi + C * DPK;
+  float* sKj = smem + ((size_t)2 * C * DPK * sizeof(S) + 15) / 16 * 4;
   float* sQ = sKj + RT * DP;
   float* sC = sQ + RT * DP;
   float* sS = sC + C * RTP;
@@ -126,8 +172,8 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
   float* lse = p.lse + chunk_id * R * L;
   T* denom = p.denom ? static_cast<T*>(p.denom) + chunk_id * R * L : nullptr;
 
-  load_tile<T>(sKi, kc + (size_t)i * C * D, C, D, DP);
-  load_tile<T>(sVi, vc + (size_t)i * C * D, C, D, DP);
+  load_tile_k<T, S>(sKi, kc + (size_t)i * C * D, C, D, DPK);
+  load_tile_k<T, S>(sVi, vc + (size_t)i * C * D, C, D, DPK);
   for (int k = tid; k < C; k += kThreads) {
     sS3[k] = cbrtf(Num<TG>::ld(ss + i * C + k));
     sCarry[k] = 0.f;
@@ -139,7 +185,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
     const float w = Num<T>::rnd(1.0f / (float)C);
     for (int d = tid; d < D; d += kThreads) {
       float acc = 0.f;
-      for (int k = 0; k < C; ++k) acc = fmaf(w, sVi[k * DP + d], acc);
+      for (int k = 0; k < C; ++k) acc = fmaf(w, KVS<S>::ld1(sVi + k * DPK + d), acc);
       sVmean[d] = acc;
     }
   }
@@ -172,7 +218,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
       float local = 0.f, c = carry;
       for (int q = 0; q < RT; ++q) {
         const int qg = j0 + q;
-        float g = dot4(sKi + k * DP, sKj + q * DP, D);
+        float g = dotk<S>(sKi + k * DPK, sKj + q * DP, D);
         float ell = log_retention(pow23(g) * s3 * sT3[q]);
         if (qg <= kg) ell = 0.f;
         local += ell;
@@ -187,7 +233,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
       __syncthreads();
       for (int k = tid; k < C; k += kThreads)
         for (int q = 0; q < RT; ++q)
-          sS[k * RTP + q] = dot4(sKi + k * DP, sQ + q * DP, D) + sC[k * RTP + q];
+          sS[k * RTP + q] = dotk<S>(sKi + k * DPK, sQ + q * DP, D) + sC[k * RTP + q];
       __syncthreads();
       column_stats(sS, sM, sL, C, RT, RTP);
       __syncthreads();
@@ -207,7 +253,7 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int k = 0; k < C; ++k) {
           const float pk = sS[k * RTP + q];
-          const float4 v = *reinterpret_cast<const float4*>(sVi + k * DP + d4 * 4);
+          const float4 v = KVS<S>::ld4(sVi + k * DPK + d4 * 4);
           acc.x = fmaf(pk, v.x, acc.x); acc.y = fmaf(pk, v.y, acc.y);
           acc.z = fmaf(pk, v.z, acc.z); acc.w = fmaf(pk, v.w, acc.w);
         }
@@ -219,9 +265,9 @@ __global__ void __launch_bounds__(kThreads) fwd_kernel(FwdParams p) {
   }
 }
 
-inline size_t bwd_smem_bytes(int C, int D, int RT) {
+inline size_t bwd_smem_bytes(int C, int D, int RT, int kv_elem = 4) {
   size_t DP = D + 4, RTP = RT + 1;
-  return sizeof(float) * (2 * C * DP + 3 * RT * DP + 5 * C * RTP + 3 * C + 5 * RT);
+  return kv_bytes(C, D, kv_elem) + sizeof(float) * (3 * RT * DP + 5 * C * RTP + 3 * C + 5 * RT);
 }
 
 // out[k][d4] (+)= sum_q A[k][q] * Bm[q][d]   for k < C; result added to global fp32 rows with atomics.
@@ -243,7 +289,8 @@ __device__ __forceinline__ void acc_rows_atomic(const float* sA, const float* sB
 }
 
 // out[q][d4] += sum_k A[k][q] * Bm[k][d]   for q < RT
-__device__ __forceinline__ void acc_cols_atomic(const float* sA, const float* sB, float* gdst, int C, int RT,
+template <typename S>
+__device__ __forceinline__ void acc_cols_atomic(const float* sA, const S* sB, float* gdst, int C, int RT,
                                                 int RTP, int D, int DP) {
   const int D4 = D >> 2;
   for (int e = threadIdx.x; e < RT * D4; e += kThreads) {
@@ -251,7 +298,7 @@ __device__ __forceinline__ void acc_cols_atomic(const float* sA, const float* sB
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k = 0; k < C; ++k) {
       const float a = sA[k * RTP + q];
-      const float4 b = *reinterpret_cast<const float4*>(sB + k * DP + d4 * 4);
+      const float4 b = KVS<S>::ld4(sB + k * DP + d4 * 4);
       acc.x = fmaf(a, b.x, acc.x); acc.y = fmaf(a, b.y, acc.y);
       acc.z = fmaf(a, b.z, acc.z); acc.w = fmaf(a, b.w, acc.w);
     }
@@ -264,14 +311,14 @@ __device__ __forceinline__ void acc_cols_atomic(const float* sA, const float* sB
 // the start of every tile (recomputed, not saved by the forward); pass 2 walks
 // them downwards so that the reverse cumulative sum of the decay gradient can
 // be carried per key (universal_attention_autograd.py:232-259).
-template <typename T, typename TG>
+template <typename T, typename TG, typename S>
 __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
   extern __shared__ __align__(16) float smem[];
   const int C = p.s.C, D = p.s.D, L = p.s.L, N = p.s.N, R = p.s.R, RT = p.rt;
-  const int DP = D + 4, RTP = RT + 1, NT = L / RT;
-  float* sKi = smem;
-  float* sVi = sKi + C * DP;
-  float* sKj = sVi + C * DP;
+  const int DP = D + 4, RTP = RT + 1, NT = L / RT, DPK = D + KVS<S>::kPad;
+  S* sKi = reinterpret_cast<S*>(smem);
+  S* sVi = sKi + C * DPK;
+  float* sKj = smem + ((size_t)2 * C * DPK * sizeof(S) + 15) / 16 * 4;
   float* sQ = sKj + RT * DP;
   float* sGo = sQ + RT * DP;
   float* sG = sGo + RT * DP;      // [C][RTP] key-key Gram tile
@@ -308,8 +355,8 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
   float* acc_ds = p.acc_ds + (size_t)bh * L;
   float* acc_dt = p.acc_dt + (size_t)bh * L;
 
-  load_tile<T>(sKi, kc + (size_t)i * C * D, C, D, DP);
-  load_tile<T>(sVi, vc + (size_t)i * C * D, C, D, DP);
+  load_tile_k<T, S>(sKi, kc + (size_t)i * C * D, C, D, DPK);
+  load_tile_k<T, S>(sVi, vc + (size_t)i * C * D, C, D, DPK);
   for (int k = tid; k < C; k += kThreads) {
     sS3[k] = cbrtf(Num<TG>::ld(ss + i * C + k));
     sCarry[k] = 0.f;
@@ -333,7 +380,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
       carry_tab[(size_t)jt * C + k] = carry;
       float local = 0.f;
       for (int q = 0; q < RT; ++q) {
-        float g = dot4(sKi + k * DP, sKj + q * DP, D);
+        float g = dotk<S>(sKi + k * DPK, sKj + q * DP, D);
         float ell = log_retention(pow23(g) * s3 * sT3[q]);
         if (j0 + q <= kg) ell = 0.f;
         local += ell;
@@ -361,7 +408,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
       float local = 0.f;
       for (int q = 0; q < RT; ++q) {
         const int qg = j0 + q;
-        float g = dot4(sKi + k * DP, sKj + q * DP, D);
+        float g = dotk<S>(sKi + k * DPK, sKj + q * DP, D);
         sG[k * RTP + q] = g;
         float ell = log_retention(pow23(g) * s3 * sT3[q]);
         if (qg <= kg) ell = 0.f;
@@ -383,8 +430,8 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
       __syncthreads();
       for (int k = tid; k < C; k += kThreads)
         for (int q = 0; q < RT; ++q) {
-          sP[k * RTP + q] = dot4(sKi + k * DP, sQ + q * DP, D) + sC[k * RTP + q];
-          sdS[k * RTP + q] = dot4(sVi + k * DP, sGo + q * DP, D);        // dP
+          sP[k * RTP + q] = dotk<S>(sKi + k * DPK, sQ + q * DP, D) + sC[k * RTP + q];
+          sdS[k * RTP + q] = dotk<S>(sVi + k * DPK, sGo + q * DP, D);        // dP
         }
       __syncthreads();
       column_stats(sP, sM, sL, C, RT, RTP);
@@ -411,7 +458,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
       __syncthreads();
       acc_rows_atomic(sP, sGo, acc_dv + (size_t)i * C * D, C, RT, RTP, D, DP);                 // dV_i += P  . g_out
       acc_rows_atomic(sdS, sQ, acc_dk + (size_t)i * C * D, C, RT, RTP, D, DP);                 // dK_i += dS . Q
-      acc_cols_atomic(sdS, sKi, acc_dq + ((size_t)r * L + j0) * D, C, RT, RTP, D, DP);         // dQ_j += dS^T . K_i
+      acc_cols_atomic<S>(sdS, sKi, acc_dq + ((size_t)r * L + j0) * D, C, RT, RTP, D, DPK);         // dQ_j += dS^T . K_i
       __syncthreads();
     }
 
@@ -449,7 +496,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
       for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (lane == 0 && acc != 0.f) atomicAdd(acc_dt + j0 + q, acc / (3.0f * sT3[q] * sT3[q]));
     }
-    acc_cols_atomic(sdS, sKi, acc_dk + (size_t)j0 * D, C, RT, RTP, D, DP);                     // dK_j += dG^T . K_i
+    acc_cols_atomic<S>(sdS, sKi, acc_dk + (size_t)j0 * D, C, RT, RTP, D, DPK);                     // dK_j += dG^T . K_i
     acc_rows_atomic(sdS, sKj, acc_dk + (size_t)i * C * D, C, RT, RTP, D, DP);                  // dK_i += dG . K_j
     __syncthreads();
   }
