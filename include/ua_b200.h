@@ -136,6 +136,32 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
                 void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
 
+/* Sequence-chunk sharding of the forward (long contexts: one GPU owns a contiguous range of row
+ * tiles of 128 rows).  The reference has no multi-device code; these entry points are what a
+ * sequence-parallel caller needs on top of ua_fwd.  Supported where the tensor-core forward is
+ * (bf16, chunk 128, head_dim 64 or 128); UA_ERR_UNSUPPORTED otherwise.
+ *
+ *   ua_fwd_rows            forward for the row tiles [row_tile_begin, row_tile_end) only.  kc, vc and
+ *                          static_src cover the WHOLE sequence (all n chunks); xq_rows (b,h,r,Lr,d),
+ *                          static_dest_rows (b,h,Lr), out_cm_rows (b,h,n,r,Lr,d), lse_cm_rows and
+ *                          denom_cm_rows (b,h,n,r,Lr) hold just the Lr = 128 * (end - begin) rows of the
+ *                          range.  carry_in (b,h,n,128) fp32, may be NULL (= zeros): for every key, the sum
+ *                          of its log-retention over all rows BEFORE the range, i.e. what the ranks that
+ *                          own the earlier rows computed with ua_decay_totals_rows.
+ *   ua_decay_totals_rows   decay-only pass over the same range: total_out (b,h,n,128) = carry_in (or 0) +
+ *                          the sum of every key's log-retention over the rows of the range.  Cheap (no
+ *                          values, queries or outputs); ranks run it first, exchange the totals, and form
+ *                          their carry_in as the sum of the totals of the ranks before them. */
+int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                const void* kc, const void* vc, const void* xq_rows,
+                const void* static_src, const void* static_dest_rows, const float* carry_in,
+                void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows,
+                void* workspace, size_t workspace_bytes, int flags, void* stream);
+int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                         const void* kc, const void* static_src, const void* static_dest_rows,
+                         const float* carry_in, float* total_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
 /* Backward for callers that must not allocate.  No counterpart in the reference.
  *
  * Some hosts of this library cannot hand it a workspace: an inference or

@@ -271,3 +271,34 @@ def test_backward_with_kept_decay_table_matches_prepass():
     b = ops.backward_cm(*cu, g_out, g_lse)
     for x, y, key in zip(a, b, GRADS):
         assert rel_fro(x.float().cpu(), y.float().cpu()) <= 1e-3, key
+
+
+@pytest.mark.parametrize("shape,ranges", [((1, 2, 2, 1024, 128, 64), [(0, 3), (3, 8)]),
+                                           ((1, 1, 1, 768, 128, 128), [(0, 2), (2, 4), (4, 6)])])
+def test_forward_over_row_ranges_matches_whole_forward(shape, ranges):
+    """ua_decay_totals_rows + ua_fwd_rows (the sequence-sharded forward), the ranks emulated one after the
+    other on one GPU: the concatenated rows equal the whole-sequence forward up to fp32 association of the carry."""
+    from universal_attention_triton_b200 import ops
+    B, H, R, L, c, D = shape
+    n = L // c
+    ins, _ = _bf16_case(*shape, seed=51)
+    kc, vc, xq, ss, sd = _cuda(*ins)
+    out_full, lse_full, _ = ops.forward_cm(kc, vc, xq, ss, sd)
+    totals = [ops.decay_totals_rows(kc, ss, sd[:, :, b * 128:e * 128], b, e) for b, e in ranges]
+    outs, lses = [], []
+    carry = torch.zeros_like(totals[0])
+    for (b, e), tot in zip(ranges, totals):
+        o, l, _ = ops.forward_rows_cm(kc, vc, xq[:, :, :, b * 128:e * 128], ss, sd[:, :, b * 128:e * 128], b, e, carry)
+        outs.append(o); lses.append(l)
+        carry = carry + tot
+    out_sp = torch.cat(outs, dim=4)
+    lse_sp = torch.cat(lses, dim=4)
+    valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda().view(1, 1, n, 1, L)
+    assert torch.equal(lse_sp[~valid.expand_as(lse_sp)], lse_full[~valid.expand_as(lse_full)])
+    dl = (lse_sp - lse_full).abs()
+    assert ((dl <= 1e-3 + 1e-6 * lse_full.abs()) | ~valid).all(), (dl * valid).max().item()
+    err = (out_sp.float() - out_full.float()).abs()
+    assert (err <= 2e-2 + out_full.float().abs() * 2.0 ** -7).all(), err.max().item()
+    # chained totals: passing the running carry through carry_in gives the same table as summing per-range totals
+    chained = ops.decay_totals_rows(kc, ss, sd[:, :, ranges[1][0] * 128:ranges[1][1] * 128], *ranges[1], carry_in=totals[0])
+    assert (chained - (totals[0] + totals[1])).abs().max() <= 1e-2 + 1e-6 * chained.abs().max()

@@ -1,0 +1,88 @@
+"""Two-GPU tests over NCCL (skipped on a single-GPU box): the sequence-sharded forward against the
+single-GPU forward of the same library, and (batch, kv-head) sharding of forward + backward."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _sp_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import ua_oracle as O
+    from universal_attention_triton_b200 import ops
+    from universal_attention_triton_b200.sequence_parallel import sp_forward
+    B, H, R, L, c, D = 1, 2, 2, 1024, 128, 64
+    ins = [t.cuda() for t in O.make_inputs(B, H, R, L, c, D, dtype=torch.bfloat16, seed=61)]
+    kc, vc, xq, ss, sd = ins
+    n = L // c
+    n_l, L_l = n // world, L // world
+    sc, sr = slice(rank * n_l, (rank + 1) * n_l), slice(rank * L_l, (rank + 1) * L_l)
+    out, denom, lse = sp_forward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
+                                 ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous())
+    out_cm, lse_cm, _ = ops.forward_cm(kc, vc, xq, ss, sd)
+    ref_out = ops.as_reference_out(out_cm)[:, :, :, sr]
+    ref_lse = ops.as_reference_denom(lse_cm)[:, :, :, sr]
+    valid = (torch.arange(L).view(L, 1) >= torch.arange(n).view(1, n) * c).cuda()[sr]
+    ok = bool((((lse - ref_lse).abs() <= 1e-3 + 1e-6 * ref_lse.abs()) | ~valid).all().item())
+    ok = ok and bool(((out.float() - ref_out.float()).abs() <= 2e-2 + ref_out.float().abs() * 2.0 ** -7).all().item())
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ret["ok"] = int(flag.item())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def _bh_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from oracle import ua_oracle as O
+    from universal_attention_triton_b200 import UniversalAttention
+    from universal_attention_triton_b200.sharding import run_sharded
+    B, H, R, L, c, D = 3, 1, 2, 512, 128, 64             # 3 units over 2 ranks
+    ins = [t.cuda() for t in O.make_inputs(B, H, R, L, c, D, dtype=torch.bfloat16, seed=62)]
+    (out, denom), (lo, hi) = run_sharded(UniversalAttention.apply, ins, world, rank)
+    full_out, full_denom = UniversalAttention.apply(*ins)
+    flat = full_out.reshape((B * H,) + tuple(full_out.shape[2:]))
+    ok = torch.equal(out[0], flat[lo:hi])
+    cnt = torch.tensor([hi - lo], device="cuda")
+    dist.all_reduce(cnt)
+    flag = torch.tensor([1 if ok else 0], device="cuda")
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ret["ok"] = int(flag.item())
+        ret["units"] = int(cnt.item())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_sharded_forward_two_gpus():
+    ret = mp.Manager().dict()
+    mp.spawn(_sp_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["ok"] == 1
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_batch_head_sharding_two_gpus():
+    ret = mp.Manager().dict()
+    mp.spawn(_bh_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    assert ret["ok"] == 1 and ret["units"] == 3

@@ -225,7 +225,8 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     fp.out = static_cast<bf16*>(out_cm); fp.lse = lse_cm; fp.denom = static_cast<bf16*>(denom_cm);
     fp.status = static_cast<int*>(workspace);
     fp.carry = ua_carry_bytes(dims, dtype, flags) ? static_cast<float*>(carry_out) : nullptr;
-    return ua::sm100::launch_fwd(s, gate_dtype, kc, vc, xq, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
+    ua::sm100::whole_sequence(fp);
+    return ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
   }
 
   ua::simt::FwdParams p;
@@ -239,6 +240,58 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   if (cfg.compact) return gate_dtype == UA_F32 ? launch_simt_fwd<bf16, float, bf16>(p, st) : launch_simt_fwd<bf16, bf16, bf16>(p, st);
   if (gate_dtype == UA_F32) return launch_simt_fwd<bf16, float, float>(p, st);
   return launch_simt_fwd<bf16, bf16, float>(p, st);
+}
+
+namespace {
+int check_rows(const ua::Shape& s, int dtype, int tile_begin, int tile_end) {
+  if (!ua::sm100::fwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  if (tile_begin < 0 || tile_end > s.N || tile_begin >= tile_end) return UA_ERR_BAD_DIMS;
+  return UA_OK;
+}
+}  // namespace
+
+int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end, const void* kc,
+                const void* vc, const void* xq_rows, const void* static_src, const void* static_dest_rows,
+                const float* carry_in, void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, void* workspace,
+                size_t workspace_bytes, int flags, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq_rows || !static_src || !static_dest_rows || !out_cm_rows || !lse_cm_rows) return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq_rows) || !aligned16(out_cm_rows)) return UA_ERR_ALIGNMENT;
+  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  ua::Shape s = to_shape(dims);
+  if ((e = check_rows(s, dtype, row_tile_begin, row_tile_end))) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  ua::sm100::FwdParams fp;
+  fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows;
+  fp.out = static_cast<bf16*>(out_cm_rows); fp.lse = lse_cm_rows; fp.denom = static_cast<bf16*>(denom_cm_rows);
+  fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
+  fp.j_begin = row_tile_begin; fp.j_end = row_tile_end; fp.Lr = (row_tile_end - row_tile_begin) * 128;
+  fp.carry_in = carry_in; fp.total_out = nullptr;
+  return ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq_rows, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
+}
+
+int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                         const void* kc, const void* static_src, const void* static_dest_rows, const float* carry_in,
+                         float* total_out, void* workspace, size_t workspace_bytes, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !static_src || !static_dest_rows || !total_out) return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc)) return UA_ERR_ALIGNMENT;
+  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  ua::Shape s = to_shape(dims);
+  if ((e = check_rows(s, dtype, row_tile_begin, row_tile_end))) return e;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  ua::sm100::FwdParams fp;
+  fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
+  fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
+  fp.j_begin = row_tile_begin; fp.j_end = row_tile_end; fp.Lr = (row_tile_end - row_tile_begin) * 128;
+  fp.carry_in = carry_in; fp.total_out = total_out;
+  return ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st);
 }
 
 int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,

@@ -44,6 +44,11 @@ struct FwdParams {
   __nv_bfloat16* denom;  // (b,h,n,r,L) or null
   int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
   int fill_masked;       // write the rows before the key chunk (uniform softmax) from the two otherwise idle warps
+  // Row range (sequence sharding): this call computes row tiles [j_begin, j_end) only.  xq, static_dest, out,
+  // lse and denom then hold just those Lr = (j_end - j_begin) * 128 rows; keys, values and static_src are whole.
+  int j_begin, j_end, Lr;
+  const float* carry_in;   // optional (b*h*n, 128): decay prefix of key k at its first row tile of the range
+  float* total_out;        // optional (b*h*n, 128): decay prefix after the last row tile of the range
   float* carry;          // optional (required in carry-only mode): (b*h*n, n, 128) decay prefix of key k at the start of row tile j
 };
 
@@ -90,6 +95,7 @@ struct FwdCtx {
   uint32_t tmem;
   volatile int* abort_flag;
   int i, bh, ntiles;
+  int j0;             // first row tile this block computes: max(i, j_begin)
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
   __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
   // warp-collective forms for the decay and softmax groups
@@ -115,7 +121,7 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
     if (u >= 1 && !c.wait(kKjEmpty + ks, u - 1)) return false;
     mbar_expect_tx(c.bar(kKjFull + ks), Cfg::kTileBytes);
     for (int b = 0; b < Cfg::kBoxes; ++b)
-      tma_load_2d(sbase + Cfg::oKj + ks * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmK, b * 64, c.bh * L + (c.i + T) * 128,
+      tma_load_2d(sbase + Cfg::oKj + ks * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmK, b * 64, c.bh * L + (c.j0 + T) * 128,
                   c.bar(kKjFull + ks));
     return true;
   };
@@ -133,7 +139,7 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
       mbar_expect_tx(c.bar(kQFull + qs), Cfg::kTileBytes);
       for (int b = 0; b < Cfg::kBoxes; ++b)
         tma_load_2d(sbase + Cfg::oQ + qs * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmQ, b * 64,
-                    (c.bh * R + r) * L + (c.i + T) * 128, c.bar(kQFull + qs));
+                    (c.bh * R + r) * p.Lr + (c.j0 + T - p.j_begin) * 128, c.bar(kQFull + qs));
       if (r == 0 && T + 1 < c.ntiles && !load_kj(T + 1)) return;
     }
   }
@@ -222,21 +228,22 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   const int k = threadIdx.x & 127;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
-  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * p.Lr;
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + k));
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   uint8_t* sCs = c.smem + Cfg::oCs;
-  float carry = 0.f;
+  const size_t key_id = ((size_t)c.bh * p.s.N + c.i) * 128 + k;
+  float carry = p.carry_in ? p.carry_in[key_id] : 0.f;
   for (int T = 0; T < c.ntiles; ++T) {
-    const int j = c.i + T;
+    const int j = c.j0 + T;
     float* t3buf = sT3 + (T & 1) * 128;
-    t3buf[k] = cbrtf(Num<TG>::ld(sd + j * 128 + k));
+    t3buf[k] = cbrtf(Num<TG>::ld(sd + (j - p.j_begin) * 128 + k));
     c.arrive_w(kT3Ready);
     if (!c.wait_w(kT3Ready, T)) return;
     if (!c.wait_w(kGFull, T)) return;
     tc_fence_after();
-    const bool diag = (T == 0);
-    if (kCarryOnly || p.carry) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
+    const bool diag = (j == c.i);
+    if (p.carry) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
     // The prefix inside a tile is  carry + (sum of the totals of earlier 32-row blocks + scan inside the block):
     // the backward recomputes it with four threads per key, one per block, and must get the same bits.
     float tprev = 0.f, cval = carry;
@@ -274,6 +281,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
     carry = cval;
     if (!kCarryOnly) c.arrive_w(kCReady);
   }
+  if (p.total_out) p.total_out[key_id] = carry;
 }
 
 // ------------------------------------------------------------ softmax groups --
@@ -347,9 +355,9 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       tc_wait_st();
       tc_fence_before();
       c.arrive_w(kPReady + sb);
-      const int qg = (c.i + T) * 128 + row;
+      const int qg = (c.j0 + T - p.j_begin) * 128 + row;      // row index inside the range
       const float lse = m + lg2(l) * kLn2;
-      const size_t orow = (chunk_id * R + r) * L + qg;
+      const size_t orow = (chunk_id * R + r) * p.Lr + qg;
       p.lse[orow] = lse;
       if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
       const float linv = 1.0f / l;
@@ -398,17 +406,17 @@ __device__ __forceinline__ void fwd_fill_rows(const FwdCtx<D>& c, const FwdParam
   }
   named_bar_sync(2, 64);
   const size_t chunk_id = (size_t)c.bh * N + c.i;
-  const int rows = c.i * 128;
+  const int rows = ((c.i < p.j_end ? c.i : p.j_end) - p.j_begin) * 128;    // rows of the range that lie before the chunk
   constexpr int kVecPerRow = D / 8;                    // 16-byte vectors
   const uint4 mine = reinterpret_cast<const uint4*>(vmean)[t % kVecPerRow];   // 64 % kVecPerRow == 0: fixed per thread
   for (int r = 0; r < R; ++r) {
-    uint4* o = reinterpret_cast<uint4*>(p.out + ((chunk_id * R + r) * L) * D);
+    uint4* o = reinterpret_cast<uint4*>(p.out + ((chunk_id * R + r) * p.Lr) * D);
     const size_t nvec = (size_t)rows * kVecPerRow;
     for (size_t e = t; e < nvec; e += 64) o[e] = mine;
-    float* lr = p.lse + (chunk_id * R + r) * L;
+    float* lr = p.lse + (chunk_id * R + r) * p.Lr;
     for (int q = t; q < rows; q += 64) {
       lr[q] = mask_value();
-      if (p.denom) p.denom[(chunk_id * R + r) * L + q] = __float2bfloat16_rn(mask_value());
+      if (p.denom) p.denom[(chunk_id * R + r) * p.Lr + q] = __float2bfloat16_rn(mask_value());
     }
   }
 }
@@ -430,7 +438,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   c.abort_flag = reinterpret_cast<volatile int*>(misc + 1);
   c.i = blockIdx.x / BH;                 // heavy chunks (small i: most row tiles) first
   c.bh = blockIdx.x - c.i * BH;
-  c.ntiles = p.s.N - c.i;
+  c.j0 = c.i > p.j_begin ? c.i : p.j_begin;
+  c.ntiles = p.j_end - c.j0;            // <= 0: nothing to compute for this chunk in the row range (only the fill)
 
   if (threadIdx.x == 0) {
     misc[1] = 0;
@@ -457,14 +466,17 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   c.tmem = misc[0];
 
   if (warp == 0) {
-    if (lane == 0) fwd_producer<D, kCarryOnly>(c, p, &tmK, &tmV, &tmQ);
+    if (lane == 0 && c.ntiles > 0) fwd_producer<D, kCarryOnly>(c, p, &tmK, &tmV, &tmQ);
   } else if (warp == 1) {
-    if (lane == 0) fwd_mma<D, kCarryOnly>(c, p);
+    if (lane == 0 && c.ntiles > 0) fwd_mma<D, kCarryOnly>(c, p);
   } else if (warp >= 4 && warp < 8) {
-    fwd_decay<D, TG, kCarryOnly>(c, p);
+    if (c.ntiles > 0) fwd_decay<D, TG, kCarryOnly>(c, p);
+    else if (p.total_out)      // no row of the range sees this chunk: its prefix does not move
+      p.total_out[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] =
+          p.carry_in ? p.carry_in[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] : 0.f;
   } else if (warp >= 8 && !kCarryOnly) {
-    fwd_softmax<D>(c, p, (warp - 8) >> 2);
-  } else if ((warp == 2 || warp == 3) && !kCarryOnly && p.fill_masked && c.i > 0) {
+    if (c.ntiles > 0) fwd_softmax<D>(c, p, (warp - 8) >> 2);
+  } else if ((warp == 2 || warp == 3) && !kCarryOnly && p.fill_masked && c.i > p.j_begin) {
     fwd_fill_rows<D>(c, p, reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oFill));
   }
 

@@ -44,32 +44,43 @@ inline bool fwd_supported(const Shape& s, int dtype) {
   return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128);
 }
 
-template <int D, typename TG>
+// Fills the row-range fields of FwdParams for a call over the whole sequence.
+inline void whole_sequence(FwdParams& p) {
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.carry_in = nullptr; p.total_out = nullptr;
+}
+
+// Forward (kCarryOnly = false) or decay-only pass (kCarryOnly = true: no values, queries or outputs) over the row
+// tiles [p.j_begin, p.j_end).  xq / static_dest / out hold p.Lr rows; keys, values, static_src the whole sequence.
+template <int D, typename TG, bool kCarryOnly>
 int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const FwdParams& p, bool fill_masked,
                  cudaStream_t st) {
   using Cfg = FwdCfg<D>;
   CUtensorMap tmK, tmV, tmQ;
   const uint64_t BH = (uint64_t)s.B * s.H;
-  if (!make_rows_map(&tmK, kc, BH * s.L, D) || !make_rows_map(&tmV, vc, BH * s.L, D) ||
-      !make_rows_map(&tmQ, xq, BH * s.R * s.L, D))
+  if (!make_rows_map(&tmK, kc, BH * s.L, D)) return UA_ERR_CUDA;
+  if (kCarryOnly) {
+    tmV = tmK; tmQ = tmK;          // not used by the decay-only pass
+  } else if (!make_rows_map(&tmV, vc, BH * s.L, D) || !make_rows_map(&tmQ, xq, BH * s.R * p.Lr, D)) {
     return UA_ERR_CUDA;
-  auto kern = fwd_kernel<D, TG, false>;
+  }
+  auto kern = fwd_kernel<D, TG, kCarryOnly>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   FwdParams q = p;
   q.vc = vc;
-  q.fill_masked = fill_masked ? 1 : 0;
+  q.fill_masked = (fill_masked && !kCarryOnly) ? 1 : 0;
   kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, q);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
-inline int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const FwdParams& p,
-                      bool fill_masked, cudaStream_t st) {
+template <bool kCarryOnly>
+int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const FwdParams& p,
+               bool fill_masked, cudaStream_t st) {
   if (s.D == 64) {
-    return gate_dtype == UA_F32 ? launch_fwd_t<64, float>(s, kc, vc, xq, p, fill_masked, st)
-                                : launch_fwd_t<64, __nv_bfloat16>(s, kc, vc, xq, p, fill_masked, st);
+    return gate_dtype == UA_F32 ? launch_fwd_t<64, float, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st)
+                                : launch_fwd_t<64, __nv_bfloat16, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st);
   }
-  return gate_dtype == UA_F32 ? launch_fwd_t<128, float>(s, kc, vc, xq, p, fill_masked, st)
-                              : launch_fwd_t<128, __nv_bfloat16>(s, kc, vc, xq, p, fill_masked, st);
+  return gate_dtype == UA_F32 ? launch_fwd_t<128, float, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st)
+                              : launch_fwd_t<128, __nv_bfloat16, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st);
 }
 
 inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && s.D == 64; }
@@ -85,14 +96,12 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
       !make_rows_map(&tmQ, xq, BH * s.R * s.L, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, 64))
     return UA_ERR_CUDA;
   if (run_prepass) {
-    using Cfg = FwdCfg<64>;
     FwdParams fp;
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
     fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
-    auto kern = fwd_kernel<64, TG, true>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-    kern<<<(unsigned)(BH * s.N), 512, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, fp);
-    if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+    whole_sequence(fp);
+    int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
+    if (e) return e;
   }
   auto kern = bwd_kernel<TG>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;

@@ -229,3 +229,66 @@ def merge_bwd_cm(out_cm, lse_cm, g_merged, skip_zero_weight_blocks: bool = False
                               _lib.FLAG_SKIP_MASKED_FILL if skip_zero_weight_blocks else 0, _stream())
     _lib.check(rc, "ua_merge_bwd")
     return g_out_cm, g_lse_cm
+
+
+# ---- sequence-chunk sharding: forward over a range of row tiles ------------------------------------
+
+def decay_totals_rows(kc, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None):
+    """(b,h,n,128) fp32: for every key, ``carry_in`` (or 0) plus the sum of its log-retention over the
+    rows of the row tiles [tile_begin, tile_end).  ``kc`` / ``static_src`` cover the whole sequence,
+    ``static_dest_rows`` (b,h,Lr) only the rows of the range."""
+    _require_cuda(kc, static_src, static_dest_rows)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    dt = kc.dtype
+    code = _dtype_code(dt)
+    kc = kc.contiguous()
+    L, Lr = n * c, (tile_end - tile_begin) * 128
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    dims = UaDims(b, h, 1, n, c, d)
+    with torch.cuda.device(kc.device):
+        total = torch.empty(b, h, n, 128, dtype=torch.float32, device=kc.device)
+        ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
+        ci = carry_in.float().contiguous() if carry_in is not None else None
+        rc = lib.ua_decay_totals_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(ss),
+                                      _ptr(sd), _ptr(ci), _ptr(total), _ptr(ws), 256, _stream())
+        _lib.check(rc, "ua_decay_totals_rows")
+        _check_status(lib, ws, "ua_decay_totals_rows")
+    return total
+
+
+def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None,
+                    flags: int = 0):
+    """Forward for the row tiles [tile_begin, tile_end): returns (out_cm (b,h,n,r,Lr,d), lse_cm fp32 (b,h,n,r,Lr),
+    denom_cm).  ``kc``, ``vc``, ``static_src`` cover the whole sequence; ``xq_rows`` (b,h,r,Lr,d) and
+    ``static_dest_rows`` (b,h,Lr) the rows of the range; ``carry_in`` (b,h,n,128) as from ``decay_totals_rows``
+    summed over the earlier ranges."""
+    _require_cuda(kc, vc, xq_rows, static_src, static_dest_rows)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq_rows.shape[2]
+    dt = xq_rows.dtype
+    code = _dtype_code(dt)
+    L, Lr = n * c, (tile_end - tile_begin) * 128
+    kc, vc = kc.contiguous(), vc.contiguous()
+    q = xq_rows.reshape(b, h, r, Lr, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    dims = UaDims(b, h, r, n, c, d)
+    with torch.cuda.device(kc.device):
+        out_cm = torch.empty(b, h, n, r, Lr, d, dtype=dt, device=kc.device)
+        lse_cm = torch.empty(b, h, n, r, Lr, dtype=torch.float32, device=kc.device)
+        denom_cm = torch.empty(b, h, n, r, Lr, dtype=dt, device=kc.device)
+        ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
+        ci = carry_in.float().contiguous() if carry_in is not None else None
+        rc = lib.ua_fwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc), _ptr(q),
+                             _ptr(ss), _ptr(sd), _ptr(ci), _ptr(out_cm), _ptr(lse_cm), _ptr(denom_cm), _ptr(ws), 256, flags,
+                             _stream())
+        _lib.check(rc, "ua_fwd_rows")
+        _check_status(lib, ws, "ua_fwd_rows")
+    return out_cm, lse_cm, denom_cm
