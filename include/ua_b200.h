@@ -162,6 +162,31 @@ int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_
                          const float* carry_in, float* total_out,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/* Sequence-chunk sharding of the backward (bf16, chunk 128, head_dim 64).  No counterpart in the reference.
+ * A rank that owns the row tiles [row_tile_begin, row_tile_end) runs
+ *   1. ua_bwd_rows: gradients of everything its rows touch.  Row-indexed tensors (xq_rows, static_dest_rows,
+ *      g_out_cm_rows (b,h,n,r,Lr,d), g_denom_cm_rows (b,h,n,r,Lr), dxq_rows, ddest_rows_f32 (b,h,Lr)) hold the Lr rows
+ *      of the range; dk_f32, dv_f32 (b,h,L,d) and dsrc_f32 (b,h,L) are fp32, cover ALL keys and are this rank's PARTIAL
+ *      sums (overwritten; the caller adds them over the ranks).  carry_in as for ua_fwd_rows.  suffix_in (b,h,n,128) or
+ *      NULL: reverse decay carry entering from later rows.  dctot_out (b,h,n,128) or NULL: per key, the sum of the
+ *      decay-prefix gradient dC over the rows of the range -- what the ranks owning EARLIER rows need.
+ *   2. after exchanging the dctot tables: suffix = sum of dctot of the ranks that own later rows, and
+ *      ua_bwd_rows_suffix ADDS the gradient that this suffix induces (every gradient is linear in it) into dk_f32,
+ *      dsrc_f32 and ddest_rows_f32: a decay-only pass, no queries, values or upstream gradients involved.
+ * Workspace: ua_bwd_rows_workspace_bytes() for ua_bwd_rows, 256 bytes for ua_bwd_rows_suffix. */
+size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype, int row_tile_begin, int row_tile_end);
+int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                const void* kc, const void* vc, const void* xq_rows,
+                const void* static_src, const void* static_dest_rows,
+                const void* g_out_cm_rows, const void* g_denom_cm_rows, int g_denom_dtype,
+                const float* carry_in, const float* suffix_in,
+                float* dk_f32, float* dv_f32, void* dxq_rows, float* dsrc_f32, float* ddest_rows_f32, float* dctot_out,
+                void* workspace, size_t workspace_bytes, int flags, void* stream);
+int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                       const void* kc, const void* vc, const void* static_src, const void* static_dest_rows,
+                       const float* suffix, float* dk_f32, float* dsrc_f32, float* ddest_rows_f32,
+                       void* workspace, size_t workspace_bytes, void* stream);
+
 /* Backward for callers that must not allocate.  No counterpart in the reference.
  *
  * Some hosts of this library cannot hand it a workspace: an inference or

@@ -302,3 +302,45 @@ def test_forward_over_row_ranges_matches_whole_forward(shape, ranges):
     # chained totals: passing the running carry through carry_in gives the same table as summing per-range totals
     chained = ops.decay_totals_rows(kc, ss, sd[:, :, ranges[1][0] * 128:ranges[1][1] * 128], *ranges[1], carry_in=totals[0])
     assert (chained - (totals[0] + totals[1])).abs().max() <= 1e-2 + 1e-6 * chained.abs().max()
+
+
+@pytest.mark.parametrize("ranges,skip", [([(0, 3), (3, 8)], False), ([(0, 2), (2, 5), (5, 8)], True)])
+def test_backward_over_row_ranges_matches_whole_backward(ranges, skip):
+    """ua_bwd_rows + ua_bwd_rows_suffix (the sequence-sharded backward), ranks emulated one after the other on one
+    GPU: partial key-side gradients summed over the ranges, row-side gradients concatenated, against the
+    whole-sequence backward of the same library."""
+    from universal_attention_triton_b200 import _lib, ops
+    shape = (1, 2, 2, 1024, 128, 64)
+    B, H, R, L, c, D = shape
+    n = L // c
+    ins, _ = _bf16_case(*shape, seed=71)
+    kc, vc, xq, ss, sd = _cuda(*ins)
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    flags = _lib.FLAG_SKIP_MASKED_GRADS if skip else 0
+    if skip:
+        valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda().view(1, 1, n, 1, L)
+        g_out = g_out * valid.unsqueeze(-1)
+        g_lse = g_lse * valid
+    ref = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse, flags=flags)
+    totals = [ops.decay_totals_rows(kc, ss, sd[:, :, b * 128:e * 128], b, e) for b, e in ranges]
+    carries = [sum(totals[:g], torch.zeros_like(totals[0])) for g in range(len(ranges))]
+    parts = []
+    for (b, e), carry in zip(ranges, carries):
+        rows = slice(b * 128, e * 128)
+        parts.append(ops.backward_rows(kc, vc, xq[:, :, :, rows], ss, sd[:, :, rows], g_out[:, :, :, :, rows].contiguous(),
+                                       g_lse[:, :, :, :, rows].contiguous(), b, e, carry_in=carry, flags=flags))
+    # second step: reverse carry from the later ranges
+    for g, ((b, e), part) in enumerate(zip(ranges, parts)):
+        if g + 1 < len(ranges):
+            suffix = sum([p[5] for p in parts[g + 1:]], torch.zeros_like(parts[0][5]))
+            ops.backward_rows_suffix(kc, vc, ss, sd[:, :, b * 128:e * 128], b, e, suffix, part[0], part[3], part[4])
+    dk = sum(p[0] for p in parts).view(kc.shape)
+    dv = sum(p[1] for p in parts).view(vc.shape)
+    dxq = torch.cat([p[2] for p in parts], dim=3)
+    dsrc = sum(p[3] for p in parts).view(ss.shape)
+    ddest = torch.cat([p[4] for p in parts], dim=2)
+    for got, want, key in zip((dk, dv, dxq, dsrc, ddest), ref, GRADS):
+        assert torch.isfinite(got.float()).all(), key
+        assert rel_fro(got.float().cpu(), want.float().cpu()) <= 1e-2, (key, rel_fro(got.float().cpu(), want.float().cpu()))

@@ -41,6 +41,19 @@ def _sp_worker(rank, world, port, ret):
     valid = (torch.arange(L).view(L, 1) >= torch.arange(n).view(1, n) * c).cuda()[sr]
     ok = bool((((lse - ref_lse).abs() <= 1e-3 + 1e-6 * ref_lse.abs()) | ~valid).all().item())
     ok = ok and bool(((out.float() - ref_out.float()).abs() <= 2e-2 + ref_out.float().abs() * 2.0 ** -7).all().item())
+    # backward: random upstream gradients of the rank's rows, against the single-GPU backward
+    from universal_attention_triton_b200.sequence_parallel import sp_backward
+    gen = torch.Generator(device="cuda").manual_seed(63)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    want = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse)
+    got = sp_backward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
+                      ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(),
+                      ops.as_reference_out(g_out)[:, :, :, sr], ops.as_reference_denom(g_lse)[:, :, :, sr])
+    want_local = (want[0][:, :, sc], want[1][:, :, sc], want[2][:, :, :, sr], want[3][:, :, sc], want[4][:, :, sr])
+    for a, b_ in zip(got, want_local):
+        rel = ((a.float() - b_.float()).norm() / b_.float().norm().clamp_min(1e-20)).item()
+        ok = ok and a.shape == b_.shape and rel <= 1e-2
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -75,7 +88,7 @@ def _bh_worker(rank, world, port, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sequence_sharded_forward_two_gpus():
+def test_sequence_sharded_forward_and_backward_two_gpus():
     ret = mp.Manager().dict()
     mp.spawn(_sp_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
     assert ret["ok"] == 1

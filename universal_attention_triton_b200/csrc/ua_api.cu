@@ -294,6 +294,93 @@ int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_
   return ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st);
 }
 
+namespace {
+struct RowsWs { size_t off_dq, off_carry, total; };
+RowsWs rows_ws(const ua::Shape& s, int tile_begin, int tile_end) {
+  RowsWs w;
+  const size_t BH = (size_t)s.B * s.H, f = sizeof(float), Lr = (size_t)(tile_end - tile_begin) * 128;
+  size_t o = 256;
+  w.off_dq = o; o = align_up(o + BH * s.R * Lr * s.D * f, 256);
+  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 128 * f, 256);
+  w.total = o;
+  return w;
+}
+}  // namespace
+
+size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype, int row_tile_begin, int row_tile_end) {
+  if (check_dims(dims) != UA_OK) return 0;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::bwd_supported(s, dtype) || row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return 0;
+  return rows_ws(s, row_tile_begin, row_tile_end).total;
+}
+
+int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end, const void* kc,
+                const void* vc, const void* xq_rows, const void* static_src, const void* static_dest_rows,
+                const void* g_out_cm_rows, const void* g_denom_cm_rows, int g_denom_dtype, const float* carry_in,
+                const float* suffix_in, float* dk_f32, float* dv_f32, void* dxq_rows, float* dsrc_f32,
+                float* ddest_rows_f32, float* dctot_out, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (g_denom_dtype != UA_F32 && g_denom_dtype != dtype) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq_rows || !static_src || !static_dest_rows || !g_out_cm_rows || !g_denom_cm_rows || !dk_f32 || !dv_f32 ||
+      !dxq_rows || !dsrc_f32 || !ddest_rows_f32)
+    return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq_rows) || !aligned16(g_out_cm_rows) || !aligned16(dk_f32) ||
+      !aligned16(dv_f32) || !aligned16(dxq_rows))
+    return UA_ERR_ALIGNMENT;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  if (row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return UA_ERR_BAD_DIMS;
+  const RowsWs w = rows_ws(s, row_tile_begin, row_tile_end);
+  if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  const size_t BH = (size_t)s.B * s.H, Lr = (size_t)(row_tile_end - row_tile_begin) * 128;
+  if (cudaMemsetAsync(ws, 0, w.off_carry, st) != cudaSuccess) return UA_ERR_CUDA;                       // status + dQ accumulator
+  if (cudaMemsetAsync(dk_f32, 0, BH * s.L * s.D * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(dv_f32, 0, BH * s.L * s.D * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(dsrc_f32, 0, BH * s.L * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(ddest_rows_f32, 0, BH * Lr * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  ua::sm100::BwdParams bp;
+  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
+  bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+  float* carry_tab = reinterpret_cast<float*>(ws + w.off_carry);
+  bp.carry = carry_tab;
+  bp.acc_dk = dk_f32; bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq); bp.acc_dt = ddest_rows_f32;
+  bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
+  bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
+  bp.j_begin = row_tile_begin; bp.j_end = row_tile_end; bp.Lr = (int)Lr;
+  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0;
+  e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
+  if (e) return e;
+  return convert_any(dtype, bp.acc_dq, dxq_rows, BH * s.R * Lr * s.D, st);
+}
+
+int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+                       const void* kc, const void* vc, const void* static_src, const void* static_dest_rows,
+                       const float* suffix, float* dk_f32, float* dsrc_f32, float* ddest_rows_f32, void* workspace,
+                       size_t workspace_bytes, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !static_src || !static_dest_rows || !suffix || !dk_f32 || !dsrc_f32 || !ddest_rows_f32) return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(dk_f32)) return UA_ERR_ALIGNMENT;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  if (row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return UA_ERR_BAD_DIMS;
+  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  ua::sm100::BwdParams bp;
+  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows; bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
+  bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
+  bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
+  bp.j_begin = row_tile_begin; bp.j_end = row_tile_end; bp.Lr = (row_tile_end - row_tile_begin) * 128;
+  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1;
+  return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
+}
+
 int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
            const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
            int g_denom_dtype, void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
@@ -335,7 +422,8 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     bp.dss = dstatic_src;
     bp.status = reinterpret_cast<int*>(ws);
     bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, carry_tab, carry_in == nullptr, st);
+    ua::sm100::whole_sequence(bp);
+    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, carry_tab, carry_in == nullptr, nullptr, st);
     if (e) return e;
     const size_t BHs = (size_t)s.B * s.H;
     if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;

@@ -46,6 +46,14 @@ struct BwdParams {
   void* dss;               // gate dtype, written directly
   int* status;
   int skip_masked;
+  // Row range (sequence sharding): only the row tiles [j_begin, j_end) are swept; xq, static_dest, g_out, g_denom,
+  // acc_dq and acc_dt then hold just those Lr = 128 * (j_end - j_begin) rows.  Keys, values, static_src, acc_dk whole.
+  int j_begin, j_end, Lr;
+  const float* suffix_in;  // optional (b*h*n, 128): reverse decay carry entering from the rows after the range
+  float* dctot_out;        // optional (b*h*n, 128): per key, sum of dC over the rows of the range (what earlier ranges need)
+  float* acc_dv;           // optional (b*h, L, 64) fp32: dV_i is stored here instead of dvc
+  float* acc_ds;           // optional (b*h, L) fp32: d static_src is added here instead of written to dss
+  int decay_only;          // correction pass: only the decay gradient that suffix_in induces (no heads, no dV)
 };
 
 struct BwdCfg {
@@ -74,13 +82,16 @@ struct BwdCtx {
   uint32_t tmem;
   volatile int* abort_flag;
   int i, bh, nvalid, ntiles;
+  int j_begin, j_end;
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
   __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
   // warp-collective forms for the worker groups
   __device__ __forceinline__ bool wait_w(int idx, uint32_t parity) const { return mbar_wait_warp(bar(idx), parity & 1u, abort_flag); }
   __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
   // row tile index of sweep step T: valid tiles n-1 .. i first, then the masked ones i-1 .. 0
-  __device__ __forceinline__ int tile_j(int T, int N) const { return T < nvalid ? N - 1 - T : i - 1 - (T - nvalid); }
+  __device__ __forceinline__ int tile_j(int T, int) const {
+    return T < nvalid ? j_end - 1 - T : (i < j_end ? i : j_end) - 1 - (T - nvalid);
+  }
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -117,8 +128,8 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
   // shared-memory slot frees up only pays L2 latency.
   auto coords = [&](int T, int r, int& qrow, int& grow) {
     const int j = c.tile_j(T, N);
-    qrow = (c.bh * R + r) * L + j * 128;
-    grow = (int)((chunk_id * R + r) * L + (size_t)j * 128);
+    qrow = (c.bh * R + r) * p.Lr + (j - p.j_begin) * 128;
+    grow = (int)((chunk_id * R + r) * p.Lr + (size_t)(j - p.j_begin) * 128);
   };
   int rc = 0;
   for (int T = 0; T < c.ntiles; ++T) {
@@ -129,7 +140,7 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
       mbar_expect_tx(c.bar(bKjFull), BwdCfg::kTileBytes);
       tma_load_2d(sbase + BwdCfg::oKj, tmK, 0, c.bh * L + j * 128, c.bar(bKjFull));
     }
-    for (int r = 0; r < R; ++r, ++rc) {
+    for (int r = 0; r < (p.decay_only ? 0 : R); ++r, ++rc) {
       int qrow, grow;
       {
         int Tn = T, rn = r + 1;
@@ -157,7 +168,7 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
 //   issuer A: X0 (G, S_r, G again), dV_i, dK_i          issuer B: X1 (dP_r, dQ_r, dK_j), dC
 // MMAs into one accumulator always come from the same issuer, so their order is kept.
 __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, const int which) {
-  const int R = p.s.R;
+  const int R = p.decay_only ? 0 : p.s.R;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_nt = idesc_bf16(128, 128, 0, 0);   // A K-major, B K-major, N = 128
   constexpr uint32_t id_tt = idesc_bf16(128, 64, 1, 1);    // A MN-major, B MN-major, N = 64
@@ -207,11 +218,13 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
       // ------------------------------------------------------------- issuer A
       if (valid) {
         if (!c.wait(bKjFull, T)) return;
-        if (x_uses >= 1 && !c.wait(bX0Free, x_uses - 1)) return;
-        tc_fence_after();
-        mma_nt(X0, kKi, kKj);                                           // G = K_i K_j^T
-        tc_commit(c.bar(bGFull));
-        ++x_uses;
+        if (!p.decay_only) {
+          if (x_uses >= 1 && !c.wait(bX0Free, x_uses - 1)) return;
+          tc_fence_after();
+          mma_nt(X0, kKi, kKj);                                         // G = K_i K_j^T
+          tc_commit(c.bar(bGFull));
+          ++x_uses;
+        }
       }
       for (int r = 0; r < R; ++r, ++rc) {
         if (!c.wait(bInFull, rc)) return;
@@ -231,14 +244,15 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
         tc_commit(c.bar(bRDone));
       }
       if (valid) {
-        if (!c.wait(bX0Free, x_uses - 1)) return;
+        if (x_uses >= 1 && !c.wait(bX0Free, x_uses - 1)) return;
         tc_fence_after();
         mma_nt(X0, kKi, kKj);                                           // G again for the decay backward
         tc_commit(c.bar(bG2Full));
         ++x_uses;
         if (!c.wait(bDgReady, T)) return;
         tc_fence_after();
-        mma_nn(DK, kdG, mKj, true);                                     // dK_i += dG K_j
+        mma_nn(DK, kdG, mKj, have_acc);                                 // dK_i += dG K_j
+        have_acc = true;
         tc_commit(c.bar(bDkjFull));
       }
     } else {
@@ -264,7 +278,7 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
       }
       if (valid) {
         if (!c.wait(bDgReady, T)) return;
-        if (!c.wait(bX1Free, x_uses - 1)) return;
+        if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
         tc_fence_after();
         mma_tt(X1, mP, mKi, false);                                     // dK_j = dG^T K_i
         ++x_uses;
@@ -331,11 +345,11 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 
 template <typename TG>
 __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part) {
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int L = p.s.L, R = p.decay_only ? 0 : p.s.R, N = p.s.N, Rq = p.s.R;
   const int tid = threadIdx.x & 127, lane = threadIdx.x & 31;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
-  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * p.Lr;
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + tid));
   float* sT3 = reinterpret_cast<float*>(c.smem + BwdCfg::oT3);
   uint8_t* sCs = c.smem + BwdCfg::oCs;
@@ -349,7 +363,8 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   const float kLog2e = 1.4426950408889634f;
   const uint32_t swz = (uint32_t)(tid & 7);
   Mailbox mb{&c, reinterpret_cast<float*>(c.smem + BwdCfg::oXch), part, tid, 0, true};
-  float suffix = 0.f, ds_acc = 0.f;
+  const size_t key_id = chunk_id * 128 + tid;
+  float suffix = p.suffix_in ? p.suffix_in[key_id] : 0.f, ds_acc = 0.f, dct = 0.f;
   UA_PH_DECL
 
   // this thread's 32 columns of row `tid` of a [row][key] bf16 tile: 4 chunks of box part/2
@@ -379,11 +394,17 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     const bool valid = T < c.nvalid;
     const int j = c.tile_j(T, N);
     const bool diag = (j == c.i);
+    const int jl = j - p.j_begin;                 // row tile index inside the range
     float* t3buf = sT3 + (T & 1) * 128;
 
-    if (valid) {
+    if (valid && p.decay_only) {
+      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + jl * 128 + tid));
+      mb.sync();
+      if (!mb.ok) return;
+    }
+    if (valid && !p.decay_only) {
       // ---- decay prefix (forward recomputation): thread = key, C^T[row][key] to shared memory ----
-      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + j * 128 + tid));
+      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + jl * 128 + tid));
       const float carry = p.carry[(chunk_id * N + j) * 128 + tid];
       mb.sync();                                  // t3 visible; every reader of the previous tile's C^T is done
       UA_PH(0)
@@ -431,7 +452,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     }
 
     for (int r = 0; r < R; ++r, ++rc) {
-      const size_t grow = (chunk_id * R + r) * L + (size_t)j * 128 + tid;
+      const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)jl * 128 + tid;
       const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
       if (!c.wait_w(bSdpFull, rc)) return;
@@ -533,7 +554,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bRDone, rc)) return;
       UA_PH(5)
       tc_fence_after();
-      drain_x1(p.acc_dq + (((size_t)c.bh * R + r) * L + (size_t)j * 128 + tid) * 64);
+      drain_x1(p.acc_dq + (((size_t)c.bh * Rq + r) * p.Lr + (size_t)jl * 128 + tid) * 64);
       UA_PH(6)
     }
 
@@ -543,7 +564,11 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       UA_PH(7)
       tc_fence_after();
       float dcs[32];
-      {
+      if (p.decay_only) {
+        // correction pass: no dC of its own; d ell = suffix_in on every unmasked (key, row) pair
+#pragma unroll
+        for (int x = 0; x < 32; ++x) dcs[x] = 0.f;
+      } else {
         uint32_t t[32];
         tmem_ld32(XC, t);
         tc_wait_ld();
@@ -556,6 +581,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
         float4 tots[kParts];
         mb.gather(make_float4(run, 0.f, 0.f, 0.f), tots);
         if (!mb.ok) return;
+        dct += (tots[0].x + tots[1].x) + (tots[2].x + tots[3].x);
         // rows after this thread's block: the carried suffix plus the totals of the later blocks
 #pragma unroll
         for (int q = kParts - 1; q >= 0; --q)
@@ -604,13 +630,15 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       {
         const float colsum = warp_transpose_reduce(dcs, lane);
         const float t3l = t3buf[col0 + lane];
-        if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + j * 128 + col0 + lane, colsum / (3.0f * t3l * t3l));
+        if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + jl * 128 + col0 + lane, colsum / (3.0f * t3l * t3l));
       }
       // the suffix carried to the next (lower) tile is d ell at the tile's first row
-      float4 f[kParts];
-      mb.gather(make_float4(first, 0.f, 0.f, 0.f), f);
-      if (!mb.ok) return;
-      suffix = f[0].x;
+      if (!p.decay_only) {
+        float4 f[kParts];
+        mb.gather(make_float4(first, 0.f, 0.f, 0.f), f);
+        if (!mb.ok) return;
+        suffix = f[0].x;
+      }
       UA_PH(8)
       if (!c.wait_w(bDkjFull, T)) return;
       UA_PH(9)
@@ -627,17 +655,27 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   const size_t krow = (size_t)c.bh * L + c.i * 128 + tid;
   {
     uint32_t o[16];
-    tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
-    tc_wait_ld();
-    uint32_t pk[8];
+    if (!p.decay_only) {
+      tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
+      tc_wait_ld();
+      if (p.acc_dv) {
+        float4* dst = reinterpret_cast<float4*>(p.acc_dv + krow * 64 + 16 * part);
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]), __uint_as_float(o[2 * u + 1]));
-      pk[u] = *reinterpret_cast<uint32_t*>(&h);
+        for (int u = 0; u < 4; ++u)
+          dst[u] = make_float4(__uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]), __uint_as_float(o[u * 4 + 2]),
+                               __uint_as_float(o[u * 4 + 3]));
+      } else {
+        uint32_t pk[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]), __uint_as_float(o[2 * u + 1]));
+          pk[u] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * 64 + 16 * part);
+        dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+      }
     }
-    uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * 64 + 16 * part);
-    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     tmem_ld16(c.tmem + BwdCfg::tDK + lane_base + 16 * part, o);
     tc_wait_ld();
     float* dk = p.acc_dk + krow * 64 + 16 * part;
@@ -648,8 +686,12 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   }
   float4 od[kParts];
   mb.gather(make_float4(ds_acc, 0.f, 0.f, 0.f), od);
-  if (mb.ok && part == 0)
-    Num<TG>::st(static_cast<TG*>(p.dss) + krow, ((od[0].x + od[1].x) + (od[2].x + od[3].x)) / (3.0f * s3 * s3));
+  if (mb.ok && part == 0) {
+    const float dsv = ((od[0].x + od[1].x) + (od[2].x + od[3].x)) / (3.0f * s3 * s3);
+    if (p.acc_ds) atomicAdd(p.acc_ds + krow, dsv);
+    else Num<TG>::st(static_cast<TG*>(p.dss) + krow, dsv);
+    if (p.dctot_out) p.dctot_out[key_id] = dct;
+  }
 }
 
 template <typename TG>
@@ -668,8 +710,15 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   c.abort_flag = reinterpret_cast<volatile int*>(misc + 1);
   c.i = blockIdx.x / BH;
   c.bh = blockIdx.x - c.i * BH;
-  c.nvalid = p.s.N - c.i;
-  c.ntiles = c.nvalid + (p.skip_masked ? 0 : c.i);
+  c.j_begin = p.j_begin;
+  c.j_end = p.j_end;
+  {
+    const int lo = c.i > p.j_begin ? c.i : p.j_begin;               // first row tile of the range that sees the chunk
+    const int top = c.i < p.j_end ? c.i : p.j_end;                  // rows below this tile index lie before the chunk
+    c.nvalid = p.j_end > lo ? p.j_end - lo : 0;
+    const int nmask = (p.skip_masked || p.decay_only || top <= p.j_begin) ? 0 : top - p.j_begin;
+    c.ntiles = c.nvalid + nmask;
+  }
 
   if (threadIdx.x == 0) {
     misc[1] = 0;
@@ -700,7 +749,10 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   tc_fence_after();
   c.tmem = misc[0];
 
-  if (warp == 0) {
+  if (c.ntiles == 0) {
+    // no row of the range touches this chunk (sequence sharding only): nothing to add anywhere
+    if (warp >= 4 && warp < 8 && p.dctot_out) p.dctot_out[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] = 0.f;
+  } else if (warp == 0) {
     if (lane == 0) bwd_producer(c, p, &tmK, &tmV, &tmQ, &tmG);
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) bwd_mma(c, p, warp - 1);

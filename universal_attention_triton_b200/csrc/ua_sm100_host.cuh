@@ -85,21 +85,31 @@ int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, c
 
 inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && s.D == 64; }
 
-// Backward: (1) carry-only run of the forward kernel fills the decay-prefix table,
-// (2) the backward kernel proper.  The caller zeroes the fp32 accumulators.
+// Fills the row-range / sharding fields of BwdParams for a call over the whole sequence.
+inline void whole_sequence(BwdParams& p) {
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.suffix_in = nullptr; p.dctot_out = nullptr;
+  p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0;
+}
+
+// Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
+// decay-only run of the forward kernel fills it (starting from carry_in for a row range), (2) the backward kernel.
+// The caller zeroes the fp32 accumulators.
 template <typename TG>
 int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const BwdParams& p,
-                 float* carry, bool run_prepass, cudaStream_t st) {
+                 float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
   CUtensorMap tmK, tmV, tmQ, tmG;
   const uint64_t BH = (uint64_t)s.B * s.H;
-  if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64) ||
-      !make_rows_map(&tmQ, xq, BH * s.R * s.L, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, 64))
+  if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64)) return UA_ERR_CUDA;
+  if (p.decay_only) {
+    tmQ = tmK; tmG = tmK;          // the correction pass touches neither queries nor upstream gradients
+  } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * p.Lr, 64)) {
     return UA_ERR_CUDA;
-  if (run_prepass) {
+  }
+  if (run_prepass && !p.decay_only) {
     FwdParams fp;
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
     fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
-    whole_sequence(fp);
+    fp.j_begin = p.j_begin; fp.j_end = p.j_end; fp.Lr = p.Lr; fp.carry_in = carry_in; fp.total_out = nullptr;
     int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
     if (e) return e;
   }
@@ -110,9 +120,9 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
 }
 
 inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const void* g_out,
-                      const BwdParams& p, float* carry, bool run_prepass, cudaStream_t st) {
-  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, run_prepass, st)
-                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, run_prepass, st);
+                      const BwdParams& p, float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
+  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st)
+                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st);
 }
 
 }  // namespace sm100

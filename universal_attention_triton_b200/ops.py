@@ -292,3 +292,72 @@ def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: i
         _lib.check(rc, "ua_fwd_rows")
         _check_status(lib, ws, "ua_fwd_rows")
     return out_cm, lse_cm, denom_cm
+
+
+def backward_rows(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows, tile_begin: int,
+                  tile_end: int, carry_in=None, suffix_in=None, flags: int = 0):
+    """Backward for the row tiles [tile_begin, tile_end) (sequence sharding).  Returns
+    ``(dk_f32 (b,h,L,d), dv_f32 (b,h,L,d), dxq_rows, dsrc_f32 (b,h,L), ddest_rows_f32 (b,h,Lr), dctot (b,h,n,128))``:
+    the key-side gradients are this range's partial sums over ALL keys, in fp32, to be added over the ranges."""
+    _require_cuda(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq_rows.shape[2]
+    dt = xq_rows.dtype
+    code = _dtype_code(dt)
+    L, Lr = n * c, (tile_end - tile_begin) * 128
+    kc, vc = kc.contiguous(), vc.contiguous()
+    q = xq_rows.reshape(b, h, r, Lr, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    g_out_cm_rows = g_out_cm_rows.to(dt).contiguous()
+    if g_denom_cm_rows.dtype not in (torch.float32, dt):
+        g_denom_cm_rows = g_denom_cm_rows.float()
+    g_denom_cm_rows = g_denom_cm_rows.contiguous()
+    dims = UaDims(b, h, r, n, c, d)
+    dev = kc.device
+    with torch.cuda.device(dev):
+        dk = torch.empty(b, h, L, d, dtype=torch.float32, device=dev)
+        dv = torch.empty(b, h, L, d, dtype=torch.float32, device=dev)
+        dsrc = torch.empty(b, h, L, dtype=torch.float32, device=dev)
+        ddest = torch.empty(b, h, Lr, dtype=torch.float32, device=dev)
+        dxq = torch.empty_like(q)
+        dctot = torch.empty(b, h, n, 128, dtype=torch.float32, device=dev)
+        ws_bytes = lib.ua_bwd_rows_workspace_bytes(ctypes.byref(dims), code, tile_begin, tile_end)
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+        ci = carry_in.float().contiguous() if carry_in is not None else None
+        si = suffix_in.float().contiguous() if suffix_in is not None else None
+        rc = lib.ua_bwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc), _ptr(q),
+                             _ptr(ss), _ptr(sd), _ptr(g_out_cm_rows), _ptr(g_denom_cm_rows), _dtype_code(g_denom_cm_rows.dtype),
+                             _ptr(ci), _ptr(si), _ptr(dk), _ptr(dv), _ptr(dxq), _ptr(dsrc), _ptr(ddest), _ptr(dctot),
+                             _ptr(ws), ws_bytes, flags, _stream())
+        _lib.check(rc, "ua_bwd_rows")
+        _check_status(lib, ws, "ua_bwd_rows")
+    return dk, dv, dxq.view(xq_rows.shape), dsrc, ddest, dctot
+
+
+def backward_rows_suffix(kc, vc, static_src, static_dest_rows, tile_begin: int, tile_end: int, suffix, dk, dsrc, ddest):
+    """Adds to ``dk``, ``dsrc``, ``ddest`` (fp32, as returned by ``backward_rows``) the gradient induced by the reverse
+    decay carry ``suffix`` (b,h,n,128) that enters the range from the rows after it."""
+    _require_cuda(kc, vc, static_src, static_dest_rows, suffix, dk, dsrc, ddest)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    dt = kc.dtype
+    code = _dtype_code(dt)
+    L, Lr = n * c, (tile_end - tile_begin) * 128
+    kc, vc = kc.contiguous(), vc.contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    assert dk.is_contiguous() and dsrc.is_contiguous() and ddest.is_contiguous()
+    dims = UaDims(b, h, 1, n, c, d)
+    with torch.cuda.device(kc.device):
+        ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
+        sf = suffix.float().contiguous()
+        rc = lib.ua_bwd_rows_suffix(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc),
+                                    _ptr(ss), _ptr(sd), _ptr(sf), _ptr(dk), _ptr(dsrc), _ptr(ddest), _ptr(ws), 256, _stream())
+        _lib.check(rc, "ua_bwd_rows_suffix")
+        _check_status(lib, ws, "ua_bwd_rows_suffix")
