@@ -42,6 +42,9 @@ WORKLOADS = {
     "c2": dict(B=4, H=8, R=4, L=4096, c=128, D=64, dtype="bf16", std=1.0, gm=0.0, gs=1.0, fwd_only=False),
     # a (batch, kv-head) slice of c2 for profiler captures: small on the device, out tensor still larger than L2
     "c2s": dict(B=1, H=2, R=4, L=4096, c=128, D=64, dtype="bf16", std=1.0, gm=0.0, gs=1.0, fwd_only=False),
+    # long context for sequence-chunk sharding (--mode sp): config 4's sequence regime at the chunk / head_dim the
+    # tensor-core backward supports; L is the TOTAL sequence, split over the ranks
+    "long": dict(B=1, H=8, R=4, L=32768, c=128, D=64, dtype="bf16", std=1.0, gm=0.0, gs=1.0, fwd_only=False),
     "c3": dict(B=16, H=8, R=4, L=8192, c=128, D=128, dtype="bf16", std=0.5, gm=0.0, gs=1.0, fwd_only=True),
     "c5": dict(B=8, H=16, R=1, L=16384, c=128, D=128, dtype="bf16", std=1.0, gm=-4.0, gs=2.0, fwd_only=False),
 }
@@ -185,6 +188,68 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
+def run_sequence_parallel(args, w, rank, world, device, W, K):
+    """One long sequence, rows sharded contiguously over the ranks (strong scaling): sp_forward + sp_backward."""
+    import torch.distributed as dist
+    from universal_attention_triton_b200 import ops
+    from universal_attention_triton_b200.sequence_parallel import sp_backward, sp_forward
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    B, H, R, L, c, D = w["B"], w["H"], w["R"], w["L"], w["c"], w["D"]
+    n = L // c
+    n_l, L_l = n // world, L // world
+    _, dev = make_device_inputs(w, seed=0, device=device)          # same full inputs on every rank, then sliced
+    kc, vc, xq, ss, sd = dev
+    sc, sr = slice(rank * n_l, (rank + 1) * n_l), slice(rank * L_l, (rank + 1) * L_l)
+    loc = [kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(), ss[:, :, sc].contiguous(),
+           sd[:, :, sr].contiguous()]
+    del dev, kc, vc, xq, ss, sd
+    gen = torch.Generator(device=device).manual_seed(99 + rank)
+    g_out_cm = torch.randn(B, H, n, R, L_l, D, generator=gen, device=device, dtype=torch.bfloat16)
+    g_lse_cm = torch.randn(B, H, n, R, L_l, generator=gen, device=device)
+    g_out, g_den = ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm)
+
+    def step():
+        out, denom, lse = sp_forward(*loc)
+        return sp_backward(*loc, g_out, g_den)
+
+    for _ in range(W):
+        step()
+    dist.barrier(); torch.cuda.synchronize()
+    sampler = ClockSampler(device.index)
+    if rank == 0:
+        sampler.start()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(K):
+        step()
+    b.record()
+    dist.barrier(); torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    tt = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = tt.item() / K
+    if rank == 0:
+        f_fwd, f_bwd = flops(w)
+        peaks, src = load_peaks()
+        line = {"metric": METRIC, "value": B * L / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
+                "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
+                "data": "synthetic",
+                "config": {"workload": f"{args.workload}: one sequence B={B} H_kv={H} R={R} L={L} chunk={c} D={D} bf16 fwd+bwd, rows "
+                                       f"sharded contiguously over {world} rank(s), random upstream grads, masked-block grads included",
+                           "global_batch": B, "seq_len": L,
+                           "parallelism": f"sequence-chunk x{world}: all-gather K/V/src, all-gather decay totals and dC totals, "
+                                          "all-reduce dK/dV/dsrc (NCCL)",
+                           "l2_policy": "working set exceeds L2"},
+                "tflops": (f_fwd + f_bwd) / (ms * 1e-3) / 1e12,
+                "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] * world),
+                "clocks": clocks, "peak_source": src}
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -196,6 +261,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--skip-masked-grads", action="store_true",
                     help="device-resident step without the gradient through fully masked blocks (valid when SMVecMatMul is upstream)")
+    ap.add_argument("--mode", default="bh", choices=["bh", "sp"],
+                    help="bh: every rank runs its own batch shard (default); sp: ONE long sequence sharded by rows over "
+                         "the ranks with NCCL exchange of keys and decay carries (use --workload long)")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture run: honour --warmup below 3; the printed numbers are not bench values")
     args = ap.parse_args()
@@ -226,6 +294,9 @@ def main():
         dist.init_process_group("nccl", device_id=device)
 
     W, K = (args.warmup if args.profile else max(args.warmup, 3)), max(args.steps, 1)
+    if args.mode == "sp":
+        run_sequence_parallel(args, w, rank, world, device, W, K)
+        return
     host, dev = make_device_inputs(w, seed=rank, device=device)
     kc, vc, xq, ss, sd = dev
     B, H, R, L, c, D = w["B"], w["H"], w["R"], w["L"], w["c"], w["D"]

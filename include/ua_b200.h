@@ -136,53 +136,56 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
                 void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
 
-/* Sequence-chunk sharding of the forward (long contexts: one GPU owns a contiguous range of row
- * tiles of 128 rows).  The reference has no multi-device code; these entry points are what a
- * sequence-parallel caller needs on top of ua_fwd.  Supported where the tensor-core forward is
- * (bf16, chunk 128, head_dim 64 or 128); UA_ERR_UNSUPPORTED otherwise.
+/* ---- Sequence-chunk sharding (long contexts).  No counterpart in the reference, which is single-device. ----
  *
- *   ua_fwd_rows            forward for the row tiles [row_tile_begin, row_tile_end) only.  kc, vc and
- *                          static_src cover the WHOLE sequence (all n chunks); xq_rows (b,h,r,Lr,d),
- *                          static_dest_rows (b,h,Lr), out_cm_rows (b,h,n,r,Lr,d), lse_cm_rows and
- *                          denom_cm_rows (b,h,n,r,Lr) hold just the Lr = 128 * (end - begin) rows of the
- *                          range.  carry_in (b,h,n,128) fp32, may be NULL (= zeros): for every key, the sum
- *                          of its log-retention over all rows BEFORE the range, i.e. what the ranks that
- *                          own the earlier rows computed with ua_decay_totals_rows.
- *   ua_decay_totals_rows   decay-only pass over the same range: total_out (b,h,n,128) = carry_in (or 0) +
- *                          the sum of every key's log-retention over the rows of the range.  Cheap (no
- *                          values, queries or outputs); ranks run it first, exchange the totals, and form
- *                          their carry_in as the sum of the totals of the ranks before them. */
-int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+ * A rank owns one or more contiguous ranges of row tiles (128 rows each) and computes those rows against ALL key
+ * chunks.  kc, vc and static_src always cover the whole sequence.  The row-indexed tensors (xq_rows (b,h,r,Ls,d),
+ * static_dest_rows (b,h,Ls), out_cm_rows (b,h,n,r,Ls,d), lse/denom_cm_rows (b,h,n,r,Ls), and in the backward
+ * g_out_cm_rows, g_denom_cm_rows, dxq_rows_f32, ddest_rows_f32) hold "slabs" of Ls = rows_total rows, in which the
+ * range occupies the rows [row_offset, row_offset + 128 * (tile_end - tile_begin)); several ranges (e.g. the two halves
+ * of a zig-zag assignment) can share the slabs.  Tensor-core shapes only: bf16, chunk 128, head_dim 64 or 128 forward,
+ * head_dim 64 backward; UA_ERR_UNSUPPORTED otherwise.
+ *
+ *   ua_decay_totals_rows  decay-only pass: total_out (b,h,n,128) = carry_in (or 0) + the sum of every key's
+ *                         log-retention over the rows of the range.  Ranks run it first and exchange the totals.
+ *   ua_fwd_rows           forward for the rows of the range; carry_in (b,h,n,128) fp32 or NULL (= zeros): per key,
+ *                         the sum of its log-retention over ALL rows before the range (= sum of the totals of the
+ *                         ranges before it).
+ *   ua_bwd_rows           gradients of everything the rows of the range touch, ADDED into caller-zeroed fp32 buffers:
+ *                         dk_f32, dv_f32 (b,h,L,d), dsrc_f32 (b,h,L) cover ALL keys (partial sums, to be added over the
+ *                         ranges / ranks); dxq_rows_f32 (b,h,r,Ls,d), ddest_rows_f32 (b,h,Ls) the rows of the range.
+ *                         carry_in as above.  suffix_in (b,h,n,128) or NULL: reverse decay carry entering from later
+ *                         rows.  dctot_out (b,h,n,128) or NULL (overwritten): per key, the sum of the decay-prefix
+ *                         gradient dC over the rows of the range -- what the ranges before it need.
+ *   ua_bwd_rows_suffix    every gradient is linear in the reverse carry: after exchanging the dctot tables,
+ *                         suffix = sum of dctot over the ranges AFTER this one, and this decay-only pass adds what it
+ *                         induces into dk_f32, dsrc_f32 and ddest_rows_f32 (no queries, values or upstream gradients).
+ * Workspace: 256 bytes, except ua_bwd_rows: ua_bwd_rows_workspace_bytes(). */
+typedef struct UaRows {
+  int32_t tile_begin;   /* first row tile of the range (global tile index) */
+  int32_t tile_end;     /* one past the last */
+  int32_t rows_total;   /* Ls: rows per slab of the row-indexed tensors */
+  int32_t row_offset;   /* row of the slab where the range starts (multiple of 128) */
+} UaRows;
+
+int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
+                         const void* kc, const void* static_src, const void* static_dest_rows,
+                         const float* carry_in, float* total_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                 const void* kc, const void* vc, const void* xq_rows,
                 const void* static_src, const void* static_dest_rows, const float* carry_in,
                 void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
-int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
-                         const void* kc, const void* static_src, const void* static_dest_rows,
-                         const float* carry_in, float* total_out,
-                         void* workspace, size_t workspace_bytes, void* stream);
-
-/* Sequence-chunk sharding of the backward (bf16, chunk 128, head_dim 64).  No counterpart in the reference.
- * A rank that owns the row tiles [row_tile_begin, row_tile_end) runs
- *   1. ua_bwd_rows: gradients of everything its rows touch.  Row-indexed tensors (xq_rows, static_dest_rows,
- *      g_out_cm_rows (b,h,n,r,Lr,d), g_denom_cm_rows (b,h,n,r,Lr), dxq_rows, ddest_rows_f32 (b,h,Lr)) hold the Lr rows
- *      of the range; dk_f32, dv_f32 (b,h,L,d) and dsrc_f32 (b,h,L) are fp32, cover ALL keys and are this rank's PARTIAL
- *      sums (overwritten; the caller adds them over the ranks).  carry_in as for ua_fwd_rows.  suffix_in (b,h,n,128) or
- *      NULL: reverse decay carry entering from later rows.  dctot_out (b,h,n,128) or NULL: per key, the sum of the
- *      decay-prefix gradient dC over the rows of the range -- what the ranks owning EARLIER rows need.
- *   2. after exchanging the dctot tables: suffix = sum of dctot of the ranks that own later rows, and
- *      ua_bwd_rows_suffix ADDS the gradient that this suffix induces (every gradient is linear in it) into dk_f32,
- *      dsrc_f32 and ddest_rows_f32: a decay-only pass, no queries, values or upstream gradients involved.
- * Workspace: ua_bwd_rows_workspace_bytes() for ua_bwd_rows, 256 bytes for ua_bwd_rows_suffix. */
-size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype, int row_tile_begin, int row_tile_end);
-int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype);
+int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                 const void* kc, const void* vc, const void* xq_rows,
                 const void* static_src, const void* static_dest_rows,
                 const void* g_out_cm_rows, const void* g_denom_cm_rows, int g_denom_dtype,
                 const float* carry_in, const float* suffix_in,
-                float* dk_f32, float* dv_f32, void* dxq_rows, float* dsrc_f32, float* ddest_rows_f32, float* dctot_out,
+                float* dk_f32, float* dv_f32, float* dxq_rows_f32, float* dsrc_f32, float* ddest_rows_f32, float* dctot_out,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
-int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
+int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                        const void* kc, const void* vc, const void* static_src, const void* static_dest_rows,
                        const float* suffix, float* dk_f32, float* dsrc_f32, float* ddest_rows_f32,
                        void* workspace, size_t workspace_bytes, void* stream);

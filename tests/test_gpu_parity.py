@@ -338,9 +338,73 @@ def test_backward_over_row_ranges_matches_whole_backward(ranges, skip):
             ops.backward_rows_suffix(kc, vc, ss, sd[:, :, b * 128:e * 128], b, e, suffix, part[0], part[3], part[4])
     dk = sum(p[0] for p in parts).view(kc.shape)
     dv = sum(p[1] for p in parts).view(vc.shape)
-    dxq = torch.cat([p[2] for p in parts], dim=3)
+    dxq = torch.cat([p[2] for p in parts], dim=3).to(torch.bfloat16)
     dsrc = sum(p[3] for p in parts).view(ss.shape)
     ddest = torch.cat([p[4] for p in parts], dim=2)
     for got, want, key in zip((dk, dv, dxq, dsrc, ddest), ref, GRADS):
         assert torch.isfinite(got.float()).all(), key
+        assert rel_fro(got.float().cpu(), want.float().cpu()) <= 1e-2, (key, rel_fro(got.float().cpu(), want.float().cpu()))
+
+
+def test_two_row_ranges_sharing_slabs_zigzag_style():
+    """One owner of the row-tile blocks {0, 3} and another of {1, 2} (the zig-zag assignment of two ranks), every owner
+    with its two blocks in shared slabs (row_offset): forward and backward against the whole-sequence kernels."""
+    from universal_attention_triton_b200 import ops
+    shape = (1, 1, 2, 1024, 128, 64)
+    B, H, R, L, c, D = shape
+    n, nb = L // c, 2                                       # 4 blocks of 2 tiles
+    ins, _ = _bf16_case(*shape, seed=81)
+    kc, vc, xq, ss, sd = _cuda(*ins)
+    gen = torch.Generator(device="cuda").manual_seed(10)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    out_full, lse_full, _ = ops.forward_cm(kc, vc, xq, ss, sd)
+    ref = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse)
+    owners = [[0, 3], [1, 2]]
+    rows_of = lambda blks: torch.cat([torch.arange(p * nb * 128, (p + 1) * nb * 128) for p in blks]).cuda()
+    # decay totals of every block, carries in block order
+    totals = {}
+    for blks in owners:
+        sd_l = sd[:, :, rows_of(blks)]
+        for li, p in enumerate(blks):
+            totals[p] = ops.decay_totals_rows(kc, ss, sd_l, p * nb, (p + 1) * nb, row_offset=li * nb * 128)
+    carries, run = {}, torch.zeros_like(totals[0])
+    for p in range(4):
+        carries[p] = run
+        run = run + totals[p]
+    results = []
+    for blks in owners:
+        idx = rows_of(blks)
+        xq_l, sd_l = xq[:, :, :, idx].contiguous(), sd[:, :, idx].contiguous()
+        out = ops.alloc_forward_rows(kc, xq_l)
+        for li, p in enumerate(blks):
+            ops.forward_rows_cm(kc, vc, xq_l, ss, sd_l, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * 128, out=out)
+        assert ((out[1] - lse_full[:, :, :, :, idx]).abs() <= 1e-3 + 1e-6 * lse_full[:, :, :, :, idx].abs()).all()
+        err = (out[0].float() - out_full[:, :, :, :, idx].float()).abs()
+        assert (err <= 2e-2 + out_full[:, :, :, :, idx].float().abs() * 2.0 ** -7).all()
+        acc = ops.alloc_backward_rows(kc, xq_l)
+        go, gl = g_out[:, :, :, :, idx].contiguous(), g_lse[:, :, :, :, idx].contiguous()
+        dct = {}
+        for li, p in enumerate(blks):
+            dct[p] = ops.backward_rows(kc, vc, xq_l, ss, sd_l, go, gl, p * nb, (p + 1) * nb, carry_in=carries[p],
+                                       row_offset=li * nb * 128, acc=acc)[5]
+        results.append((blks, idx, sd_l, acc, dct))
+    all_dct = {}
+    for r_ in results:
+        all_dct.update(r_[4])
+    for blks, idx, sd_l, acc, _ in results:
+        for li, p in enumerate(blks):
+            if p < 3:
+                suffix = sum([all_dct[q] for q in range(p + 1, 4)], torch.zeros_like(all_dct[0]))
+                ops.backward_rows_suffix(kc, vc, ss, sd_l, p * nb, (p + 1) * nb, suffix, acc[0], acc[3], acc[4],
+                                         row_offset=li * nb * 128)
+    dk = sum(r_[3][0] for r_ in results).view(kc.shape)
+    dv = sum(r_[3][1] for r_ in results).view(vc.shape)
+    dsrc = sum(r_[3][3] for r_ in results).view(ss.shape)
+    dxq = torch.empty_like(xq, dtype=torch.float32)
+    ddest = torch.empty_like(sd, dtype=torch.float32)
+    for blks, idx, sd_l, acc, _ in results:
+        dxq[:, :, :, idx] = acc[2]
+        ddest[:, :, idx] = acc[4]
+    for got, want, key in zip((dk, dv, dxq, dsrc, ddest), ref, GRADS):
         assert rel_fro(got.float().cpu(), want.float().cpu()) <= 1e-2, (key, rel_fro(got.float().cpu(), want.float().cpu()))

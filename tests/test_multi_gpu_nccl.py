@@ -19,7 +19,7 @@ def _free_port():
     return p
 
 
-def _sp_worker(rank, world, port, ret):
+def _sp_worker(rank, world, port, ret, zigzag):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
@@ -30,11 +30,14 @@ def _sp_worker(rank, world, port, ret):
     B, H, R, L, c, D = 1, 2, 2, 1024, 128, 64
     ins = [t.cuda() for t in O.make_inputs(B, H, R, L, c, D, dtype=torch.bfloat16, seed=61)]
     kc, vc, xq, ss, sd = ins
+    from universal_attention_triton_b200.sequence_parallel import owned_blocks
     n = L // c
-    n_l, L_l = n // world, L // world
-    sc, sr = slice(rank * n_l, (rank + 1) * n_l), slice(rank * L_l, (rank + 1) * L_l)
+    P, mine = owned_blocks(world, rank, zigzag)
+    nb = n // P
+    sc = torch.cat([torch.arange(p * nb, (p + 1) * nb) for p in mine]).cuda()
+    sr = torch.cat([torch.arange(p * nb * c, (p + 1) * nb * c) for p in mine]).cuda()
     out, denom, lse = sp_forward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
-                                 ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous())
+                                 ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(), zigzag=zigzag)
     out_cm, lse_cm, _ = ops.forward_cm(kc, vc, xq, ss, sd)
     ref_out = ops.as_reference_out(out_cm)[:, :, :, sr]
     ref_lse = ops.as_reference_denom(lse_cm)[:, :, :, sr]
@@ -49,7 +52,7 @@ def _sp_worker(rank, world, port, ret):
     want = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse)
     got = sp_backward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
                       ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(),
-                      ops.as_reference_out(g_out)[:, :, :, sr], ops.as_reference_denom(g_lse)[:, :, :, sr])
+                      ops.as_reference_out(g_out)[:, :, :, sr], ops.as_reference_denom(g_lse)[:, :, :, sr], zigzag=zigzag)
     want_local = (want[0][:, :, sc], want[1][:, :, sc], want[2][:, :, :, sr], want[3][:, :, sc], want[4][:, :, sr])
     for a, b_ in zip(got, want_local):
         rel = ((a.float() - b_.float()).norm() / b_.float().norm().clamp_min(1e-20)).item()
@@ -88,9 +91,10 @@ def _bh_worker(rank, world, port, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_sequence_sharded_forward_and_backward_two_gpus():
+@pytest.mark.parametrize("zigzag", [False, True])
+def test_sequence_sharded_forward_and_backward_two_gpus(zigzag):
     ret = mp.Manager().dict()
-    mp.spawn(_sp_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    mp.spawn(_sp_worker, args=(2, _free_port(), ret, zigzag), nprocs=2, join=True)
     assert ret["ok"] == 1
 
 

@@ -21,12 +21,18 @@ class UaDims(ctypes.Structure):
                 ("n_chunks", ctypes.c_int32), ("chunk", ctypes.c_int32), ("head_dim", ctypes.c_int32)]
 
 
+class UaRows(ctypes.Structure):
+    _fields_ = [("tile_begin", ctypes.c_int32), ("tile_end", ctypes.c_int32), ("rows_total", ctypes.c_int32),
+                ("row_offset", ctypes.c_int32)]
+
+
 class UaLibraryError(RuntimeError):
     pass
 
 
 _vp, _i, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t
 _dp = ctypes.POINTER(UaDims)
+_rp = ctypes.POINTER(UaRows)
 
 # name -> (restype, argtypes); every symbol include/ua_b200.h declares
 SIGNATURES = {
@@ -39,11 +45,11 @@ SIGNATURES = {
     "ua_carry_bytes": (_sz, [_dp, _i, _i]),
     "ua_fwd_keep": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_bwd_kept": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "ua_fwd_rows": (_i, [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "ua_decay_totals_rows": (_i, [_dp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
-    "ua_bwd_rows_workspace_bytes": (_sz, [_dp, _i, _i, _i]),
-    "ua_bwd_rows": (_i, [_dp, _i, _i, _i, _i] + [_vp] * 7 + [_i] + [_vp] * 9 + [_sz, _i, _vp]),
-    "ua_bwd_rows_suffix": (_i, [_dp, _i, _i, _i, _i] + [_vp] * 9 + [_sz, _vp]),
+    "ua_fwd_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "ua_decay_totals_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "ua_bwd_rows_workspace_bytes": (_sz, [_dp, _i]),
+    "ua_bwd_rows": (_i, [_dp, _i, _i, _rp] + [_vp] * 7 + [_i] + [_vp] * 9 + [_sz, _i, _vp]),
+    "ua_bwd_rows_suffix": (_i, [_dp, _i, _i, _rp] + [_vp] * 9 + [_sz, _vp]),
     "ua_static_scratch_bytes": (_sz, []),
     "ua_bwd_static": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ua_static_status": (_i, [_vp]),

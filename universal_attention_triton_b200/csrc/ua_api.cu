@@ -243,17 +243,21 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
 }
 
 namespace {
-int check_rows(const ua::Shape& s, int dtype, int tile_begin, int tile_end) {
-  if (!ua::sm100::fwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
-  if (tile_begin < 0 || tile_end > s.N || tile_begin >= tile_end) return UA_ERR_BAD_DIMS;
+// Row range [tile_begin, tile_end) placed at row `row_offset` of slabs of `rows_total` rows.
+int check_rows(const ua::Shape& s, bool ok_shape, const UaRows* rows) {
+  if (!rows) return UA_ERR_NULL_POINTER;
+  if (!ok_shape) return UA_ERR_UNSUPPORTED;
+  if (rows->tile_begin < 0 || rows->tile_end > s.N || rows->tile_begin >= rows->tile_end) return UA_ERR_BAD_DIMS;
+  const int len = (rows->tile_end - rows->tile_begin) * 128;
+  if (rows->row_offset < 0 || rows->row_offset % 128 != 0 || rows->rows_total < rows->row_offset + len) return UA_ERR_BAD_DIMS;
   return UA_OK;
 }
 }  // namespace
 
-int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end, const void* kc,
-                const void* vc, const void* xq_rows, const void* static_src, const void* static_dest_rows,
-                const float* carry_in, void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, void* workspace,
-                size_t workspace_bytes, int flags, void* stream) {
+int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
+                const void* xq_rows, const void* static_src, const void* static_dest_rows, const float* carry_in,
+                void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, void* workspace, size_t workspace_bytes,
+                int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -261,21 +265,21 @@ int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begi
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq_rows) || !aligned16(out_cm_rows)) return UA_ERR_ALIGNMENT;
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   ua::Shape s = to_shape(dims);
-  if ((e = check_rows(s, dtype, row_tile_begin, row_tile_end))) return e;
+  if ((e = check_rows(s, ua::sm100::fwd_supported(s, dtype), rows))) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
   ua::sm100::FwdParams fp;
   fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows;
   fp.out = static_cast<bf16*>(out_cm_rows); fp.lse = lse_cm_rows; fp.denom = static_cast<bf16*>(denom_cm_rows);
   fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
-  fp.j_begin = row_tile_begin; fp.j_end = row_tile_end; fp.Lr = (row_tile_end - row_tile_begin) * 128;
+  fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
   fp.carry_in = carry_in; fp.total_out = nullptr;
   return ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq_rows, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
 }
 
-int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
-                         const void* kc, const void* static_src, const void* static_dest_rows, const float* carry_in,
-                         float* total_out, void* workspace, size_t workspace_bytes, void* stream) {
+int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc,
+                         const void* static_src, const void* static_dest_rows, const float* carry_in, float* total_out,
+                         void* workspace, size_t workspace_bytes, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -283,92 +287,69 @@ int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, int row_
   if (!aligned16(kc)) return UA_ERR_ALIGNMENT;
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   ua::Shape s = to_shape(dims);
-  if ((e = check_rows(s, dtype, row_tile_begin, row_tile_end))) return e;
+  if ((e = check_rows(s, ua::sm100::fwd_supported(s, dtype), rows))) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
   ua::sm100::FwdParams fp;
   fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
   fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
-  fp.j_begin = row_tile_begin; fp.j_end = row_tile_end; fp.Lr = (row_tile_end - row_tile_begin) * 128;
+  fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
   fp.carry_in = carry_in; fp.total_out = total_out;
   return ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st);
 }
 
-namespace {
-struct RowsWs { size_t off_dq, off_carry, total; };
-RowsWs rows_ws(const ua::Shape& s, int tile_begin, int tile_end) {
-  RowsWs w;
-  const size_t BH = (size_t)s.B * s.H, f = sizeof(float), Lr = (size_t)(tile_end - tile_begin) * 128;
-  size_t o = 256;
-  w.off_dq = o; o = align_up(o + BH * s.R * Lr * s.D * f, 256);
-  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 128 * f, 256);
-  w.total = o;
-  return w;
-}
-}  // namespace
-
-size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype, int row_tile_begin, int row_tile_end) {
+size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
-  if (!ua::sm100::bwd_supported(s, dtype) || row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return 0;
-  return rows_ws(s, row_tile_begin, row_tile_end).total;
+  if (!ua::sm100::bwd_supported(s, dtype)) return 0;
+  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 128 * sizeof(float), 256);      // status | decay-prefix table
 }
 
-int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end, const void* kc,
-                const void* vc, const void* xq_rows, const void* static_src, const void* static_dest_rows,
-                const void* g_out_cm_rows, const void* g_denom_cm_rows, int g_denom_dtype, const float* carry_in,
-                const float* suffix_in, float* dk_f32, float* dv_f32, void* dxq_rows, float* dsrc_f32,
-                float* ddest_rows_f32, float* dctot_out, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
+                const void* xq_rows, const void* static_src, const void* static_dest_rows, const void* g_out_cm_rows,
+                const void* g_denom_cm_rows, int g_denom_dtype, const float* carry_in, const float* suffix_in,
+                float* dk_f32, float* dv_f32, float* dxq_rows_f32, float* dsrc_f32, float* ddest_rows_f32,
+                float* dctot_out, void* workspace, size_t workspace_bytes, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
   if (g_denom_dtype != UA_F32 && g_denom_dtype != dtype) return UA_ERR_BAD_DTYPE;
   if (!kc || !vc || !xq_rows || !static_src || !static_dest_rows || !g_out_cm_rows || !g_denom_cm_rows || !dk_f32 || !dv_f32 ||
-      !dxq_rows || !dsrc_f32 || !ddest_rows_f32)
+      !dxq_rows_f32 || !dsrc_f32 || !ddest_rows_f32)
     return UA_ERR_NULL_POINTER;
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq_rows) || !aligned16(g_out_cm_rows) || !aligned16(dk_f32) ||
-      !aligned16(dv_f32) || !aligned16(dxq_rows))
+      !aligned16(dv_f32) || !aligned16(dxq_rows_f32))
     return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
-  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
-  if (row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return UA_ERR_BAD_DIMS;
-  const RowsWs w = rows_ws(s, row_tile_begin, row_tile_end);
-  if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  if ((e = check_rows(s, ua::sm100::bwd_supported(s, dtype), rows))) return e;
+  const size_t need = ua_bwd_rows_workspace_bytes(dims, dtype);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
-  const size_t BH = (size_t)s.B * s.H, Lr = (size_t)(row_tile_end - row_tile_begin) * 128;
-  if (cudaMemsetAsync(ws, 0, w.off_carry, st) != cudaSuccess) return UA_ERR_CUDA;                       // status + dQ accumulator
-  if (cudaMemsetAsync(dk_f32, 0, BH * s.L * s.D * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
-  if (cudaMemsetAsync(dv_f32, 0, BH * s.L * s.D * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
-  if (cudaMemsetAsync(dsrc_f32, 0, BH * s.L * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
-  if (cudaMemsetAsync(ddest_rows_f32, 0, BH * Lr * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
   ua::sm100::BwdParams bp;
   bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
   bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-  float* carry_tab = reinterpret_cast<float*>(ws + w.off_carry);
+  float* carry_tab = reinterpret_cast<float*>(ws + 256);
   bp.carry = carry_tab;
-  bp.acc_dk = dk_f32; bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq); bp.acc_dt = ddest_rows_f32;
+  bp.acc_dk = dk_f32; bp.acc_dq = dxq_rows_f32; bp.acc_dt = ddest_rows_f32;
   bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
   bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-  bp.j_begin = row_tile_begin; bp.j_end = row_tile_end; bp.Lr = (int)Lr;
+  bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
   bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0;
-  e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
-  if (e) return e;
-  return convert_any(dtype, bp.acc_dq, dxq_rows, BH * s.R * Lr * s.D, st);
+  return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
 }
 
-int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, int row_tile_begin, int row_tile_end,
-                       const void* kc, const void* vc, const void* static_src, const void* static_dest_rows,
-                       const float* suffix, float* dk_f32, float* dsrc_f32, float* ddest_rows_f32, void* workspace,
-                       size_t workspace_bytes, void* stream) {
+int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
+                       const void* static_src, const void* static_dest_rows, const float* suffix, float* dk_f32,
+                       float* dsrc_f32, float* ddest_rows_f32, void* workspace, size_t workspace_bytes, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
   if (!kc || !vc || !static_src || !static_dest_rows || !suffix || !dk_f32 || !dsrc_f32 || !ddest_rows_f32) return UA_ERR_NULL_POINTER;
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(dk_f32)) return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
-  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
-  if (row_tile_begin < 0 || row_tile_end > s.N || row_tile_begin >= row_tile_end) return UA_ERR_BAD_DIMS;
+  if ((e = check_rows(s, ua::sm100::bwd_supported(s, dtype), rows))) return e;
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
@@ -376,7 +357,7 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, int row_ti
   bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows; bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
   bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
   bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
-  bp.j_begin = row_tile_begin; bp.j_end = row_tile_end; bp.Lr = (row_tile_end - row_tile_begin) * 128;
+  bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
   bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
 }

@@ -48,10 +48,11 @@ struct BwdParams {
   int skip_masked;
   // Row range (sequence sharding): only the row tiles [j_begin, j_end) are swept; xq, static_dest, g_out, g_denom,
   // acc_dq and acc_dt then hold just those Lr = 128 * (j_end - j_begin) rows.  Keys, values, static_src, acc_dk whole.
-  int j_begin, j_end, Lr;
+  int j_begin, j_end, Lr;  // Lr: rows per slab of the row-indexed tensors
+  int r0;                  // row of the slab where the range starts
   const float* suffix_in;  // optional (b*h*n, 128): reverse decay carry entering from the rows after the range
   float* dctot_out;        // optional (b*h*n, 128): per key, sum of dC over the rows of the range (what earlier ranges need)
-  float* acc_dv;           // optional (b*h, L, 64) fp32: dV_i is stored here instead of dvc
+  float* acc_dv;           // optional (b*h, L, 64) fp32: dV_i is ADDED here instead of written to dvc
   float* acc_ds;           // optional (b*h, L) fp32: d static_src is added here instead of written to dss
   int decay_only;          // correction pass: only the decay gradient that suffix_in induces (no heads, no dV)
 };
@@ -128,8 +129,8 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
   // shared-memory slot frees up only pays L2 latency.
   auto coords = [&](int T, int r, int& qrow, int& grow) {
     const int j = c.tile_j(T, N);
-    qrow = (c.bh * R + r) * p.Lr + (j - p.j_begin) * 128;
-    grow = (int)((chunk_id * R + r) * p.Lr + (size_t)(j - p.j_begin) * 128);
+    qrow = (c.bh * R + r) * p.Lr + p.r0 + (j - p.j_begin) * 128;
+    grow = (int)((chunk_id * R + r) * p.Lr + p.r0 + (size_t)(j - p.j_begin) * 128);
   };
   int rc = 0;
   for (int T = 0; T < c.ntiles; ++T) {
@@ -394,17 +395,17 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     const bool valid = T < c.nvalid;
     const int j = c.tile_j(T, N);
     const bool diag = (j == c.i);
-    const int jl = j - p.j_begin;                 // row tile index inside the range
+    const int rl = p.r0 + (j - p.j_begin) * 128;  // first row of the tile inside the slab
     float* t3buf = sT3 + (T & 1) * 128;
 
     if (valid && p.decay_only) {
-      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + jl * 128 + tid));
+      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + rl + tid));
       mb.sync();
       if (!mb.ok) return;
     }
     if (valid && !p.decay_only) {
       // ---- decay prefix (forward recomputation): thread = key, C^T[row][key] to shared memory ----
-      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + jl * 128 + tid));
+      if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + rl + tid));
       const float carry = p.carry[(chunk_id * N + j) * 128 + tid];
       mb.sync();                                  // t3 visible; every reader of the previous tile's C^T is done
       UA_PH(0)
@@ -452,7 +453,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     }
 
     for (int r = 0; r < R; ++r, ++rc) {
-      const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)jl * 128 + tid;
+      const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
       const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
       if (!c.wait_w(bSdpFull, rc)) return;
@@ -554,7 +555,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bRDone, rc)) return;
       UA_PH(5)
       tc_fence_after();
-      drain_x1(p.acc_dq + (((size_t)c.bh * Rq + r) * p.Lr + (size_t)jl * 128 + tid) * 64);
+      drain_x1(p.acc_dq + (((size_t)c.bh * Rq + r) * p.Lr + (size_t)rl + tid) * 64);
       UA_PH(6)
     }
 
@@ -630,7 +631,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       {
         const float colsum = warp_transpose_reduce(dcs, lane);
         const float t3l = t3buf[col0 + lane];
-        if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + jl * 128 + col0 + lane, colsum / (3.0f * t3l * t3l));
+        if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + rl + col0 + lane, colsum / (3.0f * t3l * t3l));
       }
       // the suffix carried to the next (lower) tile is d ell at the tile's first row
       if (!p.decay_only) {
@@ -659,11 +660,11 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
       tc_wait_ld();
       if (p.acc_dv) {
-        float4* dst = reinterpret_cast<float4*>(p.acc_dv + krow * 64 + 16 * part);
+        float* dst = p.acc_dv + krow * 64 + 16 * part;          // several row ranges may add to the same keys
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-          dst[u] = make_float4(__uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]), __uint_as_float(o[u * 4 + 2]),
-                               __uint_as_float(o[u * 4 + 3]));
+          red_add_v4(dst + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]), __uint_as_float(o[u * 4 + 2]),
+                     __uint_as_float(o[u * 4 + 3]));
       } else {
         uint32_t pk[8];
 #pragma unroll

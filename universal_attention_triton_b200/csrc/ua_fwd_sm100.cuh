@@ -46,7 +46,8 @@ struct FwdParams {
   int fill_masked;       // write the rows before the key chunk (uniform softmax) from the two otherwise idle warps
   // Row range (sequence sharding): this call computes row tiles [j_begin, j_end) only.  xq, static_dest, out,
   // lse and denom then hold just those Lr = (j_end - j_begin) * 128 rows; keys, values and static_src are whole.
-  int j_begin, j_end, Lr;
+  int j_begin, j_end, Lr;  // Lr: rows per (chunk, head) slab of the row-indexed tensors
+  int r0;                  // row of the slab where the range starts (several ranges can share one slab)
   const float* carry_in;   // optional (b*h*n, 128): decay prefix of key k at its first row tile of the range
   float* total_out;        // optional (b*h*n, 128): decay prefix after the last row tile of the range
   float* carry;          // optional (required in carry-only mode): (b*h*n, n, 128) decay prefix of key k at the start of row tile j
@@ -139,7 +140,7 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
       mbar_expect_tx(c.bar(kQFull + qs), Cfg::kTileBytes);
       for (int b = 0; b < Cfg::kBoxes; ++b)
         tma_load_2d(sbase + Cfg::oQ + qs * Cfg::kTileBytes + b * Cfg::kBoxBytes, tmQ, b * 64,
-                    (c.bh * R + r) * p.Lr + (c.j0 + T - p.j_begin) * 128, c.bar(kQFull + qs));
+                    (c.bh * R + r) * p.Lr + p.r0 + (c.j0 + T - p.j_begin) * 128, c.bar(kQFull + qs));
       if (r == 0 && T + 1 < c.ntiles && !load_kj(T + 1)) return;
     }
   }
@@ -237,7 +238,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   for (int T = 0; T < c.ntiles; ++T) {
     const int j = c.j0 + T;
     float* t3buf = sT3 + (T & 1) * 128;
-    t3buf[k] = cbrtf(Num<TG>::ld(sd + (j - p.j_begin) * 128 + k));
+    t3buf[k] = cbrtf(Num<TG>::ld(sd + p.r0 + (j - p.j_begin) * 128 + k));
     c.arrive_w(kT3Ready);
     if (!c.wait_w(kT3Ready, T)) return;
     if (!c.wait_w(kGFull, T)) return;
@@ -355,7 +356,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       tc_wait_st();
       tc_fence_before();
       c.arrive_w(kPReady + sb);
-      const int qg = (c.j0 + T - p.j_begin) * 128 + row;      // row index inside the range
+      const int qg = p.r0 + (c.j0 + T - p.j_begin) * 128 + row;      // row index inside the slab
       const float lse = m + lg2(l) * kLn2;
       const size_t orow = (chunk_id * R + r) * p.Lr + qg;
       p.lse[orow] = lse;
@@ -410,13 +411,13 @@ __device__ __forceinline__ void fwd_fill_rows(const FwdCtx<D>& c, const FwdParam
   constexpr int kVecPerRow = D / 8;                    // 16-byte vectors
   const uint4 mine = reinterpret_cast<const uint4*>(vmean)[t % kVecPerRow];   // 64 % kVecPerRow == 0: fixed per thread
   for (int r = 0; r < R; ++r) {
-    uint4* o = reinterpret_cast<uint4*>(p.out + ((chunk_id * R + r) * p.Lr) * D);
+    uint4* o = reinterpret_cast<uint4*>(p.out + ((chunk_id * R + r) * p.Lr + p.r0) * D);
     const size_t nvec = (size_t)rows * kVecPerRow;
     for (size_t e = t; e < nvec; e += 64) o[e] = mine;
-    float* lr = p.lse + (chunk_id * R + r) * p.Lr;
+    float* lr = p.lse + (chunk_id * R + r) * p.Lr + p.r0;
     for (int q = t; q < rows; q += 64) {
       lr[q] = mask_value();
-      if (p.denom) p.denom[(chunk_id * R + r) * p.Lr + q] = __float2bfloat16_rn(mask_value());
+      if (p.denom) p.denom[(chunk_id * R + r) * p.Lr + p.r0 + q] = __float2bfloat16_rn(mask_value());
     }
   }
 }

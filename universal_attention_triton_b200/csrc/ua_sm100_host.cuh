@@ -46,7 +46,7 @@ inline bool fwd_supported(const Shape& s, int dtype) {
 
 // Fills the row-range fields of FwdParams for a call over the whole sequence.
 inline void whole_sequence(FwdParams& p) {
-  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.carry_in = nullptr; p.total_out = nullptr;
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.carry_in = nullptr; p.total_out = nullptr;
 }
 
 // Forward (kCarryOnly = false) or decay-only pass (kCarryOnly = true: no values, queries or outputs) over the row
@@ -87,7 +87,7 @@ inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 &
 
 // Fills the row-range / sharding fields of BwdParams for a call over the whole sequence.
 inline void whole_sequence(BwdParams& p) {
-  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.suffix_in = nullptr; p.dctot_out = nullptr;
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
   p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0;
 }
 
@@ -109,7 +109,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     FwdParams fp;
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
     fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
-    fp.j_begin = p.j_begin; fp.j_end = p.j_end; fp.Lr = p.Lr; fp.carry_in = carry_in; fp.total_out = nullptr;
+    fp.j_begin = p.j_begin; fp.j_end = p.j_end; fp.Lr = p.Lr; fp.r0 = p.r0; fp.carry_in = carry_in; fp.total_out = nullptr;
     int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
     if (e) return e;
   }

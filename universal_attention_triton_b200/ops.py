@@ -231,62 +231,76 @@ def merge_bwd_cm(out_cm, lse_cm, g_merged, skip_zero_weight_blocks: bool = False
     return g_out_cm, g_lse_cm
 
 
-# ---- sequence-chunk sharding: forward over a range of row tiles ------------------------------------
+# ---- sequence-chunk sharding: forward / backward over a range of row tiles ---------------------------
+# Row-indexed tensors are "slabs" of Ls rows (Ls = xq_rows.shape[3]); the range [tile_begin, tile_end) sits at
+# row `row_offset` of the slabs, so that several ranges (zig-zag halves) can share them.
 
-def decay_totals_rows(kc, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None):
-    """(b,h,n,128) fp32: for every key, ``carry_in`` (or 0) plus the sum of its log-retention over the
-    rows of the row tiles [tile_begin, tile_end).  ``kc`` / ``static_src`` cover the whole sequence,
-    ``static_dest_rows`` (b,h,Lr) only the rows of the range."""
+def _rows(tile_begin, tile_end, rows_total, row_offset):
+    return _lib.UaRows(tile_begin, tile_end, rows_total, row_offset)
+
+
+def _gates_rows(static_src, static_dest_rows, b, h, L, dt):
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest_rows.reshape(b, h, -1), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    return ss, sd
+
+
+def decay_totals_rows(kc, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None, row_offset: int = 0):
+    """(b,h,n,128) fp32: for every key, ``carry_in`` (or 0) plus the sum of its log-retention over the rows of
+    the row tiles [tile_begin, tile_end).  ``static_dest_rows`` (b,h,Ls) is a slab holding the range at ``row_offset``."""
     _require_cuda(kc, static_src, static_dest_rows)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
     dt = kc.dtype
     code = _dtype_code(dt)
     kc = kc.contiguous()
-    L, Lr = n * c, (tile_end - tile_begin) * 128
-    ss = _gate_cast(static_src.reshape(b, h, L), dt)
-    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
-    if ss.dtype != sd.dtype:
-        ss, sd = ss.float(), sd.float()
+    ss, sd = _gates_rows(static_src, static_dest_rows, b, h, n * c, dt)
     dims = UaDims(b, h, 1, n, c, d)
+    rows = _rows(tile_begin, tile_end, sd.shape[-1], row_offset)
     with torch.cuda.device(kc.device):
         total = torch.empty(b, h, n, 128, dtype=torch.float32, device=kc.device)
         ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
         ci = carry_in.float().contiguous() if carry_in is not None else None
-        rc = lib.ua_decay_totals_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(ss),
+        rc = lib.ua_decay_totals_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(ss),
                                       _ptr(sd), _ptr(ci), _ptr(total), _ptr(ws), 256, _stream())
         _lib.check(rc, "ua_decay_totals_rows")
         _check_status(lib, ws, "ua_decay_totals_rows")
     return total
 
 
+def alloc_forward_rows(kc, xq_rows):
+    """Output slabs for ``forward_rows_cm``: (out_cm (b,h,n,r,Ls,d), lse_cm fp32 (b,h,n,r,Ls), denom_cm)."""
+    b, h, n, c, d = kc.shape
+    r, Ls = xq_rows.shape[2], xq_rows.shape[3]
+    dev, dt = kc.device, xq_rows.dtype
+    return (torch.empty(b, h, n, r, Ls, d, dtype=dt, device=dev), torch.empty(b, h, n, r, Ls, dtype=torch.float32, device=dev),
+            torch.empty(b, h, n, r, Ls, dtype=dt, device=dev))
+
+
 def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None,
-                    flags: int = 0):
-    """Forward for the row tiles [tile_begin, tile_end): returns (out_cm (b,h,n,r,Lr,d), lse_cm fp32 (b,h,n,r,Lr),
-    denom_cm).  ``kc``, ``vc``, ``static_src`` cover the whole sequence; ``xq_rows`` (b,h,r,Lr,d) and
-    ``static_dest_rows`` (b,h,Lr) the rows of the range; ``carry_in`` (b,h,n,128) as from ``decay_totals_rows``
-    summed over the earlier ranges."""
+                    flags: int = 0, row_offset: int = 0, out=None):
+    """Forward for the row tiles [tile_begin, tile_end), written into the rows [row_offset, ...) of the output slabs
+    ``out`` (from ``alloc_forward_rows``; allocated here when None).  ``kc``, ``vc``, ``static_src`` cover the whole
+    sequence; ``xq_rows`` (b,h,r,Ls,d) / ``static_dest_rows`` (b,h,Ls) are slabs; ``carry_in`` (b,h,n,128): sum of the
+    ``decay_totals_rows`` of all rows before the range."""
     _require_cuda(kc, vc, xq_rows, static_src, static_dest_rows)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
-    r = xq_rows.shape[2]
+    r, Ls = xq_rows.shape[2], xq_rows.shape[3]
     dt = xq_rows.dtype
     code = _dtype_code(dt)
-    L, Lr = n * c, (tile_end - tile_begin) * 128
     kc, vc = kc.contiguous(), vc.contiguous()
-    q = xq_rows.reshape(b, h, r, Lr, d).contiguous()
-    ss = _gate_cast(static_src.reshape(b, h, L), dt)
-    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
-    if ss.dtype != sd.dtype:
-        ss, sd = ss.float(), sd.float()
+    q = xq_rows.contiguous()
+    ss, sd = _gates_rows(static_src, static_dest_rows, b, h, n * c, dt)
     dims = UaDims(b, h, r, n, c, d)
+    rows = _rows(tile_begin, tile_end, Ls, row_offset)
     with torch.cuda.device(kc.device):
-        out_cm = torch.empty(b, h, n, r, Lr, d, dtype=dt, device=kc.device)
-        lse_cm = torch.empty(b, h, n, r, Lr, dtype=torch.float32, device=kc.device)
-        denom_cm = torch.empty(b, h, n, r, Lr, dtype=dt, device=kc.device)
+        out_cm, lse_cm, denom_cm = out if out is not None else alloc_forward_rows(kc, q)
         ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
         ci = carry_in.float().contiguous() if carry_in is not None else None
-        rc = lib.ua_fwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc), _ptr(q),
+        rc = lib.ua_fwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
                              _ptr(ss), _ptr(sd), _ptr(ci), _ptr(out_cm), _ptr(lse_cm), _ptr(denom_cm), _ptr(ws), 256, flags,
                              _stream())
         _lib.check(rc, "ua_fwd_rows")
@@ -294,70 +308,70 @@ def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: i
     return out_cm, lse_cm, denom_cm
 
 
+def alloc_backward_rows(kc, xq_rows):
+    """Zeroed fp32 accumulators for ``backward_rows``: (dk (b,h,L,d), dv (b,h,L,d), dxq (b,h,r,Ls,d), dsrc (b,h,L),
+    ddest (b,h,Ls))."""
+    b, h, n, c, d = kc.shape
+    r, Ls = xq_rows.shape[2], xq_rows.shape[3]
+    z = lambda *shape: torch.zeros(*shape, dtype=torch.float32, device=kc.device)
+    return z(b, h, n * c, d), z(b, h, n * c, d), z(b, h, r, Ls, d), z(b, h, n * c), z(b, h, Ls)
+
+
 def backward_rows(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows, tile_begin: int,
-                  tile_end: int, carry_in=None, suffix_in=None, flags: int = 0):
-    """Backward for the row tiles [tile_begin, tile_end) (sequence sharding).  Returns
-    ``(dk_f32 (b,h,L,d), dv_f32 (b,h,L,d), dxq_rows, dsrc_f32 (b,h,L), ddest_rows_f32 (b,h,Lr), dctot (b,h,n,128))``:
-    the key-side gradients are this range's partial sums over ALL keys, in fp32, to be added over the ranges."""
+                  tile_end: int, carry_in=None, suffix_in=None, flags: int = 0, row_offset: int = 0, acc=None):
+    """Backward for the row tiles [tile_begin, tile_end) (sequence sharding), ADDED into the fp32 accumulators ``acc``
+    (from ``alloc_backward_rows``; allocated here when None).  Returns ``(dk, dv, dxq, dsrc, ddest, dctot)``: dk, dv,
+    dsrc are partial sums over ALL keys; dctot (b,h,n,128) is the per-key sum of the decay-prefix gradient over the rows."""
     _require_cuda(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
-    r = xq_rows.shape[2]
+    r, Ls = xq_rows.shape[2], xq_rows.shape[3]
     dt = xq_rows.dtype
     code = _dtype_code(dt)
-    L, Lr = n * c, (tile_end - tile_begin) * 128
     kc, vc = kc.contiguous(), vc.contiguous()
-    q = xq_rows.reshape(b, h, r, Lr, d).contiguous()
-    ss = _gate_cast(static_src.reshape(b, h, L), dt)
-    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
-    if ss.dtype != sd.dtype:
-        ss, sd = ss.float(), sd.float()
+    q = xq_rows.contiguous()
+    ss, sd = _gates_rows(static_src, static_dest_rows, b, h, n * c, dt)
     g_out_cm_rows = g_out_cm_rows.to(dt).contiguous()
     if g_denom_cm_rows.dtype not in (torch.float32, dt):
         g_denom_cm_rows = g_denom_cm_rows.float()
     g_denom_cm_rows = g_denom_cm_rows.contiguous()
     dims = UaDims(b, h, r, n, c, d)
+    rows = _rows(tile_begin, tile_end, Ls, row_offset)
     dev = kc.device
     with torch.cuda.device(dev):
-        dk = torch.empty(b, h, L, d, dtype=torch.float32, device=dev)
-        dv = torch.empty(b, h, L, d, dtype=torch.float32, device=dev)
-        dsrc = torch.empty(b, h, L, dtype=torch.float32, device=dev)
-        ddest = torch.empty(b, h, Lr, dtype=torch.float32, device=dev)
-        dxq = torch.empty_like(q)
+        dk, dv, dxq, dsrc, ddest = acc if acc is not None else alloc_backward_rows(kc, q)
         dctot = torch.empty(b, h, n, 128, dtype=torch.float32, device=dev)
-        ws_bytes = lib.ua_bwd_rows_workspace_bytes(ctypes.byref(dims), code, tile_begin, tile_end)
+        ws_bytes = lib.ua_bwd_rows_workspace_bytes(ctypes.byref(dims), code)
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
         ci = carry_in.float().contiguous() if carry_in is not None else None
         si = suffix_in.float().contiguous() if suffix_in is not None else None
-        rc = lib.ua_bwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc), _ptr(q),
+        rc = lib.ua_bwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
                              _ptr(ss), _ptr(sd), _ptr(g_out_cm_rows), _ptr(g_denom_cm_rows), _dtype_code(g_denom_cm_rows.dtype),
                              _ptr(ci), _ptr(si), _ptr(dk), _ptr(dv), _ptr(dxq), _ptr(dsrc), _ptr(ddest), _ptr(dctot),
                              _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_bwd_rows")
         _check_status(lib, ws, "ua_bwd_rows")
-    return dk, dv, dxq.view(xq_rows.shape), dsrc, ddest, dctot
+    return dk, dv, dxq, dsrc, ddest, dctot
 
 
-def backward_rows_suffix(kc, vc, static_src, static_dest_rows, tile_begin: int, tile_end: int, suffix, dk, dsrc, ddest):
-    """Adds to ``dk``, ``dsrc``, ``ddest`` (fp32, as returned by ``backward_rows``) the gradient induced by the reverse
-    decay carry ``suffix`` (b,h,n,128) that enters the range from the rows after it."""
+def backward_rows_suffix(kc, vc, static_src, static_dest_rows, tile_begin: int, tile_end: int, suffix, dk, dsrc, ddest,
+                         row_offset: int = 0):
+    """Adds to ``dk``, ``dsrc``, ``ddest`` (the fp32 accumulators of ``backward_rows``) the gradient induced by the
+    reverse decay carry ``suffix`` (b,h,n,128) that enters the range from the rows after it."""
     _require_cuda(kc, vc, static_src, static_dest_rows, suffix, dk, dsrc, ddest)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
     dt = kc.dtype
     code = _dtype_code(dt)
-    L, Lr = n * c, (tile_end - tile_begin) * 128
     kc, vc = kc.contiguous(), vc.contiguous()
-    ss = _gate_cast(static_src.reshape(b, h, L), dt)
-    sd = _gate_cast(static_dest_rows.reshape(b, h, Lr), dt)
-    if ss.dtype != sd.dtype:
-        ss, sd = ss.float(), sd.float()
+    ss, sd = _gates_rows(static_src, static_dest_rows, b, h, n * c, dt)
     assert dk.is_contiguous() and dsrc.is_contiguous() and ddest.is_contiguous()
     dims = UaDims(b, h, 1, n, c, d)
+    rows = _rows(tile_begin, tile_end, sd.shape[-1], row_offset)
     with torch.cuda.device(kc.device):
         ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
         sf = suffix.float().contiguous()
-        rc = lib.ua_bwd_rows_suffix(ctypes.byref(dims), code, _dtype_code(ss.dtype), tile_begin, tile_end, _ptr(kc), _ptr(vc),
+        rc = lib.ua_bwd_rows_suffix(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc),
                                     _ptr(ss), _ptr(sd), _ptr(sf), _ptr(dk), _ptr(dsrc), _ptr(ddest), _ptr(ws), 256, _stream())
         _lib.check(rc, "ua_bwd_rows_suffix")
         _check_status(lib, ws, "ua_bwd_rows_suffix")

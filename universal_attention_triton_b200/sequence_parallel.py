@@ -1,31 +1,30 @@
-"""Sequence-chunk sharding of the forward for long contexts.
+"""Sequence-chunk sharding of the operator for long contexts (one process per GPU, NCCL through
+``torch.distributed``).
 
-Every rank owns a contiguous, equally long slice of the sequence (a whole number of 128-row
-tiles) of all five inputs.  What crosses ranks (NCCL over NVLink through ``torch.distributed``):
+The sequence is cut into P equal blocks of whole 128-row tiles.  With the contiguous assignment P = G
+and rank g owns block g; with the zig-zag assignment P = 2G and rank g owns blocks g and 2G-1-g, which
+balances the causal work (a row sees all earlier keys, so late blocks are the expensive ones).  A rank's
+local tensors are its blocks concatenated along the sequence, for all five inputs.
 
-1. all-gather of the keys, values and ``static_src`` (small next to ``out``: the output of one
-   (b, h) is n times larger than its keys);
-2. the decay carry: every rank sums, for every key of the sequence, the log-retention over its
-   own rows (``decay_totals_rows``, a decay-only pass), the (b,h,n,128) totals are all-gathered,
-   and a rank's carry is the sum of the totals of the ranks before it.
+What crosses ranks:
+
+1. all-gather of the keys, values and ``static_src`` (small next to ``out``: the output of one (b, h)
+   is n times larger than its keys);
+2. the decay carry: for every block, its owner sums every key's log-retention over the block's rows
+   (``decay_totals_rows``, a decay-only pass); the (b,h,n,128) totals are all-gathered and a block's
+   carry-in is the sum of the totals of the blocks before it;
+3. (backward) the reverse decay carry runs from later rows to earlier ones, but every gradient is
+   LINEAR in it, so nobody waits: each block's backward runs with a zero reverse carry and also returns
+   the per-key sum of the decay-prefix gradient over its rows (``dctot``); these are all-gathered, a
+   block's reverse carry is the sum over the blocks AFTER it, and a decay-only correction pass adds the
+   gradient it induces;
+4. (backward) dK, dV, d static_src -- fp32 partial sums over a rank's rows for ALL keys -- are
+   all-reduced and every rank keeps the slice of its own keys.  dQ and d static_dest are row-local.
 
 The per-(row, key-chunk) softmax statistics need no exchange with the reference's output format:
-``denom[row, chunk]`` is complete on the rank that owns the row (it is itself the partial
-log-sum-exp that a later merge over chunks consumes).
-
-The prefix a row sees is then  carry(ranks before) + prefix inside the rank's own rows, which is
-the single-GPU value up to the association of the fp32 sums.
-
-Backward (``sp_backward``, bf16 / head_dim 64): the reverse decay carry runs from later rows to
-earlier ones, but every gradient is LINEAR in it, so no rank waits for another:
-
-3. every rank runs the backward of its own rows with a zero reverse carry and also returns, per
-   key, the sum of the decay-prefix gradient over its rows (``dctot``);
-4. the (b,h,n,128) ``dctot`` tables are all-gathered; a rank's reverse carry is the sum over the
-   ranks AFTER it, and a decay-only correction pass adds the gradient that this carry induces;
-5. the key-side gradients (dK, dV, d static_src: partial sums over the rank's rows for all keys)
-   are summed over the ranks (all-reduce) and every rank keeps the slice of its own keys; dQ and
-   d static_dest are row-local.
+``denom[row, chunk]`` is complete on the rank that owns the row (it is itself the partial log-sum-exp
+that a later merge over chunks consumes).  Results equal the single-GPU ones up to the association of
+the fp32 carry sums.
 """
 from __future__ import annotations
 
@@ -39,78 +38,113 @@ class CudaBackend:
     """The CUDA library (default)."""
     decay_totals_rows = staticmethod(ops.decay_totals_rows)
     forward_rows_cm = staticmethod(ops.forward_rows_cm)
+    alloc_forward_rows = staticmethod(ops.alloc_forward_rows)
     backward_rows = staticmethod(ops.backward_rows)
     backward_rows_suffix = staticmethod(ops.backward_rows_suffix)
+    alloc_backward_rows = staticmethod(ops.alloc_backward_rows)
 
 
-def _all_gather_cat(t, dim, group):
+def owned_blocks(world: int, rank: int, zigzag: bool):
+    """(P, [blocks of this rank in local order])."""
+    if zigzag:
+        return 2 * world, [rank, 2 * world - 1 - rank]
+    return world, [rank]
+
+
+def _gather_sequence(t_local, dim, group, zigzag):
+    """All-gather a tensor whose axis `dim` holds this rank's blocks, and put the blocks in sequence order."""
     world = dist.get_world_size(group)
-    parts = [torch.empty_like(t) for _ in range(world)]
-    dist.all_gather(parts, t.contiguous(), group=group)
-    return torch.cat(parts, dim=dim)
+    parts = [torch.empty_like(t_local) for _ in range(world)]
+    dist.all_gather(parts, t_local.contiguous(), group=group)
+    if not zigzag:
+        return torch.cat(parts, dim=dim)
+    P = 2 * world
+    blocks = [None] * P
+    for g, t in enumerate(parts):
+        first, second = t.chunk(2, dim=dim)
+        blocks[g], blocks[P - 1 - g] = first, second
+    return torch.cat(blocks, dim=dim)
 
 
-def sp_forward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, group=None, backend=CudaBackend):
-    """kc/vc_local (b,h,n_l,128,d), xq_local (b,h,r,L_l,d), static_src_local (b,h,n_l,128),
-    static_dest_local (b,h,L_l): this rank's slice of the sequence, ``L_l = n_l * 128``, same on every rank.
+def _gather_block_tables(tables, world, rank, zigzag, group):
+    """tables: list (one per owned block, local order) of (b,h,n,128) tensors -> list of P tensors in block order."""
+    stacked = torch.stack(tables)
+    parts = [torch.empty_like(stacked) for _ in range(world)]
+    dist.all_gather(parts, stacked, group=group)
+    P, _ = owned_blocks(world, rank, zigzag)
+    out = [None] * P
+    for g in range(world):
+        _, blks = owned_blocks(world, g, zigzag)
+        for li, p in enumerate(blks):
+            out[p] = parts[g][li]
+    return out
+
+
+def _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backend, zigzag):
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    P, mine = owned_blocks(world, rank, zigzag)
+    nb = kc_local.shape[2] // len(mine)                      # tiles (= key chunks of 128) per block
+    kc = _gather_sequence(kc_local, 2, group, zigzag)
+    vc = _gather_sequence(vc_local, 2, group, zigzag)
+    ss = _gather_sequence(static_src_local, 2, group, zigzag)
+    sd = static_dest_local.reshape(static_dest_local.shape[0], static_dest_local.shape[1], -1)
+    rows_b = nb * kc.shape[3]                               # rows per block (row tile = key chunk = 128 rows on the GPU)
+    totals = [backend.decay_totals_rows(kc, ss, sd, p * nb, (p + 1) * nb, row_offset=li * rows_b) for li, p in enumerate(mine)]
+    all_tot = _gather_block_tables(totals, world, rank, zigzag, group)
+    carries = []
+    run = torch.zeros_like(all_tot[0])
+    for p in range(P):                                       # fixed order: every rank forms the same partial sums
+        carries.append(run)
+        run = run + all_tot[p]
+    return world, rank, P, mine, nb, kc, vc, ss, sd, carries
+
+
+def sp_forward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, group=None, backend=CudaBackend,
+               zigzag: bool = False):
+    """kc/vc_local (b,h,n_l,128,d), xq_local (b,h,r,L_l,d), static_src_local (b,h,n_l,128), static_dest_local (b,h,L_l):
+    this rank's blocks of the sequence (``L_l = n_l * 128``, same on every rank; two blocks when ``zigzag``).
     Returns ``(out, denom, lse)`` for the rank's rows against ALL key chunks, in the reference's shapes
     ``(b,h,r,L_l,d,n)`` / ``(b,h,r,L_l,n)`` (permuted views; ``lse`` is the fp32 denom)."""
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    n_l = kc_local.shape[2]
-    kc = _all_gather_cat(kc_local, 2, group)
-    vc = _all_gather_cat(vc_local, 2, group)
-    ss = _all_gather_cat(static_src_local, 2, group)
-    begin, end = rank * n_l, (rank + 1) * n_l
-    totals = backend.decay_totals_rows(kc, ss, static_dest_local, begin, end)
-    parts = [torch.empty_like(totals) for _ in range(world)]
-    dist.all_gather(parts, totals, group=group)
-    carry = torch.zeros_like(totals)
-    for g in range(rank):                     # fixed order: every rank forms the same partial sums
-        carry = carry + parts[g]
-    out_cm, lse_cm, denom_cm = backend.forward_rows_cm(kc, vc, xq_local, ss, static_dest_local, begin, end, carry)
+    world, rank, P, mine, nb, kc, vc, ss, sd, carries = _setup(kc_local, vc_local, static_src_local, static_dest_local,
+                                                                group, backend, zigzag)
+    xq = xq_local.contiguous()
+    out = backend.alloc_forward_rows(kc, xq)
+    for li, p in enumerate(mine):
+        backend.forward_rows_cm(kc, vc, xq, ss, sd, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * kc.shape[3], out=out)
+    out_cm, lse_cm, denom_cm = out
     return ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm), ops.as_reference_denom(lse_cm)
 
 
-def _carry_before(totals, rank, group):
-    world = dist.get_world_size(group)
-    parts = [torch.empty_like(totals) for _ in range(world)]
-    dist.all_gather(parts, totals, group=group)
-    carry = torch.zeros_like(totals)
-    for g in range(rank):
-        carry = carry + parts[g]
-    return carry
-
-
 def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, g_out_local, g_denom_local,
-                group=None, backend=CudaBackend, skip_masked_grads: bool = False):
+                group=None, backend=CudaBackend, zigzag: bool = False, skip_masked_grads: bool = False):
     """Gradients of the sequence-sharded operator.  Inputs as for ``sp_forward``; ``g_out_local (b,h,r,L_l,d,n)`` and
     ``g_denom_local (b,h,r,L_l,n)`` are the upstream gradients of the rank's rows (any strides).  Returns
-    ``(dkc, dvc, dxq, dstatic_src, dstatic_dest)`` for the rank's own slice, shaped and typed like the local inputs."""
+    ``(dkc, dvc, dxq, dstatic_src, dstatic_dest)`` for the rank's own blocks, shaped and typed like the local inputs."""
     from . import _lib
-    world = dist.get_world_size(group)
-    rank = dist.get_rank(group)
-    n_l = kc_local.shape[2]
-    kc = _all_gather_cat(kc_local, 2, group)
-    vc = _all_gather_cat(vc_local, 2, group)
-    ss = _all_gather_cat(static_src_local, 2, group)
-    begin, end = rank * n_l, (rank + 1) * n_l
-    carry = _carry_before(backend.decay_totals_rows(kc, ss, static_dest_local, begin, end), rank, group)
+    world, rank, P, mine, nb, kc, vc, ss, sd, carries = _setup(kc_local, vc_local, static_src_local, static_dest_local,
+                                                                group, backend, zigzag)
     flags = _lib.FLAG_SKIP_MASKED_GRADS if skip_masked_grads else 0
-    dk, dv, dxq, dsrc, ddest, dctot = backend.backward_rows(
-        kc, vc, xq_local, ss, static_dest_local, ops.out_to_chunk_major(g_out_local), ops.denom_to_chunk_major(g_denom_local),
-        begin, end, carry_in=carry, flags=flags)
-    parts = [torch.empty_like(dctot) for _ in range(world)]
-    dist.all_gather(parts, dctot, group=group)
-    if rank + 1 < world:
-        suffix = torch.zeros_like(dctot)
-        for g in range(rank + 1, world):
-            suffix = suffix + parts[g]
-        backend.backward_rows_suffix(kc, vc, ss, static_dest_local, begin, end, suffix, dk, dsrc, ddest)
+    xq = xq_local.contiguous()
+    g_out_cm = ops.out_to_chunk_major(g_out_local)
+    g_den_cm = ops.denom_to_chunk_major(g_denom_local)
+    acc = backend.alloc_backward_rows(kc, xq)
+    dctots = []
+    for li, p in enumerate(mine):
+        res = backend.backward_rows(kc, vc, xq, ss, sd, g_out_cm, g_den_cm, p * nb, (p + 1) * nb, carry_in=carries[p],
+                                    flags=flags, row_offset=li * nb * kc.shape[3], acc=acc)
+        dctots.append(res[5])
+    dk, dv, dxq, dsrc, ddest = acc
+    all_dct = _gather_block_tables(dctots, world, rank, zigzag, group)
+    for li, p in enumerate(mine):
+        if p + 1 < P:
+            suffix = torch.zeros_like(all_dct[0])
+            for q in range(p + 1, P):
+                suffix = suffix + all_dct[q]
+            backend.backward_rows_suffix(kc, vc, ss, sd, p * nb, (p + 1) * nb, suffix, dk, dsrc, ddest, row_offset=li * nb * kc.shape[3])
     for t in (dk, dv, dsrc):
         dist.all_reduce(t, group=group)
-    b, h, n, c, d = kc.shape
-    keys = slice(begin * c, end * c)
-    return (dk[:, :, keys].reshape(kc_local.shape).to(kc_local.dtype), dv[:, :, keys].reshape(vc_local.shape).to(vc_local.dtype),
-            dxq, dsrc[:, :, keys].reshape(static_src_local.shape).to(static_src_local.dtype),
+    c = kc.shape[3]
+    pick = lambda t: torch.cat([t[:, :, p * nb * c:(p + 1) * nb * c] for p in mine], dim=2)
+    return (pick(dk).reshape(kc_local.shape).to(kc_local.dtype), pick(dv).reshape(vc_local.shape).to(vc_local.dtype),
+            dxq.reshape(xq_local.shape).to(xq_local.dtype), pick(dsrc).reshape(static_src_local.shape).to(static_src_local.dtype),
             ddest.reshape(static_dest_local.shape).to(static_dest_local.dtype))
