@@ -189,10 +189,11 @@ def run_reference(args, w, rank):
 
 
 def run_sequence_parallel(args, w, rank, world, device, W, K):
-    """One long sequence, rows sharded contiguously over the ranks (strong scaling): sp_forward + sp_backward."""
+    """One long sequence, rows sharded over the ranks (strong scaling): sp_forward + sp_backward.  Contiguous blocks by
+    default; --zigzag gives rank g the blocks g and 2G-1-g, which balances the causal work."""
     import torch.distributed as dist
     from universal_attention_triton_b200 import ops
-    from universal_attention_triton_b200.sequence_parallel import sp_backward, sp_forward
+    from universal_attention_triton_b200.sequence_parallel import owned_blocks, sp_backward, sp_forward
     if world == 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ.setdefault("MASTER_PORT", "29533")
@@ -202,9 +203,11 @@ def run_sequence_parallel(args, w, rank, world, device, W, K):
     n_l, L_l = n // world, L // world
     _, dev = make_device_inputs(w, seed=0, device=device)          # same full inputs on every rank, then sliced
     kc, vc, xq, ss, sd = dev
-    sc, sr = slice(rank * n_l, (rank + 1) * n_l), slice(rank * L_l, (rank + 1) * L_l)
-    loc = [kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(), ss[:, :, sc].contiguous(),
-           sd[:, :, sr].contiguous()]
+    P, mine = owned_blocks(world, rank, args.zigzag)
+    nb = n // P                                                   # key chunks per block
+    cat_n = lambda t: torch.cat([t[:, :, p * nb:(p + 1) * nb] for p in mine], dim=2).contiguous()
+    loc = [cat_n(kc), cat_n(vc), torch.cat([xq[:, :, :, p * nb * c:(p + 1) * nb * c] for p in mine], dim=3).contiguous(),
+           cat_n(ss), torch.cat([sd[:, :, p * nb * c:(p + 1) * nb * c] for p in mine], dim=2).contiguous()]
     del dev, kc, vc, xq, ss, sd
     gen = torch.Generator(device=device).manual_seed(99 + rank)
     g_out_cm = torch.randn(B, H, n, R, L_l, D, generator=gen, device=device, dtype=torch.bfloat16)
@@ -212,8 +215,8 @@ def run_sequence_parallel(args, w, rank, world, device, W, K):
     g_out, g_den = ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm)
 
     def step():
-        out, denom, lse = sp_forward(*loc)
-        return sp_backward(*loc, g_out, g_den)
+        out, denom, lse = sp_forward(*loc, zigzag=args.zigzag)
+        return sp_backward(*loc, g_out, g_den, zigzag=args.zigzag)
 
     for _ in range(W):
         step()
@@ -238,7 +241,7 @@ def run_sequence_parallel(args, w, rank, world, device, W, K):
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
                 "data": "synthetic",
                 "config": {"workload": f"{args.workload}: one sequence B={B} H_kv={H} R={R} L={L} chunk={c} D={D} bf16 fwd+bwd, rows "
-                                       f"sharded contiguously over {world} rank(s), random upstream grads, masked-block grads included",
+                                       f"sharded {'zig-zag' if args.zigzag else 'contiguously'} over {world} rank(s), random upstream grads, masked-block grads included",
                            "global_batch": B, "seq_len": L,
                            "parallelism": f"sequence-chunk x{world}: all-gather K/V/src, all-gather decay totals and dC totals, "
                                           "all-reduce dK/dV/dsrc (NCCL)",
@@ -259,6 +262,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--zigzag", action="store_true", help="with --mode sp: balanced block assignment")
     ap.add_argument("--skip-masked-grads", action="store_true",
                     help="device-resident step without the gradient through fully masked blocks (valid when SMVecMatMul is upstream)")
     ap.add_argument("--mode", default="bh", choices=["bh", "sp"],

@@ -21,8 +21,10 @@
 //   G again (recomputed rather than kept, TMEM is full), decay group: reverse scan
 //   of dC, d log-retention -> d affinity -> dG (bf16, shared memory), d src, d dest
 //   dK_j = dG^T K_i     dK_i += dG K_j
-// dQ_rj and dK_j leave through fp32 red.global (other key chunks add to the same
-// rows); dV_i, dK_i and d src stay in TMEM / registers until the sweep ends.
+// dQ_rj and dK_j are added to fp32 global accumulators (other key chunks add to the
+// same rows): the tile is staged in shared memory and leaves as a TMA reduce-add, which
+// runs behind the next phase; dV_i, dK_i and d src stay in TMEM / registers until the
+// sweep ends.
 //
 // TMEM (512 columns): X0 [0,128) G / S_r | X1 [128,256) dP_r, then dQ_r / dK_j |
 //                     XC [256,384) dC | dV [384,448) | dK_i [448,512)
@@ -74,7 +76,7 @@ struct BwdCfg {
 
 enum BwdBar {
   bKvFull = 0, bKjFull, bInFull, bGFull, bX0Free, bSdpFull, bX1Free, bCReady, bCsFree, bPdsReady, bRDone, bG2Full,
-  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bNumBars
+  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bNumBars
 };
 
 struct BwdCtx {
@@ -309,6 +311,7 @@ struct Mailbox {
     slot[(part * 3 + 0) * 128 + tid] = mine.x;
     slot[(part * 3 + 1) * 128 + tid] = mine.y;
     slot[(part * 3 + 2) * 128 + tid] = mine.z;
+    if (part == 0 && tid == 0) bulk_wait_read_all();   // see drain_x1: the staging buffer is rewritten after a rendezvous
     c->arrive_w(bXchg);
     if (!c->wait_w(bXchg, n)) ok = false;
 #pragma unroll
@@ -317,6 +320,7 @@ struct Mailbox {
     ++n;
   }
   __device__ __forceinline__ void sync() {
+    if (part == 0 && tid == 0) bulk_wait_read_all();
     c->arrive_w(bXchg);
     if (!c->wait_w(bXchg, n)) ok = false;
     ++n;
@@ -345,7 +349,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 }
 
 template <typename TG>
-__device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part) {
+__device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part, const CUtensorMap* tmDQ,
+                                           const CUtensorMap* tmDK) {
   const int L = p.s.L, R = p.decay_only ? 0 : p.s.R, N = p.s.N, Rq = p.s.R;
   const int tid = threadIdx.x & 127, lane = threadIdx.x & 31;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
@@ -377,17 +382,32 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
           make_uint4(v[u * 4], v[u * 4 + 1], v[u * 4 + 2], v[u * 4 + 3]);
     }
   };
-  // 16 of the 64 accumulator columns of X1 (dQ_rj or dK_j), row `tid`, added to global fp32 rows
-  auto drain_x1 = [&](float* dst_row) {
+  // The 128 x 64 fp32 tile in X1 (dQ_rj or dK_j) is added to rows [y, y+128) of a global accumulator: every thread
+  // moves 16 columns of row `tid` into the (idle) P buffer as two 128-byte-swizzled [128][32] boxes, and once all 16
+  // warps have arrived the group leader issues two TMA reduce-adds.  The buffer is rewritten only after a mailbox
+  // rendezvous, before which the leader waits until the reduce has read it.
+  int nstage = 0;
+  auto drain_x1 = [&](const CUtensorMap* tm, int y) -> bool {
     uint32_t o[16];
     tmem_ld16(X1 + 16 * part, o);
     tc_wait_ld();
     tc_fence_before();
     c.arrive_w(bX1Free);
-#pragma unroll
-    for (int u = 0; u < 4; ++u)
-      red_add_v4(dst_row + 16 * part + u * 4, __uint_as_float(o[u * 4]), __uint_as_float(o[u * 4 + 1]),
-                 __uint_as_float(o[u * 4 + 2]), __uint_as_float(o[u * 4 + 3]));
+    store_row(sP, o);
+    fence_proxy_async();
+    c.arrive_w(bStage);
+    bool ok = true;
+    if (part == 0 && tid == 0) {
+      ok = c.wait(bStage, nstage);
+      if (ok) {
+        tma_reduce_add_2d(tm, 0, y, smem_u32(sP));
+        tma_reduce_add_2d(tm, 32, y, smem_u32(sP) + 16384);
+        bulk_commit_group();
+      }
+    }
+    __syncwarp();
+    ++nstage;
+    return ok;
   };
 
   int rc = 0;
@@ -555,7 +575,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bRDone, rc)) return;
       UA_PH(5)
       tc_fence_after();
-      drain_x1(p.acc_dq + (((size_t)c.bh * Rq + r) * p.Lr + (size_t)rl + tid) * 64);
+      drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl);
       UA_PH(6)
     }
 
@@ -644,7 +664,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bDkjFull, T)) return;
       UA_PH(9)
       tc_fence_after();
-      drain_x1(p.acc_dk + ((size_t)c.bh * L + (size_t)j * 128 + tid) * 64);      // dK_j
+      drain_x1(tmDK, c.bh * L + j * 128);      // dK_j
       UA_PH(10)
     }
   }
@@ -698,7 +718,8 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
 template <typename TG>
 __global__ void __launch_bounds__(640, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-           const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG, BwdParams p) {
+           const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
+           const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK, BwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + BwdCfg::oMisc);
@@ -725,12 +746,13 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     misc[1] = 0;
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
-      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg) count = 16;   // one arrival per worker warp
+      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage) count = 16;   // one arrival per worker warp
       if (b == bSdpFull || b == bRDone || b == bDkjFull || b == bFinal) count = 2;                       // one commit per MMA issuer
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
     prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmQ); prefetch_tmap(&tmG);
+    prefetch_tmap(&tmDQ); prefetch_tmap(&tmDK);
   }
   // identity tile: 16 rows x 64 bf16 (128-byte swizzled rows), ones on the diagonal of the first 16 columns
   for (int e = threadIdx.x; e < 512; e += blockDim.x) reinterpret_cast<uint32_t*>(smem + BwdCfg::oI)[e] = 0u;
@@ -758,7 +780,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) bwd_mma(c, p, warp - 1);
   } else if (warp >= 4) {
-    bwd_worker<TG>(c, p, (warp - 4) >> 2);
+    bwd_worker<TG>(c, p, (warp - 4) >> 2, &tmDQ, &tmDK);
+    if (threadIdx.x == 128) bulk_wait_all();      // the leader's reduce-adds have landed before the block retires
   }
 
   tc_fence_before();

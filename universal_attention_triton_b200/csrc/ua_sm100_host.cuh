@@ -40,6 +40,21 @@ inline bool make_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int
   return r == CUDA_SUCCESS;
 }
 
+// 2-D fp32 tensor [rows][64] row-major (the dQ / dK accumulators), boxes of 128 rows x 32 floats, 128-byte swizzle:
+// the target of the backward kernel's shared-memory -> global reductions.
+inline bool make_f32_rows_map(CUtensorMap* map, const void* base, uint64_t rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t gdim[2] = {64, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {256};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 inline bool fwd_supported(const Shape& s, int dtype) {
   return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128);
 }
@@ -97,9 +112,12 @@ inline void whole_sequence(BwdParams& p) {
 template <typename TG>
 int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const BwdParams& p,
                  float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
-  CUtensorMap tmK, tmV, tmQ, tmG;
+  CUtensorMap tmK, tmV, tmQ, tmG, tmDQ, tmDK;
   const uint64_t BH = (uint64_t)s.B * s.H;
   if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64)) return UA_ERR_CUDA;
+  if (!make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L)) return UA_ERR_CUDA;
+  if (p.decay_only) tmDQ = tmDK;   // no query gradient in the correction pass
+  else if (!make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr)) return UA_ERR_CUDA;
   if (p.decay_only) {
     tmQ = tmK; tmG = tmK;          // the correction pass touches neither queries nor upstream gradients
   } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * p.Lr, 64)) {
@@ -115,7 +133,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
   }
   auto kern = bwd_kernel<TG>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, p);
+  kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
