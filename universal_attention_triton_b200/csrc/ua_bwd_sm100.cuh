@@ -21,6 +21,14 @@
 //   G again (recomputed rather than kept, TMEM is full), decay group: reverse scan
 //   of dC, d log-retention -> d affinity -> dG (bf16, shared memory), d src, d dest
 //   dK_j = dG^T K_i     dK_i += dG K_j
+// Rows before the chunk (j < i): every score is -1e12 there, the softmax is uniform (P = 1/128) and
+//   dS[k][q] = ( (v_k - vbar) . g_q + gd_q ) / 128      (g = dO row, gd = g_denom, vbar = mean of the chunk's values)
+// is of rank <= 65, so nothing is done per (key, row) pair.  With E = a [128][64] tile whose column 0 holds gd:
+//   dQ_rj    = [g | E] [ M_i ; ksum_i ] / 128,   M_i = sum_k (v_k - vbar)^T k_k  (64 x 64, once per block)
+//   N_i     += [g | E]^T Q_rj                    (64 x 64 plus the row  w = sum_q gd_q q_q ; accumulates in TMEM)
+//   dV_i    += (1/128) 1^T g
+//   dK_i    += [V_i - vbar | 1] [ N_i ; w ] / 128    (once, after the sweep)
+//
 // dQ_rj and dK_j are added to fp32 global accumulators (other key chunks add to the
 // same rows): the tile is staged in shared memory and leaves as a TMA reduce-add, which
 // runs behind the next phase; dV_i, dK_i and d src stay in TMEM / registers until the
@@ -72,11 +80,16 @@ struct BwdCfg {
   static constexpr int oMisc = oBar + 256;
   static constexpr int kSmemBytes = oMisc + 64 + 1024;
   static constexpr uint32_t tX0 = 0, tX1 = 128, tXC = 256, tDV = 384, tDK = 448;
+  // Shared memory of the phase for the rows before the chunk (the decay-prefix tile and dS are idle then):
+  static constexpr int oE = oCs;                // [128][64] bf16, column 0 = g_denom: second 64-wide box after dO
+  static constexpr int oOnes = oCs + 16384;     // two [16][64] bf16 boxes (16 KB apart) filled with 1/128
+  static constexpr int oBm = odS;               // [80][64] bf16 rows: M_i / 128 (64 rows), ksum_i / 128, zeros
+  static_assert(oE == oGo + 16384, "E must follow the dO slot: together they form one two-box operand");
 };
 
 enum BwdBar {
   bKvFull = 0, bKjFull, bInFull, bGFull, bX0Free, bSdpFull, bX1Free, bCReady, bCsFree, bPdsReady, bRDone, bG2Full,
-  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bNumBars
+  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bMraw, bMask2, bFinal2, bNumBars
 };
 
 struct BwdCtx {
@@ -189,6 +202,8 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
   const uint32_t mP = desc_lo(sb + BwdCfg::oP, 16384), mdS = desc_lo(sb + BwdCfg::odS, 16384);
   const uint32_t mGo = desc_lo(sb + BwdCfg::oGo, 16384), mQ = desc_lo(sb + BwdCfg::oQ, 16384);
   const uint32_t mKi = desc_lo(sb + BwdCfg::oKi, 16384), mKj = desc_lo(sb + BwdCfg::oKj, 16384);
+  const uint32_t mVi = desc_lo(sb + BwdCfg::oVi, 16384), mOnes = desc_lo(sb + BwdCfg::oOnes, 16384);
+  const uint32_t mBm = desc_lo(sb + BwdCfg::oBm, 16384);
 
   // D[128x128] = A[128][64] B[128][64]^T (both K-major, one 64-element box)
   auto mma_nt = [&](uint32_t d, uint32_t a, uint32_t b) {
@@ -212,9 +227,18 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
       mma_ss_c<true>(d, desc_from_lo(a + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(b + ks * 128), id_nt64);
   };
 
+  // D[128x64] (+)= [A0 | A1] Bm with A0 = the dO slot, A1 = the 16 leading columns of the E tile (K = 80), Bm [80][64]
+  auto mma_aug = [&](uint32_t d, bool acc) {
+    if (acc) mma_ss_c<true>(d, desc_from_lo(kGo), desc_from_lo(mBm), id_nt64);
+    else mma_ss_c<false>(d, desc_from_lo(kGo), desc_from_lo(mBm), id_nt64);
+#pragma unroll
+    for (int ks = 1; ks < 5; ++ks)
+      mma_ss_c<true>(d, desc_from_lo(kGo + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(mBm + ks * 128), id_nt64);
+  };
+
   if (!c.wait(bKvFull, 0)) return;
   int x_uses = 0, rc = 0;    // writes so far into the issuer's own scratch region (X0 for A, X1 for B)
-  bool have_acc = false;     // dV / dK_i accumulators hold something
+  bool have_dv = false, have_dk = false, have_n = false;     // dV_i / dK_i / N_i accumulators hold something
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
     if (which == 0) {
@@ -229,6 +253,14 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
           ++x_uses;
         }
       }
+      if (!valid && T == c.nvalid) {
+        // first tile before the chunk: V_i^T K_i (rows 0..63 of the result; the second box of A is whatever the K_j slot holds)
+        if (x_uses >= 1 && !c.wait(bX0Free, x_uses - 1)) return;
+        tc_fence_after();
+        mma_tt(X0, mVi, mKi, false);
+        tc_commit(c.bar(bMraw));
+        ++x_uses;
+      }
       for (int r = 0; r < R; ++r, ++rc) {
         if (!c.wait(bInFull, rc)) return;
         if (valid) {
@@ -239,10 +271,23 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
         }
         tc_commit(c.bar(bSdpFull));
         if (!c.wait(bPdsReady, rc)) return;
-        tc_fence_after();
-        mma_tt(DV, mP, mGo, have_acc);                                  // dV_i += P^T dO
-        mma_tt(DK, mdS, mQ, have_acc);                                  // dK_i += dS^T Q
-        have_acc = true;
+        if (valid) {
+          tc_fence_after();
+          mma_tt(DV, mP, mGo, have_dv);                                 // dV_i += P^T dO
+          mma_tt(DK, mdS, mQ, have_dk);                                 // dK_i += dS^T Q
+          have_dk = true;
+        } else {
+          if (!have_n && !c.wait(bX0Free, x_uses - 1)) return;          // M_i has been read out of X0
+          tc_fence_after();
+          mma_tt(X0, mGo, mQ, have_n);                                  // N_i += [g | E]^T Q
+          have_n = true;
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {                              // dV_i += (1/128) 1^T g
+            if (ks == 0 && !have_dv) mma_ss_c<false>(DV, desc_from_lo(mOnes), desc_from_lo(mGo), id_tt);
+            else mma_ss_c<true>(DV, desc_from_lo(mOnes), desc_from_lo(mGo + ks * 128), id_tt);
+          }
+        }
+        have_dv = true;
         tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
         tc_commit(c.bar(bRDone));
       }
@@ -254,28 +299,35 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
         ++x_uses;
         if (!c.wait(bDgReady, T)) return;
         tc_fence_after();
-        mma_nn(DK, kdG, mKj, have_acc);                                 // dK_i += dG K_j
-        have_acc = true;
+        mma_nn(DK, kdG, mKj, have_dk);                                  // dK_i += dG K_j
+        have_dk = true;
         tc_commit(c.bar(bDkjFull));
       }
     } else {
       // ------------------------------------------------------------- issuer B
       for (int r = 0; r < R; ++r, ++rc) {
         if (!c.wait(bInFull, rc)) return;
-        if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
-        tc_fence_after();
-        mma_nt(X1, kGo, kVi);                                           // dP = dO V_i^T
-        ++x_uses;
+        if (valid) {
+          if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
+          tc_fence_after();
+          mma_nt(X1, kGo, kVi);                                         // dP = dO V_i^T
+          ++x_uses;
+        }
         tc_commit(c.bar(bSdpFull));
         if (!c.wait(bPdsReady, rc)) return;
-        tc_fence_after();
-        mma_nn(X1, kdS, mKi, false);                                    // dQ = dS K_i  (dP has been consumed)
         if (valid) {
+          tc_fence_after();
+          mma_nn(X1, kdS, mKi, false);                                  // dQ = dS K_i  (dP has been consumed)
 #pragma unroll
           for (int nb = 0; nb < 8; ++nb) {                              // dC[key][row] (+)= dS^T I
             if (r > 0) mma_ss_c<true>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
             else mma_ss_c<false>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
           }
+        } else {
+          if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
+          tc_fence_after();
+          mma_aug(X1, false);                                           // dQ = [g | E] [M_i ; ksum_i] / 128
+          ++x_uses;
         }
         tc_commit(c.bar(bRDone));
       }
@@ -290,6 +342,12 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
     }
   }
   tc_commit(c.bar(bFinal));
+  if (which == 0 && c.ntiles > c.nvalid) {
+    if (!c.wait(bMask2, 0)) return;
+    tc_fence_after();
+    mma_aug(DK, have_dk);                                               // dK_i += [V_i - vbar | 1] [N_i ; w] / 128
+    tc_commit(c.bar(bFinal2));
+  }
 }
 
 // ------------------------------------------------------------ worker groups --
@@ -472,6 +530,65 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       UA_PH(2)
     }
 
+    if (!valid && T == c.nvalid) {
+      // ---- first tile before the chunk: constants of the rank-65 form of dS (see the head of this file) ----
+      const int wt = part * 128 + tid;
+      mb.sync();                                  // every reader of C^T / dS / staged tiles is done (and the reduce has read them)
+      if (!mb.ok || !c.wait_w(bKvFull, 0)) return;   // K_i, V_i are read from shared memory below
+      {
+        uint4* e4 = reinterpret_cast<uint4*>(c.smem + BwdCfg::oE);
+        e4[wt] = make_uint4(0u, 0u, 0u, 0u);
+        e4[wt + 512] = make_uint4(0u, 0u, 0u, 0u);
+        __nv_bfloat162 h = __floats2bfloat162_rn(1.0f / 128.0f, 1.0f / 128.0f);
+        const uint32_t o2 = *reinterpret_cast<uint32_t*>(&h);
+        if (wt < 128) reinterpret_cast<uint4*>(c.smem + BwdCfg::oOnes)[wt] = make_uint4(o2, o2, o2, o2);
+        else if (wt < 256) reinterpret_cast<uint4*>(c.smem + BwdCfg::oOnes + 16384)[wt - 128] = make_uint4(o2, o2, o2, o2);
+        else if (wt < 384) reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + 64 * 128)[wt - 256] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (part == 0) {                            // column sums: sT3[0..63] = sum_k K_i, sT3[64..127] = sum_k V_i
+        const uint8_t* tile = c.smem + (tid < 64 ? BwdCfg::oKi : BwdCfg::oVi);
+        const int col = tid & 63;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int k = 0; k < 128; ++k)
+          acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + k * 128 + ((((col >> 3) ^ k) & 7) << 4) + (col & 7) * 2));
+        sT3[tid] = acc;
+      }
+      mb.sync();
+      if (!mb.ok || !c.wait_w(bMraw, 0)) return;
+      tc_fence_after();
+      if (part == 0 && tid < 64) {                // warps of lanes 0..63: row e = tid of M_i = V_i^T K_i - vsum_e ksum / 128
+        const float vb = sT3[64 + tid] * (1.0f / 128.0f);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t m[32];
+          tmem_ld32(c.tmem + BwdCfg::tX0 + lane_base + 32 * half, m);
+          tc_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int d0 = 32 * half + 8 * u + 2 * x;
+              const float a0 = (__uint_as_float(m[8 * u + 2 * x]) - vb * sT3[d0]) * (1.0f / 128.0f);
+              const float a1 = (__uint_as_float(m[8 * u + 2 * x + 1]) - vb * sT3[d0 + 1]) * (1.0f / 128.0f);
+              __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
+              w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + tid * 128 + ((((4 * half + u) ^ tid) & 7) << 4)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+      }
+      if (part == 0 && tid >= 64) {               // row 64 of the operand: ksum / 128 (64 threads x 1 element)
+        const int d0 = tid - 64;
+        *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oBm + 64 * 128 + (((d0 >> 3) & 7) << 4) + (d0 & 7) * 2) =
+            __float2bfloat16_rn(sT3[d0] * (1.0f / 128.0f));
+      }
+      tc_fence_before();
+      c.arrive_w(bX0Free);
+    }
+
     for (int r = 0; r < R; ++r, ++rc) {
       const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
       const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
@@ -540,32 +657,15 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
           pp[u] = *reinterpret_cast<uint32_t*>(&hp);
           dd[u] = *reinterpret_cast<uint32_t*>(&hd);
         }
-      } else {
-        // ---- rows before the chunk: uniform softmax P = 1/128 (universal_attention_autograd.py:154) ----
-        uint32_t dp[32];
-        tmem_ld32(X1 + col0, dp);
-        tc_wait_ld();
-        float sum = 0.f;
-#pragma unroll
-        for (int x = 0; x < 32; ++x) sum += __uint_as_float(dp[x]);
-        float4 all[kParts];
-        mb.gather(make_float4(sum, 0.f, 0.f, 0.f), all);
-        if (!mb.ok) return;
-        sum = (all[0].x + all[1].x) + (all[2].x + all[3].x);
-        const float pu = 1.0f / 128.0f;
-        const float corr = gd - sum * pu;
-        __nv_bfloat162 hp = __floats2bfloat162_rn(pu, pu);
-        const uint32_t pconst = *reinterpret_cast<uint32_t*>(&hp);
-#pragma unroll
-        for (int u = 0; u < 16; ++u) {
-          __nv_bfloat162 hd = __floats2bfloat162_rn(pu * (__uint_as_float(dp[2 * u]) + corr), pu * (__uint_as_float(dp[2 * u + 1]) + corr));
-          pp[u] = pconst;
-          dd[u] = *reinterpret_cast<uint32_t*>(&hd);
-        }
+      } else if (part == 0) {
+        // ---- rows before the chunk: only g_denom enters per row (column 0 of the E tile, row `tid`) ----
+        *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oE + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
       }
       UA_PH(15)
-      store_row(sP, pp);
-      store_row(sdS, dd);
+      if (valid) {
+        store_row(sP, pp);
+        store_row(sdS, dd);
+      }
       UA_PH(16)
       fence_proxy_async();
       tc_fence_before();
@@ -673,6 +773,55 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, 16 of the 64 columns each) ----
   if (!c.wait_w(bFinal, 0)) return;
   tc_fence_after();
+  if (c.ntiles > c.nvalid) {
+    // rows before the chunk: dK_i += [V_i - vbar | 1] [N_i ; w] / 128 through one more MMA
+    if (part == 0 && tid < 96) {                  // lanes 0..63 hold N_i, lane 64 holds w (warps of lanes 0..95 load)
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t m[32];
+        tmem_ld32(c.tmem + BwdCfg::tX0 + lane_base + 32 * half, m);
+        tc_wait_ld();
+        if (tid <= 64) {
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              __nv_bfloat162 hh = __floats2bfloat162_rn(__uint_as_float(m[8 * u + 2 * x]) * (1.0f / 128.0f),
+                                                        __uint_as_float(m[8 * u + 2 * x + 1]) * (1.0f / 128.0f));
+              w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + tid * 128 + ((((4 * half + u) ^ tid) & 7) << 4)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+      }
+    }
+    {                                             // V_i - vbar into the dO slot, 16 columns of key `tid` per thread
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t off = (uint32_t)tid * 128 + ((((uint32_t)(2 * part + u) ^ swz) & 7) << 4);
+        const uint4 raw = *reinterpret_cast<const uint4*>(c.smem + BwdCfg::oVi + off);
+        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t w4[4];
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&rw[x]);
+          const int d0 = 16 * part + 8 * u + 2 * x;
+          __nv_bfloat162 hh = __floats2bfloat162_rn(__bfloat162float(hv.x) - sT3[64 + d0] * (1.0f / 128.0f),
+                                                    __bfloat162float(hv.y) - sT3[64 + d0 + 1] * (1.0f / 128.0f));
+          w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+        }
+        *reinterpret_cast<uint4*>(c.smem + BwdCfg::oGo + off) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      }
+      if (part == 0) *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oE + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(1.0f);
+    }
+    fence_proxy_async();
+    tc_fence_before();
+    c.arrive_w(bMask2);
+    if (!c.wait_w(bFinal2, 0)) return;
+    tc_fence_after();
+  }
   const size_t krow = (size_t)c.bh * L + c.i * 128 + tid;
   {
     uint32_t o[16];
@@ -746,7 +895,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     misc[1] = 0;
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
-      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage) count = 16;   // one arrival per worker warp
+      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage || b == bMask2) count = 16;   // one arrival per worker warp
       if (b == bSdpFull || b == bRDone || b == bDkjFull || b == bFinal) count = 2;                       // one commit per MMA issuer
       mbar_init(c.bar(b), count);
     }
