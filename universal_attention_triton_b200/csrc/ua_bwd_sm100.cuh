@@ -26,7 +26,7 @@
 // is of rank <= 65, so nothing is done per (key, row) pair.  With E = a [128][64] tile whose column 0 holds gd:
 //   dQ_rj    = [g | E] [ M_i ; ksum_i ] / 128,   M_i = sum_k (v_k - vbar)^T k_k  (64 x 64, once per block)
 //   N_i     += [g | E]^T Q_rj                    (64 x 64 plus the row  w = sum_q gd_q q_q ; accumulates in TMEM)
-//   dV_i    += (1/128) 1^T g
+//   dV_i    += (1/128) 1^T g                     (column sums of g on the CUDA cores of the otherwise idle worker groups)
 //   dK_i    += [V_i - vbar | 1] [ N_i ; w ] / 128    (once, after the sweep)
 //
 // dQ_rj and dK_j are added to fp32 global accumulators (other key chunks add to the
@@ -82,7 +82,6 @@ struct BwdCfg {
   static constexpr uint32_t tX0 = 0, tX1 = 128, tXC = 256, tDV = 384, tDK = 448;
   // Shared memory of the phase for the rows before the chunk (the decay-prefix tile and dS are idle then):
   static constexpr int oE = oCs;                // [128][64] bf16, column 0 = g_denom: second 64-wide box after dO
-  static constexpr int oOnes = oCs + 16384;     // two [16][64] bf16 boxes (16 KB apart) filled with 1/128
   static constexpr int oBm = odS;               // [80][64] bf16 rows: M_i / 128 (64 rows), ksum_i / 128, zeros
   static_assert(oE == oGo + 16384, "E must follow the dO slot: together they form one two-box operand");
 };
@@ -202,7 +201,7 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
   const uint32_t mP = desc_lo(sb + BwdCfg::oP, 16384), mdS = desc_lo(sb + BwdCfg::odS, 16384);
   const uint32_t mGo = desc_lo(sb + BwdCfg::oGo, 16384), mQ = desc_lo(sb + BwdCfg::oQ, 16384);
   const uint32_t mKi = desc_lo(sb + BwdCfg::oKi, 16384), mKj = desc_lo(sb + BwdCfg::oKj, 16384);
-  const uint32_t mVi = desc_lo(sb + BwdCfg::oVi, 16384), mOnes = desc_lo(sb + BwdCfg::oOnes, 16384);
+  const uint32_t mVi = desc_lo(sb + BwdCfg::oVi, 16384);
   const uint32_t mBm = desc_lo(sb + BwdCfg::oBm, 16384);
 
   // D[128x128] = A[128][64] B[128][64]^T (both K-major, one 64-element box)
@@ -276,18 +275,13 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
           mma_tt(DV, mP, mGo, have_dv);                                 // dV_i += P^T dO
           mma_tt(DK, mdS, mQ, have_dk);                                 // dK_i += dS^T Q
           have_dk = true;
+          have_dv = true;
         } else {
           if (!have_n && !c.wait(bX0Free, x_uses - 1)) return;          // M_i has been read out of X0
           tc_fence_after();
           mma_tt(X0, mGo, mQ, have_n);                                  // N_i += [g | E]^T Q
           have_n = true;
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks) {                              // dV_i += (1/128) 1^T g
-            if (ks == 0 && !have_dv) mma_ss_c<false>(DV, desc_from_lo(mOnes), desc_from_lo(mGo), id_tt);
-            else mma_ss_c<true>(DV, desc_from_lo(mOnes), desc_from_lo(mGo + ks * 128), id_tt);
-          }
         }
-        have_dv = true;
         tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
         tc_commit(c.bar(bRDone));
       }
@@ -469,8 +463,9 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   };
 
   int rc = 0;
-  for (int T = 0; T < c.ntiles; ++T) {
-    const bool valid = T < c.nvalid;
+  // ================================ row tiles that see the chunk (j >= i), swept downwards ================================
+  for (int T = 0; T < c.nvalid; ++T) {
+    constexpr bool valid = true;
     const int j = c.tile_j(T, N);
     const bool diag = (j == c.i);
     const int rl = p.r0 + (j - p.j_begin) * 128;  // first row of the tile inside the slab
@@ -528,65 +523,6 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       mb.sync();                                  // C^T complete
       if (!mb.ok) return;
       UA_PH(2)
-    }
-
-    if (!valid && T == c.nvalid) {
-      // ---- first tile before the chunk: constants of the rank-65 form of dS (see the head of this file) ----
-      const int wt = part * 128 + tid;
-      mb.sync();                                  // every reader of C^T / dS / staged tiles is done (and the reduce has read them)
-      if (!mb.ok || !c.wait_w(bKvFull, 0)) return;   // K_i, V_i are read from shared memory below
-      {
-        uint4* e4 = reinterpret_cast<uint4*>(c.smem + BwdCfg::oE);
-        e4[wt] = make_uint4(0u, 0u, 0u, 0u);
-        e4[wt + 512] = make_uint4(0u, 0u, 0u, 0u);
-        __nv_bfloat162 h = __floats2bfloat162_rn(1.0f / 128.0f, 1.0f / 128.0f);
-        const uint32_t o2 = *reinterpret_cast<uint32_t*>(&h);
-        if (wt < 128) reinterpret_cast<uint4*>(c.smem + BwdCfg::oOnes)[wt] = make_uint4(o2, o2, o2, o2);
-        else if (wt < 256) reinterpret_cast<uint4*>(c.smem + BwdCfg::oOnes + 16384)[wt - 128] = make_uint4(o2, o2, o2, o2);
-        else if (wt < 384) reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + 64 * 128)[wt - 256] = make_uint4(0u, 0u, 0u, 0u);
-      }
-      if (part == 0) {                            // column sums: sT3[0..63] = sum_k K_i, sT3[64..127] = sum_k V_i
-        const uint8_t* tile = c.smem + (tid < 64 ? BwdCfg::oKi : BwdCfg::oVi);
-        const int col = tid & 63;
-        float acc = 0.f;
-#pragma unroll 8
-        for (int k = 0; k < 128; ++k)
-          acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + k * 128 + ((((col >> 3) ^ k) & 7) << 4) + (col & 7) * 2));
-        sT3[tid] = acc;
-      }
-      mb.sync();
-      if (!mb.ok || !c.wait_w(bMraw, 0)) return;
-      tc_fence_after();
-      if (part == 0 && tid < 64) {                // warps of lanes 0..63: row e = tid of M_i = V_i^T K_i - vsum_e ksum / 128
-        const float vb = sT3[64 + tid] * (1.0f / 128.0f);
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          uint32_t m[32];
-          tmem_ld32(c.tmem + BwdCfg::tX0 + lane_base + 32 * half, m);
-          tc_wait_ld();
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            uint32_t w4[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-              const int d0 = 32 * half + 8 * u + 2 * x;
-              const float a0 = (__uint_as_float(m[8 * u + 2 * x]) - vb * sT3[d0]) * (1.0f / 128.0f);
-              const float a1 = (__uint_as_float(m[8 * u + 2 * x + 1]) - vb * sT3[d0 + 1]) * (1.0f / 128.0f);
-              __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
-              w4[x] = *reinterpret_cast<uint32_t*>(&hh);
-            }
-            *reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + tid * 128 + ((((4 * half + u) ^ tid) & 7) << 4)) =
-                make_uint4(w4[0], w4[1], w4[2], w4[3]);
-          }
-        }
-      }
-      if (part == 0 && tid >= 64) {               // row 64 of the operand: ksum / 128 (64 threads x 1 element)
-        const int d0 = tid - 64;
-        *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oBm + 64 * 128 + (((d0 >> 3) & 7) << 4) + (d0 & 7) * 2) =
-            __float2bfloat16_rn(sT3[d0] * (1.0f / 128.0f));
-      }
-      tc_fence_before();
-      c.arrive_w(bX0Free);
     }
 
     for (int r = 0; r < R; ++r, ++rc) {
@@ -657,15 +593,10 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
           pp[u] = *reinterpret_cast<uint32_t*>(&hp);
           dd[u] = *reinterpret_cast<uint32_t*>(&hd);
         }
-      } else if (part == 0) {
-        // ---- rows before the chunk: only g_denom enters per row (column 0 of the E tile, row `tid`) ----
-        *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oE + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
       }
       UA_PH(15)
-      if (valid) {
-        store_row(sP, pp);
-        store_row(sdS, dd);
-      }
+      store_row(sP, pp);
+      store_row(sdS, dd);
       UA_PH(16)
       fence_proxy_async();
       tc_fence_before();
@@ -770,6 +701,104 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   }
   UA_PH_STORE
 
+  // ================================ rows before the chunk (j < i): uniform softmax ================================
+  if (c.ntiles > c.nvalid) {
+    {
+      // ---- first tile before the chunk: constants of the rank-65 form of dS (see the head of this file) ----
+      const int wt = part * 128 + tid;
+      mb.sync();                                  // every reader of C^T / dS / staged tiles is done (and the reduce has read them)
+      if (!mb.ok || !c.wait_w(bKvFull, 0)) return;   // K_i, V_i are read from shared memory below
+      {
+        uint4* e4 = reinterpret_cast<uint4*>(c.smem + BwdCfg::oE);
+        e4[wt] = make_uint4(0u, 0u, 0u, 0u);
+        e4[wt + 512] = make_uint4(0u, 0u, 0u, 0u);
+        if (wt < 64) sT3[128 + wt] = 0.f;         // column sums of g, reduced after the sweep
+        if (wt >= 256 && wt < 384) reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + 64 * 128)[wt - 256] = make_uint4(0u, 0u, 0u, 0u);
+      }
+      if (part == 0) {                            // column sums: sT3[0..63] = sum_k K_i, sT3[64..127] = sum_k V_i
+        const uint8_t* tile = c.smem + (tid < 64 ? BwdCfg::oKi : BwdCfg::oVi);
+        const int col = tid & 63;
+        float acc = 0.f;
+#pragma unroll 8
+        for (int k = 0; k < 128; ++k)
+          acc += __bfloat162float(*reinterpret_cast<const __nv_bfloat16*>(tile + k * 128 + ((((col >> 3) ^ k) & 7) << 4) + (col & 7) * 2));
+        sT3[tid] = acc;
+      }
+      mb.sync();
+      if (!mb.ok || !c.wait_w(bMraw, 0)) return;
+      tc_fence_after();
+      if (part == 0 && tid < 64) {                // warps of lanes 0..63: row e = tid of M_i = V_i^T K_i - vsum_e ksum / 128
+        const float vb = sT3[64 + tid] * (1.0f / 128.0f);
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          uint32_t m[32];
+          tmem_ld32(c.tmem + BwdCfg::tX0 + lane_base + 32 * half, m);
+          tc_wait_ld();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            uint32_t w4[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+              const int d0 = 32 * half + 8 * u + 2 * x;
+              const float a0 = (__uint_as_float(m[8 * u + 2 * x]) - vb * sT3[d0]) * (1.0f / 128.0f);
+              const float a1 = (__uint_as_float(m[8 * u + 2 * x + 1]) - vb * sT3[d0 + 1]) * (1.0f / 128.0f);
+              __nv_bfloat162 hh = __floats2bfloat162_rn(a0, a1);
+              w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + tid * 128 + ((((4 * half + u) ^ tid) & 7) << 4)) =
+                make_uint4(w4[0], w4[1], w4[2], w4[3]);
+          }
+        }
+      }
+      if (part == 0 && tid >= 64) {               // row 64 of the operand: ksum / 128 (64 threads x 1 element)
+        const int d0 = tid - 64;
+        *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oBm + 64 * 128 + (((d0 >> 3) & 7) << 4) + (d0 & 7) * 2) =
+            __float2bfloat16_rn(sT3[d0] * (1.0f / 128.0f));
+      }
+      tc_fence_before();
+      c.arrive_w(bX0Free);
+    }
+
+    float gsum[16];                               // this thread's share of the column sums of g (for dV_i)
+#pragma unroll
+    for (int x = 0; x < 16; ++x) gsum[x] = 0.f;
+    for (int T = c.nvalid; T < c.ntiles; ++T) {
+      const int j = c.tile_j(T, N);
+      const int rl = p.r0 + (j - p.j_begin) * 128;
+      for (int r = 0; r < R; ++r, ++rc) {
+        const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
+        const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
+                                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
+        // the previous step's MMAs (readers of E) are complete: every thread has passed bRDone
+        if (part == 0) *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oE + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
+        if (!c.wait_w(bInFull, rc)) return;       // the dO tile has landed: 16 columns of row `tid` into the column sums
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(c.smem + BwdCfg::oGo + tid * 128 + ((((uint32_t)(2 * part + u) ^ swz) & 7) << 4));
+          const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&rw[x]);
+            gsum[8 * u + 2 * x] += __bfloat162float(hv.x);
+            gsum[8 * u + 2 * x + 1] += __bfloat162float(hv.y);
+          }
+        }
+        fence_proxy_async();
+        c.arrive_w(bPdsReady);
+        if (!c.wait_w(bRDone, rc)) return;
+        tc_fence_after();
+        drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl);
+      }
+    }
+#pragma unroll
+    for (int x = 0; x < 16; ++x) {
+      float v = gsum[x];
+#pragma unroll
+      for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) atomicAdd(sT3 + 128 + 16 * part + x, v);
+    }
+  }
+
   // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, 16 of the 64 columns each) ----
   if (!c.wait_w(bFinal, 0)) return;
   tc_fence_after();
@@ -819,15 +848,25 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     fence_proxy_async();
     tc_fence_before();
     c.arrive_w(bMask2);
-    if (!c.wait_w(bFinal2, 0)) return;
+    mb.sync();                                    // the column sums of g are complete
+    if (!mb.ok || !c.wait_w(bFinal2, 0)) return;
     tc_fence_after();
   }
   const size_t krow = (size_t)c.bh * L + c.i * 128 + tid;
   {
     uint32_t o[16];
     if (!p.decay_only) {
-      tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
-      tc_wait_ld();
+      if (c.nvalid > 0) {
+        tmem_ld16(c.tmem + BwdCfg::tDV + lane_base + 16 * part, o);
+        tc_wait_ld();
+      } else {
+#pragma unroll
+        for (int u = 0; u < 16; ++u) o[u] = 0u;
+      }
+      if (c.ntiles > c.nvalid) {                  // rows before the chunk: dV_i += (1/128) 1^T g for every key
+#pragma unroll
+        for (int u = 0; u < 16; ++u) o[u] = __float_as_uint(__uint_as_float(o[u]) + sT3[128 + 16 * part + u] * (1.0f / 128.0f));
+      }
       if (p.acc_dv) {
         float* dst = p.acc_dv + krow * 64 + 16 * part;          // several row ranges may add to the same keys
 #pragma unroll
