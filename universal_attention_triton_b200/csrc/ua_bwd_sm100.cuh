@@ -81,14 +81,16 @@ struct BwdCfg {
   static constexpr int kSmemBytes = oMisc + 64 + 1024;
   static constexpr uint32_t tX0 = 0, tX1 = 128, tXC = 256, tDV = 384, tDK = 448;
   // Shared memory of the phase for the rows before the chunk (the decay-prefix tile and dS are idle then):
+  // two slots of (Q, dO, E) so that the next step's loads run under the current step's MMAs; step m uses slot m & 1
+  static constexpr int oGo1 = oCs + 16384, oE1 = oCs + 32768, oQ1 = oCs + 49152;
   static constexpr int oE = oCs;                // [128][64] bf16, column 0 = g_denom: second 64-wide box after dO
-  static constexpr int oBm = odS;               // [80][64] bf16 rows: M_i / 128 (64 rows), ksum_i / 128, zeros
+  static constexpr int oBm = oKj;               // [80][64] bf16 rows: M_i / 128 (64 rows), ksum_i / 128, zeros (K_j is idle)
   static_assert(oE == oGo + 16384, "E must follow the dO slot: together they form one two-box operand");
 };
 
 enum BwdBar {
   bKvFull = 0, bKjFull, bInFull, bGFull, bX0Free, bSdpFull, bX1Free, bCReady, bCsFree, bPdsReady, bRDone, bG2Full,
-  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bMraw, bMask2, bFinal2, bNumBars
+  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bMraw, bMask2, bFinal2, bInFull1, bInFree1, bPdsM0, bPdsM1, bNumBars
 };
 
 struct BwdCtx {
@@ -108,6 +110,26 @@ struct BwdCtx {
     return T < nvalid ? j_end - 1 - T : (i < j_end ? i : j_end) - 1 - (T - nvalid);
   }
 };
+
+// Rows before the chunk: step m (counted from the first such (tile, head)) uses slot m & 1.  Slot 0 is the slot of the
+// sweep over the valid tiles (its barriers continue their phase sequence, rc0 steps old), slot 1 is fresh.
+struct MaskSlot {
+  int q, go, e, full_bar, free_bar, phase;
+  int ready_bar, ready_phase;   // "operands of the step are complete" (worker groups -> issuers), one barrier per slot:
+                                // an issuer that trails by two steps would mistake a phase of a shared barrier
+};
+__device__ __forceinline__ MaskSlot mask_slot(int m, int rc0) {
+  MaskSlot s;
+  if ((m & 1) == 0) {
+    s.q = BwdCfg::oQ; s.go = BwdCfg::oGo; s.e = BwdCfg::oE; s.full_bar = bInFull; s.free_bar = bInFree; s.phase = rc0 + (m >> 1);
+    s.ready_bar = bPdsM0;
+  } else {
+    s.q = BwdCfg::oQ1; s.go = BwdCfg::oGo1; s.e = BwdCfg::oE1; s.full_bar = bInFull1; s.free_bar = bInFree1; s.phase = m >> 1;
+    s.ready_bar = bPdsM1;
+  }
+  s.ready_phase = m >> 1;
+  return s;
+}
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
@@ -147,6 +169,7 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
     grow = (int)((chunk_id * R + r) * p.Lr + p.r0 + (size_t)(j - p.j_begin) * 128);
   };
   int rc = 0;
+  const int rc0 = c.nvalid * R;                           // steps of the sweep over the valid tiles
   for (int T = 0; T < c.ntiles; ++T) {
     const bool valid = T < c.nvalid;
     const int j = c.tile_j(T, N);
@@ -158,8 +181,8 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
     for (int r = 0; r < (p.decay_only ? 0 : R); ++r, ++rc) {
       int qrow, grow;
       {
-        int Tn = T, rn = r + 1;
-        if (rn == R) { rn = 0; ++Tn; }
+        const int nxt = T * R + r + (valid ? 1 : 2);     // two slots before the chunk: look one step further ahead
+        const int Tn = nxt / R, rn = nxt - Tn * R;
         if (Tn < c.ntiles) {
           coords(Tn, rn, qrow, grow);
           tma_prefetch_2d(tmG, 0, grow);
@@ -167,10 +190,12 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
         }
       }
       coords(T, r, qrow, grow);
-      if (rc >= 1 && !c.wait(bInFree, rc - 1)) return;
-      mbar_expect_tx(c.bar(bInFull), 2 * BwdCfg::kTileBytes);
-      tma_load_2d(sbase + BwdCfg::oQ, tmQ, 0, qrow, c.bar(bInFull));
-      tma_load_2d(sbase + BwdCfg::oGo, tmG, 0, grow, c.bar(bInFull));
+      MaskSlot ms = mask_slot(0, rc);                     // valid tiles: slot 0, phase rc
+      if (!valid) ms = mask_slot(rc - rc0, rc0);
+      if (ms.phase >= 1 && !c.wait(ms.free_bar, ms.phase - 1)) return;
+      mbar_expect_tx(c.bar(ms.full_bar), 2 * BwdCfg::kTileBytes);
+      tma_load_2d(sbase + ms.q, tmQ, 0, qrow, c.bar(ms.full_bar));
+      tma_load_2d(sbase + ms.go, tmG, 0, grow, c.bar(ms.full_bar));
     }
   }
 }
@@ -227,13 +252,14 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
   };
 
   // D[128x64] (+)= [A0 | A1] Bm with A0 = the dO slot, A1 = the 16 leading columns of the E tile (K = 80), Bm [80][64]
-  auto mma_aug = [&](uint32_t d, bool acc) {
-    if (acc) mma_ss_c<true>(d, desc_from_lo(kGo), desc_from_lo(mBm), id_nt64);
-    else mma_ss_c<false>(d, desc_from_lo(kGo), desc_from_lo(mBm), id_nt64);
+  auto mma_aug = [&](uint32_t d, uint32_t a, bool acc) {
+    if (acc) mma_ss_c<true>(d, desc_from_lo(a), desc_from_lo(mBm), id_nt64);
+    else mma_ss_c<false>(d, desc_from_lo(a), desc_from_lo(mBm), id_nt64);
 #pragma unroll
     for (int ks = 1; ks < 5; ++ks)
-      mma_ss_c<true>(d, desc_from_lo(kGo + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(mBm + ks * 128), id_nt64);
+      mma_ss_c<true>(d, desc_from_lo(a + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(mBm + ks * 128), id_nt64);
   };
+  const int rc0 = c.nvalid * R;
 
   if (!c.wait(bKvFull, 0)) return;
   int x_uses = 0, rc = 0;    // writes so far into the issuer's own scratch region (X0 for A, X1 for B)
@@ -261,28 +287,30 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
         ++x_uses;
       }
       for (int r = 0; r < R; ++r, ++rc) {
-        if (!c.wait(bInFull, rc)) return;
         if (valid) {
+          if (!c.wait(bInFull, rc)) return;
           if (!c.wait(bX0Free, x_uses - 1)) return;
           tc_fence_after();
           mma_nt(X0, kQ, kKi);                                          // S = Q K_i^T
           ++x_uses;
-        }
-        tc_commit(c.bar(bSdpFull));
-        if (!c.wait(bPdsReady, rc)) return;
-        if (valid) {
+          tc_commit(c.bar(bSdpFull));
+          if (!c.wait(bPdsReady, rc)) return;
           tc_fence_after();
           mma_tt(DV, mP, mGo, have_dv);                                 // dV_i += P^T dO
           mma_tt(DK, mdS, mQ, have_dk);                                 // dK_i += dS^T Q
           have_dk = true;
           have_dv = true;
+          tc_commit(c.bar(bInFree));                                    // Q and dO slots can be refilled (once both issuers say so)
         } else {
+          const MaskSlot ms = mask_slot(rc - rc0, rc0);
+          if (!c.wait(ms.full_bar, ms.phase) || !c.wait(ms.ready_bar, ms.ready_phase)) return;
           if (!have_n && !c.wait(bX0Free, x_uses - 1)) return;          // M_i has been read out of X0
           tc_fence_after();
-          mma_tt(X0, mGo, mQ, have_n);                                  // N_i += [g | E]^T Q
+          mma_tt(X0, desc_lo(sb + ms.go, 16384), desc_lo(sb + ms.q, 16384), have_n);   // N_i += [g | E]^T Q
           have_n = true;
+          tc_commit(c.bar(ms.free_bar));          // (bRDone of these steps belongs to issuer B alone: N_i is not waited for)
+          continue;
         }
-        tc_commit(c.bar(bInFree));                                      // Q and dO slots can be refilled
         tc_commit(c.bar(bRDone));
       }
       if (valid) {
@@ -300,16 +328,15 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
     } else {
       // ------------------------------------------------------------- issuer B
       for (int r = 0; r < R; ++r, ++rc) {
-        if (!c.wait(bInFull, rc)) return;
         if (valid) {
+          if (!c.wait(bInFull, rc)) return;
           if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
           tc_fence_after();
           mma_nt(X1, kGo, kVi);                                         // dP = dO V_i^T
           ++x_uses;
-        }
-        tc_commit(c.bar(bSdpFull));
-        if (!c.wait(bPdsReady, rc)) return;
-        if (valid) {
+          tc_commit(c.bar(bSdpFull));
+          tc_commit(c.bar(bInFree));                                    // this issuer's last read of the Q / dO slot
+          if (!c.wait(bPdsReady, rc)) return;
           tc_fence_after();
           mma_nn(X1, kdS, mKi, false);                                  // dQ = dS K_i  (dP has been consumed)
 #pragma unroll
@@ -318,10 +345,14 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
             else mma_ss_c<false>(XC + nb * 16, desc_from_lo(mdS + nb * 128), desc_from_lo(kI), id_dc);
           }
         } else {
+          const MaskSlot ms = mask_slot(rc - rc0, rc0);
+          if (!c.wait(ms.full_bar, ms.phase) || !c.wait(ms.ready_bar, ms.ready_phase)) return;
           if (x_uses >= 1 && !c.wait(bX1Free, x_uses - 1)) return;
           tc_fence_after();
-          mma_aug(X1, false);                                           // dQ = [g | E] [M_i ; ksum_i] / 128
+          mma_aug(X1, desc_lo(sb + ms.go, 16), false);                  // dQ = [g | E] [M_i ; ksum_i] / 128
           ++x_uses;
+          tc_commit(c.bar(ms.free_bar));
+          tc_commit(c.bar(bRDone));               // both arrivals: the workers wait for dQ only, N_i trails behind
         }
         tc_commit(c.bar(bRDone));
       }
@@ -339,7 +370,7 @@ __device__ __forceinline__ void bwd_mma(const BwdCtx& c, const BwdParams& p, con
   if (which == 0 && c.ntiles > c.nvalid) {
     if (!c.wait(bMask2, 0)) return;
     tc_fence_after();
-    mma_aug(DK, have_dk);                                               // dK_i += [V_i - vbar | 1] [N_i ; w] / 128
+    mma_aug(DK, kGo, have_dk);                                          // dK_i += [V_i - vbar | 1] [N_i ; w] / 128
     tc_commit(c.bar(bFinal2));
   }
 }
@@ -382,9 +413,12 @@ struct Mailbox {
 // Optional phase timing (compile with -DUA_PROFILE_PHASES): thread 0 of worker group 0 of block 0
 // accumulates clock64() deltas per phase and stores them after the status word.
 #ifdef UA_PROFILE_PHASES
+#ifndef UA_PROFILE_BLOCK
+#define UA_PROFILE_BLOCK 0
+#endif
 #define UA_PH_DECL long long ph_t = clock64(), ph_acc[20] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
 #define UA_PH(idx) { long long now_ = clock64(); ph_acc[idx] += now_ - ph_t; ph_t = now_; }
-#define UA_PH_STORE if (blockIdx.x == 0 && part == 0 && tid == 0) { for (int z = 0; z < 20; ++z) reinterpret_cast<long long*>(p.status)[2 + z] = ph_acc[z]; }
+#define UA_PH_STORE if (blockIdx.x == UA_PROFILE_BLOCK && part == 0 && tid == 0) { for (int z = 0; z < 20; ++z) reinterpret_cast<long long*>(p.status)[2 + z] = ph_acc[z]; }
 #else
 #define UA_PH_DECL
 #define UA_PH(idx)
@@ -421,9 +455,9 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   const float kLog2e = 1.4426950408889634f;
   const uint32_t swz = (uint32_t)(tid & 7);
   Mailbox mb{&c, reinterpret_cast<float*>(c.smem + BwdCfg::oXch), part, tid, 0, true};
+  UA_PH_DECL
   const size_t key_id = chunk_id * 128 + tid;
   float suffix = p.suffix_in ? p.suffix_in[key_id] : 0.f, ds_acc = 0.f, dct = 0.f;
-  UA_PH_DECL
 
   // this thread's 32 columns of row `tid` of a [row][key] bf16 tile: 4 chunks of box part/2
   auto store_row = [&](uint8_t* base, const uint32_t* v) {
@@ -437,25 +471,29 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   // The 128 x 64 fp32 tile in X1 (dQ_rj or dK_j) is added to rows [y, y+128) of a global accumulator: every thread
   // moves 16 columns of row `tid` into the (idle) P buffer as two 128-byte-swizzled [128][32] boxes, and once all 16
   // warps have arrived the group leader issues two TMA reduce-adds.  The buffer is rewritten only after a mailbox
-  // rendezvous, before which the leader waits until the reduce has read it.
+  // rendezvous, before which the leader waits until the reduce has read it.  (The rows before the chunk alternate
+  // between two staging buffers, see there.)
   int nstage = 0;
-  auto drain_x1 = [&](const CUtensorMap* tm, int y) -> bool {
+  auto drain_x1 = [&](const CUtensorMap* tm, int y, uint8_t* stage) -> bool {
     uint32_t o[16];
     tmem_ld16(X1 + 16 * part, o);
     tc_wait_ld();
     tc_fence_before();
     c.arrive_w(bX1Free);
-    store_row(sP, o);
+    store_row(stage, o);
     fence_proxy_async();
     c.arrive_w(bStage);
     bool ok = true;
     if (part == 0 && tid == 0) {
+      UA_PH(17)
       ok = c.wait(bStage, nstage);
+      UA_PH(18)
       if (ok) {
-        tma_reduce_add_2d(tm, 0, y, smem_u32(sP));
-        tma_reduce_add_2d(tm, 32, y, smem_u32(sP) + 16384);
+        tma_reduce_add_2d(tm, 0, y, smem_u32(stage));
+        tma_reduce_add_2d(tm, 32, y, smem_u32(stage) + 16384);
         bulk_commit_group();
       }
+      UA_PH(19)
     }
     __syncwarp();
     ++nstage;
@@ -606,7 +644,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bRDone, rc)) return;
       UA_PH(5)
       tc_fence_after();
-      drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl);
+      drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl, sP);
       UA_PH(6)
     }
 
@@ -695,12 +733,10 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bDkjFull, T)) return;
       UA_PH(9)
       tc_fence_after();
-      drain_x1(tmDK, c.bh * L + j * 128);      // dK_j
+      drain_x1(tmDK, c.bh * L + j * 128, sP);      // dK_j
       UA_PH(10)
     }
   }
-  UA_PH_STORE
-
   // ================================ rows before the chunk (j < i): uniform softmax ================================
   if (c.ntiles > c.nvalid) {
     {
@@ -710,8 +746,11 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!mb.ok || !c.wait_w(bKvFull, 0)) return;   // K_i, V_i are read from shared memory below
       {
         uint4* e4 = reinterpret_cast<uint4*>(c.smem + BwdCfg::oE);
+        uint4* e41 = reinterpret_cast<uint4*>(c.smem + BwdCfg::oE1);
         e4[wt] = make_uint4(0u, 0u, 0u, 0u);
         e4[wt + 512] = make_uint4(0u, 0u, 0u, 0u);
+        e41[wt] = make_uint4(0u, 0u, 0u, 0u);
+        e41[wt + 512] = make_uint4(0u, 0u, 0u, 0u);
         if (wt < 64) sT3[128 + wt] = 0.f;         // column sums of g, reduced after the sweep
         if (wt >= 256 && wt < 384) reinterpret_cast<uint4*>(c.smem + BwdCfg::oBm + 64 * 128)[wt - 256] = make_uint4(0u, 0u, 0u, 0u);
       }
@@ -759,36 +798,55 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       c.arrive_w(bX0Free);
     }
 
+    const int rc0 = rc;
     float gsum[16];                               // this thread's share of the column sums of g (for dV_i)
 #pragma unroll
     for (int x = 0; x < 16; ++x) gsum[x] = 0.f;
-    for (int T = c.nvalid; T < c.ntiles; ++T) {
-      const int j = c.tile_j(T, N);
-      const int rl = p.r0 + (j - p.j_begin) * 128;
-      for (int r = 0; r < R; ++r, ++rc) {
-        const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
-        const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
-                                          : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
-        // the previous step's MMAs (readers of E) are complete: every thread has passed bRDone
-        if (part == 0) *reinterpret_cast<__nv_bfloat16*>(c.smem + BwdCfg::oE + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
-        if (!c.wait_w(bInFull, rc)) return;       // the dO tile has landed: 16 columns of row `tid` into the column sums
+    // Steps m = 0 .. M-1 over (tile, head).  prepare(m) -- this thread's part of the operands of step m -- runs BEFORE the
+    // wait for the MMAs of step m-1, so that issuer B can start step m as soon as X1 has been read out.
+    const int M = (c.ntiles - c.nvalid) * R;
+    auto step_row0 = [&](int m) -> int {            // first row (inside the slab) of step m's tile
+      return p.r0 + (c.tile_j(c.nvalid + m / R, N) - p.j_begin) * 128;
+    };
+    // g_denom of row `tid`, fetched two steps ahead: its latency would otherwise sit in every step's chain
+    auto load_gd = [&](int m) -> float {
+      if (m >= M || part != 0) return 0.f;
+      const size_t grow = (chunk_id * Rq + (m % R)) * p.Lr + (size_t)step_row0(m) + tid;
+      return p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
+    };
+    auto prepare = [&](int m, float gd) -> bool {
+      const MaskSlot ms = mask_slot(m, rc0);
+      if (!c.wait_w(ms.full_bar, ms.phase)) return false;   // the dO tile has landed ...
+      // ... which also means that the slot was free: the MMAs of two steps ago, the readers of this slot's E, are complete
+      if (part == 0) *reinterpret_cast<__nv_bfloat16*>(c.smem + ms.e + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const uint4 raw = *reinterpret_cast<const uint4*>(c.smem + BwdCfg::oGo + tid * 128 + ((((uint32_t)(2 * part + u) ^ swz) & 7) << 4));
-          const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+      for (int u = 0; u < 2; ++u) {                 // 16 columns of row `tid` of dO into the column sums
+        const uint4 raw = *reinterpret_cast<const uint4*>(c.smem + ms.go + tid * 128 + ((((uint32_t)(2 * part + u) ^ swz) & 7) << 4));
+        const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-          for (int x = 0; x < 4; ++x) {
-            const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&rw[x]);
-            gsum[8 * u + 2 * x] += __bfloat162float(hv.x);
-            gsum[8 * u + 2 * x + 1] += __bfloat162float(hv.y);
-          }
+        for (int x = 0; x < 4; ++x) {
+          const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&rw[x]);
+          gsum[8 * u + 2 * x] += __bfloat162float(hv.x);
+          gsum[8 * u + 2 * x + 1] += __bfloat162float(hv.y);
         }
-        fence_proxy_async();
-        c.arrive_w(bPdsReady);
-        if (!c.wait_w(bRDone, rc)) return;
-        tc_fence_after();
-        drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl);
       }
+      fence_proxy_async();
+      // step m stages its dQ tile in buffer m & 1, last used by step m-2, whose reduce-add has been issued by now: it must
+      // have read the buffer before anybody passes bRDone of step m, which follows the completion of this bPdsReady
+      if (part == 0 && tid == 0) bulk_wait_read_all();
+      c.arrive_w(ms.ready_bar);
+      return true;
+    };
+    float gd0 = load_gd(0), gd1 = load_gd(1);
+    if (!prepare(0, gd0)) return;
+    for (int m = 0; m < M; ++m, ++rc) {
+      const float gd2 = load_gd(m + 2);
+      if (m + 1 < M && !prepare(m + 1, gd1)) return;
+      gd1 = gd2;
+      if (!c.wait_w(bRDone, rc)) return;
+      tc_fence_after();
+      drain_x1(tmDQ, (c.bh * Rq + (m % R)) * p.Lr + step_row0(m), (m & 1) ? sdS : sP);
     }
 #pragma unroll
     for (int x = 0; x < 16; ++x) {
@@ -798,6 +856,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (lane == 0) atomicAdd(sT3 + 128 + 16 * part + x, v);
     }
   }
+  UA_PH_STORE
 
   // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, 16 of the 64 columns each) ----
   if (!c.wait_w(bFinal, 0)) return;
@@ -934,8 +993,8 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     misc[1] = 0;
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
-      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage || b == bMask2) count = 16;   // one arrival per worker warp
-      if (b == bSdpFull || b == bRDone || b == bDkjFull || b == bFinal) count = 2;                       // one commit per MMA issuer
+      if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage || b == bMask2 || b == bPdsM0 || b == bPdsM1) count = 16;   // one arrival per worker warp
+      if (b == bSdpFull || b == bRDone || b == bDkjFull || b == bFinal || b == bInFree || b == bInFree1) count = 2;                       // one commit per MMA issuer
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
