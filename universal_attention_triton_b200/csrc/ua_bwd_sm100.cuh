@@ -101,9 +101,22 @@ struct BwdCtx {
   int i, bh, nvalid, ntiles;
   int j_begin, j_end;
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
-  __device__ __forceinline__ bool wait(int idx, uint32_t parity) const { return mbar_wait(bar(idx), parity & 1u, abort_flag); }
+  // A wait that gives up leaves (barrier index + 1) | thread << 8 | phase << 20 in the word after the abort flag (first one
+  // wins); the kernel copies it to the second status word, so that a host can see where a block stopped.
+  __device__ __forceinline__ void note_failure(int idx, uint32_t parity) const {
+    atomicCAS(const_cast<int*>(abort_flag) + 1, 0, (idx + 1) | ((int)threadIdx.x << 8) | ((int)(parity & 0x7ff) << 20));
+  }
+  __device__ __forceinline__ bool wait(int idx, uint32_t parity) const {
+    const bool ok = mbar_wait(bar(idx), parity & 1u, abort_flag);
+    if (!ok) note_failure(idx, parity);
+    return ok;
+  }
   // warp-collective forms for the worker groups
-  __device__ __forceinline__ bool wait_w(int idx, uint32_t parity) const { return mbar_wait_warp(bar(idx), parity & 1u, abort_flag); }
+  __device__ __forceinline__ bool wait_w(int idx, uint32_t parity) const {
+    const bool ok = mbar_wait_warp(bar(idx), parity & 1u, abort_flag);
+    if (!ok && (threadIdx.x & 31) == 0) note_failure(idx, parity);
+    return ok;
+  }
   __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
   // row tile index of sweep step T: valid tiles n-1 .. i first, then the masked ones i-1 .. 0
   __device__ __forceinline__ int tile_j(int T, int) const {
@@ -474,15 +487,19 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   // rendezvous, before which the leader waits until the reduce has read it.  (The rows before the chunk alternate
   // between two staging buffers, see there.)
   int nstage = 0;
-  auto drain_x1 = [&](const CUtensorMap* tm, int y, uint8_t* stage) -> bool {
+  // release_late: X1 is released only after the arrival at bStage.  Needed where no rendezvous separates two drains (the
+  // rows before the chunk): the next write into X1, and with it the next tile to stage, must not overtake a warp that has
+  // not arrived at bStage yet, or its arrival would be counted for the wrong tile.
+  auto drain_x1 = [&](const CUtensorMap* tm, int y, uint8_t* stage, bool release_late) -> bool {
     uint32_t o[16];
     tmem_ld16(X1 + 16 * part, o);
     tc_wait_ld();
     tc_fence_before();
-    c.arrive_w(bX1Free);
+    if (!release_late) c.arrive_w(bX1Free);
     store_row(stage, o);
     fence_proxy_async();
     c.arrive_w(bStage);
+    if (release_late) c.arrive_w(bX1Free);
     bool ok = true;
     if (part == 0 && tid == 0) {
       UA_PH(17)
@@ -644,7 +661,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bRDone, rc)) return;
       UA_PH(5)
       tc_fence_after();
-      drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl, sP);
+      drain_x1(tmDQ, (c.bh * Rq + r) * p.Lr + rl, sP, false);
       UA_PH(6)
     }
 
@@ -733,7 +750,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       if (!c.wait_w(bDkjFull, T)) return;
       UA_PH(9)
       tc_fence_after();
-      drain_x1(tmDK, c.bh * L + j * 128, sP);      // dK_j
+      drain_x1(tmDK, c.bh * L + j * 128, sP, false);      // dK_j
       UA_PH(10)
     }
   }
@@ -846,7 +863,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       gd1 = gd2;
       if (!c.wait_w(bRDone, rc)) return;
       tc_fence_after();
-      drain_x1(tmDQ, (c.bh * Rq + (m % R)) * p.Lr + step_row0(m), (m & 1) ? sdS : sP);
+      drain_x1(tmDQ, (c.bh * Rq + (m % R)) * p.Lr + step_row0(m), (m & 1) ? sdS : sP, true);
     }
 #pragma unroll
     for (int x = 0; x < 16; ++x) {
@@ -991,6 +1008,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
 
   if (threadIdx.x == 0) {
     misc[1] = 0;
+    misc[2] = 0;
     for (int b = 0; b < bNumBars; ++b) {
       uint32_t count = 1;
       if (b == bX0Free || b == bX1Free || b == bPdsReady || b == bDgReady || b == bXchg || b == bStage || b == bMask2 || b == bPdsM0 || b == bPdsM1) count = 16;   // one arrival per worker warp
@@ -1034,7 +1052,9 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   tc_fence_before();
   __syncthreads();
   if (*c.abort_flag) {
-    if (threadIdx.x == 0) atomicExch(p.status, 2);
+    if (threadIdx.x == 0) {
+      if (atomicExch(p.status, 2) == 0) p.status[1] = (int)misc[2];   // where the first block to give up stopped
+    }
     for (int it = 0; it < 64; ++it) __nanosleep(2000);
     __syncthreads();
   }
