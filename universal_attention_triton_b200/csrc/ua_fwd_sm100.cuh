@@ -347,8 +347,9 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           const float p0 = ex2(fmaf(__uint_as_float(s[2 * u]), kLog2e, -mb));
           const float p1 = ex2(fmaf(__uint_as_float(s[2 * u + 1]), kLog2e, -mb));
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-          // the row sum uses the rounded probabilities, the values the tensor core multiplies
-          l += __bfloat162float(h.x) + __bfloat162float(h.y);
+          // the row sum uses the unrounded probabilities: the reference normalises in fp32 and rounds P afterwards
+          // (universal_attention_autograd.py:158-159)
+          l += p0 + p1;
           pk[u] = *reinterpret_cast<uint32_t*>(&h);
         }
         tmem_st16(tS + cb * 16, pk);
