@@ -226,8 +226,11 @@ int ua_static_status(void* stream);
  * runs out makes the kernel give up and set a status word at the start of the
  * workspace it was given.  ua_workspace_status() copies that word back and
  * SYNCHRONISES the stream: 0 = every kernel of the last ua_fwd/ua_bwd call
- * that used this workspace completed, UA_ERR_TIMEOUT otherwise.  No
- * counterpart in the reference (its kernels have no device-side waits). */
+ * that used this workspace completed, UA_ERR_TIMEOUT otherwise.  After a
+ * timeout of the tensor-core backward the second 32-bit word of the workspace
+ * says where the first block to give up was waiting:
+ * (barrier index + 1) | thread << 8 | (phase & 0x7ff) << 20.  No counterpart
+ * in the reference (its kernels have no device-side waits). */
 int ua_workspace_status(const void* workspace, void* stream);
 
 /* Layout converters between chunk-major storage and the reference's contiguous
