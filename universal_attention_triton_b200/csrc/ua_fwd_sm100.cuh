@@ -312,16 +312,17 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       const uint32_t tO = c.tmem + ((Cfg::kOBufs == 2 && ob) ? Cfg::tO1 : Cfg::tO0) + lane_base;
       if (!c.wait_w(kSFull + sb, t >> 1)) return;
       tc_fence_after();
-      // pass 1: s = S + C (written back to TMEM), row max
+      // pass 1: s = S + C (written back to TMEM), row max.  64 columns per round trip: the two loads are in flight together.
       float m = -INFINITY;
 #pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t s[32];
-        tmem_ld32(tS + cb * 32, s);
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t s[64];
+        tmem_ld32(tS + cb * 64, s);
+        tmem_ld32(tS + cb * 64 + 32, s + 32);
         tc_wait_ld();
 #pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          const int chunk = cb * 8 + u;
+        for (int u = 0; u < 16; ++u) {
+          const int chunk = cb * 16 + u;
           const float4 cv = *reinterpret_cast<const float4*>(sCrow + (((chunk ^ (row & 7)) & 31) << 4));
           float a0 = __uint_as_float(s[u * 4 + 0]) + cv.x, a1 = __uint_as_float(s[u * 4 + 1]) + cv.y;
           float a2 = __uint_as_float(s[u * 4 + 2]) + cv.z, a3 = __uint_as_float(s[u * 4 + 3]) + cv.w;
@@ -329,7 +330,8 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           s[u * 4 + 0] = __float_as_uint(a0); s[u * 4 + 1] = __float_as_uint(a1);
           s[u * 4 + 2] = __float_as_uint(a2); s[u * 4 + 3] = __float_as_uint(a3);
         }
-        tmem_st32(tS + cb * 32, s);
+        tmem_st32(tS + cb * 64, s);
+        tmem_st32(tS + cb * 64 + 32, s + 32);
       }
       tc_wait_st();
       if (r == last_r) c.arrive_w(kCFree);
@@ -337,13 +339,14 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       const float mb = m * kLog2e;
       float l = 0.f;
 #pragma unroll 1
-      for (int cb = 0; cb < 4; ++cb) {
-        uint32_t s[32];
-        tmem_ld32(tS + cb * 32, s);
+      for (int cb = 0; cb < 2; ++cb) {
+        uint32_t s[64];
+        tmem_ld32(tS + cb * 64, s);
+        tmem_ld32(tS + cb * 64 + 32, s + 32);
         tc_wait_ld();
-        uint32_t pk[16];
+        uint32_t pk[32];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) {
+        for (int u = 0; u < 32; ++u) {
           const float p0 = ex2(fmaf(__uint_as_float(s[2 * u]), kLog2e, -mb));
           const float p1 = ex2(fmaf(__uint_as_float(s[2 * u + 1]), kLog2e, -mb));
           __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
@@ -352,7 +355,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           l += p0 + p1;
           pk[u] = *reinterpret_cast<uint32_t*>(&h);
         }
-        tmem_st16(tS + cb * 16, pk);
+        tmem_st32(tS + cb * 32, pk);
       }
       tc_wait_st();
       tc_fence_before();
