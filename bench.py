@@ -52,6 +52,12 @@ METRIC = "fwd+bwd tokens/sec"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
+# DRAM bytes per launch of the two kernels at workload c2, from one ncu capture (see profiles/): the capture ran a slice of
+# 2 of the 32 (batch, kv-head) units -- forward 7.13 MB read + 86.77 MB written, backward 157.01 MB + 7.91 MB -- and the
+# traffic grows in proportion to the units.
+NCU_DRAM_BYTES = {"c2": {"fwd": 16 * (7.129344e6 + 86.766592e6), "bwd": 16 * (157.008384e6 + 7.912192e6)}}
+
+
 def flops(w):
     n = w["L"] // w["c"]
     base = 2.0 * w["B"] * w["H"] * w["L"] ** 2 * w["D"] * (n + 1) / (2 * n)
@@ -468,7 +474,10 @@ def main():
             "clocks": clocks,
             "roofline": {"kernel": "ua backward" if dom_is_bwd else "ua forward", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-                         "traffic": None, "peak_source": f"{peak_src} (bf16_tflops_sustained)",
+                         "traffic": NCU_DRAM_BYTES.get(args.workload, {}).get("bwd" if dom_is_bwd else "fwd"),
+                         "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 2-of-32 (batch, kv-head) slice, "
+                                           "scaled by the units of a full launch (profiles/fwd_bwd_kernels_config2.md)",
+                         "peak_source": f"{peak_src} (bf16_tflops_sustained)",
                          "algorithmic_flops_per_launch": dom_f,
                          "hbm_view": {"bytes": b_bwd if dom_is_bwd else b_fwd,
                                       "achieved_gbs": (b_bwd if dom_is_bwd else b_fwd) / (dom_ms * 1e-3) / 1e9,
