@@ -330,7 +330,7 @@ def main():
         out_cm, lse_cm, denom_cm, carry = ops.forward_cm(kc, vc, xq, ss, sd, keep_carry=not w["fwd_only"])
         e1.record()
         if not w["fwd_only"]:
-            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags, carry=carry)
+            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags, carry=carry, lse=lse_cm)
         e2.record()
         if record:
             fwd_ms.append((e0, e1)); bwd_ms.append((e1, e2))

@@ -120,7 +120,10 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype,
  * registers anyway into carry_out (ua_carry_bytes() bytes, fp32; 0 bytes means
  * this shape has no table and carry_out is ignored), and ua_bwd_kept() is ua_bwd()
  * that reads it from carry_in instead of running the pre-pass (carry_in may be
- * NULL: then it is ua_bwd()).  Same inputs must be given to both calls.  The
+ * NULL: then it is ua_bwd()).  lse_cm (optional, NULL allowed): the fp32
+ * log-sum-exp (b,h,n,r,L) that the forward wrote; with it the tensor-core backward
+ * forms the probabilities as exp(s - lse) and skips its per-row max / sum (other
+ * kernels ignore it).  Same inputs must be given to both calls.  The
  * reference keeps nothing but the five inputs (universal_attention_autograd.py:
  * 166-169); this is the "tiny extra saved tensor" variant of the same recompute. */
 size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags);
@@ -133,6 +136,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
                 const void* kc, const void* vc, const void* xq,
                 const void* static_src, const void* static_dest,
                 const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype, const void* carry_in,
+                const float* lse_cm,
                 void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
 

@@ -44,7 +44,7 @@ SIGNATURES = {
     "ua_bwd": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_carry_bytes": (_sz, [_dp, _i, _i]),
     "ua_fwd_keep": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
-    "ua_bwd_kept": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "ua_bwd_kept": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_fwd_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_decay_totals_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ua_bwd_rows_workspace_bytes": (_sz, [_dp, _i]),

@@ -336,7 +336,7 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
   bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0;
+  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
 }
 
@@ -358,7 +358,7 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
   bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1;
+  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
 }
 
@@ -367,13 +367,13 @@ int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const 
            int g_denom_dtype, void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
            void* workspace, size_t workspace_bytes, int flags, void* stream) {
   return ua_bwd_kept(dims, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, g_denom_dtype,
-                     nullptr, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, workspace_bytes, flags, stream);
+                     nullptr, nullptr, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, workspace_bytes, flags, stream);
 }
 
 int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
                 const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
-                int g_denom_dtype, const void* carry_in, void* dkc, void* dvc, void* dxq, void* dstatic_src,
-                void* dstatic_dest, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+                int g_denom_dtype, const void* carry_in, const float* lse_cm, void* dkc, void* dvc, void* dxq,
+                void* dstatic_src, void* dstatic_dest, void* workspace, size_t workspace_bytes, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -404,6 +404,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     bp.status = reinterpret_cast<int*>(ws);
     bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
     ua::sm100::whole_sequence(bp);
+    bp.lse = lse_cm;
     e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, carry_tab, carry_in == nullptr, nullptr, st);
     if (e) return e;
     const size_t BHs = (size_t)s.B * s.H;

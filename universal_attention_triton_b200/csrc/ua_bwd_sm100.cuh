@@ -65,6 +65,7 @@ struct BwdParams {
   float* acc_dv;           // optional (b*h, L, 64) fp32: dV_i is ADDED here instead of written to dvc
   float* acc_ds;           // optional (b*h, L) fp32: d static_src is added here instead of written to dss
   int decay_only;          // correction pass: only the decay gradient that suffix_in induces (no heads, no dV)
+  const float* lse;        // optional (b,h,n,r,L) fp32: the forward's log-sum-exp; spares the per-row max / sum (whole-sequence calls)
 };
 
 struct BwdCfg {
@@ -447,7 +448,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-template <typename TG>
+template <typename TG, bool kLse>
 __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part, const CUtensorMap* tmDQ,
                                            const CUtensorMap* tmDK) {
   const int L = p.s.L, R = p.decay_only ? 0 : p.s.R, N = p.s.N, Rq = p.s.R;
@@ -584,13 +585,15 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
       const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
                                         : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
+      const float lse2 = kLse ? p.lse[grow] * kLog2e : 0.f;
       if (!c.wait_w(bSdpFull, rc)) return;
       UA_PH(3)
       tc_fence_after();
       uint32_t pp[16], dd[16];
-      if (valid) {
+      {
         // ---- thread = row: s = S + C on 32 columns held in registers ------------------------
         float sv[32];
+        uint32_t dp[32];
         {
           uint32_t t[32];
           tmem_ld32(X0, t);
@@ -607,42 +610,62 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
             sv[4 * u + 3] = __uint_as_float(t[4 * u + 3]) + cv.w;
           }
         }
-        // every group stabilises its 32 columns with its own maximum; one rendezvous then
-        // combines (max, sum e, sum e dP) of the four groups
-        float m = sv[0];
+        float corr, linv;
+        if (kLse) {
+          // the forward's log-sum-exp makes P = exp(s - lse) directly; only sum_k P dP crosses the groups
+          tmem_ld32(X1 + col0, dp);
+          tc_wait_ld();
+          float edp = 0.f;
 #pragma unroll
-        for (int x = 1; x < 32; ++x) m = fmaxf(m, sv[x]);
-        UA_PH(11)
-        const float mbias = m * kLog2e;
-        uint32_t dp[32];
-        tmem_ld32(X1 + col0, dp);
-        tc_wait_ld();
-        float l = 0.f, edp = 0.f;
+          for (int x = 0; x < 32; ++x) {
+            const float e = ex2(fmaf(sv[x], kLog2e, -lse2));
+            sv[x] = e;
+            edp = fmaf(e, __uint_as_float(dp[x]), edp);
+          }
+          UA_PH(13)
+          float4 all[kParts];
+          mb.gather(make_float4(edp, 0.f, 0.f, 0.f), all);
+          if (!mb.ok) return;
+          UA_PH(14)
+          corr = gd - ((all[0].x + all[1].x) + (all[2].x + all[3].x));       // g_denom - sum_k P dP
+          linv = 1.0f;
+        } else {
+          // every group stabilises its 32 columns with its own maximum; one rendezvous then
+          // combines (max, sum e, sum e dP) of the four groups
+          float m = sv[0];
 #pragma unroll
-        for (int x = 0; x < 32; ++x) {
-          const float e = ex2(fmaf(sv[x], kLog2e, -mbias));
-          sv[x] = e;
-          l += e;
-          edp = fmaf(e, __uint_as_float(dp[x]), edp);
+          for (int x = 1; x < 32; ++x) m = fmaxf(m, sv[x]);
+          UA_PH(11)
+          const float mbias = m * kLog2e;
+          tmem_ld32(X1 + col0, dp);
+          tc_wait_ld();
+          float l = 0.f, edp = 0.f;
+#pragma unroll
+          for (int x = 0; x < 32; ++x) {
+            const float e = ex2(fmaf(sv[x], kLog2e, -mbias));
+            sv[x] = e;
+            l += e;
+            edp = fmaf(e, __uint_as_float(dp[x]), edp);
+          }
+          UA_PH(13)
+          float4 all[kParts];
+          mb.gather(make_float4(m, l, edp, 0.f), all);
+          if (!mb.ok) return;
+          UA_PH(14)
+          const float mrow = fmaxf(fmaxf(all[0].x, all[1].x), fmaxf(all[2].x, all[3].x));
+          float lrow = 0.f, edprow = 0.f;
+#pragma unroll
+          for (int q = 0; q < kParts; ++q) {
+            const float f = ex2((all[q].x - mrow) * kLog2e);
+            lrow = fmaf(all[q].y, f, lrow);
+            edprow = fmaf(all[q].z, f, edprow);
+          }
+          linv = ex2((m - mrow) * kLog2e) / lrow;                      // own rescale folded into 1/l
+          corr = gd - edprow / lrow;                                   // g_denom - sum_k P dP
         }
-        UA_PH(13)
-        float4 all[kParts];
-        mb.gather(make_float4(m, l, edp, 0.f), all);
-        if (!mb.ok) return;
-        UA_PH(14)
-        const float mrow = fmaxf(fmaxf(all[0].x, all[1].x), fmaxf(all[2].x, all[3].x));
-        float lrow = 0.f, edprow = 0.f;
-#pragma unroll
-        for (int q = 0; q < kParts; ++q) {
-          const float f = ex2((all[q].x - mrow) * kLog2e);
-          lrow = fmaf(all[q].y, f, lrow);
-          edprow = fmaf(all[q].z, f, edprow);
-        }
-        const float linv = ex2((m - mrow) * kLog2e) / lrow;          // own rescale folded into 1/l
-        const float corr = gd - edprow / lrow;                       // g_denom - sum_k P dP
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          const float p0 = sv[2 * u] * linv, p1 = sv[2 * u + 1] * linv;
+          const float p0 = kLse ? sv[2 * u] : sv[2 * u] * linv, p1 = kLse ? sv[2 * u + 1] : sv[2 * u + 1] * linv;
           const float d0 = p0 * (__uint_as_float(dp[2 * u]) + corr), d1 = p1 * (__uint_as_float(dp[2 * u + 1]) + corr);
           __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
           pp[u] = *reinterpret_cast<uint32_t*>(&hp);
@@ -979,7 +1002,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   }
 }
 
-template <typename TG>
+template <typename TG, bool kLse>
 __global__ void __launch_bounds__(640, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
@@ -1045,7 +1068,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) bwd_mma(c, p, warp - 1);
   } else if (warp >= 4) {
-    bwd_worker<TG>(c, p, (warp - 4) >> 2, &tmDQ, &tmDK);
+    bwd_worker<TG, kLse>(c, p, (warp - 4) >> 2, &tmDQ, &tmDK);
     if (threadIdx.x == 128) bulk_wait_all();      // the leader's reduce-adds have landed before the block retires
   }
 

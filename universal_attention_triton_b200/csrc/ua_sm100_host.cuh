@@ -103,7 +103,7 @@ inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 &
 // Fills the row-range / sharding fields of BwdParams for a call over the whole sequence.
 inline void whole_sequence(BwdParams& p) {
   p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
-  p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0;
+  p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0; p.lse = nullptr;
 }
 
 // Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
@@ -131,7 +131,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
     if (e) return e;
   }
-  auto kern = bwd_kernel<TG>;
+  auto kern = p.lse ? bwd_kernel<TG, true> : bwd_kernel<TG, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;

@@ -99,9 +99,10 @@ def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0, keep_carry: 
     return out_cm, lse_cm, denom_cm
 
 
-def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0, carry=None):
+def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0, carry=None, lse=None):
     """Gradients (dkc, dvc, dxq, dstatic_src, dstatic_dest) shaped and typed like the inputs.
-    ``carry``: the table ``forward_cm(keep_carry=True)`` returned for the same inputs (skips the pre-pass)."""
+    ``carry``: the table ``forward_cm(keep_carry=True)`` returned for the same inputs (skips the pre-pass).
+    ``lse``: the fp32 ``lse_cm (b,h,n,r,L)`` of the same forward (lets the tensor-core backward skip its row max / sum)."""
     _require_cuda(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
@@ -130,8 +131,12 @@ def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
         if carry is not None and carry.numel() * 4 != lib.ua_carry_bytes(ctypes.byref(dims), code, flags):
             carry = None
+        if lse is not None:
+            if lse.dtype != torch.float32 or tuple(lse.shape) != (b, h, n, r, L) or not lse.is_cuda:
+                raise ValueError("lse must be the fp32 chunk-major (b,h,n,r,L) log-sum-exp of the forward")
+            lse = lse.contiguous()
         rc = lib.ua_bwd_kept(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
-                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype), _ptr(carry),
+                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype), _ptr(carry), _ptr(lse),
                         _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss), _ptr(dsd), _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_bwd")
         _check_status(lib, ws, "ua_bwd")
