@@ -327,7 +327,9 @@ def main():
     def step(record):
         e0, e1, e2 = ev(), ev(), ev()
         e0.record()
-        out_cm, lse_cm, denom_cm, carry = ops.forward_cm(kc, vc, xq, ss, sd, keep_carry=not w["fwd_only"])
+        res = ops.forward_cm(kc, vc, xq, ss, sd, keep_carry=not w["fwd_only"])
+        out_cm, lse_cm, denom_cm = res[:3]
+        carry = res[3] if len(res) > 3 else None
         e1.record()
         if not w["fwd_only"]:
             grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags, carry=carry, lse=lse_cm)
