@@ -269,6 +269,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--zigzag", action="store_true", help="with --mode sp: balanced block assignment")
+    ap.add_argument("--merged-entry", default=None, choices=["composed", "fused"],
+                    help="end-to-end leg through UniversalAttentionMerged (the additional one-call entry point, with the "
+                         "given backward) instead of the drop-in pair UniversalAttention + SMVecMatMul")
     ap.add_argument("--skip-masked-grads", action="store_true",
                     help="device-resident step without the gradient through fully masked blocks (valid when SMVecMatMul is upstream)")
     ap.add_argument("--mode", default="bh", choices=["bh", "sp"],
@@ -294,7 +297,10 @@ def main():
         return
 
     import torch.distributed as dist
-    from universal_attention_triton_b200 import SMVecMatMul, UniversalAttention, _lib, ops, set_strict_masked_grads
+    from universal_attention_triton_b200 import (SMVecMatMul, UniversalAttention, UniversalAttentionMerged, _lib, ops,
+                                                set_merged_backward, set_strict_masked_grads)
+    if args.merged_entry:
+        set_merged_backward(args.merged_entry)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the operator)")
     _lib.load()
@@ -414,8 +420,11 @@ def main():
                 grads = []
             else:
                 xs = [t.detach().requires_grad_() for t in dev_in[b]]
-                out, denom = UniversalAttention.apply(*xs)
-                merged = SMVecMatMul.apply(out, denom)
+                if args.merged_entry:
+                    merged = UniversalAttentionMerged.apply(*xs)
+                else:
+                    out, denom = UniversalAttention.apply(*xs)
+                    merged = SMVecMatMul.apply(out, denom)
                 loss = merged.float().pow(2).sum()
                 loss.backward()
                 grads = [x.grad for x in xs]
@@ -452,7 +461,8 @@ def main():
         set_strict_masked_grads(True)
         e2e = {"value": tokens / (e_ms / K * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms / K,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "path": "UniversalAttention.apply -> SMVecMatMul.apply -> pow(2).sum() -> backward (main.py:55-62 flow); "
+               "path": (f"UniversalAttentionMerged.apply ({args.merged_entry} backward)" if args.merged_entry else "UniversalAttention.apply -> SMVecMatMul.apply") +
+                       " -> pow(2).sum() -> backward (main.py:55-62 flow); "
                        "copies of neighbouring steps overlap the compute (three streams)"}
 
     if rank == 0:

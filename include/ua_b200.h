@@ -250,6 +250,31 @@ int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference,
 int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
                  void* merged, void* stream);
 
+/* ua_merge_fwd that also returns, per row, the log-sum-exp over ALL key chunks: row_lse (b,h,r,L) fp32 (NULL: not
+ * wanted).  It is what ua_bwd_merged needs. */
+int ua_merge_fwd_stats(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
+                       void* merged, float* row_lse, void* stream);
+
+/* out[row] = a[row] . b[row] for `rows` rows of head_dim elements (fp32 result).  With a = the gradient of the merged
+ * output and b = the merged output this is the row_delta of ua_bwd_merged. */
+int ua_row_dot(long long rows, int head_dim, int dtype, const void* a, const void* b, float* out, void* stream);
+
+/* Backward of the COMPOSITION  merged = SMVecMatMul(UniversalAttention(kc, vc, xq, static_src, static_dest))
+ * (the flow of the reference's driver, main.py:55-62; operator universal_attention_autograd.py:9-99, merge :278-297)
+ * in one kernel, for callers that only consume the merged output (b,h,r,L,d).  The merged output is the softmax over
+ * ALL keys of a row, so with row_lse (ua_merge_fwd_stats) and row_delta = g_merged . merged (ua_row_dot) the
+ * probabilities are exp(s - row_lse) and dS = P (dP - row_delta): neither the (b,h,n,r,L,d) gradient of `out` nor
+ * `out` itself is read, and the rows before a key chunk contribute nothing.  The reference has no fused form; values
+ * equal ua_merge_bwd followed by ua_bwd up to rounding (the reference rounds the merge weights and `out` to the input
+ * dtype).  carry_in as for ua_bwd_kept (NULL allowed).  Workspace: ua_bwd_workspace_bytes().  bf16, chunk 128,
+ * head_dim 64 only (UA_ERR_UNSUPPORTED otherwise: use ua_merge_bwd + ua_bwd). */
+int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype,
+                  const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest,
+                  const void* g_merged, const float* row_lse, const float* row_delta, const void* carry_in,
+                  void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* SMVecMatMul.backward (universal_attention_autograd.py:291-297) producing
  * chunk-major gradients: g_out_cm (dtype) and g_lse_cm (fp32).  head_dim must be a
  * power of two between 8 (bf16) / 4 (fp32) and 128.  With UA_FLAG_SKIP_MASKED_FILL the

@@ -33,6 +33,24 @@ def test_header_symbols_exported(lib):
     assert set(names) == set(_lib.SIGNATURES), "python binding table and header disagree"
 
 
+def declared_parameter_counts():
+    """name -> number of parameters of every function declaration in the header."""
+    text = open(os.path.join(ROOT, "include", "ua_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    counts = {}
+    for name, params in re.findall(r"\b(ua_[a-z0-9_]+)\s*\(([^()]*)\)\s*;", text):
+        params = params.strip()
+        counts[name] = 0 if params in ("", "void") else params.count(",") + 1
+    return counts
+
+
+def test_binding_table_has_the_headers_parameter_counts(lib):
+    counts = declared_parameter_counts()
+    assert set(counts) == set(_lib.SIGNATURES)
+    for name, (_, argtypes) in _lib.SIGNATURES.items():
+        assert len(argtypes) == counts[name], (name, len(argtypes), counts[name])
+
+
 def test_version_and_error_strings(lib):
     assert lib.ua_version() >= 1
     assert lib.ua_error_string(0) == b"ok"

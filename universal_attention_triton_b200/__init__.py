@@ -5,9 +5,11 @@ from .universal_attention_autograd import (  # noqa: F401
     SMVecMatMul,
     UniversalAttention,
     UniversalAttention2,
+    UniversalAttentionMerged,
+    set_merged_backward,
     set_output_layout,
     set_strict_masked_grads,
 )
 
-__all__ = ["UniversalAttention", "UniversalAttention2", "SMVecMatMul", "set_output_layout",
+__all__ = ["UniversalAttention", "UniversalAttention2", "UniversalAttentionMerged", "SMVecMatMul", "set_output_layout", "set_merged_backward",
            "set_strict_masked_grads", "ops"]

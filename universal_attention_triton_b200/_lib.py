@@ -57,6 +57,9 @@ SIGNATURES = {
     "ua_relayout": (_i, [_dp, _i, _i, _i, _vp, _vp, _vp]),
     "ua_merge_fwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp]),
     "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "ua_merge_fwd_stats": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp]),
+    "ua_row_dot": (_i, [ctypes.c_longlong, _i, _i, _vp, _vp, _vp, _vp]),
+    "ua_bwd_merged": (_i, [_dp, _i, _i] + [_vp] * 15 + [_sz, _vp]),
 }
 
 _lib = None

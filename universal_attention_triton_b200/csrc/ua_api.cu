@@ -336,7 +336,7 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
   bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr;
+  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
 }
 
@@ -358,7 +358,7 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
   bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr;
+  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
 }
 
@@ -505,6 +505,11 @@ int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference,
 }
 
 int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, void* merged, void* stream) {
+  return ua_merge_fwd_stats(dims, dtype, out_cm, lse_cm, merged, nullptr, stream);
+}
+
+int ua_merge_fwd_stats(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, void* merged, float* row_lse,
+                       void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
@@ -517,7 +522,7 @@ int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float*
   const unsigned blocks = (unsigned)((rows * tpr + ua::aux::kMergeThreads - 1) / ua::aux::kMergeThreads);
 #define UA_MERGE_FWD(T, TPR)                                                                                         \
   ua::aux::merge_fwd_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(static_cast<const T*>(out_cm), lse_cm, \
-                                                                                static_cast<T*>(merged), rows, s.N, s.R, s.L)
+                                                                                static_cast<T*>(merged), row_lse, rows, s.N, s.R, s.L)
   if (dtype == UA_BF16 && s.D == 64) UA_MERGE_FWD(bf16, 8);
   else if (dtype == UA_BF16 && s.D == 128) UA_MERGE_FWD(bf16, 16);
   else if (dtype == UA_BF16 && s.D == 32) UA_MERGE_FWD(bf16, 4);
@@ -532,6 +537,71 @@ int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float*
   else return UA_ERR_UNSUPPORTED;
 #undef UA_MERGE_FWD
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_row_dot(long long rows, int head_dim, int dtype, const void* a, const void* b, float* out, void* stream) {
+  if (rows <= 0 || head_dim <= 0) return UA_ERR_BAD_DIMS;
+  if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
+  if (!a || !b || !out) return UA_ERR_NULL_POINTER;
+  if (!aligned16(a) || !aligned16(b)) return UA_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int tpr = head_dim * (dtype == UA_F32 ? 4 : 2) / 16;
+  if (tpr < 1 || tpr > 32 || (tpr & (tpr - 1)) || tpr * 16 != head_dim * (dtype == UA_F32 ? 4 : 2)) return UA_ERR_UNSUPPORTED;
+  const unsigned blocks = (unsigned)((rows * tpr + ua::aux::kMergeThreads - 1) / ua::aux::kMergeThreads);
+#define UA_ROW_DOT(T, TPR) \
+  ua::aux::row_dot_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(static_cast<const T*>(a), static_cast<const T*>(b), out, rows)
+  if (dtype == UA_BF16) {
+    if (tpr == 16) UA_ROW_DOT(bf16, 16); else if (tpr == 8) UA_ROW_DOT(bf16, 8); else if (tpr == 4) UA_ROW_DOT(bf16, 4);
+    else if (tpr == 2) UA_ROW_DOT(bf16, 2); else if (tpr == 1) UA_ROW_DOT(bf16, 1); else return UA_ERR_UNSUPPORTED;
+  } else {
+    if (tpr == 32) UA_ROW_DOT(float, 32); else if (tpr == 16) UA_ROW_DOT(float, 16); else if (tpr == 8) UA_ROW_DOT(float, 8);
+    else if (tpr == 4) UA_ROW_DOT(float, 4); else if (tpr == 2) UA_ROW_DOT(float, 2); else UA_ROW_DOT(float, 1);
+  }
+#undef UA_ROW_DOT
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest, const void* g_merged, const float* row_lse,
+                  const float* row_delta, const void* carry_in, void* dkc, void* dvc, void* dxq, void* dstatic_src,
+                  void* dstatic_dest, void* workspace, size_t workspace_bytes, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq || !static_src || !static_dest || !g_merged || !row_lse || !row_delta || !dkc || !dvc || !dxq ||
+      !dstatic_src || !dstatic_dest)
+    return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(g_merged) || !aligned16(dvc) || !aligned16(dkc) ||
+      !aligned16(dxq))
+    return UA_ERR_ALIGNMENT;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  BwdWorkspaceTc w = bwd_layout_tc(s);
+  if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  char* ws = static_cast<char*>(workspace);
+  if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
+  ua::sm100::BwdParams bp;
+  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
+  bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
+  float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
+  bp.carry = carry_tab;
+  bp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
+  bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
+  bp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+  bp.dvc = static_cast<bf16*>(dvc);
+  bp.dss = dstatic_src;
+  bp.status = reinterpret_cast<int*>(ws);
+  bp.skip_masked = 1;
+  ua::sm100::whole_sequence(bp);
+  bp.merged = 1; bp.row_lse = row_lse; bp.row_delta = row_delta;
+  e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_merged, bp, carry_tab, carry_in == nullptr, nullptr, st);
+  if (e) return e;
+  const size_t BHs = (size_t)s.B * s.H;
+  if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;
+  if ((e = convert_any(dtype, bp.acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
+  if ((e = convert_any(gate_dtype, bp.acc_dt, dstatic_dest, BHs * s.L, st))) return e;
+  return UA_OK;
 }
 
 int ua_merge_bwd(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm, const void* g_merged,

@@ -115,7 +115,8 @@ __device__ __forceinline__ void merge_row_stats(const float* lse_row, size_t nst
 // merged[row][d] = sum_n softmax_n(lse[n][row]) * out_cm[n][row][d]
 template <typename T, int TPR>
 __global__ void __launch_bounds__(kMergeThreads) merge_fwd_kernel(const T* __restrict__ out_cm, const float* __restrict__ lse_cm,
-                                                                  T* __restrict__ merged, long long rows, int N, int R, int L) {
+                                                                  T* __restrict__ merged, float* __restrict__ row_lse,
+                                                                  long long rows, int N, int R, int L) {
   constexpr int kN = Vec16<T>::kN;
   constexpr int D = TPR * kN;
   const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
@@ -143,6 +144,27 @@ __global__ void __launch_bounds__(kMergeThreads) merge_fwd_kernel(const T* __res
     }
   }
   if (live) Vec16<T>::store(merged + (size_t)row * D + sub * kN, acc);
+  if (live && sub == 0 && row_lse) row_lse[row] = m - logf(zinv);      // log-sum-exp of the row over all key chunks
+}
+
+// out[row] = a[row] . b[row] over D = TPR * kN elements (the delta = g . merged of the merged backward)
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kMergeThreads) row_dot_kernel(const T* __restrict__ a, const T* __restrict__ b,
+                                                                float* __restrict__ out, long long rows) {
+  constexpr int kN = Vec16<T>::kN;
+  constexpr int D = TPR * kN;
+  const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
+  const int sub = threadIdx.x % TPR;
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
+  float x[kN], y[kN];
+  Vec16<T>::load(a + (size_t)rr * D + sub * kN, x);
+  Vec16<T>::load(b + (size_t)rr * D + sub * kN, y);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < kN; ++i) acc = fmaf(x[i], y[i], acc);
+  acc = group_sum<TPR>(acc);
+  if (live && sub == 0) out[row] = acc;
 }
 
 // Backward of the merge: g_out_cm[n][row][:] = g[row][:] w_n ; g_lse[n][row] = (s_n - sum_m s_m w_m) w_n,

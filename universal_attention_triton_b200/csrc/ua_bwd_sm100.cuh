@@ -9,6 +9,14 @@
 // forward).  Rows before the chunk (j < i, uniform softmax) follow when the
 // masked-block gradient is requested.
 //
+// Three ways to form the probabilities (template parameter kMode):
+//   0  from the kernel's own row max / sum over the chunk's keys (inputs and upstream gradients only);
+//   1  as exp(s - lse) with the per-chunk log-sum-exp that the forward returned;
+//   2  "merged": the upstream gradient is that of the MERGED output  sum_n softmax_n(denom) out_n  (SMVecMatMul after
+//      the operator, universal_attention_autograd.py:278-297).  Then P = exp(s - L_row) with the log-sum-exp over ALL
+//      keys of the row, dO is the same (b,h,r,L,d) tile for every key chunk, dS = P (dP - delta_row) with
+//      delta_row = g . merged, nothing crosses the worker groups and the rows before a chunk contribute nothing.
+//
 // Per tile (q = rows, k = keys of the chunk, all tcgen05.mma with fp32 TMEM accumulators):
 //   G    = K_i K_j^T                keys on lanes  -> decay group: C^T to shared memory
 //   S_r  = Q_rj K_i^T,  dP_r = dO_rj V_i^T         rows on lanes -> softmax group
@@ -66,6 +74,10 @@ struct BwdParams {
   float* acc_ds;           // optional (b*h, L) fp32: d static_src is added here instead of written to dss
   int decay_only;          // correction pass: only the decay gradient that suffix_in induces (no heads, no dV)
   const float* lse;        // optional (b,h,n,r,L) fp32: the forward's log-sum-exp; spares the per-row max / sum (whole-sequence calls)
+  // merged mode: g_out is the (b,h,r,L,d) gradient of the merged output (g_denom unused)
+  int merged;
+  const float* row_lse;    // (b,h,r,L) fp32: log-sum-exp of the row over all keys
+  const float* row_delta;  // (b,h,r,L) fp32: g . merged
 };
 
 struct BwdCfg {
@@ -91,7 +103,7 @@ struct BwdCfg {
 
 enum BwdBar {
   bKvFull = 0, bKjFull, bInFull, bGFull, bX0Free, bSdpFull, bX1Free, bCReady, bCsFree, bPdsReady, bRDone, bG2Full,
-  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bMraw, bMask2, bFinal2, bInFull1, bInFree1, bPdsM0, bPdsM1, bNumBars
+  bDgReady, bDkjFull, bXchg, bFinal, bInFree, bStage, bMraw, bMask2, bFinal2, bInFull1, bInFree1, bPdsM0, bPdsM1, bStageFree, bNumBars
 };
 
 struct BwdCtx {
@@ -180,7 +192,7 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
   auto coords = [&](int T, int r, int& qrow, int& grow) {
     const int j = c.tile_j(T, N);
     qrow = (c.bh * R + r) * p.Lr + p.r0 + (j - p.j_begin) * 128;
-    grow = (int)((chunk_id * R + r) * p.Lr + p.r0 + (size_t)(j - p.j_begin) * 128);
+    grow = p.merged ? qrow : (int)((chunk_id * R + r) * p.Lr + p.r0 + (size_t)(j - p.j_begin) * 128);
   };
   int rc = 0;
   const int rc0 = c.nvalid * R;                           // steps of the sweep over the valid tiles
@@ -448,7 +460,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
-template <typename TG, bool kLse>
+template <typename TG, int kMode>
 __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, const int part, const CUtensorMap* tmDQ,
                                            const CUtensorMap* tmDK) {
   const int L = p.s.L, R = p.decay_only ? 0 : p.s.R, N = p.s.N, Rq = p.s.R;
@@ -583,9 +595,16 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
 
     for (int r = 0; r < R; ++r, ++rc) {
       const size_t grow = (chunk_id * Rq + r) * p.Lr + (size_t)rl + tid;
-      const float gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
-                                        : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
-      const float lse2 = kLse ? p.lse[grow] * kLog2e : 0.f;
+      const size_t qrow = ((size_t)c.bh * Rq + r) * p.Lr + (size_t)rl + tid;
+      float gd = 0.f, lse2 = 0.f;
+      if (kMode == 2) {
+        gd = -p.row_delta[qrow];
+        lse2 = p.row_lse[qrow] * kLog2e;
+      } else {
+        gd = p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
+                              : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
+        if (kMode == 1) lse2 = p.lse[grow] * kLog2e;
+      }
       if (!c.wait_w(bSdpFull, rc)) return;
       UA_PH(3)
       tc_fence_after();
@@ -611,7 +630,15 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
           }
         }
         float corr, linv;
-        if (kLse) {
+        if (kMode == 2) {
+          // merged upstream gradient: P = exp(s - L_row), dS = P (dP - g.merged); nothing crosses the groups
+          tmem_ld32(X1 + col0, dp);
+          tc_wait_ld();
+#pragma unroll
+          for (int x = 0; x < 32; ++x) sv[x] = ex2(fmaf(sv[x], kLog2e, -lse2));
+          corr = gd;
+          linv = 1.0f;
+        } else if (kMode == 1) {
           // the forward's log-sum-exp makes P = exp(s - lse) directly; only sum_k P dP crosses the groups
           tmem_ld32(X1 + col0, dp);
           tc_wait_ld();
@@ -665,7 +692,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
         }
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          const float p0 = kLse ? sv[2 * u] : sv[2 * u] * linv, p1 = kLse ? sv[2 * u + 1] : sv[2 * u + 1] * linv;
+          const float p0 = kMode ? sv[2 * u] : sv[2 * u] * linv, p1 = kMode ? sv[2 * u + 1] : sv[2 * u + 1] * linv;
           const float d0 = p0 * (__uint_as_float(dp[2 * u]) + corr), d1 = p1 * (__uint_as_float(dp[2 * u + 1]) + corr);
           __nv_bfloat162 hp = __floats2bfloat162_rn(p0, p1), hd = __floats2bfloat162_rn(d0, d1);
           pp[u] = *reinterpret_cast<uint32_t*>(&hp);
@@ -673,6 +700,15 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
         }
       }
       UA_PH(15)
+      if (kMode == 2) {
+        // No rendezvous has happened since the previous head's dQ tile was staged in the P buffer: the leader tells
+        // everybody when the reduce-add has read it.
+        if (part == 0 && tid == 0) {
+          bulk_wait_read_all();
+          mbar_arrive(c.bar(bStageFree));
+        }
+        if (!c.wait_w(bStageFree, rc)) return;
+      }
       store_row(sP, pp);
       store_row(sdS, dd);
       UA_PH(16)
@@ -1002,7 +1038,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   }
 }
 
-template <typename TG, bool kLse>
+template <typename TG, int kMode>
 __global__ void __launch_bounds__(640, 1)
 bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
@@ -1025,7 +1061,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     const int lo = c.i > p.j_begin ? c.i : p.j_begin;               // first row tile of the range that sees the chunk
     const int top = c.i < p.j_end ? c.i : p.j_end;                  // rows below this tile index lie before the chunk
     c.nvalid = p.j_end > lo ? p.j_end - lo : 0;
-    const int nmask = (p.skip_masked || p.decay_only || top <= p.j_begin) ? 0 : top - p.j_begin;
+    const int nmask = (p.skip_masked || p.decay_only || p.merged || top <= p.j_begin) ? 0 : top - p.j_begin;
     c.ntiles = c.nvalid + nmask;
   }
 
@@ -1068,7 +1104,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) bwd_mma(c, p, warp - 1);
   } else if (warp >= 4) {
-    bwd_worker<TG, kLse>(c, p, (warp - 4) >> 2, &tmDQ, &tmDK);
+    bwd_worker<TG, kMode>(c, p, (warp - 4) >> 2, &tmDQ, &tmDK);
     if (threadIdx.x == 128) bulk_wait_all();      // the leader's reduce-adds have landed before the block retires
   }
 

@@ -104,6 +104,7 @@ inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 &
 inline void whole_sequence(BwdParams& p) {
   p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
   p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0; p.lse = nullptr;
+  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr;
 }
 
 // Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
@@ -120,7 +121,8 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
   else if (!make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr)) return UA_ERR_CUDA;
   if (p.decay_only) {
     tmQ = tmK; tmG = tmK;          // the correction pass touches neither queries nor upstream gradients
-  } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, 64) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * p.Lr, 64)) {
+  } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, 64) ||
+             !make_rows_map(&tmG, g_out, (p.merged ? BH : BH * s.N) * s.R * p.Lr, 64)) {
     return UA_ERR_CUDA;
   }
   if (run_prepass && !p.decay_only) {
@@ -131,7 +133,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
     if (e) return e;
   }
-  auto kern = p.lse ? bwd_kernel<TG, true> : bwd_kernel<TG, false>;
+  auto kern = p.merged ? bwd_kernel<TG, 2> : (p.lse ? bwd_kernel<TG, 1> : bwd_kernel<TG, 0>);
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;

@@ -215,6 +215,76 @@ def merge_fwd_cm(out_cm, lse_cm):
     return merged
 
 
+def merge_fwd_stats_cm(out_cm, lse_cm):
+    """``merge_fwd_cm`` that also returns the fp32 log-sum-exp of every row over ALL key chunks, (b,h,r,L)."""
+    _require_cuda(out_cm, lse_cm)
+    lib = _lib.load()
+    b, h, n, r, L, d = out_cm.shape
+    dims = UaDims(b, h, r, n, L // n, d)
+    out_cm = out_cm.contiguous()
+    lse_cm = lse_cm.float().contiguous()
+    merged = torch.empty(b, h, r, L, d, dtype=out_cm.dtype, device=out_cm.device)
+    row_lse = torch.empty(b, h, r, L, dtype=torch.float32, device=out_cm.device)
+    with torch.cuda.device(out_cm.device):
+        rc = lib.ua_merge_fwd_stats(ctypes.byref(dims), _dtype_code(out_cm.dtype), _ptr(out_cm), _ptr(lse_cm), _ptr(merged),
+                                    _ptr(row_lse), _stream())
+    _lib.check(rc, "ua_merge_fwd_stats")
+    return merged, row_lse
+
+
+def row_dot(a, b):
+    """fp32 ``(a * b).sum(-1)`` of two equally shaped contiguous tensors (rows of head_dim elements)."""
+    _require_cuda(a, b)
+    lib = _lib.load()
+    a, b = a.contiguous(), b.to(a.dtype).contiguous()
+    out = torch.empty(a.shape[:-1], dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        rc = lib.ua_row_dot(a.numel() // a.shape[-1], a.shape[-1], _dtype_code(a.dtype), _ptr(a), _ptr(b), _ptr(out), _stream())
+    _lib.check(rc, "ua_row_dot")
+    return out
+
+
+def merged_backward_supported(kc, xq) -> bool:
+    """Shapes the one-kernel backward of the merged output takes (bf16, chunk 128, head_dim 64)."""
+    return xq.dtype == torch.bfloat16 and kc.shape[3] == 128 and kc.shape[4] == 64
+
+
+def backward_merged(kc, vc, xq, static_src, static_dest, g_merged, merged, row_lse, carry=None):
+    """Gradients of ``merged = SMVecMatMul(UniversalAttention(...))`` with respect to the five inputs, from the gradient
+    of the merged output alone (``ua_bwd_merged``): no (b,h,n,r,L,d) tensor is read or written."""
+    _require_cuda(kc, vc, xq, static_src, static_dest, g_merged, merged, row_lse)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq.shape[2]
+    L = n * c
+    dt = xq.dtype
+    code = _dtype_code(dt)
+    kcc, vcc = kc.contiguous(), vc.contiguous()
+    q = xq.reshape(b, h, r, L, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest.reshape(b, h, L), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    g = g_merged.to(dt).reshape(b, h, r, L, d).contiguous()
+    delta = row_dot(g, merged.reshape(b, h, r, L, d))
+    row_lse = row_lse.float().contiguous()
+    dims = UaDims(b, h, r, n, c, d)
+    with torch.cuda.device(kc.device):
+        dkc, dvc, dxq = torch.empty_like(kcc), torch.empty_like(vcc), torch.empty_like(q)
+        dss, dsd = torch.empty_like(ss), torch.empty_like(sd)
+        ws_bytes = lib.ua_bwd_workspace_bytes(ctypes.byref(dims), code, 0)
+        ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=kc.device)
+        if carry is not None and carry.numel() * 4 != lib.ua_carry_bytes(ctypes.byref(dims), code, 0):
+            carry = None
+        rc = lib.ua_bwd_merged(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
+                               _ptr(g), _ptr(row_lse), _ptr(delta), _ptr(carry), _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss),
+                               _ptr(dsd), _ptr(ws), ws_bytes, _stream())
+        _lib.check(rc, "ua_bwd_merged")
+        _check_status(lib, ws, "ua_bwd_merged")
+    return (dkc.view(kc.shape), dvc.view(vc.shape), dxq.view(xq.shape),
+            dss.to(static_src.dtype).view(static_src.shape), dsd.to(static_dest.dtype).view(static_dest.shape))
+
+
 def merge_bwd_cm(out_cm, lse_cm, g_merged, skip_zero_weight_blocks: bool = False):
     """SMVecMatMul backward on chunk-major storage -> (g_out_cm, g_lse_cm fp32).
     ``skip_zero_weight_blocks``: leave the blocks whose merge weight is exactly zero unwritten

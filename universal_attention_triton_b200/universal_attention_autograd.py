@@ -38,6 +38,21 @@ def set_output_layout(layout: str) -> None:
     _OUTPUT_LAYOUT = layout
 
 
+_MERGED_BACKWARD = "composed"
+
+
+def set_merged_backward(mode: str) -> None:
+    """Backward of ``UniversalAttentionMerged``.  ``"composed"`` (default): the merge backward followed by the
+    operator's backward, as accurate as the drop-in pair (gradients within ~5e-3 relative-Frobenius of the fp32
+    reference in bf16).  ``"fused"``: one kernel (``ua_bwd_merged``) that forms ``dS = P (dP - g.merged)`` with the
+    bf16 merged output, as flash-attention backwards do with their output; about 15 % faster end to end, but the
+    rounding of ``merged`` enters the decay gradient through a cumulative sum: gradients within 1-4e-2 of the
+    reference at L = 1024..4096 (inside the 5e-2 bar, ten times the composed path's error)."""
+    global _MERGED_BACKWARD
+    assert mode in ("composed", "fused")
+    _MERGED_BACKWARD = mode
+
+
 def set_strict_masked_grads(on: bool) -> None:
     """When off, backward skips the gradient through fully masked blocks (rows
     before a key chunk).  That gradient is exactly zero when ``SMVecMatMul``
@@ -121,3 +136,40 @@ class SMVecMatMul(Function):
         g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g,
                                               skip_zero_weight_blocks=not _STRICT_MASKED_GRADS)
         return ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
+
+
+class UniversalAttentionMerged(Function):
+    """``merged = SMVecMatMul.apply(*UniversalAttention.apply(kc, vc, xq, static_src, static_dest))`` as one Function:
+    the flow of the reference's driver (``main.py:55-62``) for callers that only consume the merged output
+    ``(b,h,r,l,d)``.  No counterpart in the reference.  The merge weights come from the fp32 log-sum-exp (the
+    drop-in ``denom`` is rounded to the input dtype as in the reference, which moves bf16 weights).  Backward: see
+    ``set_merged_backward``; with ``"fused"`` the (b,h,r,l,d,n) ``out`` tensor lives only inside the forward and
+    nothing of its size is kept for or produced by the backward.  ``xq`` and ``static_dest`` in either the 1-D or
+    the 2-D form."""
+
+    @staticmethod
+    def forward(ctx, kc, vc, xq, static_src, static_dest):
+        b, h, n, c, d = kc.shape
+        assert vc.shape == kc.shape and static_src.shape == (b, h, n, c)
+        assert xq.shape[:2] == (b, h) and xq.shape[-1] == d and xq[0, 0, 0].numel() == n * c * d
+        assert static_dest.numel() == b * h * n * c
+        out_cm, lse_cm, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, keep_carry=True)
+        merged, row_lse = ops.merge_fwd_stats_cm(out_cm, lse_cm)
+        ctx.fused = _MERGED_BACKWARD == "fused" and ops.merged_backward_supported(kc, xq)
+        ctx.ua_carry = carry
+        if ctx.fused:
+            ctx.save_for_backward(kc, vc, xq, static_src, static_dest, merged, row_lse)
+        else:
+            ctx.save_for_backward(kc, vc, xq, static_src, static_dest, out_cm, lse_cm)
+        return merged.view(*xq.shape)
+
+    @staticmethod
+    def backward(ctx, g):
+        kc, vc, xq, static_src, static_dest, x, y = ctx.saved_tensors
+        if ctx.fused:
+            return ops.backward_merged(kc, vc, xq, static_src, static_dest, g, x, y, carry=ctx.ua_carry)
+        g_out_cm, g_lse_cm = ops.merge_bwd_cm(x, y, g.reshape(x.shape[0], x.shape[1], x.shape[3], x.shape[4], x.shape[5]),
+                                              skip_zero_weight_blocks=True)
+        return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_lse_cm, _lib.FLAG_SKIP_MASKED_GRADS,
+                               carry=ctx.ua_carry, lse=y)
+
