@@ -237,6 +237,19 @@ int ua_static_status(void* stream);
  * in the reference (its kernels have no device-side waits). */
 int ua_workspace_status(const void* workspace, void* stream);
 
+/* Incremental (decode) step: row t of the forward against cached keys and values.  No counterpart in the reference
+ * (which always processes whole sequences, universal_attention_autograd.py:9-38); it is the serving form of the same
+ * arithmetic.  dims: n_chunks * chunk = capacity L_cap of the caches.  k_cache, v_cache (b,h,L_cap,d), src_cache
+ * (b,h,L_cap): rows 0..t filled (row t = the new token).  q_t (b,h,r,d), dest_t (b,h): the new row.  decay_state
+ * (b,h,L_cap) fp32, in/out: for every key its decay prefix up to the previous row; entries 0..t are updated (zero it
+ * before t = 0).  Outputs for the n_t = t / chunk + 1 key chunks that hold keys <= t: out_t (b,h,n_t,r,d) in `dtype`,
+ * lse_t (b,h,n_t,r) fp32 -- row t of out_cm / lse_cm of ua_fwd.  Steps must be issued in order t = 0, 1, 2, ...
+ * chunk a multiple of 32 up to 1024, q_per_kv <= 8. */
+int ua_decode_step(const UaDims* dims, int dtype, int gate_dtype, int t,
+                   const void* k_cache, const void* v_cache, const void* src_cache,
+                   const void* q_t, const void* dest_t, float* decay_state,
+                   void* out_t, float* lse_t, void* stream);
+
 /* Layout converters between chunk-major storage and the reference's contiguous
  * layouts: out (b,h,r,L,d,n) <-> out_cm (b,h,n,r,L,d), with inner = d; and
  * denom (b,h,r,L,n) <-> denom_cm (b,h,n,r,L) with inner = 1.  Element size

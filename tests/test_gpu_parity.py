@@ -488,3 +488,33 @@ def test_merged_entry_point_matches_composition_and_oracle(shape, mode):
     for a, b2, key in zip(fused, ref, GRADS):
         assert rel_fro(a.float().cpu(), b2.float()) <= (5e-2 if mode == "fused" else 1e-2), (key, rel_fro(a.float().cpu(), b2.float()))
 
+
+@pytest.mark.parametrize("dtype,shape", [(torch.float32, (1, 2, 2, 192, 64, 32)), (torch.bfloat16, (2, 1, 4, 384, 128, 64))])
+def test_decode_steps_reproduce_the_rows_of_the_forward(dtype, shape):
+    """ua_decode_step issued for t = 0, 1, 2, ... against growing caches gives row t of the whole-sequence forward
+    (out and log-sum-exp of every key chunk that holds keys <= t), and its decay state is the forward's decay prefix.
+    fp32: 1e-4 as for the fp32 kernels; bf16: the forward's own tolerance against the oracle."""
+    from universal_attention_triton_b200 import ops
+    B, H, R, L, c, D = shape
+    n = L // c
+    kc, vc, xq, ss, sd = O.make_inputs(B, H, R, L, c, D, dtype=dtype, seed=13)
+    ref_out, _, ref_lse = O.ua_forward(*[t.float() for t in (kc, vc, xq, ss, sd)])     # (b,h,r,L,d,n), (b,h,r,L,n)
+    k_cache = kc.reshape(B, H, L, D).cuda().contiguous()
+    v_cache = vc.reshape(B, H, L, D).cuda().contiguous()
+    src = ss.reshape(B, H, L).cuda().contiguous()
+    q, dest = xq.cuda(), sd.cuda()
+    state = torch.zeros(B, H, L, dtype=torch.float32, device="cuda")
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    worst_out = worst_lse = 0.0
+    for t in range(L):
+        out_t, lse_t = ops.decode_step(t, k_cache, v_cache, src, q[:, :, :, t].contiguous(), dest[:, :, t].contiguous(), state, c)
+        nt = t // c + 1
+        assert out_t.shape == (B, H, R, D, nt) and lse_t.shape == (B, H, R, nt)
+        ro, rl = ref_out[:, :, :, t, :, :nt], ref_lse[:, :, :, t, :nt]
+        eo = (out_t.float().cpu() - ro).abs() - 2.0 ** -8 * ro.abs() * (dtype != torch.float32)
+        worst_out = max(worst_out, eo.max().item())
+        worst_lse = max(worst_lse, ((lse_t.cpu() - rl).abs() - 1e-5 * rl.abs()).max().item())
+    assert worst_out <= tol, worst_out
+    assert worst_lse <= tol, worst_lse
+    assert torch.isfinite(state).all()
+

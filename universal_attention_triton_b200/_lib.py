@@ -60,6 +60,7 @@ SIGNATURES = {
     "ua_merge_fwd_stats": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp]),
     "ua_row_dot": (_i, [ctypes.c_longlong, _i, _i, _vp, _vp, _vp, _vp]),
     "ua_bwd_merged": (_i, [_dp, _i, _i] + [_vp] * 15 + [_sz, _vp]),
+    "ua_decode_step": (_i, [_dp, _i, _i, _i] + [_vp] * 9),
 }
 
 _lib = None

@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "ua_aux.cuh"
+#include "ua_decode.cuh"
 #include "ua_simt.cuh"
 #include "ua_sm100_host.cuh"
 
@@ -501,6 +502,30 @@ int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference,
   else
     ua::aux::relayout_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(src),
                                                              static_cast<uint32_t*>(dst), s.N, s.R, X, to_reference);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_decode_step(const UaDims* dims, int dtype, int gate_dtype, int t, const void* k_cache, const void* v_cache,
+                   const void* src_cache, const void* q_t, const void* dest_t, float* decay_state, void* out_t, float* lse_t,
+                   void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!k_cache || !v_cache || !src_cache || !q_t || !dest_t || !decay_state || !out_t || !lse_t) return UA_ERR_NULL_POINTER;
+  ua::Shape s = to_shape(dims);
+  if (t < 0 || t >= s.L) return UA_ERR_BAD_DIMS;
+  if (s.R > ua::decode::kMaxR || s.C > 1024 || (s.C & 31)) return UA_ERR_UNSUPPORTED;
+  ua::decode::Params p;
+  p.BH = s.B * s.H; p.R = s.R; p.D = s.D; p.C = s.C; p.Lcap = s.L; p.t = t;
+  p.kcache = k_cache; p.vcache = v_cache; p.src = src_cache; p.q = q_t; p.dest = dest_t; p.state = decay_state;
+  p.out = out_t; p.lse = lse_t;
+  const size_t smem = ua::decode::smem_bytes(p);
+  if (smem > 48 * 1024) return UA_ERR_UNSUPPORTED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 grid((unsigned)p.BH, (unsigned)(t / s.C + 1));
+  if (dtype == UA_F32) ua::decode::step_kernel<float, float><<<grid, s.C, smem, st>>>(p);
+  else if (gate_dtype == UA_F32) ua::decode::step_kernel<bf16, float><<<grid, s.C, smem, st>>>(p);
+  else ua::decode::step_kernel<bf16, bf16><<<grid, s.C, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 

@@ -450,3 +450,33 @@ def backward_rows_suffix(kc, vc, static_src, static_dest_rows, tile_begin: int, 
                                     _ptr(ss), _ptr(sd), _ptr(sf), _ptr(dk), _ptr(dsrc), _ptr(ddest), _ptr(ws), 256, _stream())
         _lib.check(rc, "ua_bwd_rows_suffix")
         _check_status(lib, ws, "ua_bwd_rows_suffix")
+
+
+def decode_step(t, k_cache, v_cache, src_cache, q_t, dest_t, decay_state, chunk):
+    """One incremental step (``ua_decode_step``): row ``t`` of the forward against the caches.
+
+    ``k_cache, v_cache (b,h,L_cap,d)``, ``src_cache (b,h,L_cap)`` hold rows ``0..t``; ``q_t (b,h,r,d)``, ``dest_t (b,h)``
+    are the new row; ``decay_state (b,h,L_cap)`` fp32 is updated in place (zeros before ``t = 0``).  Returns
+    ``(out_t (b,h,r,d,n_t), lse_t (b,h,r,n_t) fp32)`` as views with the key-chunk index last, i.e. row ``t`` of the
+    operator's ``out`` / ``denom`` restricted to the ``n_t = t // chunk + 1`` chunks that hold keys ``<= t``."""
+    _require_cuda(k_cache, v_cache, src_cache, q_t, dest_t, decay_state)
+    lib = _lib.load()
+    b, h, Lcap, d = k_cache.shape
+    r = q_t.shape[2]
+    dt = q_t.dtype
+    assert decay_state.dtype == torch.float32 and decay_state.is_contiguous() and decay_state.shape == (b, h, Lcap)
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and Lcap % chunk == 0
+    src = _gate_cast(src_cache, dt).contiguous()
+    dst = _gate_cast(dest_t, dt).contiguous()
+    if src.dtype != dst.dtype:
+        src, dst = src.float(), dst.float()
+    nt = t // chunk + 1
+    dims = UaDims(b, h, r, Lcap // chunk, chunk, d)
+    with torch.cuda.device(k_cache.device):
+        out = torch.empty(b, h, nt, r, d, dtype=dt, device=k_cache.device)
+        lse = torch.empty(b, h, nt, r, dtype=torch.float32, device=k_cache.device)
+        rc = lib.ua_decode_step(ctypes.byref(dims), _dtype_code(dt), _dtype_code(src.dtype), int(t), _ptr(k_cache), _ptr(v_cache),
+                                _ptr(src), _ptr(q_t.contiguous()), _ptr(dst), _ptr(decay_state), _ptr(out), _ptr(lse), _stream())
+    _lib.check(rc, "ua_decode_step")
+    return out.permute(0, 1, 3, 4, 2), lse.permute(0, 1, 3, 2)
+
