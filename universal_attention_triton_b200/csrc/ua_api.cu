@@ -515,6 +515,8 @@ int ua_decode_step(const UaDims* dims, int dtype, int gate_dtype, int t, const v
   ua::Shape s = to_shape(dims);
   if (t < 0 || t >= s.L) return UA_ERR_BAD_DIMS;
   if (s.R > ua::decode::kMaxR || s.C > 1024 || (s.C & 31)) return UA_ERR_UNSUPPORTED;
+  if ((s.D * (dtype == UA_F32 ? 4 : 2)) % 16 != 0) return UA_ERR_UNSUPPORTED;
+  if (!aligned16(k_cache) || !aligned16(v_cache)) return UA_ERR_ALIGNMENT;
   ua::decode::Params p;
   p.BH = s.B * s.H; p.R = s.R; p.D = s.D; p.C = s.C; p.Lcap = s.L; p.t = t;
   p.kcache = k_cache; p.vcache = v_cache; p.src = src_cache; p.q = q_t; p.dest = dest_t; p.state = decay_state;

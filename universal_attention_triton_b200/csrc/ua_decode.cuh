@@ -10,6 +10,7 @@
 // exactly row t of the full forward.  O(t * d) work and cache reads per step: HBM-bound, one block per (b, h, chunk),
 // one thread per key of the chunk, fp32 CUDA-core arithmetic (no tile is large enough for the tensor cores).
 #pragma once
+#include "ua_aux.cuh"
 #include "ua_common.cuh"
 
 namespace ua {
@@ -53,13 +54,19 @@ __global__ void step_kernel(Params p) {
 #pragma unroll
   for (int r = 0; r < kMaxR; ++r) s[r] = 0.f;
   if (live) {
+    // the thread's key row, 16 bytes at a time (head_dim is a multiple of 16 bytes: checked by the host)
+    constexpr int kN = aux::Vec16<T>::kN;
     const T* krow = kc + (size_t)kk * D;
-    for (int e = 0; e < D; ++e) {
-      const float kv = Num<T>::ld(krow + e);
-      g = fmaf(kv, s_kt[e], g);
+    for (int e0 = 0; e0 < D; e0 += kN) {
+      float kv[kN];
+      aux::Vec16<T>::load(krow + e0, kv);
 #pragma unroll
-      for (int r = 0; r < kMaxR; ++r)
-        if (r < R) s[r] = fmaf(kv, s_q[r * D + e], s[r]);
+      for (int u = 0; u < kN; ++u) {
+        g = fmaf(kv[u], s_kt[e0 + u], g);
+#pragma unroll
+        for (int r = 0; r < kMaxR; ++r)
+          if (r < R) s[r] = fmaf(kv[u], s_q[r * D + e0 + u], s[r]);
+      }
     }
   }
   // decay state of this key after row t
