@@ -518,3 +518,40 @@ def test_decode_steps_reproduce_the_rows_of_the_forward(dtype, shape):
     assert worst_lse <= tol, worst_lse
     assert torch.isfinite(state).all()
 
+
+@pytest.mark.parametrize("shape,gate_mean,gate_fp32", [
+    ((1, 1, 1, 128, 128, 64), 0.0, False),      # a single key chunk: only the diagonal tile exists
+    ((1, 3, 3, 256, 128, 64), 0.0, False),      # odd head counts
+    ((1, 1, 8, 384, 128, 64), 0.0, False),      # eight query heads per kv head
+    ((1, 2, 2, 512, 128, 64), -4.0, False),     # weak gates: almost no decay (the numerics-stress distribution)
+    ((1, 2, 2, 512, 128, 64), 4.0, False),      # strong gates: most pairs saturate the clamp
+    ((1, 2, 2, 384, 128, 64), 0.0, True),       # fp32 gates with bf16 keys / values / queries
+])
+def test_tensor_core_kernels_on_edge_shapes_and_gates(shape, gate_mean, gate_fp32):
+    """Forward and backward of the tcgen05 kernels against the generic fp32 SIMT kernels of the same library on shapes
+    and gate distributions at the edges of what the tensor-core path takes (strict masked-block gradients, and the
+    backward both with and without the forward's log-sum-exp)."""
+    from universal_attention_triton_b200 import _lib, ops
+    B, H, R, L, c, D = shape
+    n = L // c
+    ins = list(O.make_inputs(B, H, R, L, c, D, dtype=torch.bfloat16, seed=77, gate_mean=gate_mean, gate_std=1.0))
+    if gate_fp32:
+        ins[3], ins[4] = ins[3].float(), ins[4].float()
+    cu = _cuda(*ins)
+    out_tc, lse_tc, den_tc, carry = ops.forward_cm(*cu, keep_carry=True)
+    out_sm, lse_sm, _ = ops.forward_cm(*cu, flags=_lib.FLAG_FORCE_SIMT)
+    valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda().view(1, 1, n, 1, L)
+    assert ((out_tc.float() - out_sm.float()).abs() * valid.unsqueeze(-1)).max() <= 2e-2 + 2.0 ** -8 * out_sm.float().abs().max()
+    assert (((lse_tc - lse_sm).abs() - 1e-5 * lse_sm.abs()) * valid).max() <= 2e-2
+    assert (lse_tc[~valid.expand_as(lse_tc)] <= -1e11).all()
+    gen = torch.Generator(device="cuda").manual_seed(78)
+    g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
+    g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    sm = ops.backward_cm(*cu, g_out, g_lse, flags=_lib.FLAG_FORCE_SIMT)
+    for kwargs in ({}, {"carry": carry, "lse": lse_tc}):
+        tc = ops.backward_cm(*cu, g_out, g_lse, **kwargs)
+        for a, b, key in zip(tc, sm, GRADS):
+            assert torch.isfinite(a.float()).all(), key
+            assert a.dtype == b.dtype
+            assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, kwargs.keys(), rel_fro(a.float().cpu(), b.float().cpu()))
+
