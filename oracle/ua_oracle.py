@@ -20,7 +20,7 @@ Unlike the reference (which loops over key chunks and, in the 2-D form, over
 row chunks carrying a running sum) everything here is evaluated on the full
 ``L x L`` key/row plane at once, so the fp32 summation order differs from the
 reference's; agreement is to rounding noise, not bitwise.  ``compute_dtype=
-torch.float64`` gives the arbiter used to judge which side of a disagreement is
+torch.float64`` gives the arbiter used to decide which side of a disagreement is
 closer to the exact value (the reference forces fp32 internally, so an fp64
 answer cannot be had from it by casting inputs).
 

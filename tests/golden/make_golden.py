@@ -19,7 +19,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("UA_REF_PATH", "/root/reference")
+REF = os.environ.get("UA_REF_PATH") or (sys.argv[1] if len(sys.argv) > 1 else None)
+if not REF or not os.path.isdir(REF):
+    sys.exit("set UA_REF_PATH (or pass as first argument) to a checkout of the reference implementation")
 sys.path.insert(0, REF)
 from universal_attention_autograd import SMVecMatMul, UniversalAttention, UniversalAttention2  # noqa: E402
 
