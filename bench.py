@@ -416,7 +416,7 @@ def main():
                 with torch.no_grad():
                     out, denom = UniversalAttention.apply(*dev_in[b])
                     merged = SMVecMatMul.apply(out, denom)
-                    loss = merged.float().pow(2).sum()
+                    loss = merged.pow(2).sum()
                 grads = []
             else:
                 xs = [t.detach().requires_grad_() for t in dev_in[b]]
@@ -425,7 +425,7 @@ def main():
                 else:
                     out, denom = UniversalAttention.apply(*xs)
                     merged = SMVecMatMul.apply(out, denom)
-                loss = merged.float().pow(2).sum()
+                loss = merged.pow(2).sum()
                 loss.backward()
                 grads = [x.grad for x in xs]
                 loss = loss.detach()
