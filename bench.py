@@ -269,6 +269,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--zigzag", action="store_true", help="with --mode sp: balanced block assignment")
+    ap.add_argument("--e2e-grads-to-host", action="store_true",
+                    help="end-to-end leg: also copy the five gradients back to pinned host memory every step")
     ap.add_argument("--merged-entry", default=None, choices=["composed", "fused"],
                     help="end-to-end leg through UniversalAttentionMerged (the additional one-call entry point, with the "
                          "given backward) instead of the drop-in pair UniversalAttention + SMVecMatMul")
@@ -385,7 +387,8 @@ def main():
     e2e = None
     if not args.no_e2e:
         h2d = sum(t.numel() * t.element_size() for t in host)
-        d2h = 4 + (0 if w["fwd_only"] else h2d)
+        grads_to_host = args.e2e_grads_to_host and not w["fwd_only"]
+        d2h = 4 + (h2d if grads_to_host else 0)      # the step's result is the loss; the gradients stay on the device
         set_strict_masked_grads(False)      # SMVecMatMul is upstream: the masked-block gradient is exactly zero
         host_grads = [torch.empty_like(t).pin_memory() for t in host]
         host_loss = torch.empty((), dtype=torch.float32).pin_memory()
@@ -434,7 +437,7 @@ def main():
                 s_out.wait_event(cmp_done[b])
                 host_loss.copy_(loss, non_blocking=True)
                 loss.record_stream(s_out)
-                for hg, g in zip(host_grads, grads):
+                for hg, g in zip(host_grads, grads if grads_to_host else []):
                     hg.copy_(g, non_blocking=True)
                     g.record_stream(s_out)
 
