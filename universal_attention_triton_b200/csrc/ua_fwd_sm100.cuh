@@ -34,6 +34,16 @@ namespace sm100 {
 
 using namespace ua::ptx;
 
+#ifdef UA_PROFILE_FWD
+#define UF_DECL long long uf_t = clock64(), uf_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#define UF(idx) { long long now_ = clock64(); uf_acc[idx] += now_ - uf_t; uf_t = now_; }
+#define UF_STORE(cond, base) if (blockIdx.x == 0 && (cond)) { for (int z = 0; z < 8; ++z) reinterpret_cast<long long*>(p.status)[2 + (base) + z] = uf_acc[z]; }
+#else
+#define UF_DECL
+#define UF(idx)
+#define UF_STORE(cond, base)
+#endif
+
 struct FwdParams {
   Shape s;
   const void* ssrc;
@@ -75,8 +85,12 @@ struct FwdCfg {
   static constexpr int oVi = oKi + kTileBytes;
   static constexpr int oKj = oVi + kTileBytes;
   static constexpr int oQ = oKj + kKjStages * kTileBytes;
+  // The decay prefix crosses from keys-on-lanes to rows-on-lanes through a 64 KB fp32 tile C^T[row][key].  With two
+  // of them (head_dim 64: they fit) the decay group computes tile T+1 while the softmax groups consume tile T;
+  // with one, the two alternate (measured at head_dim 64: 18.7k cycles per tile = decay 9.8k + softmax 14k, minus overlap).
+  static constexpr int kCBufs = (D == 64) ? 2 : 1;
   static constexpr int oCs = oQ + kQStages * kTileBytes;
-  static constexpr int oT3 = oCs + 65536;
+  static constexpr int oT3 = oCs + kCBufs * 65536;
   static constexpr int oBar = oT3 + 1024;
   static constexpr int oMisc = oBar + 256;
   static constexpr int oFill = oMisc + 64;                // bf16[D]: value of a fully masked output row
@@ -85,8 +99,9 @@ struct FwdCfg {
 };
 
 enum FwdBar {
-  kKvFull = 0, kKjFull = 1, kKjEmpty = 3, kQFull = 5, kQEmpty = 7, kGFull = 9, kGFree = 10, kCReady = 11, kCFree = 12,
-  kSFull = 13, kPReady = 15, kOFull = 17, kOFree = 19, kT3Ready = 21, kNumBars = 22
+  // (kCReady / kCFree: one barrier per C^T buffer, so that no waiter can fall two phases behind on a shared one)
+  kKvFull = 0, kKjFull = 1, kKjEmpty = 3, kQFull = 5, kQEmpty = 7, kGFull = 9, kGFree = 10, kCReady = 11, kCFree = 13,
+  kSFull = 15, kPReady = 17, kOFull = 19, kOFree = 21, kT3Ready = 23, kNumBars = 24
 };
 
 template <int D>
@@ -235,13 +250,16 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   uint8_t* sCs = c.smem + Cfg::oCs;
   const size_t key_id = ((size_t)c.bh * p.s.N + c.i) * 128 + k;
   float carry = p.carry_in ? p.carry_in[key_id] : 0.f;
+  UF_DECL
   for (int T = 0; T < c.ntiles; ++T) {
     const int j = c.j0 + T;
     float* t3buf = sT3 + (T & 1) * 128;
     t3buf[k] = cbrtf(Num<TG>::ld(sd + p.r0 + (j - p.j_begin) * 128 + k));
     c.arrive_w(kT3Ready);
     if (!c.wait_w(kT3Ready, T)) return;
+    UF(0)
     if (!c.wait_w(kGFull, T)) return;
+    UF(1)
     tc_fence_after();
     const bool diag = (j == c.i);
     if (p.carry) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
@@ -271,17 +289,21 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
       }
       tprev += local;
       if (!kCarryOnly) {
-        if (cb == 0 && T >= 1 && !c.wait_w(kCFree, T - 1)) return;
+        UF(2)
+        if (cb == 0 && T >= Cfg::kCBufs && !c.wait_w(kCFree + T % Cfg::kCBufs, T / Cfg::kCBufs - 1)) return;
+        UF(3)
 #pragma unroll
         for (int x = 0; x < 32; ++x) {
           const int q = cb * 32 + x;
-          *reinterpret_cast<float*>(sCs + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v[x];
+          *reinterpret_cast<float*>(sCs + (T % Cfg::kCBufs) * 65536 + q * 512 + ((((k >> 2) ^ (q & 7)) & 31) << 4) + (k & 3) * 4) = v[x];
         }
       }
     }
     carry = cval;
-    if (!kCarryOnly) c.arrive_w(kCReady);
+    if (!kCarryOnly) c.arrive_w(kCReady + T % Cfg::kCBufs);
+    UF(2)
   }
+  UF_STORE(k == 0, 0)
   if (p.total_out) p.total_out[key_id] = carry;
 }
 
@@ -292,25 +314,32 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
   const int L = p.s.L, R = p.s.R, N = p.s.N;
   const int row = threadIdx.x & 127;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
-  const uint8_t* sCrow = c.smem + Cfg::oCs + row * 512;
+  const uint8_t* sCrow0 = c.smem + Cfg::oCs + row * 512;
   const size_t chunk_id = (size_t)c.bh * N + c.i;
   const float kLog2e = 1.4426950408889634f, kLn2 = 0.6931471805599453f;
   int t = 0;
+  UF_DECL
   for (int T = 0; T < c.ntiles; ++T) {
     // Every softmax thread observes every phase of c_ready and arrives on c_free exactly
     // once per tile (after its last read of C in that tile), whether or not its group has
     // a head to process in this tile; parity waits stay within one phase of the barrier.
-    if (!c.wait_w(kCReady, T)) return;
+    UF(0)
+    const int cbuf = T % Cfg::kCBufs;
+    const uint8_t* sCrow = sCrow0 + cbuf * 65536;
+    if (!c.wait_w(kCReady + cbuf, T / Cfg::kCBufs)) return;
+    UF(1)
     int last_r = -1;
     for (int r = R - 1; r >= 0; --r)
       if (((T * R + r) & 1) == me) { last_r = r; break; }
-    if (last_r < 0) c.arrive_w(kCFree);
+    if (last_r < 0) c.arrive_w(kCFree + cbuf);
     for (int r = 0; r < R; ++r, ++t) {
       if ((t & 1) != me) continue;
       const int sb = t & 1, ob = t % Cfg::kOBufs;
       const uint32_t tS = c.tmem + (sb ? Cfg::tS1 : Cfg::tS0) + lane_base;
       const uint32_t tO = c.tmem + ((Cfg::kOBufs == 2 && ob) ? Cfg::tO1 : Cfg::tO0) + lane_base;
+      UF(0)
       if (!c.wait_w(kSFull + sb, t >> 1)) return;
+      UF(2)
       tc_fence_after();
       // pass 1: s = S + C (written back to TMEM), row max.  64 columns per round trip: the two loads are in flight together.
       float m = -INFINITY;
@@ -334,7 +363,8 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         tmem_st32(tS + cb * 64 + 32, s + 32);
       }
       tc_wait_st();
-      if (r == last_r) c.arrive_w(kCFree);
+      UF(3)
+      if (r == last_r) c.arrive_w(kCFree + cbuf);
       // pass 2: P = exp(s - m) as bf16 into the first 64 columns of the S buffer
       const float mb = m * kLog2e;
       float l = 0.f;
@@ -360,13 +390,16 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       tc_wait_st();
       tc_fence_before();
       c.arrive_w(kPReady + sb);
+      UF(4)
       const int qg = p.r0 + (c.j0 + T - p.j_begin) * 128 + row;      // row index inside the slab
       const float lse = m + lg2(l) * kLn2;
       const size_t orow = (chunk_id * R + r) * p.Lr + qg;
       p.lse[orow] = lse;
       if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
       const float linv = 1.0f / l;
+      UF(5)
       if (!c.wait_w(kOFull + sb, t >> 1)) return;
+      UF(6)
       tc_fence_after();
       __nv_bfloat16* orow_ptr = p.out + orow * D;
 #pragma unroll 1
@@ -390,8 +423,10 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         dst[2] = make_uint4(pk[8], pk[9], pk[10], pk[11]);
         dst[3] = make_uint4(pk[12], pk[13], pk[14], pk[15]);
       }
+      UF(7)
     }
   }
+  UF_STORE(row == 0 && me == 0, 8)
 }
 
 // Rows before the key chunk (j < i): every score is -1e12 (fp32 absorbs k.q), the softmax is
@@ -451,8 +486,8 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
     for (int b = 0; b < kNumBars; ++b) {
       uint32_t count = 1;
       // one arrival per warp of the group that signals
-      if (b == kGFree || b == kCReady || b == kT3Ready) count = 4;
-      if (b == kCFree) count = 8;
+      if (b == kGFree || b == kCReady || b == kCReady + 1 || b == kT3Ready) count = 4;
+      if (b == kCFree || b == kCFree + 1) count = 8;
       if (b == kPReady || b == kPReady + 1 || b == kOFree || b == kOFree + 1) count = 4;
       mbar_init(c.bar(b), count);
     }
