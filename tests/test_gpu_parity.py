@@ -555,3 +555,42 @@ def test_tensor_core_kernels_on_edge_shapes_and_gates(shape, gate_mean, gate_fp3
             assert a.dtype == b.dtype
             assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, kwargs.keys(), rel_fro(a.float().cpu(), b.float().cpu()))
 
+
+@pytest.mark.parametrize("shape", [(2, 2, 2, 256, 64), (1, 4, 1, 384, 48)])      # (b, n_kv, rep, s, d); d = 48 is zero-padded
+def test_attention_wrapper_against_global_softmax(shape):
+    """attention(q, k, v, ...) with the signature and head mapping of the reference's flash-style entry point
+    (universal_attention_kernel_opt.py:433-583): output and gradients against a direct fp32 evaluation of
+    softmax_k(q.k + decay) v over all keys, query head h reading kv head h % n_kv."""
+    from universal_attention_triton_b200.Universal_Attention.attention_opt import attention
+    b, n_kv, rep, s, d = shape
+    gen = torch.Generator().manual_seed(5)
+    q = torch.randn(b, n_kv * rep, s, d, generator=gen).bfloat16()
+    k = torch.randn(b, n_kv, s, d, generator=gen).bfloat16()
+    v = torch.randn(b, n_kv, s, d, generator=gen).bfloat16()
+    src = torch.randn(b, n_kv, s, generator=gen).sigmoid().bfloat16()
+    dst = torch.randn(b, n_kv, s, generator=gen).sigmoid().bfloat16()
+    g = torch.randn(b, n_kv * rep, s, d, generator=gen).bfloat16()
+
+    def reference(q, k, v, src, dst):
+        kf = k.float()
+        gram = kf @ kf.transpose(-1, -2)                                    # (b, kv, key, row)
+        aff = gram.clamp_min(0).pow(2 / 3) * src.float().pow(1 / 3).unsqueeze(-1) * dst.float().pow(1 / 3).unsqueeze(-2)
+        ell = torch.log1p(-aff.clamp(0, 1 - 1e-6))
+        idx = torch.arange(s)
+        ell = torch.where(idx.view(1, s) > idx.view(s, 1), ell, torch.zeros(()))
+        decay = ell.cumsum(-1).masked_fill(idx.view(1, s) < idx.view(s, 1), -1e12)      # (b, kv, key, row)
+        decay = decay.transpose(-1, -2).repeat(1, rep, 1, 1)                # head h -> kv head h % n_kv; (b, h, row, key)
+        score = q.float() @ kf.repeat(1, rep, 1, 1).transpose(-1, -2) + decay
+        return score.softmax(-1) @ v.float().repeat(1, rep, 1, 1)
+
+    ins = [t.clone().requires_grad_() for t in (q.float(), k.float(), v.float(), src.float(), dst.float())]
+    ref = reference(*ins)
+    ref.backward(g.float())
+    cu = [t.cuda().requires_grad_() for t in (q, k, v, src, dst)]
+    out = attention(cu[0], cu[1], cu[2], True, 1.0, cu[3], cu[4])
+    assert out.shape == q.shape and out.dtype == q.dtype
+    out.backward(g.cuda())
+    assert (out.float().cpu() - ref).abs().max() <= 2e-2 + 2.0 ** -8 * ref.abs().max()
+    for a, r_, key in zip(cu, ins, ["dq", "dk", "dv", "dsrc", "ddest"]):
+        assert rel_fro(a.grad.float().cpu(), r_.grad) <= 5e-2, (key, rel_fro(a.grad.float().cpu(), r_.grad))
+
