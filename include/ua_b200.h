@@ -237,6 +237,24 @@ int ua_static_status(void* stream);
  * in the reference (its kernels have no device-side waits). */
 int ua_workspace_status(const void* workspace, void* stream);
 
+/* Input prologue.  The reference's driver builds the operator's inputs from token-major projections with transposes
+ * and views (main.py:24-31): query_state (b,s,n,d) -> xq (b,n_kv,rep,s,d) (query head kv * rep + r), key_state /
+ * value_state (b,s,n_kv,d) -> kc / vc (b,n_kv,s,d) (= (b,n_kv,n_chunks,chunk,d)), gate_state (b,s,2,n_kv) ->
+ * static_src, static_dest (b,n_kv,s).  ua_prepare_inputs does this in one pass and, on request, what a model applies
+ * on the way (Universal_Attention/triton/_debug.py:470-475): UA_PREP_NORMALIZE_KEYS divides every key by (|k| + 1e-6)
+ * (key_norm (b,n_kv,s) fp32 receives |k|: the backward needs it), UA_PREP_SIGMOID_GATES passes the gate logits through a
+ * sigmoid.  ua_prepare_inputs_bwd maps the gradients of the five outputs back to the four projections (kc, static_src,
+ * static_dest: the forward's outputs).  head_dim * element size must be a multiple of 16 bytes, at most 512. */
+enum UaPrepFlags { UA_PREP_NORMALIZE_KEYS = 1, UA_PREP_SIGMOID_GATES = 2 };
+int ua_prepare_inputs(int batch, int seq, int n_heads, int n_kv_heads, int head_dim, int dtype, int flags,
+                      const void* query_state, const void* key_state, const void* value_state, const void* gate_state,
+                      void* xq, void* kc, void* vc, void* static_src, void* static_dest, float* key_norm, void* stream);
+int ua_prepare_inputs_bwd(int batch, int seq, int n_heads, int n_kv_heads, int head_dim, int dtype, int flags,
+                          const void* g_xq, const void* g_kc, const void* g_vc,
+                          const void* g_static_src, const void* g_static_dest,
+                          const void* kc, const float* key_norm, const void* static_src, const void* static_dest,
+                          void* d_query_state, void* d_key_state, void* d_value_state, void* d_gate_state, void* stream);
+
 /* Incremental (decode) step: row t of the forward against cached keys and values.  No counterpart in the reference
  * (which always processes whole sequences, universal_attention_autograd.py:9-38); it is the serving form of the same
  * arithmetic.  dims: n_chunks * chunk = capacity L_cap of the caches.  k_cache, v_cache (b,h,L_cap,d), src_cache

@@ -594,3 +594,42 @@ def test_attention_wrapper_against_global_softmax(shape):
     for a, r_, key in zip(cu, ins, ["dq", "dk", "dv", "dsrc", "ddest"]):
         assert rel_fro(a.grad.float().cpu(), r_.grad) <= 5e-2, (key, rel_fro(a.grad.float().cpu(), r_.grad))
 
+
+@pytest.mark.parametrize("dtype,norm,sig", [(torch.float32, True, True), (torch.bfloat16, True, True), (torch.bfloat16, False, False)])
+def test_input_prologue_matches_the_drivers_views(dtype, norm, sig):
+    """prepare_inputs against the reference driver's transposes and views (main.py:24-31), with and without the key
+    normalisation and gate sigmoid of its harness (_debug.py:470-475), forward and backward."""
+    from universal_attention_triton_b200.input_prep import prepare_inputs
+    b, s, n, n_kv, d, c = 2, 256, 6, 2, 64, 128
+    rep = n // n_kv
+    gen = torch.Generator().manual_seed(21)
+    qs = torch.randn(b, s, n, d, generator=gen).to(dtype)
+    ks = torch.randn(b, s, n_kv, d, generator=gen).to(dtype)
+    vs = torch.randn(b, s, n_kv, d, generator=gen).to(dtype)
+    gs = torch.randn(b, s, 2 * n_kv, generator=gen).to(dtype)
+
+    def reference(qs, ks, vs, gs):
+        if norm:
+            ks = ks / (ks.pow(2).sum(-1, True).sqrt() + 1e-6)
+        if sig:
+            gs = gs.sigmoid()
+        xq = qs.transpose(1, 2).reshape(b, n_kv, rep, s, d)
+        kc = ks.transpose(1, 2).reshape(b, n_kv, s // c, c, d)
+        vc = vs.transpose(1, 2).reshape(b, n_kv, s // c, c, d)
+        st = gs.view(b, s, 2, n_kv).permute(2, 0, 3, 1)
+        return kc, vc, xq, st[0].reshape(b, n_kv, s // c, c), st[1]
+
+    ref_in = [t.float().clone().requires_grad_() for t in (qs, ks, vs, gs)]
+    ref_out = reference(*ref_in)
+    cu_in = [t.cuda().requires_grad_() for t in (qs, ks, vs, gs)]
+    out = prepare_inputs(*cu_in, chunk=c, normalize_keys=norm, sigmoid_gates=sig)
+    gens = [torch.randn(o.shape, generator=gen).to(dtype) for o in ref_out]
+    torch.autograd.backward(ref_out, [g.float() for g in gens])
+    torch.autograd.backward(out, [g.cuda() for g in gens])
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for a, r_ in zip(out, ref_out):
+        assert a.shape == r_.shape and a.dtype == dtype
+        assert (a.float().cpu() - r_).abs().max() <= tol * max(1.0, r_.abs().max().item())
+    for a, r_, key in zip(cu_in, ref_in, ["query", "key", "value", "gates"]):
+        assert rel_fro(a.grad.float().cpu(), r_.grad) <= (1e-5 if dtype == torch.float32 else 1e-2), key
+

@@ -61,7 +61,10 @@ SIGNATURES = {
     "ua_row_dot": (_i, [ctypes.c_longlong, _i, _i, _vp, _vp, _vp, _vp]),
     "ua_bwd_merged": (_i, [_dp, _i, _i] + [_vp] * 15 + [_sz, _vp]),
     "ua_decode_step": (_i, [_dp, _i, _i, _i] + [_vp] * 9),
+    "ua_prepare_inputs": (_i, [_i] * 7 + [_vp] * 11),
+    "ua_prepare_inputs_bwd": (_i, [_i] * 7 + [_vp] * 14),
 }
+PREP_NORMALIZE_KEYS, PREP_SIGMOID_GATES = 1, 2
 
 _lib = None
 

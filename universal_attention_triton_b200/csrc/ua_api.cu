@@ -7,6 +7,8 @@
 
 #include <mutex>
 
+#include <algorithm>
+
 #include "ua_aux.cuh"
 #include "ua_decode.cuh"
 #include "ua_simt.cuh"
@@ -156,6 +158,48 @@ int static_scratch_for_current_device(void** out) {
   return UA_OK;
 }
 
+}  // namespace
+
+namespace {
+template <typename T, int TPR>
+int launch_prepare(const ua::aux::PrepDims& pd, int backward, const void* a0, const void* a1, const void* a2, const void* a3,
+                   const float* key_norm_in, void* o0, void* o1, void* o2, float* key_norm_out, cudaStream_t st) {
+  const long long rows = (long long)pd.b * pd.s * (pd.n + 2 * pd.n_kv);
+  const unsigned blocks = (unsigned)((rows * TPR + ua::aux::kMergeThreads - 1) / ua::aux::kMergeThreads);
+  if (!backward)
+    ua::aux::prepare_fwd_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(
+        pd, static_cast<const T*>(a0), static_cast<const T*>(a1), static_cast<const T*>(a2), static_cast<T*>(o0), static_cast<T*>(o1),
+        static_cast<T*>(o2), key_norm_out);
+  else
+    ua::aux::prepare_bwd_kernel<T, TPR><<<blocks, ua::aux::kMergeThreads, 0, st>>>(
+        pd, static_cast<const T*>(a0), static_cast<const T*>(a1), static_cast<const T*>(a2), static_cast<const T*>(a3), key_norm_in,
+        static_cast<T*>(o0), static_cast<T*>(o1), static_cast<T*>(o2));
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+template <typename T>
+int dispatch_prepare(int tpr, const ua::aux::PrepDims& pd, int backward, const void* a0, const void* a1, const void* a2,
+                     const void* a3, const float* kn_in, void* o0, void* o1, void* o2, float* kn_out, cudaStream_t st) {
+  switch (tpr) {
+    case 1: return launch_prepare<T, 1>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    case 2: return launch_prepare<T, 2>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    case 4: return launch_prepare<T, 4>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    case 8: return launch_prepare<T, 8>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    case 16: return launch_prepare<T, 16>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    case 32: return launch_prepare<T, 32>(pd, backward, a0, a1, a2, a3, kn_in, o0, o1, o2, kn_out, st);
+    default: return UA_ERR_UNSUPPORTED;
+  }
+}
+int prepare_common(int b, int s, int n_heads, int n_kv, int head_dim, int dtype, int flags, ua::aux::PrepDims* pd, int* tpr) {
+  if (b <= 0 || s <= 0 || n_heads <= 0 || n_kv <= 0 || head_dim <= 0 || n_heads % n_kv) return UA_ERR_BAD_DIMS;
+  if (dtype != UA_F32 && dtype != UA_BF16) return UA_ERR_BAD_DTYPE;
+  const int bytes = head_dim * (dtype == UA_F32 ? 4 : 2);
+  if (bytes % 16) return UA_ERR_UNSUPPORTED;
+  *tpr = bytes / 16;
+  pd->b = b; pd->s = s; pd->n = n_heads; pd->n_kv = n_kv;
+  pd->normalize_keys = (flags & UA_PREP_NORMALIZE_KEYS) ? 1 : 0;
+  pd->sigmoid_gates = (flags & UA_PREP_SIGMOID_GATES) ? 1 : 0;
+  return UA_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -502,6 +546,64 @@ int ua_relayout(const UaDims* dims, int inner, int elem_bytes, int to_reference,
   else
     ua::aux::relayout_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(src),
                                                              static_cast<uint32_t*>(dst), s.N, s.R, X, to_reference);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_prepare_inputs(int batch, int seq, int n_heads, int n_kv_heads, int head_dim, int dtype, int flags,
+                      const void* query_state, const void* key_state, const void* value_state, const void* gate_state,
+                      void* xq, void* kc, void* vc, void* static_src, void* static_dest, float* key_norm, void* stream) {
+  ua::aux::PrepDims pd;
+  int tpr = 0;
+  int e = prepare_common(batch, seq, n_heads, n_kv_heads, head_dim, dtype, flags, &pd, &tpr);
+  if (e) return e;
+  if (!query_state || !key_state || !value_state || !gate_state || !xq || !kc || !vc || !static_src || !static_dest) return UA_ERR_NULL_POINTER;
+  if (pd.normalize_keys && !key_norm) return UA_ERR_NULL_POINTER;
+  if (!aligned16(query_state) || !aligned16(key_state) || !aligned16(value_state) || !aligned16(xq) || !aligned16(kc) || !aligned16(vc))
+    return UA_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  e = dtype == UA_F32 ? dispatch_prepare<float>(tpr, pd, 0, query_state, key_state, value_state, nullptr, nullptr, xq, kc, vc, key_norm, st)
+                      : dispatch_prepare<bf16>(tpr, pd, 0, query_state, key_state, value_state, nullptr, nullptr, xq, kc, vc, key_norm, st);
+  if (e) return e;
+  const long long total = (long long)batch * seq * 2 * n_kv_heads;
+  const unsigned gblocks = (unsigned)std::min<long long>((total + 255) / 256, 4096);
+  if (dtype == UA_F32)
+    ua::aux::prepare_gates_kernel<float><<<gblocks, 256, 0, st>>>(pd, static_cast<const float*>(gate_state), static_cast<float*>(static_src),
+                                                                 static_cast<float*>(static_dest), 0, nullptr, nullptr, nullptr);
+  else
+    ua::aux::prepare_gates_kernel<bf16><<<gblocks, 256, 0, st>>>(pd, static_cast<const bf16*>(gate_state), static_cast<bf16*>(static_src),
+                                                                static_cast<bf16*>(static_dest), 0, nullptr, nullptr, nullptr);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+int ua_prepare_inputs_bwd(int batch, int seq, int n_heads, int n_kv_heads, int head_dim, int dtype, int flags,
+                          const void* g_xq, const void* g_kc, const void* g_vc, const void* g_static_src, const void* g_static_dest,
+                          const void* kc, const float* key_norm, const void* static_src, const void* static_dest,
+                          void* d_query_state, void* d_key_state, void* d_value_state, void* d_gate_state, void* stream) {
+  ua::aux::PrepDims pd;
+  int tpr = 0;
+  int e = prepare_common(batch, seq, n_heads, n_kv_heads, head_dim, dtype, flags, &pd, &tpr);
+  if (e) return e;
+  if (!g_xq || !g_kc || !g_vc || !g_static_src || !g_static_dest || !static_src || !static_dest || !d_query_state || !d_key_state ||
+      !d_value_state || !d_gate_state)
+    return UA_ERR_NULL_POINTER;
+  if (pd.normalize_keys && (!kc || !key_norm)) return UA_ERR_NULL_POINTER;
+  if (!aligned16(g_xq) || !aligned16(g_kc) || !aligned16(g_vc) || !aligned16(d_query_state) || !aligned16(d_key_state) ||
+      !aligned16(d_value_state) || (kc && !aligned16(kc)))
+    return UA_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  e = dtype == UA_F32 ? dispatch_prepare<float>(tpr, pd, 1, g_xq, g_kc, g_vc, kc, key_norm, d_query_state, d_key_state, d_value_state, nullptr, st)
+                      : dispatch_prepare<bf16>(tpr, pd, 1, g_xq, g_kc, g_vc, kc, key_norm, d_query_state, d_key_state, d_value_state, nullptr, st);
+  if (e) return e;
+  const long long total = (long long)batch * seq * 2 * n_kv_heads;
+  const unsigned gblocks = (unsigned)std::min<long long>((total + 255) / 256, 4096);
+  if (dtype == UA_F32)
+    ua::aux::prepare_gates_kernel<float><<<gblocks, 256, 0, st>>>(
+        pd, nullptr, const_cast<float*>(static_cast<const float*>(static_src)), const_cast<float*>(static_cast<const float*>(static_dest)), 1,
+        static_cast<const float*>(g_static_src), static_cast<const float*>(g_static_dest), static_cast<float*>(d_gate_state));
+  else
+    ua::aux::prepare_gates_kernel<bf16><<<gblocks, 256, 0, st>>>(
+        pd, nullptr, const_cast<bf16*>(static_cast<const bf16*>(static_src)), const_cast<bf16*>(static_cast<const bf16*>(static_dest)), 1,
+        static_cast<const bf16*>(g_static_src), static_cast<const bf16*>(g_static_dest), static_cast<bf16*>(d_gate_state));
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 

@@ -225,5 +225,127 @@ __global__ void __launch_bounds__(kMergeThreads) merge_bwd_kernel(const T* __res
   }
 }
 
+// ---- input prologue -----------------------------------------------------------------
+// The model hands over projections in token-major order: query_state (b,s,n,d), key_state / value_state (b,s,n_kv,d)
+// and gate logits (b,s,2,n_kv).  The operator wants head-major tensors: xq (b,n_kv,rep,s,d) (query head kv*rep + r),
+// kc / vc (b,n_kv,s,d), static_src / static_dest (b,n_kv,s) (the reference's driver does this with transposes and
+// views, main.py:24-31).  One pass does the transposes and, on request, the two things a model applies on the way
+// (Universal_Attention/triton/_debug.py:470-475): keys divided by (|k| + 1e-6) and gates through a sigmoid.
+// One group of TPR threads per row of d elements; rows = b * s * (n + 2 n_kv).
+struct PrepDims {
+  int b, s, n, n_kv, normalize_keys, sigmoid_gates;
+};
+
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kMergeThreads) prepare_fwd_kernel(PrepDims pd, const T* __restrict__ qs, const T* __restrict__ ks,
+                                                                    const T* __restrict__ vs, T* __restrict__ xq, T* __restrict__ kc,
+                                                                    T* __restrict__ vc, float* __restrict__ key_norm) {
+  constexpr int kN = Vec16<T>::kN;
+  constexpr int D = TPR * kN;
+  const int heads = pd.n + 2 * pd.n_kv;
+  const long long rows = (long long)pd.b * pd.s * heads;
+  const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
+  const int sub = threadIdx.x % TPR;
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
+  const int hh = (int)(rr % heads);
+  const long long tok = rr / heads;                 // bb * s + ss
+  const int ss = (int)(tok % pd.s);
+  const long long bb = tok / pd.s;
+  const bool is_q = hh < pd.n, is_k = !is_q && hh < pd.n + pd.n_kv;
+  const int kv = is_q ? 0 : (is_k ? hh - pd.n : hh - pd.n - pd.n_kv);
+  const size_t hm = ((size_t)bb * pd.n_kv + kv) * pd.s + ss;          // head-major row of a key / value
+  float v[kN];
+  if (is_q) Vec16<T>::load(qs + ((size_t)tok * pd.n + hh) * D + sub * kN, v);
+  else Vec16<T>::load((is_k ? ks : vs) + ((size_t)tok * pd.n_kv + kv) * D + sub * kN, v);
+  float ssq = 0.f;
+#pragma unroll
+  for (int i = 0; i < kN; ++i) ssq = fmaf(v[i], v[i], ssq);
+  ssq = group_sum<TPR>(ssq);                        // every lane takes part, whatever kind of row its group holds
+  const float nrm = sqrtf(ssq);
+  if (is_k && pd.normalize_keys) {
+    const float inv = 1.0f / (nrm + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) v[i] *= inv;
+  }
+  if (!live) return;
+  if (is_q) {
+    Vec16<T>::store(xq + (((size_t)bb * pd.n + hh) * pd.s + ss) * D + sub * kN, v);
+  } else {
+    Vec16<T>::store((is_k ? kc : vc) + hm * D + sub * kN, v);
+    if (is_k && sub == 0 && key_norm) key_norm[hm] = nrm;
+  }
+}
+
+// gates: one thread per (b, s, which, kv)
+template <typename T>
+__global__ void prepare_gates_kernel(PrepDims pd, const T* __restrict__ gs, T* __restrict__ ssrc, T* __restrict__ sdest, int backward,
+                                     const T* __restrict__ g_src, const T* __restrict__ g_dest, T* __restrict__ d_gs) {
+  const long long total = (long long)pd.b * pd.s * 2 * pd.n_kv;
+  for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+    const int kv = (int)(e % pd.n_kv);
+    const int which = (int)((e / pd.n_kv) % 2);
+    const long long tok = e / (2 * pd.n_kv);
+    const int ss = (int)(tok % pd.s);
+    const long long bb = tok / pd.s;
+    const size_t dst = ((size_t)bb * pd.n_kv + kv) * pd.s + ss;
+    if (!backward) {
+      float x = Num<T>::ld(gs + e);
+      if (pd.sigmoid_gates) x = 1.0f / (1.0f + __expf(-x));
+      Num<T>::st((which ? sdest : ssrc) + dst, x);
+    } else {
+      // ssrc / sdest hold the forward's outputs (the gate values), g_* their gradients
+      const float gate = Num<T>::ld((which ? sdest : ssrc) + dst);
+      float g = Num<T>::ld((which ? g_dest : g_src) + dst);
+      if (pd.sigmoid_gates) g *= gate * (1.0f - gate);
+      Num<T>::st(d_gs + e, g);
+    }
+  }
+}
+
+// backward of prepare_fwd_kernel: gradients flow back along the same row mapping; key rows pass through the
+// derivative of k / (|k| + eps):  dk = g / (|k| + eps) - khat (g . khat) / |k|
+template <typename T, int TPR>
+__global__ void __launch_bounds__(kMergeThreads) prepare_bwd_kernel(PrepDims pd, const T* __restrict__ g_xq, const T* __restrict__ g_kc,
+                                                                    const T* __restrict__ g_vc, const T* __restrict__ kc,
+                                                                    const float* __restrict__ key_norm, T* __restrict__ d_qs,
+                                                                    T* __restrict__ d_ks, T* __restrict__ d_vs) {
+  constexpr int kN = Vec16<T>::kN;
+  constexpr int D = TPR * kN;
+  const int heads = pd.n + 2 * pd.n_kv;
+  const long long rows = (long long)pd.b * pd.s * heads;
+  const long long row = (long long)blockIdx.x * (kMergeThreads / TPR) + threadIdx.x / TPR;
+  const int sub = threadIdx.x % TPR;
+  const bool live = row < rows;
+  const long long rr = live ? row : rows - 1;
+  const int hh = (int)(rr % heads);
+  const long long tok = rr / heads;
+  const int ss = (int)(tok % pd.s);
+  const long long bb = tok / pd.s;
+  const bool is_q = hh < pd.n, is_k = !is_q && hh < pd.n + pd.n_kv;
+  const int kv = is_q ? 0 : (is_k ? hh - pd.n : hh - pd.n - pd.n_kv);
+  const size_t hm = ((size_t)bb * pd.n_kv + kv) * pd.s + ss;
+  float g[kN], kh[kN];
+  if (is_q) Vec16<T>::load(g_xq + (((size_t)bb * pd.n + hh) * pd.s + ss) * D + sub * kN, g);
+  else Vec16<T>::load((is_k ? g_kc : g_vc) + hm * D + sub * kN, g);
+  float dot = 0.f;
+  const bool norm = is_k && pd.normalize_keys;
+  if (norm) {
+    Vec16<T>::load(kc + hm * D + sub * kN, kh);
+#pragma unroll
+    for (int i = 0; i < kN; ++i) dot = fmaf(g[i], kh[i], dot);
+  }
+  dot = group_sum<TPR>(dot);
+  if (norm) {
+    const float nrm = key_norm[hm];
+    const float a = 1.0f / (nrm + 1e-6f), c = nrm > 0.f ? dot / nrm : 0.f;
+#pragma unroll
+    for (int i = 0; i < kN; ++i) g[i] = g[i] * a - kh[i] * c;
+  }
+  if (!live) return;
+  if (is_q) Vec16<T>::store(d_qs + ((size_t)tok * pd.n + hh) * D + sub * kN, g);
+  else Vec16<T>::store((is_k ? d_ks : d_vs) + ((size_t)tok * pd.n_kv + kv) * D + sub * kN, g);
+}
+
 }  // namespace aux
 }  // namespace ua
