@@ -53,9 +53,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 
 # DRAM bytes per launch of the two kernels at workload c2, from one ncu capture (see profiles/): the capture ran a slice of
-# 2 of the 32 (batch, kv-head) units -- forward 7.13 MB read + 86.77 MB written, backward 157.01 MB + 7.91 MB -- and the
+# 2 of the 32 (batch, kv-head) units -- forward 7.16 MB read + 86.75 MB written, backward 159.26 MB + 8.13 MB -- and the
 # traffic grows in proportion to the units.
-NCU_DRAM_BYTES = {"c2": {"fwd": 16 * (7.129344e6 + 86.766592e6), "bwd": 16 * (157.008384e6 + 7.912192e6)}}
+NCU_DRAM_BYTES = {"c2": {"fwd": 16 * (7.162112e6 + 86.754816e6), "bwd": 16 * (159.264512e6 + 8.125952e6)}}
 
 
 def flops(w):
