@@ -485,7 +485,7 @@ def main():
             "tflops": (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12,
             "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms_per_step * 1e-3) / 1e12 / peak,
             "fwd_ms": fwd_avg, "bwd_ms": bwd_avg,
-            "gpu_launches": K * (2 + (0 if w["fwd_only"] else 4)),
+            "gpu_launches": K * (1 + (0 if w["fwd_only"] else 4)),      # forward kernel; backward kernel + three fp32 -> dtype conversions
             "clocks": clocks,
             "roofline": {"kernel": "ua backward" if dom_is_bwd else "ua forward", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
