@@ -221,8 +221,8 @@ def run_sequence_parallel(args, w, rank, world, device, W, K):
     g_out, g_den = ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm)
 
     def step():
-        out, denom, lse = sp_forward(*loc, zigzag=args.zigzag)
-        return sp_backward(*loc, g_out, g_den, zigzag=args.zigzag)
+        out, denom, lse, ctx = sp_forward(*loc, zigzag=args.zigzag, return_ctx=True)
+        return sp_backward(*loc, g_out, g_den, zigzag=args.zigzag, ctx=ctx)
 
     for _ in range(W):
         step()

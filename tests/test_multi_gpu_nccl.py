@@ -36,8 +36,8 @@ def _sp_worker(rank, world, port, ret, zigzag):
     nb = n // P
     sc = torch.cat([torch.arange(p * nb, (p + 1) * nb) for p in mine]).cuda()
     sr = torch.cat([torch.arange(p * nb * c, (p + 1) * nb * c) for p in mine]).cuda()
-    out, denom, lse = sp_forward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
-                                 ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(), zigzag=zigzag)
+    out, denom, lse, ctx = sp_forward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
+                                      ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(), zigzag=zigzag, return_ctx=True)
     out_cm, lse_cm, _ = ops.forward_cm(kc, vc, xq, ss, sd)
     ref_out = ops.as_reference_out(out_cm)[:, :, :, sr]
     ref_lse = ops.as_reference_denom(lse_cm)[:, :, :, sr]
@@ -52,7 +52,8 @@ def _sp_worker(rank, world, port, ret, zigzag):
     want = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse)
     got = sp_backward(kc[:, :, sc].contiguous(), vc[:, :, sc].contiguous(), xq[:, :, :, sr].contiguous(),
                       ss[:, :, sc].contiguous(), sd[:, :, sr].contiguous(),
-                      ops.as_reference_out(g_out)[:, :, :, sr], ops.as_reference_denom(g_lse)[:, :, :, sr], zigzag=zigzag)
+                      ops.as_reference_out(g_out)[:, :, :, sr], ops.as_reference_denom(g_lse)[:, :, :, sr], zigzag=zigzag,
+                      ctx=ctx if zigzag else None)       # one assignment reuses the forward's gathers and carries, the other redoes them
     want_local = (want[0][:, :, sc], want[1][:, :, sc], want[2][:, :, :, sr], want[3][:, :, sc], want[4][:, :, sr])
     for a, b_ in zip(got, want_local):
         rel = ((a.float() - b_.float()).norm() / b_.float().norm().clamp_min(1e-20)).item()

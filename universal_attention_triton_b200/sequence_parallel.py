@@ -100,29 +100,33 @@ def _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backe
 
 
 def sp_forward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, group=None, backend=CudaBackend,
-               zigzag: bool = False):
+               zigzag: bool = False, return_ctx: bool = False):
     """kc/vc_local (b,h,n_l,128,d), xq_local (b,h,r,L_l,d), static_src_local (b,h,n_l,128), static_dest_local (b,h,L_l):
     this rank's blocks of the sequence (``L_l = n_l * 128``, same on every rank; two blocks when ``zigzag``).
     Returns ``(out, denom, lse)`` for the rank's rows against ALL key chunks, in the reference's shapes
-    ``(b,h,r,L_l,d,n)`` / ``(b,h,r,L_l,n)`` (permuted views; ``lse`` is the fp32 denom)."""
-    world, rank, P, mine, nb, kc, vc, ss, sd, carries = _setup(kc_local, vc_local, static_src_local, static_dest_local,
-                                                                group, backend, zigzag)
+    ``(b,h,r,L_l,d,n)`` / ``(b,h,r,L_l,n)`` (permuted views; ``lse`` is the fp32 denom).  With ``return_ctx`` a
+    fourth value: the gathered keys / values / gates and the decay carries, which ``sp_backward(ctx=...)`` reuses
+    instead of gathering and summing them again."""
+    setup = _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backend, zigzag)
+    world, rank, P, mine, nb, kc, vc, ss, sd, carries = setup
     xq = xq_local.contiguous()
     out = backend.alloc_forward_rows(kc, xq)
     for li, p in enumerate(mine):
         backend.forward_rows_cm(kc, vc, xq, ss, sd, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * kc.shape[3], out=out)
     out_cm, lse_cm, denom_cm = out
-    return ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm), ops.as_reference_denom(lse_cm)
+    res = (ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm), ops.as_reference_denom(lse_cm))
+    return res + (setup,) if return_ctx else res
 
 
 def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, g_out_local, g_denom_local,
-                group=None, backend=CudaBackend, zigzag: bool = False, skip_masked_grads: bool = False):
+                group=None, backend=CudaBackend, zigzag: bool = False, skip_masked_grads: bool = False, ctx=None):
     """Gradients of the sequence-sharded operator.  Inputs as for ``sp_forward``; ``g_out_local (b,h,r,L_l,d,n)`` and
     ``g_denom_local (b,h,r,L_l,n)`` are the upstream gradients of the rank's rows (any strides).  Returns
     ``(dkc, dvc, dxq, dstatic_src, dstatic_dest)`` for the rank's own blocks, shaped and typed like the local inputs."""
     from . import _lib
-    world, rank, P, mine, nb, kc, vc, ss, sd, carries = _setup(kc_local, vc_local, static_src_local, static_dest_local,
-                                                                group, backend, zigzag)
+    if ctx is None:         # ``ctx``: what ``sp_forward(return_ctx=True)`` returned for the same inputs and assignment
+        ctx = _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backend, zigzag)
+    world, rank, P, mine, nb, kc, vc, ss, sd, carries = ctx
     flags = _lib.FLAG_SKIP_MASKED_GRADS if skip_masked_grads else 0
     xq = xq_local.contiguous()
     g_out_cm = ops.out_to_chunk_major(g_out_local)
