@@ -499,6 +499,12 @@ def main():
                                       "peak_gbs": peaks["hbm_gbs"]}},
             "e2e": e2e,
         }
+        if not w["fwd_only"]:       # the other kernel of the step, same arithmetic
+            o_f, o_ms = (f_fwd, fwd_avg) if dom_is_bwd else (f_bwd, bwd_avg)
+            line["roofline_other_kernel"] = {"kernel": "ua forward" if dom_is_bwd else "ua backward", "bound": "tensor",
+                                             "achieved": o_f / (o_ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                                             "frac": o_f / (o_ms * 1e-3) / 1e12 / peak,
+                                             "traffic": NCU_DRAM_BYTES.get(args.workload, {}).get("fwd" if dom_is_bwd else "bwd")}
         if not args.no_cpu_baseline and world == 1:
             val, t_unit, sample = cpu_reference_step_time(w, 2, 1)
             line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
