@@ -52,10 +52,11 @@ METRIC = "fwd+bwd tokens/sec"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
-# DRAM bytes per launch of the two kernels at workload c2, from one ncu capture (see profiles/): the capture ran a slice of
-# 2 of the 32 (batch, kv-head) units -- forward 7.16 MB read + 86.75 MB written, backward 159.26 MB + 8.13 MB -- and the
-# traffic grows in proportion to the units.
-NCU_DRAM_BYTES = {"c2": {"fwd": 16 * (7.162112e6 + 86.754816e6), "bwd": 16 * (159.264512e6 + 8.125952e6)}}
+# DRAM bytes per launch of the backward kernel at workload c2, from one ncu capture of a slice of 2 of the 32 (batch,
+# kv-head) units (159.26 MB read + 8.13 MB written); the traffic grows in proportion to the units.  No figure is given for
+# the forward: a capture of that slice ends with part of the 134 MB it writes still in the 126 MB L2, so its DRAM write
+# count understates a full launch.
+NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (159.264512e6 + 8.125952e6)}}
 
 
 def flops(w):
@@ -269,8 +270,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--zigzag", action="store_true", help="with --mode sp: balanced block assignment")
-    ap.add_argument("--e2e-grads-to-host", action="store_true",
-                    help="end-to-end leg: also copy the five gradients back to pinned host memory every step")
+    ap.add_argument("--e2e-loss-only", action="store_true",
+                    help="end-to-end leg: return only the loss to the host (default: the loss and the five gradients); "
+                         "the default run reports both variants")
     ap.add_argument("--merged-entry", default=None, choices=["composed", "fused"],
                     help="end-to-end leg through UniversalAttentionMerged (the additional one-call entry point, with the "
                          "given backward) instead of the drop-in pair UniversalAttention + SMVecMatMul")
@@ -387,8 +389,6 @@ def main():
     e2e = None
     if not args.no_e2e:
         h2d = sum(t.numel() * t.element_size() for t in host)
-        grads_to_host = args.e2e_grads_to_host and not w["fwd_only"]
-        d2h = 4 + (h2d if grads_to_host else 0)      # the step's result is the loss; the gradients stay on the device
         set_strict_masked_grads(False)      # SMVecMatMul is upstream: the masked-block gradient is exactly zero
         host_grads = [torch.empty_like(t).pin_memory() for t in host]
         host_loss = torch.empty((), dtype=torch.float32).pin_memory()
@@ -400,6 +400,8 @@ def main():
         dev_in = [[torch.empty_like(t, device=device) for t in host] for _ in range(2)]
         in_ready = [None, None]
         cmp_done = [None, None]
+
+        grads_to_host = False      # set per variant below
 
         def upload(k):
             b = k & 1
@@ -448,22 +450,35 @@ def main():
             s_cmp.wait_stream(s_out)
             s_cmp.wait_stream(s_in)
 
-        e2e_run(2)
-        cmp_done = [None, None]
-        barrier()
-        a, b = ev(), ev()
-        a.record()
-        e2e_run(K)
-        b.record()
-        barrier()
-        e_ms = a.elapsed_time(b)
-        if world > 1:
-            tt = torch.tensor([e_ms], device=device, dtype=torch.float64)
-            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-            e_ms = tt.item()
+        def e2e_timed():
+            nonlocal cmp_done
+            e2e_run(2)
+            cmp_done = [None, None]
+            barrier()
+            a, b = ev(), ev()
+            a.record()
+            e2e_run(K)
+            b.record()
+            barrier()
+            ms = a.elapsed_time(b)
+            if world > 1:
+                tt = torch.tensor([ms], device=device, dtype=torch.float64)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                ms = tt.item()
+            return ms
+
+        # The step's result is the loss AND the five gradients (what the CPU arm leaves in host memory): both come back
+        # by default.  The loss-only variant (gradients stay on the device, as a fused optimizer would use them) is timed
+        # beside it.
+        loss_only_ms = e2e_timed()
+        grads_to_host = not w["fwd_only"] and not args.e2e_loss_only
+        e_ms = e2e_timed() if grads_to_host else loss_only_ms
+        d2h = 4 + (h2d if grads_to_host else 0)
         set_strict_masked_grads(True)
         e2e = {"value": tokens / (e_ms / K * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms / K,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "returns": "loss + five gradients" if grads_to_host else "loss",
+               "loss_only": {"value": tokens / (loss_only_ms / K * 1e-3), "ms_per_step": loss_only_ms / K, "d2h_bytes_per_step": 4},
                "path": (f"UniversalAttentionMerged.apply ({args.merged_entry} backward)" if args.merged_entry else "UniversalAttention.apply -> SMVecMatMul.apply") +
                        " -> pow(2).sum() -> backward (main.py:55-62 flow); "
                        "copies of neighbouring steps overlap the compute (three streams)"}
@@ -473,7 +488,12 @@ def main():
         dom_is_bwd = bwd_avg >= fwd_avg
         dom_f, dom_ms = (f_bwd, bwd_avg) if dom_is_bwd else (f_fwd, fwd_avg)
         achieved = dom_f / (dom_ms * 1e-3) / 1e12
-        peak = peaks["bf16_tflops_sustained"]
+        # The denominator is the burst figure unless this run itself was in the power-limited regime the sustained figure
+        # was measured in: a timed region of seconds, or SM clocks sampled well below their maximum.
+        sustained_regime = total_ms >= 2000.0 or bool(clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz")
+                                                     and clocks["sm_mhz"] < 0.9 * clocks["sm_max_mhz"])
+        peak_key = "bf16_tflops_sustained" if sustained_regime else "bf16_tflops"
+        peak = peaks[peak_key]
         line = {
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -491,8 +511,9 @@ def main():
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": NCU_DRAM_BYTES.get(args.workload, {}).get("bwd" if dom_is_bwd else "fwd"),
                          "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of a 2-of-32 (batch, kv-head) slice, "
-                                           "scaled by the units of a full launch (profiles/fwd_bwd_kernels_config2.md)",
-                         "peak_source": f"{peak_src} (bf16_tflops_sustained)",
+                                           "scaled by the units of a full launch",
+                         "peak_source": f"{peak_src} ({peak_key}: timed region {total_ms / 1e3:.2f} s, median SM clock "
+                                        f"{clocks.get('sm_mhz') if clocks else None} MHz)",
                          "algorithmic_flops_per_launch": dom_f,
                          "hbm_view": {"bytes": b_bwd if dom_is_bwd else b_fwd,
                                       "achieved_gbs": (b_bwd if dom_is_bwd else b_fwd) / (dom_ms * 1e-3) / 1e9,

@@ -76,6 +76,15 @@ def _decay_terms(k, s, t, cd):
     return gram, pw, aff, ell, s3, t3, strict
 
 
+def _absorb(score, before, cd):
+    """In the reference's fp32 arithmetic ``k.q + (-1e12)`` IS -1e12 (fp32 spacing there is 65536), which makes the
+    softmax of a fully masked block exactly uniform (universal_attention_autograd.py:28-35).  The fp64 arbiter keeps
+    that semantics instead of resolving ``k.q`` next to -1e12."""
+    if cd == torch.float32:
+        return score
+    return torch.where(before, torch.full((), MASK_VALUE, dtype=cd), score)
+
+
 def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32):
     """Forward of the operator; returns ``(out, denom)`` in ``xq.dtype`` plus the
     fp32/fp64 log-sum-exp before the cast, as a third value.
@@ -90,7 +99,7 @@ def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32)
     decay = ell.cumsum(-1)
     decay = torch.where(before, torch.full((), MASK_VALUE, dtype=cd), decay)
     score = k.to(cd).unsqueeze(2) @ q.to(cd).transpose(-1, -2)      # (b,h,r,Lk,Lq)
-    score = score + decay.unsqueeze(2)
+    score = _absorb(score + decay.unsqueeze(2), before, cd)
     score = score.view(b, h, r, n, c, L)
     lse = score.logsumexp(dim=-2)                          # (b,h,r,n,Lq)
     prob = score.softmax(dim=-2)                           # over the chunk's keys (uniform where all are -1e12)
@@ -118,7 +127,7 @@ def ua_backward(kc, vc, xq, static_src, static_dest, g_out, g_denom, compute_dty
     before = idx.view(1, L) < idx.view(L, 1)
     decay = torch.where(before, torch.full((), MASK_VALUE, dtype=cd), ell.cumsum(-1))
     kf, vf, qf = k.to(cd), v.to(cd), q.to(cd)
-    score = (kf.unsqueeze(2) @ qf.transpose(-1, -2) + decay.unsqueeze(2)).view(b, h, r, n, c, L)
+    score = _absorb(kf.unsqueeze(2) @ qf.transpose(-1, -2) + decay.unsqueeze(2), before, cd).view(b, h, r, n, c, L)
     prob = score.softmax(dim=-2)                           # (b,h,r,n,c,Lq) fp32, per key chunk
     go = g_out.to(cd).permute(0, 1, 2, 5, 3, 4)            # (b,h,r,n,Lq,d)
     gd = g_denom.to(cd).permute(0, 1, 2, 4, 3)             # (b,h,r,n,Lq)

@@ -4,6 +4,8 @@ import os
 import numpy as np
 import torch
 
+from oracle import ua_oracle as O
+
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
@@ -40,16 +42,57 @@ def fwd_errors(out, denom, ref_out, ref_denom, c):
     return dict(out_valid=e_out_valid, out_masked=e_out_masked, denom_valid=e_den_valid, masked_denom_ok=masked_ok)
 
 
-def robust_rel_fro(a, b, fraction=1e-3):
-    """Relative Frobenius error of a against b without the few largest elements of b.
+K_NOISE = 2.0
+GRADS = ["dkc", "dvc", "dxq", "dsrc", "ddest"]
 
-    The gradient of log1p(-affinity) carries 1 / (1 - affinity), which reaches 1e6 for the pairs just below the clamp
-    at 1 - 1e-6; there one ulp of the fp32 affinity (the summation order of k.k already moves it) changes the result by
-    several per cent in the reference itself, and a single such element can hold the whole norm of a tensor.  The
-    ``ceil(fraction * numel)`` elements of b of largest magnitude are left out."""
-    a = a.double().reshape(-1)
-    b = b.double().reshape(-1)
-    k = max(1, int(-(-fraction * b.numel() // 1)))
-    keep = torch.ones_like(b, dtype=torch.bool)
-    keep[b.abs().topk(k).indices] = False
-    return ((a - b)[keep].norm() / b[keep].norm().clamp_min(1e-30)).item()
+# Noise-pinned checks.  The stated bars (bf16 forward max-abs 2e-2, gradients 5e-2 relative-Frobenius, against the fp32
+# oracle fed the same bf16-rounded values) are asserted as
+#       kernel_error <= max(stated bar, K_NOISE * oracle_noise),
+# where oracle_noise is the SAME metric on the SAME inputs between the oracle evaluated in fp32 and in fp64: a bound
+# above the stated bar is only granted where the reference arithmetic itself is that uncertain (at L = 4096 its fp32
+# cumulative sum reaches -2e4, where fp32 spacing is 2e-3).  Figures are printed (pytest -s).
+
+
+def check_forward(tag, out, lse, ins32, c):
+    """out (b,h,r,L,d,n) bf16 values as float, lse (b,h,r,L,n) fp32; both CPU.  Returns the figures it asserted on."""
+    ref_out, _, ref_lse = O.ua_forward(*ins32)
+    arb_out, _, arb_lse = O.ua_forward(*ins32, compute_dtype=torch.float64)
+    L, n = lse.shape[-2], lse.shape[-1]
+    valid = valid_row_mask(L, n, c)
+    vo = valid.view(L, 1, n)
+    e_out = ((out - ref_out.float()).abs() * vo).max().item()
+    n_out = ((ref_out.float() - arb_out.float()).abs() * vo).max().item()
+    e_lse = ((lse - ref_lse).abs() * valid).max().item()
+    n_lse = ((ref_lse.double() - arb_lse).abs() * valid).max().item()
+    frac_k = (((out - ref_out.float()).abs() > 2e-2) & vo).float().mean().item()
+    frac_n = (((ref_out.float() - arb_out.float()).abs() > 2e-2) & vo).float().mean().item()
+    merged = O.merge_forward(out, lse)
+    merged_ref = O.merge_forward(arb_out.double(), arb_lse).float()
+    e_merged = (merged - merged_ref).abs().max().item()
+    print(f"[{tag}] out max-abs {e_out:.3e} (oracle fp32-vs-fp64 {n_out:.3e}); elements over 2e-2: {frac_k:.2e} "
+          f"(oracle {frac_n:.2e}); lse {e_lse:.3e} (oracle {n_lse:.3e}); merged vs fp64 {e_merged:.3e}")
+    assert e_out <= max(2e-2, K_NOISE * n_out), (tag, e_out, n_out)
+    assert frac_k <= max(1e-6, K_NOISE * frac_n), (tag, frac_k, frac_n)
+    assert e_lse <= max(2e-2, K_NOISE * n_lse), (tag, e_lse, n_lse)
+    assert e_merged <= 2e-2, (tag, e_merged)      # the merged output is well conditioned: the plain bar
+    masked = ~valid
+    if masked.any():
+        assert (lse[..., masked] <= -1e11).all()
+    return dict(out=e_out, out_noise=n_out, lse=e_lse, lse_noise=n_lse)
+
+
+def check_backward(tag, grads, ins32, g_out, g_den):
+    ref = O.ua_backward(*ins32, g_out, g_den)
+    arb = O.ua_backward(*[t.double() for t in ins32], g_out.double(), g_den.double(), compute_dtype=torch.float64)
+    res = {}
+    for got, r32, r64, key in zip(grads, ref, arb, GRADS):
+        got = got.float().cpu()
+        assert torch.isfinite(got).all(), (tag, key)
+        err = rel_fro(got, r32)
+        noise = rel_fro(r32, r64)
+        err64 = rel_fro(got, r64)
+        print(f"[{tag}] {key}: rel-Frobenius vs fp32 oracle {err:.3e}; oracle fp32-vs-fp64 {noise:.3e}; "
+              f"kernel vs fp64 oracle {err64:.3e}")
+        assert err <= max(5e-2, K_NOISE * noise), (tag, key, err, noise)
+        res[key] = (err, noise, err64)
+    return res

@@ -9,7 +9,7 @@ import pytest
 import torch
 
 from oracle import ua_oracle as O
-from tests._util import fwd_errors, load_golden, rel_fro, robust_rel_fro
+from tests._util import check_backward, check_forward, fwd_errors, load_golden, rel_fro
 
 pytestmark = pytest.mark.gpu
 
@@ -91,13 +91,9 @@ def test_bf16_against_oracle(shape):
     assert out.dtype == torch.bfloat16 and denom.dtype == torch.bfloat16
     e = fwd_errors(out.float().cpu(), denom.float().cpu(), ref_out, ref_denom, c)
     assert e["out_masked"] <= 2e-2 and e["masked_denom_ok"], e
-    # 2e-2 absolute, plus half a bf16 ulp of the reference value: the rounding of the bf16 output itself,
-    # which exceeds 1e-2 wherever |out| > 4 (out is a convex combination of N(0,1) value rows)
-    from tests._util import valid_row_mask as _vm
-    err = (out.float().cpu() - ref_out).abs()
-    bound = 2e-2 + ref_out.abs() * 2.0 ** -8
-    assert ((err <= bound) | ~_vm(L, n, c).view(L, 1, n)).all(), (err - bound).max().item()
-    assert e["out_valid"] <= 4e-2, e
+    from universal_attention_triton_b200 import ops
+    lse32 = ops.as_reference_denom(ops.forward_cm(*_cuda(*ins))[1]).cpu()
+    check_forward(f"bf16 {shape}", out.float().cpu(), lse32, ins32, c)      # out <= 2e-2 (noise-pinned), fp32 lse <= 2e-2
     # denom is the fp32 log-sum-exp rounded to bf16: within one bf16 ulp of the reference value
     ulp = ref_denom.abs().clamp_min(1.0) * 2.0 ** -7
     from tests._util import valid_row_mask
@@ -118,33 +114,6 @@ def test_fp32_lse_is_returned_by_the_library():
     valid = valid_row_mask(256, 4, 64)
     assert ((lse - ref_lse).abs() * valid).max() <= 2e-2
     assert lse_cm.dtype == torch.float32 and denom_cm.dtype == torch.bfloat16
-
-
-def test_kernel_backed_function_and_driver_flow_bf16():
-    """Universal_Attention.universal_attention.UniversalAttention (2-D) in the driver flow, both
-    masked-gradient modes (identical under SMVecMatMul)."""
-    ua = _ua()
-    from universal_attention_triton_b200.Universal_Attention.universal_attention import UniversalAttention as KUA
-    B, H, R, L, c, D = 1, 2, 2, 256, 64, 64
-    ins, ins32 = _bf16_case(B, H, R, L, c, D, seed=9)
-    ins2d = [ins[0], ins[1], ins[2].view(B, H, R, L // c, c, D), ins[3], ins[4].view(B, H, L // c, c)]
-    loss_ref, merged_ref, _, _, grads_ref = O.driver_step(*ins32)
-    results = []
-    for strict in (True, False):
-        ua.set_strict_masked_grads(strict)
-        xs = [t.clone().requires_grad_() for t in _cuda(*ins2d)]
-        out, denom = KUA.apply(*xs)
-        # merge on the fp32 log-sum-exp is more accurate than on the bf16 denom; here the drop-in path is used
-        merged = ua.SMVecMatMul.apply(out, denom)
-        merged.float().pow(2).sum().backward()
-        results.append([t.grad.float().cpu() for t in xs])
-    ua.set_strict_masked_grads(True)
-    for a, b in zip(*results):
-        assert torch.equal(a, b) or rel_fro(a, b) < 1e-3
-    # bf16 denom feeds the merge (as in the reference), so only a loose check against the fp32 oracle
-    for got, ref in zip(results[0], grads_ref):
-        assert torch.isfinite(got).all()
-        assert got.reshape(-1).shape == ref.reshape(-1).shape
 
 
 def test_reference_layout_mode_and_relayout_roundtrip():
@@ -200,32 +169,6 @@ def test_tensor_core_forward_matches_simt_forward(shape):
     assert (err <= bound).all(), (err - bound).max().item()
 
 
-def test_tensor_core_forward_config2_shape_slice_against_oracle():
-    """A (b, h) slice of BASELINE config 2 (R=4, L=4096, chunk=128, D=64) against the CPU oracle."""
-    shape = (1, 1, 4, 4096, 128, 64)
-    B, H, R, L, c, D = shape
-    ua = _ua()
-    ins, ins32 = _bf16_case(*shape, seed=0)
-    ref_out, ref_denom, ref_lse = O.ua_forward(*ins32)
-    from universal_attention_triton_b200 import ops
-    out_cm, lse_cm, _ = ops.forward_cm(*_cuda(*ins))
-    out = ops.as_reference_out(out_cm).float().cpu()
-    lse = ops.as_reference_denom(lse_cm).cpu()
-    from tests._util import valid_row_mask
-    valid = valid_row_mask(L, L // c, c)
-    # far chunks are ill-conditioned in fp32 (the decay prefix reaches -2e4, where fp32 spacing is 2e-3
-    # and the reference's own 1-D and 2-D forms differ by 4e-3): compare the log-sum-exp relative to its size
-    dl = (lse - ref_lse).abs()
-    assert ((dl <= 2e-2 + 1e-5 * ref_lse.abs()) | ~valid).all(), (dl * valid).max().item()
-    err = (out - ref_out).abs()
-    bound = 2e-2 + ref_out.abs() * 2.0 ** -8
-    frac_bad = ((err > bound) & valid.view(L, 1, -1)).float().mean().item()
-    assert frac_bad <= 1e-5, frac_bad
-    merged = O.merge_forward(out, lse)
-    merged_ref = O.merge_forward(ref_out, ref_lse)
-    assert (merged - merged_ref).abs().max() <= 2e-2
-
-
 @pytest.mark.parametrize("L", [4096, 8192])
 def test_tensor_core_backward_config2_length_against_oracle(L):
     """Backward at the sequence length of BASELINE config 2 (L=4096, chunk 128, D=64; one (b, h) unit, R=2) and at twice
@@ -241,7 +184,6 @@ def test_tensor_core_backward_config2_length_against_oracle(L):
     gen = torch.Generator().manual_seed(4)
     g_out = torch.randn(B, H, R, L, D, n, generator=gen).bfloat16()
     g_den = torch.randn(B, H, R, L, n, generator=gen)
-    ref = O.ua_backward(*ins32, g_out.float(), g_den)
     cu = _cuda(*ins)
     g_out_cm = ops.out_to_chunk_major(g_out.cuda())
     g_den_cm = ops.denom_to_chunk_major(g_den.cuda())
@@ -252,12 +194,7 @@ def test_tensor_core_backward_config2_length_against_oracle(L):
     del ref_lse, dl
     for kwargs in ({}, {"carry": carry, "lse": lse_cm}):
         got = ops.backward_cm(*cu, g_out_cm, g_den_cm, **kwargs)
-        for a, b, key in zip(got, ref, GRADS):
-            assert torch.isfinite(a.float()).all(), key
-            # (at L = 8192 one element of d static_src is 6e7 against a typical 10: see robust_rel_fro)
-            err = robust_rel_fro(a.float().cpu(), b.float())
-            assert err <= 5e-2, (key, list(kwargs), err)
-            assert rel_fro(a.float().cpu(), b.float()) <= 1e-1, (key, list(kwargs), rel_fro(a.float().cpu(), b.float()))
+        check_backward(f"L={L} {sorted(kwargs)}", got, ins32, g_out.float(), g_den)      # 5e-2, noise-pinned
 
 
 @pytest.mark.parametrize("shape,skip", [((1, 2, 4, 1024, 128, 64), False), ((2, 1, 1, 768, 128, 64), False),
@@ -667,3 +604,22 @@ def test_input_prologue_matches_the_drivers_views(dtype, norm, sig):
     for a, r_, key in zip(cu_in, ref_in, ["query", "key", "value", "gates"]):
         assert rel_fro(a.grad.float().cpu(), r_.grad) <= (1e-5 if dtype == torch.float32 else 1e-2), key
 
+
+
+def test_status_word_path_reports_a_timeout_without_any_kernel():
+    """The path a host sees when a bounded device-side wait ran out: the first word of the workspace is non-zero and
+    ``ua_workspace_status`` returns UA_ERR_TIMEOUT (9).  The word is written by the host here (no kernel, no hang);
+    a cleared word reads UA_OK again, and the Python wrapper turns the code into an exception."""
+    import ctypes
+    from universal_attention_triton_b200 import _lib
+    lib = _lib.load()
+    ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.ua_workspace_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0
+    ws[0] = 1
+    rc = lib.ua_workspace_status(ctypes.c_void_p(ws.data_ptr()), stream)
+    assert rc == 9 and b"bounded device-side wait" in lib.ua_error_string(rc)
+    with pytest.raises(_lib.UaLibraryError, match="bounded device-side wait"):
+        _lib.check(rc, "status")
+    ws.zero_()
+    assert lib.ua_workspace_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0

@@ -13,10 +13,12 @@ dtypes.  By default they are permuted views of chunk-major storage (see
 ``ops.py``); ``set_output_layout("reference")`` makes them contiguous in the
 reference's order at the cost of one extra pass over ``out``.
 
-The five inputs are saved for backward and everything is recomputed from them
-(universal_attention_autograd.py:41-44, :166-169); the only extra is the small
-fp32 decay-prefix table the forward kernel has in registers anyway (16.8 MB at
-B4 H8 L4096), which spares the backward its pre-pass.  Tensors must be CUDA
+The Functions follow the reference's protocol: a ``forward`` without ``ctx``, ``setup_context``
+and ``backward`` (universal_attention_autograd.py:9, :41-44, :47).  The five inputs are saved
+for backward as in the reference (:41-44, :166-169); two by-products of the forward kernel are
+saved with them through ``save_for_backward`` -- the fp32 log-sum-exp and the small decay-prefix
+table (16.8 MB at B4 H8 L4096) -- which spare the backward a second forward pass; a backward
+that finds only the inputs recomputes both.  Tensors must be CUDA
 tensors: there is no CPU or PyTorch fallback.
 """
 from __future__ import annotations
@@ -61,37 +63,69 @@ def set_strict_masked_grads(on: bool) -> None:
     _STRICT_MASKED_GRADS = bool(on)
 
 
-def _forward(ctx, kc, vc, xq, static_src, static_dest):
+def _forward(kc, vc, xq, static_src, static_dest):
+    """Shared new-style forward (no ctx): returns ``(out, denom)``.  The fp32 log-sum-exp and the decay-prefix table that
+    the forward kernel produces anyway ride on the returned ``denom`` as ``_ua_extras`` so that ``_setup_context`` can
+    hand them to ``ctx.save_for_backward``; a backward that does not find them recomputes them."""
     out_cm, lse_cm, denom_cm, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, keep_carry=True)
-    ctx.save_for_backward(kc, vc, xq, static_src, static_dest)
-    ctx.ua_carry = carry
-    ctx.ua_lse = lse_cm            # fp32 log-sum-exp (33 MB at B4 H8 R4 L4096): spares the backward its row max / sum
     if _OUTPUT_LAYOUT == "reference":
-        return ops.to_reference_layout(out_cm, denom_cm)
-    return ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm)
+        out, denom = ops.to_reference_layout(out_cm, denom_cm)
+    else:
+        out, denom = ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm)
+    denom._ua_extras = (lse_cm, carry)
+    return out, denom
+
+
+def _setup_context(ctx, inputs, outputs):
+    """Saves the five inputs, as the reference does (universal_attention_autograd.py:41-44, :166-169), plus -- when the
+    forward left them on ``denom`` -- the fp32 log-sum-exp (33 MB at B4 H8 R4 L4096) and the decay-prefix table, all
+    through ``save_for_backward`` so that saved-tensor hooks and version checks apply to them too."""
+    kc, vc, xq, static_src, static_dest = inputs
+    extras = getattr(outputs[1], "_ua_extras", None) if isinstance(outputs, tuple) else None
+    if extras is not None and isinstance(extras[0], torch.Tensor):
+        lse_cm, carry = extras
+        del outputs[1]._ua_extras                   # denom must not keep the two tensors alive on its own
+        ctx.ua_has_carry = carry is not None
+        saved = (kc, vc, xq, static_src, static_dest, lse_cm) + ((carry,) if carry is not None else ())
+        ctx.save_for_backward(*saved)
+        ctx.ua_has_extras = True
+    else:
+        ctx.save_for_backward(kc, vc, xq, static_src, static_dest)
+        ctx.ua_has_extras = False
 
 
 def _backward(ctx, g_out, g_denom):
-    kc, vc, xq, static_src, static_dest = ctx.saved_tensors
+    saved = ctx.saved_tensors
+    kc, vc, xq, static_src, static_dest = saved[:5]
+    if getattr(ctx, "ua_has_extras", False):
+        lse = saved[5]
+        carry = saved[6] if ctx.ua_has_carry else None
+    else:                      # only the inputs were saved: recompute what the forward would have handed over
+        _, lse, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, flags=_lib.FLAG_SKIP_MASKED_FILL, keep_carry=True)
     flags = 0 if _STRICT_MASKED_GRADS else _lib.FLAG_SKIP_MASKED_GRADS
     g_out_cm = ops.out_to_chunk_major(g_out)
     g_denom_cm = ops.denom_to_chunk_major(g_denom)
-    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags,
-                           carry=getattr(ctx, "ua_carry", None), lse=getattr(ctx, "ua_lse", None))
+    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags, carry=carry, lse=lse)
 
 
 class UniversalAttention(Function):
-    """kc, vc (b,h,n,c,d); xq (b,h,r,l,d); static_src (b,h,n,c); static_dest (b,h,l)."""
+    """kc, vc (b,h,n,c,d); xq (b,h,r,l,d); static_src (b,h,n,c); static_dest (b,h,l).
+    Same protocol as the reference class: new-style ``forward`` without ctx, ``setup_context``, ``backward``
+    (universal_attention_autograd.py:9, :41-44, :47)."""
 
     @staticmethod
-    def forward(ctx, kc, vc, xq, static_src, static_dest):
+    def forward(kc, vc, xq, static_src, static_dest):
         b, h, r, l, d = xq.shape
         _, _, n, c, _ = kc.shape
         assert kc.shape == (b, h, n, c, d) and n * c == l
         assert vc.shape == (b, h, n, c, d)
         assert static_src.shape == (b, h, n, c)
         assert static_dest.shape == (b, h, l)
-        return _forward(ctx, kc, vc, xq, static_src, static_dest)
+        return _forward(kc, vc, xq, static_src, static_dest)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        _setup_context(ctx, inputs, outputs)
 
     @staticmethod
     def backward(ctx, g_out, g_denom):
@@ -100,17 +134,22 @@ class UniversalAttention(Function):
 
 class UniversalAttention2(Function):
     """kc, vc (b,h,n_,c_,d); xq (b,h,r,_n,_c,d); static_src (b,h,n_,c_); static_dest (b,h,_n,_c).
-    The row chunking (_n,_c) is only a view of the rows; the result does not depend on it."""
+    The row chunking (_n,_c) is only a view of the rows; the result does not depend on it
+    (universal_attention_autograd.py:104, :166-169, :172)."""
 
     @staticmethod
-    def forward(ctx, kc, vc, xq, static_src, static_dest):
+    def forward(kc, vc, xq, static_src, static_dest):
         b, h, r, _n, _c, d = xq.shape
         _, _, n_, c_, _ = kc.shape
         assert kc.shape == (b, h, n_, c_, d) and n_ * c_ == _n * _c
         assert vc.shape == (b, h, n_, c_, d)
         assert static_src.shape == (b, h, n_, c_)
         assert static_dest.shape == (b, h, _n, _c)
-        return _forward(ctx, kc, vc, xq, static_src, static_dest)
+        return _forward(kc, vc, xq, static_src, static_dest)
+
+    @staticmethod
+    def setup_context(ctx, inputs, outputs):
+        _setup_context(ctx, inputs, outputs)
 
     @staticmethod
     def backward(ctx, g_out, g_denom):
@@ -148,28 +187,33 @@ class UniversalAttentionMerged(Function):
     the 2-D form."""
 
     @staticmethod
-    def forward(ctx, kc, vc, xq, static_src, static_dest):
+    def forward(kc, vc, xq, static_src, static_dest):
         b, h, n, c, d = kc.shape
         assert vc.shape == kc.shape and static_src.shape == (b, h, n, c)
         assert xq.shape[:2] == (b, h) and xq.shape[-1] == d and xq[0, 0, 0].numel() == n * c * d
         assert static_dest.numel() == b * h * n * c
         out_cm, lse_cm, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, keep_carry=True)
         merged, row_lse = ops.merge_fwd_stats_cm(out_cm, lse_cm)
-        ctx.fused = _MERGED_BACKWARD == "fused" and ops.merged_backward_supported(kc, xq)
-        ctx.ua_carry = carry
-        if ctx.fused:
-            ctx.save_for_backward(kc, vc, xq, static_src, static_dest, merged, row_lse)
-        else:
-            ctx.save_for_backward(kc, vc, xq, static_src, static_dest, out_cm, lse_cm)
-        return merged.view(*xq.shape)
+        fused = _MERGED_BACKWARD == "fused" and ops.merged_backward_supported(kc, xq)
+        merged = merged.view(*xq.shape)
+        merged._ua_extras = (fused, (merged, row_lse) if fused else (out_cm, lse_cm), carry)
+        return merged
+
+    @staticmethod
+    def setup_context(ctx, inputs, output):
+        ctx.fused, (x, y), carry = output._ua_extras
+        del output._ua_extras                       # (it holds a reference to the output itself in fused mode)
+        ctx.ua_has_carry = carry is not None
+        ctx.save_for_backward(*inputs, x, y, *((carry,) if carry is not None else ()))
 
     @staticmethod
     def backward(ctx, g):
-        kc, vc, xq, static_src, static_dest, x, y = ctx.saved_tensors
+        kc, vc, xq, static_src, static_dest, x, y = ctx.saved_tensors[:7]
+        carry = ctx.saved_tensors[7] if ctx.ua_has_carry else None
         if ctx.fused:
-            return ops.backward_merged(kc, vc, xq, static_src, static_dest, g, x, y, carry=ctx.ua_carry)
+            return ops.backward_merged(kc, vc, xq, static_src, static_dest, g, x, y, carry=carry)
         g_out_cm, g_lse_cm = ops.merge_bwd_cm(x, y, g.reshape(x.shape[0], x.shape[1], x.shape[3], x.shape[4], x.shape[5]),
                                               skip_zero_weight_blocks=True)
         return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_lse_cm, _lib.FLAG_SKIP_MASKED_GRADS,
-                               carry=ctx.ua_carry, lse=y)
+                               carry=carry, lse=y)
 
