@@ -54,7 +54,7 @@ def _canon(kc, vc, xq, static_src, static_dest):
     return k, v, q, s, t, (b, h, r, n, c, d, L)
 
 
-def _decay_terms(k, s, t, cd):
+def _decay_terms(k, s, t, cd, pow_rel_noise=0.0):
     """Steps 1-3 of the forward: Gram matrix, gated affinity, log-retention.
 
     Returns (gram, pw, aff, ell) on the (key, row) plane, all in ``cd``;
@@ -65,6 +65,13 @@ def _decay_terms(k, s, t, cd):
     kf = k.to(cd)
     gram = kf @ kf.transpose(-1, -2)                       # (b,h,Lk,Lq)
     pw = gram.clamp_min(0).pow(2.0 / 3.0)
+    if pow_rel_noise:
+        # conditioning probe: the power perturbed by a seeded random relative error of the given size (what a
+        # hardware exp2 / log2 pair of that accuracy would do); the change of the results measures how far the
+        # reference arithmetic itself pins them
+        gen = torch.Generator().manual_seed(12345)
+        sign = torch.randint(0, 2, pw.shape, generator=gen).to(cd) * 2 - 1
+        pw = pw * (1 + pow_rel_noise * sign)
     s3 = s.to(cd).pow(1.0 / 3.0)
     t3 = t.to(cd).pow(1.0 / 3.0)
     aff = pw * s3.unsqueeze(-1) * t3.unsqueeze(-2)
@@ -85,7 +92,7 @@ def _absorb(score, before, cd):
     return torch.where(before, torch.full((), MASK_VALUE, dtype=cd), score)
 
 
-def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32):
+def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32, pow_rel_noise=0.0):
     """Forward of the operator; returns ``(out, denom)`` in ``xq.dtype`` plus the
     fp32/fp64 log-sum-exp before the cast, as a third value.
 
@@ -93,7 +100,7 @@ def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32)
     """
     cd = compute_dtype
     k, v, q, s, t, (b, h, r, n, c, d, L) = _canon(kc, vc, xq, static_src, static_dest)
-    _, _, _, ell, _, _, _ = _decay_terms(k, s, t, cd)
+    _, _, _, ell, _, _, _ = _decay_terms(k, s, t, cd, pow_rel_noise)
     idx = torch.arange(L)
     before = idx.view(1, L) < idx.view(L, 1)               # row < key
     decay = ell.cumsum(-1)
@@ -112,7 +119,7 @@ def ua_forward(kc, vc, xq, static_src, static_dest, compute_dtype=torch.float32)
     return out.to(xq.dtype), lse.to(xq.dtype), lse
 
 
-def ua_backward(kc, vc, xq, static_src, static_dest, g_out, g_denom, compute_dtype=torch.float32):
+def ua_backward(kc, vc, xq, static_src, static_dest, g_out, g_denom, compute_dtype=torch.float32, pow_rel_noise=0.0):
     """Gradients ``(dkc, dvc, dxq, dstatic_src, dstatic_dest)`` for upstream
     ``g_out (b,h,r,L,d,n)`` and ``g_denom (b,h,r,L,n)``.
 
@@ -122,7 +129,7 @@ def ua_backward(kc, vc, xq, static_src, static_dest, g_out, g_denom, compute_dty
     cd = compute_dtype
     k, v, q, s, t, (b, h, r, n, c, d, L) = _canon(kc, vc, xq, static_src, static_dest)
     round_in = (lambda x: x.to(xq.dtype).to(cd)) if cd == torch.float32 else (lambda x: x)
-    gram, pw, aff, ell, s3, t3, strict = _decay_terms(k, s, t, cd)
+    gram, pw, aff, ell, s3, t3, strict = _decay_terms(k, s, t, cd, pow_rel_noise)
     idx = torch.arange(L)
     before = idx.view(1, L) < idx.view(L, 1)
     decay = torch.where(before, torch.full((), MASK_VALUE, dtype=cd), ell.cumsum(-1))

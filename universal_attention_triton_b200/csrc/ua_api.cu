@@ -78,18 +78,22 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
 }
 
 struct BwdWorkspaceTc {
-  size_t off_dk, off_dq, off_dt, off_carry, acc_bytes, total;
+  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, acc_bytes, total;
 };
 
+// Scratch of the tensor-core backward: status | fp32 accumulators dK, dV (the part from the rows before a chunk), dQ,
+// d dest | decay-prefix table (two entries per 128-row tile) | log-sum-exp (only written when the caller has none).
 BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   BwdWorkspaceTc w;
   const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
   size_t o = 256;   // [0, 256): status word
   w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
+  w.off_dv = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
   w.off_dt = o; o = align_up(o + BH * s.L * f, 256);
   w.acc_bytes = o;
-  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 128 * f, 256);
+  w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 256 * f, 256);
+  w.off_lse = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
   w.total = o;
   return w;
 }
@@ -231,7 +235,7 @@ size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
 size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
-  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd_supported(s, dtype)) return bwd_layout_tc(s).total;
+  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd2_supported(s, dtype)) return bwd_layout_tc(s).total;
   const SimtCfg cfg = simt_cfg(s.C, s.D, dtype, true);
   if (!cfg.rt) return 0;
   return bwd_layout(s, cfg.rt).total;
@@ -240,8 +244,8 @@ size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
 size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
-  if ((flags & UA_FLAG_FORCE_SIMT) || !ua::sm100::bwd_supported(s, dtype)) return 0;
-  return (size_t)s.B * s.H * s.N * s.N * 128 * sizeof(float);
+  if ((flags & UA_FLAG_FORCE_SIMT) || !ua::sm100::bwd2_supported(s, dtype)) return 0;
+  return (size_t)s.B * s.H * s.N * s.N * 256 * sizeof(float);
 }
 
 int ua_fwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
@@ -347,7 +351,7 @@ size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
   if (!ua::sm100::bwd_supported(s, dtype)) return 0;
-  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 128 * sizeof(float), 256);      // status | decay-prefix table
+  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 256 * sizeof(float), 256);      // status | decay-prefix table
 }
 
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
@@ -403,7 +407,7 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
   bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr;
+  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
 }
 
@@ -430,32 +434,70 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ua::Shape s = to_shape(dims);
 
-  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd_supported(s, dtype)) {
+  if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd2_supported(s, dtype)) {
     if (!aligned16(dvc) || !aligned16(dkc) || !aligned16(dxq)) return UA_ERR_ALIGNMENT;
     BwdWorkspaceTc w = bwd_layout_tc(s);
     if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
     char* ws = static_cast<char*>(workspace);
     if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
-    ua::sm100::BwdParams bp;
-    bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
-    bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
     float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
-    bp.carry = carry_tab;
-    bp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
-    bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
-    bp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
-    bp.dvc = static_cast<bf16*>(dvc);
-    bp.dss = dstatic_src;
-    bp.status = reinterpret_cast<int*>(ws);
-    bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-    ua::sm100::whole_sequence(bp);
-    bp.lse = lse_cm;
-    e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, carry_tab, carry_in == nullptr, nullptr, st);
-    if (e) return e;
+    float* acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
+    float* acc_dv = reinterpret_cast<float*>(ws + w.off_dv);
+    float* acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
+    float* acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+    const bool skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) != 0;
     const size_t BHs = (size_t)s.B * s.H;
-    if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;
-    if ((e = convert_any(dtype, bp.acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
-    if ((e = convert_any(gate_dtype, bp.acc_dt, dstatic_dest, BHs * s.L, st))) return e;
+    // What the keys-on-lanes kernel needs besides the inputs: the decay-prefix table and the forward's log-sum-exp.  A
+    // caller that has neither gets both from one statistics-only run of the forward kernel (no output tile is written).
+    const float* lse = lse_cm;
+    if (!lse || !carry_in) {
+      ua::sm100::FwdParams fp;
+      fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest; fp.out = nullptr; fp.denom = nullptr;
+      fp.lse = lse ? nullptr : reinterpret_cast<float*>(ws + w.off_lse);
+      fp.status = reinterpret_cast<int*>(ws);
+      fp.carry = carry_in ? nullptr : carry_tab;
+      ua::sm100::whole_sequence(fp);
+      if (lse) e = ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st);      // decay-only pass
+      else e = ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq, fp, false, st);
+      if (e) return e;
+      if (!lse) lse = fp.lse;
+    }
+    // Rows before a chunk (uniform softmax): their gradient is added to the accumulators by a kernel of its own.
+    if (!skip_masked && s.N > 1) {
+      if (ua::sm100::bwd_supported(s, dtype)) {
+        ua::sm100::BwdParams bp;
+        bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
+        bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+        bp.carry = nullptr; bp.acc_dk = acc_dk; bp.acc_dq = acc_dq; bp.acc_dt = acc_dt;
+        bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws); bp.skip_masked = 0;
+        ua::sm100::whole_sequence(bp);
+        bp.acc_dv = acc_dv; bp.masked_only = 1;
+        e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, nullptr, false, nullptr, st);
+      } else {
+        const SimtCfg mcfg = simt_cfg(s.C, s.D, dtype, true);
+        if (!mcfg.rt) return UA_ERR_UNSUPPORTED;
+        ua::simt::BwdParams mp;
+        mp.s = s; mp.kc = kc; mp.vc = vc; mp.xq = xq; mp.ssrc = static_src; mp.sdest = static_dest;
+        mp.g_out = g_out_cm; mp.g_denom = g_denom_cm; mp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+        mp.acc_dk = acc_dk; mp.acc_dv = acc_dv; mp.acc_dq = acc_dq; mp.acc_ds = acc_dt; mp.acc_dt = acc_dt;   // (nothing is added to the gates)
+        mp.carry = nullptr; mp.rt = mcfg.rt; mp.skip_masked = 0; mp.masked_only = 1;
+        if (mcfg.compact) e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, bf16>(mp, st) : launch_simt_bwd<bf16, bf16, bf16>(mp, st);
+        else e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, float>(mp, st) : launch_simt_bwd<bf16, bf16, float>(mp, st);
+      }
+      if (e) return e;
+    }
+    ua::sm100::Bwd2Params qp;
+    qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest;
+    qp.g_denom = g_denom_cm; qp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+    qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
+    qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
+    qp.acc_dv_in = (!skip_masked && s.N > 1) ? acc_dv : nullptr;
+    qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
+    e = ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, xq, g_out_cm, qp, st);
+    if (e) return e;
+    if ((e = convert_any(dtype, acc_dk, dkc, BHs * s.L * s.D, st))) return e;
+    if ((e = convert_any(dtype, acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
+    if ((e = convert_any(gate_dtype, acc_dt, dstatic_dest, BHs * s.L, st))) return e;
     return UA_OK;
   }
 
@@ -478,6 +520,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   p.carry = reinterpret_cast<float*>(ws + w.off_carry);
   p.rt = rt;
   p.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
+  p.masked_only = 0;
   if (dtype == UA_F32) e = launch_simt_bwd<float, float, float>(p, st);
   else if (cfg.compact) e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, bf16>(p, st) : launch_simt_bwd<bf16, bf16, bf16>(p, st);
   else if (gate_dtype == UA_F32) e = launch_simt_bwd<bf16, float, float>(p, st);
@@ -704,32 +747,34 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
       !aligned16(dxq))
     return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
-  if (!ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  if (!ua::sm100::bwd2_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   BwdWorkspaceTc w = bwd_layout_tc(s);
   if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   char* ws = static_cast<char*>(workspace);
   if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::BwdParams bp;
-  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
-  bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
   float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
-  bp.carry = carry_tab;
-  bp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
-  bp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
-  bp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
-  bp.dvc = static_cast<bf16*>(dvc);
-  bp.dss = dstatic_src;
-  bp.status = reinterpret_cast<int*>(ws);
-  bp.skip_masked = 1;
-  ua::sm100::whole_sequence(bp);
-  bp.merged = 1; bp.row_lse = row_lse; bp.row_delta = row_delta;
-  e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_merged, bp, carry_tab, carry_in == nullptr, nullptr, st);
+  if (!carry_in) {
+    ua::sm100::FwdParams fp;
+    fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
+    fp.status = reinterpret_cast<int*>(ws); fp.carry = carry_tab;
+    ua::sm100::whole_sequence(fp);
+    if ((e = ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st))) return e;
+  }
+  ua::sm100::Bwd2Params qp;
+  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr; qp.g_denom_is_f32 = 1;
+  qp.lse = nullptr; qp.row_lse = row_lse; qp.row_delta = row_delta; qp.carry = carry_tab;
+  qp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
+  qp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
+  qp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+  qp.acc_dv_in = nullptr;
+  qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
+  e = ua::sm100::launch_bwd2(s, gate_dtype, true, kc, vc, xq, g_merged, qp, st);
   if (e) return e;
   const size_t BHs = (size_t)s.B * s.H;
-  if ((e = convert_any(dtype, bp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;
-  if ((e = convert_any(dtype, bp.acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
-  if ((e = convert_any(gate_dtype, bp.acc_dt, dstatic_dest, BHs * s.L, st))) return e;
+  if ((e = convert_any(dtype, qp.acc_dk, dkc, BHs * s.L * s.D, st))) return e;
+  if ((e = convert_any(dtype, qp.acc_dq, dxq, BHs * s.R * s.L * s.D, st))) return e;
+  if ((e = convert_any(gate_dtype, qp.acc_dt, dstatic_dest, BHs * s.L, st))) return e;
   return UA_OK;
 }
 

@@ -56,7 +56,7 @@ struct BwdParams {
   const void* sdest;
   const void* g_denom;     // (b,h,n,r,L) fp32 or bf16
   int g_denom_is_f32;
-  const float* carry;      // (b*h*n, n, 128) decay prefix at the start of row tile j
+  const float* carry;      // (b*h*n, n, 2, 128) decay prefix at the start of each 64-row half of row tile j (the first half is used)
   float* acc_dk;           // (b*h, L, 64) fp32, zeroed
   float* acc_dq;           // (b*h, r, L, 64) fp32, zeroed
   float* acc_dt;           // (b*h, L) fp32, zeroed
@@ -78,6 +78,8 @@ struct BwdParams {
   int merged;
   const float* row_lse;    // (b,h,r,L) fp32: log-sum-exp of the row over all keys
   const float* row_delta;  // (b,h,r,L) fp32: g . merged
+  int masked_only;         // only the rows before the chunk (the rows that see it are another kernel's): dV_i and dK_i are
+                           // ADDED to acc_dv / acc_dk, d static_src is left alone
 };
 
 struct BwdCfg {
@@ -547,7 +549,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     if (valid && !p.decay_only) {
       // ---- decay prefix (forward recomputation): thread = key, C^T[row][key] to shared memory ----
       if (part == 0) t3buf[tid] = cbrtf(Num<TG>::ld(sd + rl + tid));
-      const float carry = p.carry[(chunk_id * N + j) * 128 + tid];
+      const float carry = p.carry[(chunk_id * N + j) * 256 + tid];
       mb.sync();                                  // t3 visible; every reader of the previous tile's C^T is done
       UA_PH(0)
       if (!mb.ok || !c.wait_w(bGFull, T)) return;
@@ -1030,7 +1032,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
   }
   float4 od[kParts];
   mb.gather(make_float4(ds_acc, 0.f, 0.f, 0.f), od);
-  if (mb.ok && part == 0) {
+  if (mb.ok && part == 0 && !p.masked_only) {
     const float dsv = ((od[0].x + od[1].x) + (od[2].x + od[3].x)) / (3.0f * s3 * s3);
     if (p.acc_ds) atomicAdd(p.acc_ds + krow, dsv);
     else Num<TG>::st(static_cast<TG*>(p.dss) + krow, dsv);
@@ -1060,7 +1062,7 @@ bwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   {
     const int lo = c.i > p.j_begin ? c.i : p.j_begin;               // first row tile of the range that sees the chunk
     const int top = c.i < p.j_end ? c.i : p.j_end;                  // rows below this tile index lie before the chunk
-    c.nvalid = p.j_end > lo ? p.j_end - lo : 0;
+    c.nvalid = (p.j_end > lo && !p.masked_only) ? p.j_end - lo : 0;
     const int nmask = (p.skip_masked || p.decay_only || p.merged || top <= p.j_begin) ? 0 : top - p.j_begin;
     c.ntiles = c.nvalid + nmask;
   }

@@ -49,7 +49,7 @@ struct FwdParams {
   const void* ssrc;
   const void* sdest;
   const void* vc;        // values, for the masked-row fill
-  __nv_bfloat16* out;    // chunk-major (b,h,n,r,L,d)
+  __nv_bfloat16* out;    // chunk-major (b,h,n,r,L,d); null: only lse / denom are produced
   float* lse;            // (b,h,n,r,L)
   __nv_bfloat16* denom;  // (b,h,n,r,L) or null
   int* status;           // device word: 0 = ok, otherwise a role-specific timeout code
@@ -60,7 +60,7 @@ struct FwdParams {
   int r0;                  // row of the slab where the range starts (several ranges can share one slab)
   const float* carry_in;   // optional (b*h*n, 128): decay prefix of key k at its first row tile of the range
   float* total_out;        // optional (b*h*n, 128): decay prefix after the last row tile of the range
-  float* carry;          // optional (required in carry-only mode): (b*h*n, n, 128) decay prefix of key k at the start of row tile j
+  float* carry;          // optional (required in carry-only mode): (b*h*n, n, 2, 128) decay prefix of key k at the start of each 64-row half of row tile j
 };
 
 // Gated affinity and log-retention of one (key, row) pair from the Gram value
@@ -249,7 +249,10 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   uint8_t* sCs = c.smem + Cfg::oCs;
   const size_t key_id = ((size_t)c.bh * p.s.N + c.i) * 128 + k;
-  float carry = p.carry_in ? p.carry_in[key_id] : 0.f;
+  // The prefix carried from tile to tile reaches -2e4 at L = 4096, where fp32 spacing is 2e-3: it is kept as an
+  // unevaluated sum carry + carry_lo (the rounding error of every tile's addition is carried along), so that what a
+  // row sees is one rounding away from the exact sum however many tiles came before it.
+  float carry = p.carry_in ? p.carry_in[key_id] : 0.f, carry_lo = 0.f;
   UF_DECL
   for (int T = 0; T < c.ntiles; ++T) {
     const int j = c.j0 + T;
@@ -262,10 +265,10 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
     UF(1)
     tc_fence_after();
     const bool diag = (j == c.i);
-    if (p.carry) p.carry[(((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 128 + k] = carry;
-    // The prefix inside a tile is  carry + (sum of the totals of earlier 32-row blocks + scan inside the block):
-    // the backward recomputes it with four threads per key, one per block, and must get the same bits.
-    float tprev = 0.f, cval = carry;
+    float* carry_row = p.carry ? p.carry + (((size_t)c.bh * p.s.N + c.i) * p.s.N + j) * 256 + k : nullptr;
+    if (carry_row) carry_row[0] = carry;
+    // The prefix inside a tile is  carry + (carry_lo + sum of the totals of earlier 32-row blocks + scan inside the block).
+    float tprev = carry_lo, cval = carry;
 #pragma unroll 1
     for (int cb = 0; cb < 4; ++cb) {
       uint32_t g[32];
@@ -275,6 +278,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
         tc_fence_before();
         c.arrive_w(kGFree);
       }
+      if (cb == 2 && carry_row) carry_row[128] = cval;      // prefix after the first 64 rows of the tile
       float v[32];
       float local = 0.f;
 #pragma unroll
@@ -299,7 +303,12 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
         }
       }
     }
-    carry = cval;
+    {
+      // carry + tprev (tprev = carry_lo + the tile's total) as an exact two-term sum
+      const float sum = carry + tprev, bb = sum - carry;
+      carry_lo = (carry - (sum - bb)) + (tprev - bb);
+      carry = sum;
+    }
     if (!kCarryOnly) c.arrive_w(kCReady + T % Cfg::kCBufs);
     UF(2)
   }
@@ -411,6 +420,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           tc_fence_before();
           c.arrive_w(kOFree + sb);
         }
+        if (!p.out) continue;                 // statistics-only run (the log-sum-exp for a backward that was not given one)
         uint32_t pk[16];
 #pragma unroll
         for (int u = 0; u < 16; ++u) {

@@ -43,6 +43,7 @@ struct BwdParams {
   float* carry;   // (b*h*n, L/rt, c) decay prefix at the start of each row tile
   int rt;
   int skip_masked;
+  int masked_only;   // only the row tiles that lie wholly before the chunk (the others are another kernel's)
 };
 
 __device__ __forceinline__ float dot4(const float* a, const float* b, int D) {
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
   __syncthreads();
 
   // ---- pass 1: decay prefix at the start of every row tile --------------------
-  for (int jt = 0; jt < NT; ++jt) {
+  for (int jt = 0; jt < NT && !p.masked_only; ++jt) {
     const int j0 = jt * RT;
     if (j0 + RT <= i * C) {
       for (int k = tid; k < C; k += kThreads) carry_tab[(size_t)jt * C + k] = 0.f;
@@ -395,6 +396,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
     const int j0 = jt * RT;
     const bool fully_masked = (j0 + RT <= i * C);
     if (fully_masked && p.skip_masked) break;     // every remaining tile is masked too
+    if (!fully_masked && p.masked_only) continue;
     load_tile<T>(sKj, kc + (size_t)j0 * D, RT, D, DP);
     for (int q = tid; q < RT; q += kThreads) {
       sT3[q] = cbrtf(Num<TG>::ld(sd + j0 + q));
@@ -404,7 +406,7 @@ __global__ void __launch_bounds__(kThreads) bwd_kernel(BwdParams p) {
     // recompute Gram tile and decay prefix
     for (int k = tid; k < C; k += kThreads) {
       const int kg = i * C + k;
-      const float carry = carry_tab[(size_t)jt * C + k], s3 = sS3[k];
+      const float carry = fully_masked ? 0.f : carry_tab[(size_t)jt * C + k], s3 = sS3[k];
       float local = 0.f;
       for (int q = 0; q < RT; ++q) {
         const int qg = j0 + q;

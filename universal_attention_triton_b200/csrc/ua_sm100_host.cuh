@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 
 #include "../../include/ua_b200.h"
+#include "ua_bwd2_sm100.cuh"
 #include "ua_bwd_sm100.cuh"
 #include "ua_fwd_sm100.cuh"
 
@@ -26,13 +27,13 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor [rows][D] row-major, boxes of 128 rows x 64 elements, 128-byte swizzle.
-inline bool make_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int D) {
+// 2-D bf16 tensor [rows][D] row-major, boxes of box_rows (128 or 64) rows x 64 elements, 128-byte swizzle.
+inline bool make_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int D, int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
   cuuint64_t gdim[2] = {(cuuint64_t)D, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)D * 2};
-  cuuint32_t box[2] = {64, 128};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -42,12 +43,12 @@ inline bool make_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int
 
 // 2-D fp32 tensor [rows][64] row-major (the dQ / dK accumulators), boxes of 128 rows x 32 floats, 128-byte swizzle:
 // the target of the backward kernel's shared-memory -> global reductions.
-inline bool make_f32_rows_map(CUtensorMap* map, const void* base, uint64_t rows) {
+inline bool make_f32_rows_map(CUtensorMap* map, const void* base, uint64_t rows, int D = 64, int box_rows = 128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t gdim[2] = {64, (cuuint64_t)rows};
-  cuuint64_t gstride[1] = {256};
-  cuuint32_t box[2] = {32, 128};
+  cuuint64_t gdim[2] = {(cuuint64_t)D, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)D * 4};
+  cuuint32_t box[2] = {32, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -98,13 +99,17 @@ int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, c
                               : launch_fwd_t<128, __nv_bfloat16, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st);
 }
 
+// Shapes of the first tensor-core backward kernel (rows-on-lanes): still the kernel of the row-range entry points and of
+// the rows before a chunk.
 inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && s.D == 64; }
+// Shapes of the keys-on-lanes backward kernel.
+inline bool bwd2_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128); }
 
 // Fills the row-range / sharding fields of BwdParams for a call over the whole sequence.
 inline void whole_sequence(BwdParams& p) {
   p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
   p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0; p.lse = nullptr;
-  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr;
+  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr; p.masked_only = 0;
 }
 
 // Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
@@ -143,6 +148,33 @@ inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void
                       const BwdParams& p, float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
   return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st)
                               : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st);
+}
+
+// Keys-on-lanes backward over the whole sequence (rows that see the chunk only).  kMode 1: per-chunk log-sum-exp and
+// g_denom; kMode 2: merged upstream gradient.  The caller zeroes the fp32 accumulators.
+template <int D, typename TG, int kMode>
+int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const Bwd2Params& p,
+                  cudaStream_t st) {
+  using Cfg = Bwd2Cfg<D>;
+  CUtensorMap tmK, tmV, tmQ, tmG, tmDQ, tmDK;
+  const uint64_t BH = (uint64_t)s.B * s.H;
+  if (!make_rows_map(&tmK, kc, BH * s.L, D, 64) || !make_rows_map(&tmV, vc, BH * s.L, D, 64) ||
+      !make_rows_map(&tmQ, xq, BH * s.R * s.L, D, 64) ||
+      !make_rows_map(&tmG, g_out, (kMode == 2 ? BH : BH * s.N) * s.R * s.L, D, 64) ||
+      !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * s.L, D, 64) || !make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L, D, 64))
+    return UA_ERR_CUDA;
+  auto kern = bwd2_kernel<D, TG, kMode>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
+  kern<<<(unsigned)(BH * s.N), 320, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+inline int launch_bwd2(const Shape& s, int gate_dtype, bool merged, const void* kc, const void* vc, const void* xq,
+                       const void* g_out, const Bwd2Params& p, cudaStream_t st) {
+#define UA_BWD2(D_, TG_) (merged ? launch_bwd2_t<D_, TG_, 2>(s, kc, vc, xq, g_out, p, st) : launch_bwd2_t<D_, TG_, 1>(s, kc, vc, xq, g_out, p, st))
+  if (s.D == 64) return gate_dtype == UA_F32 ? UA_BWD2(64, float) : UA_BWD2(64, __nv_bfloat16);
+  return gate_dtype == UA_F32 ? UA_BWD2(128, float) : UA_BWD2(128, __nv_bfloat16);
+#undef UA_BWD2
 }
 
 }  // namespace sm100

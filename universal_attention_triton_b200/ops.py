@@ -26,8 +26,27 @@ def _dtype_code(t: torch.dtype) -> int:
     raise TypeError(f"Universal Attention kernels support float32 and bfloat16, got {t}")
 
 
+def plain(*tensors):
+    """Strips functorch wrappers (``torch.func.grad`` hands the backward its gradients and saved tensors wrapped, alive
+    or already dead) so that the kernels get tensors with storage; first-order transforms only."""
+    try:
+        from torch._C._functorch import get_unwrapped, maybe_get_level, unwrap_if_dead
+    except ImportError:      # pragma: no cover
+        return tensors if len(tensors) != 1 else tensors[0]
+    out = []
+    for t in tensors:
+        if isinstance(t, torch.Tensor):
+            for _ in range(16):
+                if maybe_get_level(t) == -1:
+                    break
+                u = unwrap_if_dead(t)
+                t = u if u is not t else get_unwrapped(t)
+        out.append(t)
+    return tuple(out) if len(out) != 1 else out[0]
+
+
 def _ptr(t):
-    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+    return ctypes.c_void_p(plain(t).data_ptr()) if t is not None else ctypes.c_void_p(0)
 
 
 def _stream():
@@ -245,8 +264,8 @@ def row_dot(a, b):
 
 
 def merged_backward_supported(kc, xq) -> bool:
-    """Shapes the one-kernel backward of the merged output takes (bf16, chunk 128, head_dim 64)."""
-    return xq.dtype == torch.bfloat16 and kc.shape[3] == 128 and kc.shape[4] == 64
+    """Shapes the one-kernel backward of the merged output takes (bf16, chunk 128, head_dim 64 or 128)."""
+    return xq.dtype == torch.bfloat16 and kc.shape[3] == 128 and kc.shape[4] in (64, 128)
 
 
 def backward_merged(kc, vc, xq, static_src, static_dest, g_merged, merged, row_lse, carry=None):

@@ -18,8 +18,12 @@ What crosses ranks:
    the per-key sum of the decay-prefix gradient over its rows (``dctot``); these are all-gathered, a
    block's reverse carry is the sum over the blocks AFTER it, and a decay-only correction pass adds the
    gradient it induces;
-4. (backward) dK, dV, d static_src -- fp32 partial sums over a rank's rows for ALL keys -- are
-   all-reduced and every rank keeps the slice of its own keys.  dQ and d static_dest are row-local.
+4. (backward) dK, dV, d static_src -- fp32 partial sums over a rank's rows for ALL keys -- are packed
+   destination-rank-major and reduce-scattered in ONE collective: every rank receives only the sums for
+   its own keys.  dQ and d static_dest are row-local.
+
+Collectives per step: forward 1 all-gather (K | V | src, byte-packed) + 1 all-gather of the decay totals;
+backward 1 all-gather of the dC totals + 1 reduce-scatter (dK | dV | dsrc, fp32).
 
 The per-(row, key-chunk) softmax statistics need no exchange with the reference's output format:
 ``denom[row, chunk]`` is complete on the rank that owns the row (it is itself the partial log-sum-exp
@@ -51,51 +55,96 @@ def owned_blocks(world: int, rank: int, zigzag: bool):
     return world, [rank]
 
 
-def _gather_sequence(t_local, dim, group, zigzag):
-    """All-gather a tensor whose axis `dim` holds this rank's blocks, and put the blocks in sequence order."""
+def _block_order(world: int, zigzag: bool):
+    """Block ids in the order (rank 0's blocks, rank 1's blocks, ...)."""
+    return [p for g in range(world) for p in owned_blocks(world, g, zigzag)[1]]
+
+
+def _gather_sequence(locals_, group, zigzag):
+    """ONE all-gather for several local tensors whose axis 2 holds this rank's blocks (keys, values, static_src:
+    byte-packed into one send buffer, received into one preallocated buffer), then the blocks of each tensor are put
+    in sequence order with a single copy."""
     world = dist.get_world_size(group)
-    parts = [torch.empty_like(t_local) for _ in range(world)]
-    dist.all_gather(parts, t_local.contiguous(), group=group)
-    if not zigzag:
-        return torch.cat(parts, dim=dim)
-    P = 2 * world
-    blocks = [None] * P
-    for g, t in enumerate(parts):
-        first, second = t.chunk(2, dim=dim)
-        blocks[g], blocks[P - 1 - g] = first, second
-    return torch.cat(blocks, dim=dim)
+    flat = [t.contiguous().view(torch.uint8).reshape(-1) for t in locals_]
+    sizes = [f.numel() for f in flat]
+    assert all(sz % 4 == 0 for sz in sizes)
+    send = torch.cat(flat)
+    recv = torch.empty(world * send.numel(), dtype=torch.uint8, device=send.device)
+    dist.all_gather_into_tensor(recv, send, group=group)
+    recv = recv.view(world, -1)
+    outs, off = [], 0
+    for t, sz in zip(locals_, sizes):
+        parts = recv[:, off:off + sz].view(t.dtype).reshape((world,) + tuple(t.shape))      # (G, b, h, n_l, ...)
+        off += sz
+        nd = parts.dim()
+        tail = list(range(4, nd))
+        if not zigzag:
+            full = parts.permute(1, 2, 0, 3, *tail)                                              # (b, h, G, n_l, ...)
+        else:
+            nb = t.shape[2] // 2
+            halves = parts.reshape((world, t.shape[0], t.shape[1], 2, nb) + tuple(t.shape[3:]))    # (G, b, h, 2, nb, ...)
+            tail2 = list(range(5, halves.dim()))
+            first = halves[:, :, :, 0].permute(1, 2, 0, 3, *[x - 1 for x in tail2])               # blocks 0 .. G-1
+            second = halves[:, :, :, 1].flip(0).permute(1, 2, 0, 3, *[x - 1 for x in tail2])      # blocks G .. 2G-1
+            full = torch.cat([first, second], dim=2)
+        outs.append(full.reshape((t.shape[0], t.shape[1], -1) + tuple(t.shape[3:])))
+    return outs
 
 
 def _gather_block_tables(tables, world, rank, zigzag, group):
-    """tables: list (one per owned block, local order) of (b,h,n,128) tensors -> list of P tensors in block order."""
-    stacked = torch.stack(tables)
-    parts = [torch.empty_like(stacked) for _ in range(world)]
-    dist.all_gather(parts, stacked, group=group)
-    P, _ = owned_blocks(world, rank, zigzag)
-    out = [None] * P
-    for g in range(world):
-        _, blks = owned_blocks(world, g, zigzag)
-        for li, p in enumerate(blks):
-            out[p] = parts[g][li]
+    """tables: list (one per owned block, local order) of (b,h,n,128) tensors -> (P, b,h,n,128) stacked in block order."""
+    stacked = torch.stack(tables).contiguous()
+    recv = torch.empty(world * stacked.numel(), dtype=stacked.dtype, device=stacked.device)
+    dist.all_gather_into_tensor(recv, stacked.reshape(-1), group=group)
+    recv = recv.reshape((-1,) + tuple(stacked.shape[1:]))                # (rank-major, local block) = _block_order
+    order = torch.tensor(_block_order(world, zigzag), device=recv.device)
+    out = torch.empty_like(recv)
+    out[order] = recv
     return out
+
+
+def _reduce_scatter_keys(parts, kc_local_shape, world, zigzag, group):
+    """``parts``: fp32 partial sums over this rank's rows for ALL keys, each (b,h,L[,d]).  Every rank needs only the sum for
+    its OWN keys: the tensors are packed destination-rank-major and ONE reduce-scatter returns this rank's segment
+    (1/G of the bytes an all-reduce would bring back).  Returns the tensors restricted to the rank's blocks, (b,h,L_l[,d])."""
+    order = _block_order(world, zigzag)
+    P = len(order)
+    idx = torch.tensor(order, device=parts[0].device)
+    packed, shapes = [], []
+    for t in parts:
+        b, h, L = t.shape[:3]
+        blk = t.reshape((b, h, P, L // P) + tuple(t.shape[3:]))
+        perm = blk.permute(2, 0, 1, 3, *range(4, blk.dim()))[idx]         # (P in destination order, b, h, rows, ...)
+        shapes.append(tuple(perm.shape[1:]))
+        packed.append(perm.reshape(world, -1))
+    send = torch.cat(packed, dim=1).contiguous()
+    recv = torch.empty(send.shape[1], dtype=send.dtype, device=send.device)
+    if dist.get_backend(group) == "gloo":      # no reduce-scatter on the CPU backend of the tests
+        dist.all_reduce(send, group=group)
+        recv = send[dist.get_rank(group)].clone()
+    else:
+        dist.reduce_scatter_tensor(recv, send, group=group)
+    outs, off = [], 0
+    per = P // world
+    for shp in shapes:
+        nel = per * int(torch.tensor(shp).prod())
+        mine = recv[off:off + nel].reshape((per,) + shp)                 # (own blocks, b, h, rows, ...)
+        off += nel
+        mine = mine.permute(1, 2, 0, 3, *range(4, mine.dim()))
+        outs.append(mine.reshape((shp[0], shp[1], -1) + shp[3:]))
+    return outs
 
 
 def _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backend, zigzag):
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     P, mine = owned_blocks(world, rank, zigzag)
     nb = kc_local.shape[2] // len(mine)                      # tiles (= key chunks of 128) per block
-    kc = _gather_sequence(kc_local, 2, group, zigzag)
-    vc = _gather_sequence(vc_local, 2, group, zigzag)
-    ss = _gather_sequence(static_src_local, 2, group, zigzag)
+    kc, vc, ss = _gather_sequence([kc_local, vc_local, static_src_local], group, zigzag)
     sd = static_dest_local.reshape(static_dest_local.shape[0], static_dest_local.shape[1], -1)
     rows_b = nb * kc.shape[3]                               # rows per block (row tile = key chunk = 128 rows on the GPU)
     totals = [backend.decay_totals_rows(kc, ss, sd, p * nb, (p + 1) * nb, row_offset=li * rows_b) for li, p in enumerate(mine)]
     all_tot = _gather_block_tables(totals, world, rank, zigzag, group)
-    carries = []
-    run = torch.zeros_like(all_tot[0])
-    for p in range(P):                                       # fixed order: every rank forms the same partial sums
-        carries.append(run)
-        run = run + all_tot[p]
+    carries = all_tot.cumsum(0) - all_tot                    # exclusive prefix over the blocks (same order on every rank)
     return world, rank, P, mine, nb, kc, vc, ss, sd, carries
 
 
@@ -139,16 +188,12 @@ def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_loca
         dctots.append(res[5])
     dk, dv, dxq, dsrc, ddest = acc
     all_dct = _gather_block_tables(dctots, world, rank, zigzag, group)
+    suffixes = all_dct.flip(0).cumsum(0).flip(0) - all_dct   # sum over the blocks AFTER each block
     for li, p in enumerate(mine):
         if p + 1 < P:
-            suffix = torch.zeros_like(all_dct[0])
-            for q in range(p + 1, P):
-                suffix = suffix + all_dct[q]
-            backend.backward_rows_suffix(kc, vc, ss, sd, p * nb, (p + 1) * nb, suffix, dk, dsrc, ddest, row_offset=li * nb * kc.shape[3])
-    for t in (dk, dv, dsrc):
-        dist.all_reduce(t, group=group)
-    c = kc.shape[3]
-    pick = lambda t: torch.cat([t[:, :, p * nb * c:(p + 1) * nb * c] for p in mine], dim=2)
-    return (pick(dk).reshape(kc_local.shape).to(kc_local.dtype), pick(dv).reshape(vc_local.shape).to(vc_local.dtype),
-            dxq.reshape(xq_local.shape).to(xq_local.dtype), pick(dsrc).reshape(static_src_local.shape).to(static_src_local.dtype),
+            backend.backward_rows_suffix(kc, vc, ss, sd, p * nb, (p + 1) * nb, suffixes[p], dk, dsrc, ddest,
+                                         row_offset=li * nb * kc.shape[3])
+    dk_l, dv_l, dsrc_l = _reduce_scatter_keys([dk, dv, dsrc], kc_local.shape, world, zigzag, group)
+    return (dk_l.reshape(kc_local.shape).to(kc_local.dtype), dv_l.reshape(vc_local.shape).to(vc_local.dtype),
+            dxq.reshape(xq_local.shape).to(xq_local.dtype), dsrc_l.reshape(static_src_local.shape).to(static_src_local.dtype),
             ddest.reshape(static_dest_local.shape).to(static_dest_local.dtype))

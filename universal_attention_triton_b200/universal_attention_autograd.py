@@ -95,7 +95,8 @@ def _setup_context(ctx, inputs, outputs):
 
 
 def _backward(ctx, g_out, g_denom):
-    saved = ctx.saved_tensors
+    saved = ops.plain(*ctx.saved_tensors)
+    g_out, g_denom = ops.plain(g_out, g_denom)
     kc, vc, xq, static_src, static_dest = saved[:5]
     if getattr(ctx, "ua_has_extras", False):
         lse = saved[5]
@@ -171,7 +172,7 @@ class SMVecMatMul(Function):
 
     @staticmethod
     def backward(ctx, g):
-        mat, vec = ctx.saved_tensors
+        mat, vec, g = ops.plain(*ctx.saved_tensors, g)
         g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g,
                                               skip_zero_weight_blocks=not _STRICT_MASKED_GRADS)
         return ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
@@ -208,8 +209,10 @@ class UniversalAttentionMerged(Function):
 
     @staticmethod
     def backward(ctx, g):
-        kc, vc, xq, static_src, static_dest, x, y = ctx.saved_tensors[:7]
-        carry = ctx.saved_tensors[7] if ctx.ua_has_carry else None
+        saved = ops.plain(*ctx.saved_tensors)
+        g = ops.plain(g)
+        kc, vc, xq, static_src, static_dest, x, y = saved[:7]
+        carry = saved[7] if ctx.ua_has_carry else None
         if ctx.fused:
             return ops.backward_merged(kc, vc, xq, static_src, static_dest, g, x, y, carry=carry)
         g_out_cm, g_lse_cm = ops.merge_bwd_cm(x, y, g.reshape(x.shape[0], x.shape[1], x.shape[3], x.shape[4], x.shape[5]),
