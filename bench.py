@@ -195,22 +195,19 @@ def run_reference(args, w, rank):
     print(json.dumps(line), flush=True)
 
 
-def run_sequence_parallel(args, w, rank, world, device, W, K):
-    """One long sequence, rows sharded over the ranks (strong scaling): sp_forward + sp_backward.  Contiguous blocks by
-    default; --zigzag gives rank g the blocks g and 2G-1-g, which balances the causal work."""
+def sp_leg(w, device, rank, world, group, W, K, zigzag):
+    """One long sequence, rows sharded over the ranks of ``group`` (strong scaling): sp_forward + sp_backward, K timed
+    steps after W warm-up steps; returns ms per step (max over the ranks).  Contiguous blocks, or zig-zag (rank g owns
+    blocks g and 2G-1-g, which balances the causal work)."""
     import torch.distributed as dist
     from universal_attention_triton_b200 import ops
     from universal_attention_triton_b200.sequence_parallel import owned_blocks, sp_backward, sp_forward
-    if world == 1 and not dist.is_initialized():
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
     B, H, R, L, c, D = w["B"], w["H"], w["R"], w["L"], w["c"], w["D"]
     n = L // c
-    n_l, L_l = n // world, L // world
+    L_l = L // world
     _, dev = make_device_inputs(w, seed=0, device=device)          # same full inputs on every rank, then sliced
     kc, vc, xq, ss, sd = dev
-    P, mine = owned_blocks(world, rank, args.zigzag)
+    P, mine = owned_blocks(world, rank, zigzag)
     nb = n // P                                                   # key chunks per block
     cat_n = lambda t: torch.cat([t[:, :, p * nb:(p + 1) * nb] for p in mine], dim=2).contiguous()
     loc = [cat_n(kc), cat_n(vc), torch.cat([xq[:, :, :, p * nb * c:(p + 1) * nb * c] for p in mine], dim=3).contiguous(),
@@ -222,40 +219,74 @@ def run_sequence_parallel(args, w, rank, world, device, W, K):
     g_out, g_den = ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm)
 
     def step():
-        out, denom, lse, ctx = sp_forward(*loc, zigzag=args.zigzag, return_ctx=True)
-        return sp_backward(*loc, g_out, g_den, zigzag=args.zigzag, ctx=ctx)
+        out, denom, lse, ctx = sp_forward(*loc, group=group, zigzag=zigzag, return_ctx=True)
+        return sp_backward(*loc, g_out, g_den, group=group, zigzag=zigzag, ctx=ctx)
 
     for _ in range(W):
         step()
-    dist.barrier(); torch.cuda.synchronize()
-    sampler = ClockSampler(device.index)
-    if rank == 0:
-        sampler.start()
+    dist.barrier(group=group); torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     a.record()
     for _ in range(K):
         step()
     b.record()
-    dist.barrier(); torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
+    dist.barrier(group=group); torch.cuda.synchronize()
     tt = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
-    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms = tt.item() / K
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX, group=group)
+    del loc, g_out_cm, g_lse_cm, g_out, g_den
+    torch.cuda.empty_cache()
+    return tt.item() / K
+
+
+SP_COLLECTIVES = ("forward: 1 all-gather (K | V | src, byte-packed) + 1 all-gather of the per-key decay totals; backward: 1 all-gather "
+                  "of the per-key dC totals + 1 reduce-scatter (dK | dV | dsrc, fp32); NCCL")
+
+
+def sequence_parallel_report(w, device, rank, world, W, K, zigzag):
+    """The sequence-sharded leg at ``world`` ranks plus, for the ratio, the same sequence on rank 0 alone."""
+    import torch.distributed as dist
+    solo = dist.new_group([0])                                     # every rank takes part in creating it
+    ms = sp_leg(w, device, rank, world, None, W, K, zigzag)
+    ms_1 = None
+    if world > 1:
+        if rank == 0:
+            ms_1 = sp_leg(w, device, 0, 1, solo, 1, max(1, min(K, 2)), False)
+        dist.barrier()
+    B, L = w["B"], w["L"]
+    rep = {"workload": f"one sequence B={B} H_kv={w['H']} R={w['R']} L={L} chunk={w['c']} D={w['D']} bf16 fwd+bwd, rows sharded "
+                       f"{'zig-zag' if zigzag else 'contiguously'} over {world} rank(s), random upstream grads, masked-block grads included",
+           "scaling": "strong", "ms_per_step": ms, "tokens_per_s": B * L / (ms * 1e-3), "collectives": SP_COLLECTIVES}
+    if ms_1 is not None:
+        rep["ms_per_step_1gpu"] = ms_1
+        rep["speedup_vs_1gpu"] = ms_1 / ms
+    return rep
+
+
+def run_sequence_parallel(args, w, rank, world, device, W, K):
+    """``--mode sp``: only the sequence-sharded leg, printed as a line of its own."""
+    import torch.distributed as dist
+    if world == 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=device)
+    sampler = ClockSampler(device.index)
     if rank == 0:
+        sampler.start()
+    rep = sequence_parallel_report(w, device, rank, world, W, K, args.zigzag)
+    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        B, L = w["B"], w["L"]
+        ms = rep["ms_per_step"]
         f_fwd, f_bwd = flops(w)
         peaks, src = load_peaks()
         line = {"metric": METRIC, "value": B * L / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": w["dtype"],
                 "data": "synthetic",
-                "config": {"workload": f"{args.workload}: one sequence B={B} H_kv={H} R={R} L={L} chunk={c} D={D} bf16 fwd+bwd, rows "
-                                       f"sharded {'zig-zag' if args.zigzag else 'contiguously'} over {world} rank(s), random upstream grads, masked-block grads included",
-                           "global_batch": B, "seq_len": L,
-                           "parallelism": f"sequence-chunk x{world}: all-gather K/V/src, all-gather decay totals and dC totals, "
-                                          "all-reduce dK/dV/dsrc (NCCL)",
-                           "l2_policy": "working set exceeds L2"},
+                "config": {"workload": f"{args.workload}: " + rep["workload"], "global_batch": B, "seq_len": L,
+                           "parallelism": f"sequence-chunk x{world}: " + SP_COLLECTIVES, "l2_policy": "working set exceeds L2"},
                 "tflops": (f_fwd + f_bwd) / (ms * 1e-3) / 1e12,
                 "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms * 1e-3) / 1e12 / (peaks["bf16_tflops_sustained"] * world),
-                "clocks": clocks, "peak_source": src}
+                "sequence_parallel": rep, "clocks": clocks, "peak_source": src}
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
 
@@ -281,6 +312,8 @@ def main():
     ap.add_argument("--mode", default="bh", choices=["bh", "sp"],
                     help="bh: every rank runs its own batch shard (default); sp: ONE long sequence sharded by rows over "
                          "the ranks with NCCL exchange of keys and decay carries (use --workload long)")
+    ap.add_argument("--no-scaling-legs", action="store_true",
+                    help="N > 1: skip the strong-scaling and sequence-sharded legs that follow the headline")
     ap.add_argument("--profile", action="store_true",
                     help="profiler capture run: honour --warmup below 3; the printed numbers are not bench values")
     args = ap.parse_args()
@@ -483,6 +516,44 @@ def main():
                        " -> pow(2).sum() -> backward (main.py:55-62 flow); "
                        "copies of neighbouring steps overlap the compute (three streams)"}
 
+    # ---- multi-GPU legs beside the (unchanged) headline: the SAME 32 (batch, kv-head) units of the workload split over the
+    # ranks (strong scaling, no collective), and one long sequence sharded by rows (NCCL exchange of keys and decay carries)
+    strong = None
+    seqpar = None
+    if world > 1 and not args.no_scaling_legs and not w["fwd_only"]:
+        BH = B * H
+        if BH % world == 0:
+            per = BH // world
+            lo = rank * per
+            flat = lambda t: t.reshape((1, BH) + tuple(t.shape[2:]))[:, lo:lo + per].contiguous()
+            skc, svc, sxq, sss, ssd = (flat(t) for t in (kc, vc, xq, ss, sd))
+            sgo, sgl = flat(g_out_cm), flat(g_lse_cm)
+
+            def strong_step():
+                res = ops.forward_cm(skc, svc, sxq, sss, ssd, keep_carry=True)
+                ops.backward_cm(skc, svc, sxq, sss, ssd, sgo, sgl, flags=bwd_flags, carry=res[3], lse=res[1])
+
+            for _ in range(3):
+                strong_step()
+            barrier()
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(K):
+                strong_step()
+            b.record()
+            barrier()
+            tt = torch.tensor([a.elapsed_time(b)], device=device, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            s_ms = tt.item() / K
+            strong = {"workload": f"{args.workload}: the {BH} (batch, kv-head) units of ONE batch B={B} split over {world} ranks "
+                                  f"({per} units each), no collective", "scaling": "strong", "ms_per_step": s_ms,
+                      "tokens_per_s": B * L / (s_ms * 1e-3), "ms_per_step_1gpu": ms_per_step,
+                      "speedup_vs_1gpu": ms_per_step / s_ms}
+            del skc, svc, sxq, sss, ssd, sgo, sgl
+        del kc, vc, xq, ss, sd, dev, g_out_cm, g_lse_cm
+        torch.cuda.empty_cache()
+        seqpar = sequence_parallel_report(dict(WORKLOADS["long"]), device, rank, world, 1, 3, True)
+
     if rank == 0:
         peaks, peak_src = load_peaks()
         dom_is_bwd = bwd_avg >= fwd_avg
@@ -520,6 +591,10 @@ def main():
                                       "peak_gbs": peaks["hbm_gbs"]}},
             "e2e": e2e,
         }
+        if strong is not None:
+            line["strong"] = strong
+        if seqpar is not None:
+            line["sequence_parallel"] = seqpar
         if not w["fwd_only"]:       # the other kernel of the step, same arithmetic
             o_f, o_ms = (f_fwd, fwd_avg) if dom_is_bwd else (f_bwd, bwd_avg)
             line["roofline_other_kernel"] = {"kernel": "ua forward" if dom_is_bwd else "ua backward", "bound": "tensor",

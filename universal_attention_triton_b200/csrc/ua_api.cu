@@ -5,6 +5,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include <algorithm>
@@ -493,6 +494,10 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
     qp.acc_dv_in = (!skip_masked && s.N > 1) ? acc_dv : nullptr;
     qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
+    qp.trace = nullptr;
+#ifdef UA_PROFILE_BWD2
+    if (const char* tp = getenv("UA_TRACE_PTR")) qp.trace = reinterpret_cast<long long*>(strtoull(tp, nullptr, 0));
+#endif
     e = ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, xq, g_out_cm, qp, st);
     if (e) return e;
     if ((e = convert_any(dtype, acc_dk, dkc, BHs * s.L * s.D, st))) return e;
@@ -769,6 +774,7 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
   qp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
   qp.acc_dv_in = nullptr;
   qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
+  qp.trace = nullptr;
   e = ua::sm100::launch_bwd2(s, gate_dtype, true, kc, vc, xq, g_merged, qp, st);
   if (e) return e;
   const size_t BHs = (size_t)s.B * s.H;

@@ -10,8 +10,9 @@
 //   S_r  = K_i Q_rj^T,  dP_r = V_i dO_rj^T
 //        P  = exp(S + C - lse_row)          (lse: the forward's per-chunk log-sum-exp, or the row's
 //                                             log-sum-exp over all keys in "merged" mode)
-//        dS = P (dP - sum_k P dP + g_denom) (the sum over the keys is the one cross-lane step: a
-//                                             32 x 32 shuffle transpose per warp, then shared-memory adds)
+//        dS = P (dP - sum_k P dP + g_denom) (the sum over the keys is the one cross-lane step: a transpose
+//                                             per warp through a shared-memory scratch tile or by shuffles,
+//                                             then shared-memory adds across the four warps of a group)
 //        dC += dS                           stays in registers for the whole half tile
 //   dV_i += P dO      (P as bf16 in TMEM: the A operand)      dK_i += dS Q     (dS as bf16 in shared memory)
 //   dQ_rj = dS^T K_i  (the same shared-memory tile read MN-major)
@@ -23,9 +24,9 @@
 // holds a ring of (Q, dO) slots and, at head_dim 64, a second (S, dP) pair in TMEM: the loads and the
 // MMAs of the next head run under the element-wise work of the current one.
 //
-// Warps: 0 = TMA producer + "front" MMA issuer (G, S, dP: everything that only needs loaded tiles),
-// 1 = "back" MMA issuer (dV, dK, dQ, dK_j: everything that needs a tile the workers wrote), 2..9 = workers:
-// two column groups of 128 threads (thread = key, 32 of the 64 columns each, held in registers).
+// Warps: 0 = "front" MMA issuer (G, S, dP: everything that only needs loaded tiles), 1 and 3 = "back" MMA issuers
+// (1: dV, dK_i; 3: dQ, dK_j: everything that needs a tile the workers wrote), 2 = TMA producer, 4.. = workers:
+// 64 / CG column groups of 128 threads (thread = key, CG of the 64 columns each, held in registers; CG = 16 or 32).
 // dQ_rj / dK_j (64 rows, M = 128 MMAs whose upper 64 lanes compute on whatever the next buffer holds and are
 // never read) leave as TMA reduce-adds into fp32 accumulators.  Rows BEFORE the chunk are not handled here.
 //
@@ -54,6 +55,7 @@ struct Bwd2Params {
   __nv_bfloat16* dvc;
   void* dss;
   int* status;
+  long long* trace;          // profile builds only: per-unit time stamps of block UA_PROFILE_BLOCK (else null)
 };
 
 template <int D>
@@ -76,13 +78,20 @@ struct Bwd2Cfg {
   static constexpr int oT3 = oStage + 256 * D;             // float [2][64]
   static constexpr int oLse = oT3 + 512;                   // float [3][64]  lse * log2(e) of the head's rows
   static constexpr int oCc = oLse + 768;                   // float [3][64]  g_denom - sum_k P dP  (or -delta)
-  static constexpr int oXch = oCc + 768;                   // float [3][128] totals crossing the two column groups
-  static constexpr int oBar = oXch + 1536;
+  static constexpr int oXch = oCc + 768;                   // float [8][128] totals crossing the column groups
+  static constexpr int oBar = oXch + 4096;
   static constexpr int oMisc = oBar + 256;
-  static constexpr int kSmemBytes = oMisc + 64 + 1024;     // + slack to align the base to 1024 B
+  // per-warp scratch tiles for the column sums over the keys ([32 lanes][CG] floats each, 32 KB in all); head_dim 128
+  // has no room for them and transposes with shuffles
+  static constexpr bool kScratch = (D == 64);
+  static constexpr int oScr = oMisc + 256;
+  static constexpr int kSmemBytes = oScr + (kScratch ? 32768 : 0) + 1024;     // + slack to align the base to 1024 B
   // TMEM columns
   static constexpr uint32_t tDV = 0, tDK = D, tY = 2 * D;
   static constexpr uint32_t tS0 = (D == 64) ? 192 : 384, tP0 = tS0 + 64, tS1 = tS0 + 128, tP1 = tS0 + 192;
+  // probabilities (bf16 pairs, 32 columns per head): a buffer pair of their own where TMEM has room, else over S
+  static constexpr bool kPtSeparate = (D == 64);
+  static constexpr uint32_t tPT = 448;
   static_assert(D == 64 || D == 128, "head_dim 64 or 128");
   static_assert(D == 64 ? (tP1 + 64 <= 512) : (tP0 + 64 <= 512), "TMEM budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
@@ -92,7 +101,7 @@ enum Bwd2Bar {
   qKvFull = 0,
   qKjFull = 1, qKjFree = 3,        // [2]
   qInFull = 5, qInFree = 9,        // [4]
-  qSFull = 13, qLdDone = 15, qMmaDone = 17,   // [2] per (S, dP) buffer
+  qSFull = 13, qLdDone = 15, qPtFree = 17,   // [2] per (S, dP) buffer / per probability buffer
   qDsReady = 19, qDsFree = 21,     // [2] per dS buffer
   qYFull = 23, qYFree = 24, qDgReady = 25, qDgFree = 26, qFinal = 27, qNumBars = 28
 };
@@ -121,19 +130,68 @@ struct Bwd2Ctx {
   // half tile ht of the sweep: row tile j (descending), upper half first
   __device__ __forceinline__ int tile_j(int ht, int N) const { return N - 1 - (ht >> 1); }
   __device__ __forceinline__ int half_of(int ht) const { return 1 - (ht & 1); }
+  __device__ __forceinline__ int row0_of(int ht, int N) const { return tile_j(ht, N) * 128 + 64 * half_of(ht); }
 };
 
-// ------------------------------------------------- producer + front MMA issuer --
+// Optional phase timing (compile with -DUA_PROFILE_BWD2): thread 0 of worker warp 4 of block UA_PROFILE_BLOCK accumulates
+// clock64() deltas per phase and stores them after the status words.
+#ifdef UA_PROFILE_BWD2
+#ifndef UA_PROFILE_BLOCK
+#define UA_PROFILE_BLOCK 0
+#endif
+#define UQ_DECL long long uq_t = clock64(), uq_acc[16] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+#define UQ(idx) { long long now_ = clock64(); uq_acc[idx] += now_ - uq_t; uq_t = now_; }
+#define UQ_STORE if (blockIdx.x == UA_PROFILE_BLOCK && warp == 8 && lane == 0) { for (int z = 0; z < 16; ++z) reinterpret_cast<long long*>(p.status)[2 + z] = uq_acc[z]; }
+#define UQ_STORE_AT(base) if (blockIdx.x == UA_PROFILE_BLOCK) { for (int z = 0; z < 4; ++z) reinterpret_cast<long long*>(p.status)[2 + (base) + z] = uq_acc[z]; }
+#define UQ_TRACE(unit, slot) if (p.trace && blockIdx.x == UA_PROFILE_BLOCK && (unit) < 96) p.trace[(unit) * 8 + (slot)] = clock64();
+#else
+#define UQ_DECL
+#define UQ(idx)
+#define UQ_STORE
+#define UQ_STORE_AT(base)
+#define UQ_TRACE(unit, slot)
+#endif
+
+// Four tcgen05.mma of one accumulation chain from ONE asm statement: what limits a single issuing thread is the
+// instruction count per MMA (descriptor arithmetic, predicate set-up), so the chain shares one predicate set-up and
+// advances the 64-bit descriptors by immediate-like steps (in 16-byte units of the descriptor's address field).
+__device__ __forceinline__ void mma4_ss(uint32_t d, uint64_t a, uint64_t b, uint64_t sa, uint64_t sb, uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 a1, a2, a3, b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.eq.u32 q, 1, 1;\n\t"
+      "add.s64 a1, %1, %3;\n\tadd.s64 b1, %2, %4;\n\tadd.s64 a2, a1, %3;\n\tadd.s64 b2, b1, %4;\n\t"
+      "add.s64 a3, a2, %3;\n\tadd.s64 b3, b2, %4;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %5, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %5, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %5, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %5, q;\n\t}" ::"r"(d),
+      "l"(a), "l"(b), "l"(sa), "l"(sb), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+// ... with the A operand in TMEM at four given column addresses
+__device__ __forceinline__ void mma4_ts(uint32_t d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint64_t b, uint64_t sb,
+                                        uint32_t idesc, uint32_t acc_first) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 b1, b2, b3;\n\t"
+      "setp.ne.b32 p, %8, 0;\n\tsetp.eq.u32 q, 1, 1;\n\t"
+      "add.s64 b1, %5, %6;\n\tadd.s64 b2, b1, %6;\n\tadd.s64 b3, b2, %6;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %5, %7, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], b1, %7, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], b2, %7, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], b3, %7, q;\n\t}" ::"r"(d),
+      "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(b), "l"(sb), "r"(idesc), "r"(acc_first)
+      : "memory");
+}
+
+// ------------------------------------------------------------- TMA producer --
 template <int D, int kMode>
-__device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
-                                           const CUtensorMap* tmQ, const CUtensorMap* tmG) {
+__device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
+                                              const CUtensorMap* tmQ, const CUtensorMap* tmG) {
   using Cfg = Bwd2Cfg<D>;
   const int L = p.s.L, R = p.s.R, N = p.s.N;
   const uint32_t sb = smem_u32(c.smem);
   const int krow = c.bh * L + c.i * 128;
   const size_t chunk_id = (size_t)c.bh * N + c.i;
-  constexpr uint32_t id_g = idesc_bf16(128, 64, 0, 0);
-
   mbar_expect_tx(c.bar(qKvFull), 2 * Cfg::kFull);
 #pragma unroll
   for (int b = 0; b < Cfg::kBoxes; ++b)
@@ -142,59 +200,58 @@ __device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p
       tma_load_2d(sb + Cfg::oKi + b * 16384 + h * 8192, tmK, b * 64, krow + h * 64, c.bar(qKvFull));
       tma_load_2d(sb + Cfg::oVi + b * 16384 + h * 8192, tmV, b * 64, krow + h * 64, c.bar(qKvFull));
     }
-
-  auto row0_of = [&](int ht) { return c.tile_j(ht, N) * 128 + 64 * c.half_of(ht); };
-  auto load_kj = [&](int ht) -> bool {
-    const int sl = ht % Cfg::kKj, use = ht / Cfg::kKj;
-    if (use >= 1 && !c.wait(qKjFree + sl, use - 1)) return false;
-    mbar_expect_tx(c.bar(qKjFull + sl), Cfg::kHalf);
+  // in sweep order: K_j of half tile ht, then the (Q, dO) pairs of its heads; a slot is refilled as soon as the MMAs
+  // that read it have completed
+  int hc = 0;
+  for (int ht = 0; ht < c.nht; ++ht) {
+    const int row0 = c.row0_of(ht, N);
+    {
+      const int sl = ht % Cfg::kKj, use = ht / Cfg::kKj;
+      if (use >= 1 && !c.wait(qKjFree + sl, use - 1)) return;
+      mbar_expect_tx(c.bar(qKjFull + sl), Cfg::kHalf);
 #pragma unroll
-    for (int b = 0; b < Cfg::kBoxes; ++b)
-      tma_load_2d(sb + Cfg::oKj + sl * Cfg::kHalf + b * 8192, tmK, b * 64, c.bh * L + row0_of(ht), c.bar(qKjFull + sl));
-    return true;
-  };
-  const int total_heads = c.nht * R;
-  int next_load = 0;
-  auto load_head = [&](int hc) -> bool {
-    const int ht = hc / R, r = hc - ht * R;
-    const int sl = hc % Cfg::kNS, use = hc / Cfg::kNS;
-    if (use >= 1 && !c.wait(qInFree + sl, use - 1)) return false;
-    const int qrow = (c.bh * R + r) * L + row0_of(ht);
-    const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * L + row0_of(ht));
-    const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot;
-    mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf);
+      for (int b = 0; b < Cfg::kBoxes; ++b)
+        tma_load_2d(sb + Cfg::oKj + sl * Cfg::kHalf + b * 8192, tmK, b * 64, c.bh * L + row0, c.bar(qKjFull + sl));
+    }
+    for (int r = 0; r < R; ++r, ++hc) {
+      const int sl = hc % Cfg::kNS, use = hc / Cfg::kNS;
+      if (use >= 1 && !c.wait(qInFree + sl, use - 1)) return;
+      const int qrow = (c.bh * R + r) * L + row0;
+      const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * L + row0);
+      const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot;
+      mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf);
 #pragma unroll
-    for (int b = 0; b < Cfg::kBoxes; ++b) {
-      tma_load_2d(dst + b * 8192, tmQ, b * 64, qrow, c.bar(qInFull + sl));
-      tma_load_2d(dst + Cfg::kHalf + b * 8192, tmG, b * 64, grow, c.bar(qInFull + sl));
+      for (int b = 0; b < Cfg::kBoxes; ++b) {
+        tma_load_2d(dst + b * 8192, tmQ, b * 64, qrow, c.bar(qInFull + sl));
+        tma_load_2d(dst + Cfg::kHalf + b * 8192, tmG, b * 64, grow, c.bar(qInFull + sl));
+      }
     }
-    return true;
-  };
-  auto topup = [&](int upto) -> bool {
-    while (next_load < total_heads && next_load <= upto) {
-      if (!load_head(next_load)) return false;
-      ++next_load;
-    }
-    return true;
-  };
+  }
+}
 
+// ----------------------------------------------------------- front MMA issuer --
+// G, S^T and dP^T: everything that only needs loaded tiles and a free (S, dP) buffer.
+template <int D>
+__device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p) {
+  using Cfg = Bwd2Cfg<D>;
+  const int R = p.s.R;
+  const uint32_t sb = smem_u32(c.smem);
+  constexpr uint32_t id_g = idesc_bf16(128, 64, 0, 0);
   // D[128 keys x 64 rows] = A[128][D] B[64][D]^T, both K-major; A boxes 16 KB apart, B boxes 8 KB apart
   auto mma_kk = [&](uint32_t d, uint32_t a_lo, uint32_t b_lo) {
-    mma_ss_c<false>(d, desc_from_lo(a_lo), desc_from_lo(b_lo), id_g);
-#pragma unroll
-    for (int ks = 1; ks < D / 16; ++ks)
-      mma_ss_c<true>(d, desc_from_lo(a_lo + (ks >> 2) * 1024 + (ks & 3) * 2), desc_from_lo(b_lo + (ks >> 2) * 512 + (ks & 3) * 2), id_g);
+    mma4_ss(d, desc_from_lo(a_lo), desc_from_lo(b_lo), 2, 2, id_g, 0);
+    if (D == 128) mma4_ss(d, desc_from_lo(a_lo + 1024), desc_from_lo(b_lo + 512), 2, 2, id_g, 1);
   };
   const uint32_t kKi = desc_lo(sb + Cfg::oKi, 16), kVi = desc_lo(sb + Cfg::oVi, 16);
 
-  // (S, dP) buffer b is free again when its previous unit has been consumed: a G unit once the workers have loaded it,
-  // a head unit once the dV MMA has read the probabilities the workers wrote over S.
+  // (S, dP) buffer b is free again when its previous unit has been consumed: once the workers have loaded it, or -- where
+  // the probabilities are written over S (head_dim 128) -- once the dV MMA of a head unit has read them.
   int u = 0, head_uses[2] = {0, 0};
   bool last_was_head[2] = {false, false};
   auto acquire = [&](int b) -> bool {
-    const int uses = (u - b + Cfg::kNB - 1) / Cfg::kNB;            // units before u that used buffer b
+    const int uses = u / Cfg::kNB;                                // units before u that used buffer b = u % kNB
     if (uses == 0) return true;
-    if (last_was_head[b]) return c.wait(qMmaDone + b, head_uses[b] - 1);
+    if (!Cfg::kPtSeparate && last_was_head[b]) return c.wait(qPtFree + b, head_uses[b] - 1);
     return c.wait(qLdDone + b, uses - 1);
   };
   auto unit_g = [&](int ht) -> bool {
@@ -203,220 +260,336 @@ __device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p
     tc_fence_after();
     mma_kk(c.tmem + (b ? Cfg::tS1 : Cfg::tS0), kKi, desc_lo(sb + Cfg::oKj + (ht % Cfg::kKj) * Cfg::kHalf, 16));
     tc_commit(c.bar(qSFull + b));
+    UQ_TRACE(u, 0)
     last_was_head[b] = false;
     ++u;
     return true;
   };
 
   if (!c.wait(qKvFull, 0)) return;
-  if (!load_kj(0)) return;
-  if (!topup(Cfg::kNS - 1)) return;
   int hc = 0;
+  UQ_DECL
   for (int ht = 0; ht < c.nht; ++ht) {
     if (!c.wait(qKjFull + ht % Cfg::kKj, ht / Cfg::kKj)) return;
     if (!unit_g(ht)) return;                                        // G for the decay recomputation
-    if (Cfg::kKj > 1 && ht + 1 < c.nht && !load_kj(ht + 1)) return;
+    UQ(0)
     for (int r = 0; r < R; ++r, ++hc) {
       const int sl = hc % Cfg::kNS, b = u % Cfg::kNB;
       if (!c.wait(qInFull + sl, hc / Cfg::kNS)) return;
+      UQ(1)
       if (!acquire(b)) return;
+      UQ(2)
+      UQ_TRACE(u, 4)
       tc_fence_after();
       const uint32_t slot = sb + Cfg::oSlot + sl * Cfg::kSlot;
       mma_kk(c.tmem + (b ? Cfg::tS1 : Cfg::tS0), kKi, desc_lo(slot, 16));                    // S^T  = K_i Q^T
       mma_kk(c.tmem + (b ? Cfg::tP1 : Cfg::tP0), kVi, desc_lo(slot + Cfg::kHalf, 16));       // dP^T = V_i dO^T
       tc_commit(c.bar(qSFull + b));
+      UQ_TRACE(u, 0)
       last_was_head[b] = true;
       ++head_uses[b];
       ++u;
-      if (!topup(hc + Cfg::kNS - 1)) return;
+      UQ(3)
     }
     if (!unit_g(ht)) return;                                        // G again for the decay gradient
-    if (Cfg::kKj == 1 && ht + 1 < c.nht && !load_kj(ht + 1)) return;
+    UQ(0)
   }
+  UQ_STORE_AT(16)
 }
 
-// ------------------------------------------------------------ back MMA issuer --
-template <int D>
-__device__ __forceinline__ void bwd2_back(const Bwd2Ctx& c, const Bwd2Params& p) {
+// ------------------------------------------------------------ back MMA issuers --
+// which = 0: the accumulators that live for the whole sweep (dV_i += P dO, dK_i += dS Q, dK_i += dG K_j);
+// which = 1: the row-side results that leave after every unit (Y = dQ_rj = dS^T K_i, Y = dK_j = dG^T K_i).
+// MMAs into one accumulator always come from the same thread, so their order is kept.
+template <int D, int CG>
+__device__ __forceinline__ void bwd2_back(const Bwd2Ctx& c, const Bwd2Params& p, const int which) {
   using Cfg = Bwd2Cfg<D>;
   const int R = p.s.R;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_kn = idesc_bf16(128, D, 0, 1);     // A K-major (or TMEM), B MN-major
   constexpr uint32_t id_tn = idesc_bf16(128, D, 1, 1);     // A MN-major, B MN-major
   const uint32_t DV = c.tmem + Cfg::tDV, DK = c.tmem + Cfg::tDK, Y = c.tmem + Cfg::tY;
-  const uint32_t mKi = desc_lo(sb + Cfg::oKi, 16384);      // K_i as [K = keys][N = D] (MN-major, 64-wide groups 16 KB apart)
-  const uint32_t kdG = desc_lo(sb + Cfg::oDg, 16), mdG = desc_lo(sb + Cfg::oDg, 16384);
-  bool have_dv = false, have_dk = false;
+  const uint64_t mKi = desc_from_lo(desc_lo(sb + Cfg::oKi, 16384));      // K_i as [K = keys][N = D] (MN-major, 64-wide groups 16 KB apart)
+  const uint64_t kdG = desc_from_lo(desc_lo(sb + Cfg::oDg, 16)), mdG = desc_from_lo(desc_lo(sb + Cfg::oDg, 16384));
+  uint32_t have_dv = 0, have_dk = 0;
   int yc = 0, hc = 0;
   // Y[rows][D] = T^T K_i with T a [128 keys][64 rows] bf16 tile read MN-major; M = 128: lanes 64..127 come from the 16 KB
   // after the tile and are never read
-  auto mma_rows_out = [&](uint32_t t_mn) {
-    mma_ss_c<false>(Y, desc_from_lo(t_mn), desc_from_lo(mKi), id_tn);
-#pragma unroll
-    for (int ks = 1; ks < 8; ++ks) mma_ss_c<true>(Y, desc_from_lo(t_mn + ks * 128), desc_from_lo(mKi + ks * 128), id_tn);
+  auto mma_rows_out = [&](uint64_t t_mn) {
+    mma4_ss(Y, t_mn, mKi, 128, 128, id_tn, 0);
+    mma4_ss(Y, t_mn + 512, mKi + 512, 128, 128, id_tn, 1);
   };
+  if (!c.wait(qKvFull, 0)) return;
+  UQ_DECL
   for (int ht = 0; ht < c.nht; ++ht) {
     const int u0 = ht * (R + 2);
     for (int r = 0; r < R; ++r, ++hc) {
       const int b = (u0 + 1 + r) % Cfg::kNB, sl = hc % Cfg::kNS, db = hc % Cfg::kDs;
-      if (!c.wait(qInFull + sl, hc / Cfg::kNS)) return;
+      const uint32_t dsb = sb + Cfg::oDs + db * 16384;
+      UQ(0)
       if (!c.wait(qDsReady + db, hc / Cfg::kDs)) return;
+      UQ(1)
+      if (which == 0) {
+        if (!c.wait(qInFull + sl, hc / Cfg::kNS)) return;
+        tc_fence_after();
+        const uint32_t slot = sb + Cfg::oSlot + sl * Cfg::kSlot;
+        const uint64_t mQ = desc_from_lo(desc_lo(slot, 8192)), mGo = desc_from_lo(desc_lo(slot + Cfg::kHalf, 8192));
+        // dV_i += P dO: P^T as bf16 pairs in TMEM (its own buffer, or over the S columns of each column group)
+        uint32_t pa[4];
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          pa[ks] = Cfg::kPtSeparate ? c.tmem + Cfg::tPT + 32 * (hc & 1) + 8 * ks
+                                    : c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + CG * ((16 * ks) / CG) + ((16 * ks) % CG) / 2;
+        mma4_ts(DV, pa[0], pa[1], pa[2], pa[3], mGo, 128, id_kn, have_dv);
+        have_dv = 1;
+        tc_commit(c.bar(qPtFree + (Cfg::kPtSeparate ? (hc & 1) : b)));
+        mma4_ss(DK, desc_from_lo(desc_lo(dsb, 16)), mQ, 2, 128, id_kn, have_dk);          // dK_i += dS Q
+        have_dk = 1;
+        tc_commit(c.bar(qInFree + sl));
+        tc_commit(c.bar(qDsFree + db));
+      } else {
+        if (yc >= 1 && !c.wait(qYFree, yc - 1)) return;
+        UQ(2)
+        tc_fence_after();
+        mma_rows_out(desc_from_lo(desc_lo(dsb, 16384)));                                  // dQ_rj = dS^T K_i
+        ++yc;
+        tc_commit(c.bar(qYFull));
+        tc_commit(c.bar(qDsFree + db));
+      }
+    }
+    UQ(0)
+    if (!c.wait(qDgReady, ht)) return;
+    UQ(3)
+    if (which == 0) {
       tc_fence_after();
-      const uint32_t slot = sb + Cfg::oSlot + sl * Cfg::kSlot;
-      const uint32_t mQ = desc_lo(slot, 8192), mGo = desc_lo(slot + Cfg::kHalf, 8192);
-      const uint32_t tS = c.tmem + (b ? Cfg::tS1 : Cfg::tS0);
-      const uint32_t kdS = desc_lo(sb + Cfg::oDs + db * 16384, 16), mdS = desc_lo(sb + Cfg::oDs + db * 16384, 16384);
-      // dV_i += P dO: P^T as bf16 pairs in TMEM, group g's 32 rows at columns [32 g, 32 g + 16)
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const uint32_t acol = (uint32_t)((ks >> 1) * 32 + (ks & 1) * 8);
-        if (ks == 0 && !have_dv) mma_ts_c<false>(DV, tS + acol, desc_from_lo(mGo + ks * 128), id_kn);
-        else mma_ts_c<true>(DV, tS + acol, desc_from_lo(mGo + ks * 128), id_kn);
-      }
-      have_dv = true;
-      // dK_i += dS Q
-#pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        if (ks == 0 && !have_dk) mma_ss_c<false>(DK, desc_from_lo(kdS + ks * 2), desc_from_lo(mQ + ks * 128), id_kn);
-        else mma_ss_c<true>(DK, desc_from_lo(kdS + ks * 2), desc_from_lo(mQ + ks * 128), id_kn);
-      }
-      have_dk = true;
-      tc_commit(c.bar(qMmaDone + b));
-      tc_commit(c.bar(qInFree + sl));
+      const uint64_t mKj = desc_from_lo(desc_lo(sb + Cfg::oKj + (ht % Cfg::kKj) * Cfg::kHalf, 8192));
+      mma4_ss(DK, kdG, mKj, 2, 128, id_kn, have_dk);                                      // dK_i += dG K_j
+      have_dk = 1;
+      tc_commit(c.bar(qKjFree + ht % Cfg::kKj));
+      tc_commit(c.bar(qDgFree));
+    } else {
       if (yc >= 1 && !c.wait(qYFree, yc - 1)) return;
       tc_fence_after();
-      mma_rows_out(mdS);                                            // dQ_rj = dS^T K_i
+      mma_rows_out(mdG);                                                                  // dK_j = dG^T K_i
       ++yc;
       tc_commit(c.bar(qYFull));
-      tc_commit(c.bar(qDsFree + db));
+      tc_commit(c.bar(qDgFree));
     }
-    if (!c.wait(qDgReady, ht)) return;
-    if (yc >= 1 && !c.wait(qYFree, yc - 1)) return;
-    tc_fence_after();
-    mma_rows_out(mdG);                                              // dK_j = dG^T K_i
-    ++yc;
-    tc_commit(c.bar(qYFull));
-    const uint32_t mKj = desc_lo(sb + Cfg::oKj + (ht % Cfg::kKj) * Cfg::kHalf, 8192);
-#pragma unroll
-    for (int ks = 0; ks < 4; ++ks) {                                // dK_i += dG K_j
-      if (ks == 0 && !have_dk) mma_ss_c<false>(DK, desc_from_lo(kdG + ks * 2), desc_from_lo(mKj + ks * 128), id_kn);
-      else mma_ss_c<true>(DK, desc_from_lo(kdG + ks * 2), desc_from_lo(mKj + ks * 128), id_kn);
-    }
-    have_dk = true;
-    tc_commit(c.bar(qKjFree + ht % Cfg::kKj));
-    tc_commit(c.bar(qDgFree));
   }
   tc_commit(c.bar(qFinal));
+  UQ_STORE_AT(20 + 4 * which)
 }
 
 // --------------------------------------------------------------------- workers --
-constexpr int kBarAll = 1, kBarGroup = 2, kBarDrain = 4;     // named barriers (0 is __syncthreads)
+constexpr int kBarAll = 1, kBarDrain = 2, kBarGroup = 3;     // named barriers (0 is __syncthreads); groups use kBarGroup + g
 
-template <int D, typename TG, int kMode>
-__device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmDQ,
-                                            const CUtensorMap* tmDK) {
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]), "r"(r[1]),
+               "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t* r) {
+  if (N == 32) tmem_ld32(taddr, r);
+  else tmem_ld16(taddr, r);
+}
+
+// Sum over the 32 lanes of a warp of v[0..CG): afterwards every lane holds the sum of column (lane % CG).
+// With a per-warp shared-memory scratch tile ([32 lanes][CG] floats, 16-byte chunks XOR-swizzled so that both the row writes
+// and the column reads are conflict free) this costs CG/4 vector stores + 32 * CG / 32 loads and adds per lane; without one
+// it is a shuffle transpose (about 4 instructions per element).
+template <int CG>
+__device__ __forceinline__ float warp_colsum(float* v, float* scr, int lane) {
+  if (scr == nullptr) {
+    if (CG == 32) return warp_transpose_reduce(v, lane);
+    // 16 columns: halve 8, 4, 2, 1 (the lane keeps the half its bit selects), then the two half warps add up
+#pragma unroll
+    for (int s = 8; s >= 1; s >>= 1) {
+      const bool upper = (lane & s) != 0;
+#pragma unroll
+      for (int x = 0; x < s; ++x) {
+        const float send = upper ? v[x] : v[x + s];
+        const float keep = upper ? v[x + s] : v[x];
+        v[x] = keep + __shfl_xor_sync(0xffffffffu, send, s);
+      }
+    }
+    return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 16);
+  }
+  constexpr int CH = CG / 4;
+  const int f = (CG == 32) ? (lane & 7) : ((lane >> 1) & 3);
+  float4* row = reinterpret_cast<float4*>(scr + lane * CG);
+#pragma unroll
+  for (int cidx = 0; cidx < CH; ++cidx) row[cidx ^ f] = make_float4(v[4 * cidx], v[4 * cidx + 1], v[4 * cidx + 2], v[4 * cidx + 3]);
+  __syncwarp();
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (CG == 32) {
+    const int jc = lane >> 2, jw = lane & 3;
+#pragma unroll
+    for (int t = 0; t < 32; t += 4) {
+      a0 += scr[(t + 0) * 32 + ((jc ^ ((t + 0) & 7)) << 2) + jw];
+      a1 += scr[(t + 1) * 32 + ((jc ^ ((t + 1) & 7)) << 2) + jw];
+      a2 += scr[(t + 2) * 32 + ((jc ^ ((t + 2) & 7)) << 2) + jw];
+      a3 += scr[(t + 3) * 32 + ((jc ^ ((t + 3) & 7)) << 2) + jw];
+    }
+  } else {
+    const int j = lane & 15, hi = lane >> 4, jc = j >> 2, jw = j & 3;
+#pragma unroll
+    for (int t = 0; t < 16; t += 4) {
+#pragma unroll
+      for (int z = 0; z < 4; ++z) {
+        const int r = hi * 16 + ((t + z + hi) & 15);       // the two half warps read rows of opposite bank parity
+        const float val = scr[r * 16 + ((jc ^ ((r >> 1) & 3)) << 2) + jw];
+        if (z == 0) a0 += val; else if (z == 1) a1 += val; else if (z == 2) a2 += val; else a3 += val;
+      }
+    }
+  }
+  float acc = (a0 + a1) + (a2 + a3);
+  if (CG == 16) acc += __shfl_xor_sync(0xffffffffu, acc, 16);
+  __syncwarp();
+  return acc;
+}
+
+// ----------------------------------------------------------------- drain warps --
+// Two warps (TMEM lanes 0..63 = the 64 result rows) take every row-side result out of Y, in sweep order: dQ_rj of each
+// head, then dK_j of the half tile.  The 64 x D fp32 tile is staged in shared memory as boxes of [64][32] floats and
+// leaves as TMA reduce-adds into the fp32 accumulators (other key chunks add to the same rows), which run behind the
+// next unit; the workers never touch it.
+template <int D>
+__device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmDQ, const CUtensorMap* tmDK) {
   using Cfg = Bwd2Cfg<D>;
   const int L = p.s.L, R = p.s.R, N = p.s.N;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int g = (warp - 2) >> 2;                 // column group: columns [32 g, 32 g + 32) of a half tile
-  const int quad = warp & 3;                     // TMEM lane quadrant this warp may touch
-  const int slotw = (warp - 2) & 3;              // position of the warp inside its group (helper duties)
+  const int row = (warp & 3) * 32 + lane;               // 0..63
+  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+  const bool leader = (warp == 4 && lane == 0);
+  const uint32_t swz = (uint32_t)(row & 7);
+  uint8_t* sStage = c.smem + Cfg::oStage;
+  int yc = 0;
+  for (int ht = 0; ht < c.nht; ++ht) {
+    const int row0 = c.row0_of(ht, N);
+    for (int r = 0; r <= R; ++r, ++yc) {
+      if (!c.wait_w(qYFull, yc)) return;
+      tc_fence_after();
+      if (leader) bulk_wait_read_all();                 // the previous reduce-add has read the staging tile
+      named_bar_sync(kBarDrain, 64);
+#pragma unroll 1
+      for (int hb = 0; hb < D / 32; ++hb) {
+        uint32_t o[32];
+        tmem_ld32(c.tmem + Cfg::tY + lane_base + 32 * hb, o);
+        tc_wait_ld();
+        if (hb == D / 32 - 1) {
+          tc_fence_before();
+          c.arrive_w(qYFree);
+        }
+        uint8_t* box = sStage + hb * 8192 + row * 128;
+#pragma unroll
+        for (int x = 0; x < 8; ++x)
+          *reinterpret_cast<uint4*>(box + ((((uint32_t)x ^ swz) & 7) << 4)) = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
+      }
+      fence_proxy_async();
+      named_bar_sync(kBarDrain, 64);
+      if (leader) {
+        const CUtensorMap* tm = (r < R) ? tmDQ : tmDK;
+        const int y = (r < R) ? (c.bh * R + r) * L + row0 : c.bh * L + row0;
+#pragma unroll
+        for (int bx = 0; bx < D / 32; ++bx) tma_reduce_add_2d(tm, 32 * bx, y, smem_u32(sStage) + bx * 8192);
+        bulk_commit_group();
+      }
+      __syncwarp();
+    }
+  }
+  if (leader) bulk_wait_all();                          // the reduce-adds have landed before the block retires
+}
+
+// CG: columns of a half tile per thread (32: two column groups, 8 worker warps; 16: four groups, 16 worker warps)
+template <int D, typename TG, int kMode, int CG>
+__device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& p) {
+  using Cfg = Bwd2Cfg<D>;
+  constexpr int NG = 64 / CG;                    // column groups
+  constexpr int H2 = CG / 2;                     // packed pairs per thread
+  constexpr int kWorkers = 128 * NG;
+  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = (warp - 8) >> 2;                 // column group: columns [CG g, CG g + CG) of a half tile
+  const int quad = warp & 3;                     // TMEM lane quadrant this warp may touch; also its helper duty inside the group
   const int key = quad * 32 + lane;
   const uint32_t lane_base = (uint32_t)(quad * 32) << 16;
-  const int col0 = 32 * g;
-  const bool is_drain = quad < 2;                // the 64 result rows of dQ / dK_j sit on lanes 0..63
-  const bool drain_leader = (g == 0 && quad == 0 && lane == 0);
+  const int col0 = CG * g;
+  const bool helper = lane < CG;                 // lanes that fetch table entries (lane = column of the group)
   const float kLog2e = 1.4426950408889634f;
+  const float2 kLog2e2 = make_float2(kLog2e, kLog2e);
   const size_t chunk_id = (size_t)c.bh * N + c.i;
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
   const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + key));
+  const float2 s32 = make_float2(s3, s3);
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   float* sLse = reinterpret_cast<float*>(c.smem + Cfg::oLse);
   float* sCc = reinterpret_cast<float*>(c.smem + Cfg::oCc);
   float* sXch = reinterpret_cast<float*>(c.smem + Cfg::oXch);
-  uint8_t* sStage = c.smem + Cfg::oStage;
+  float* scr = Cfg::kScratch ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * CG) : nullptr;
   const uint32_t swz = (uint32_t)(key & 7);
   const int total_heads = c.nht * R;
+  UQ_DECL
 
   auto row0_of = [&](int ht) { return c.tile_j(ht, N) * 128 + 64 * c.half_of(ht); };
   auto carry_at = [&](int ht) -> float {
     return p.carry[((chunk_id * N + c.tile_j(ht, N)) * 2 + c.half_of(ht)) * 128 + key];
   };
-  // helper duties, one warp of each group per table, lane = column: values of head hc for the group's 32 columns
+  // helper duties, one warp of each group per table, lane = column: values of head hc for the group's columns.  The
+  // fetch_* functions only ISSUE the global load and return its raw bits; the arithmetic on them (*_value) is done where
+  // the value is stored, a whole phase later, so that the load's latency never stalls the warp.
   auto fetch_lse = [&](int hc) -> float {
     const int ht = hc / R, r = hc - ht * R;
     const int row = row0_of(ht) + col0 + lane;
     return (kMode == 2) ? p.row_lse[((size_t)c.bh * R + r) * L + row] : p.lse[(chunk_id * R + r) * L + row];
   };
-  auto fetch_cc = [&](int hc) -> float {
+  auto lse_value = [&](float raw) -> float { return -raw * kLog2e; };
+  auto fetch_cc = [&](int hc) -> uint32_t {
     const int ht = hc / R, r = hc - ht * R;
     const int row = row0_of(ht) + col0 + lane;
-    if (kMode == 2) return -p.row_delta[((size_t)c.bh * R + r) * L + row];
+    if (kMode == 2) return __float_as_uint(p.row_delta[((size_t)c.bh * R + r) * L + row]);
     const size_t o = (chunk_id * R + r) * L + row;
-    return p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[o]
-                            : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[o]);
+    return p.g_denom_is_f32 ? __float_as_uint(static_cast<const float*>(p.g_denom)[o])
+                            : (uint32_t) static_cast<const unsigned short*>(p.g_denom)[o];
   };
-  auto fetch_t3 = [&](int ht) -> float { return cbrtf(Num<TG>::ld(sd + row0_of(ht) + col0 + lane)); };
+  auto cc_value = [&](uint32_t raw) -> float {
+    if (kMode == 2) return -__uint_as_float(raw);
+    return p.g_denom_is_f32 ? __uint_as_float(raw) : __uint_as_float(raw << 16);
+  };
+  auto fetch_t3 = [&](int ht) -> TG { return sd[row0_of(ht) + col0 + lane]; };
+  auto t3_value = [&](TG raw) -> float { return cbrtf(Num<TG>::ld(&raw)); };
+  // CG floats of a table row for this group's columns, as pairs
+  auto load_pairs = [&](const float* src, float2* dst) {
+#pragma unroll
+    for (int x = 0; x < CG / 4; ++x) {
+      const float4 v = reinterpret_cast<const float4*>(src)[x];
+      dst[2 * x] = make_float2(v.x, v.y);
+      dst[2 * x + 1] = make_float2(v.z, v.w);
+    }
+  };
 
-  // this thread's 32 columns of row `key` of a [128 keys][64 rows] bf16 tile (128-byte swizzled rows): chunks 4g .. 4g+3
+  // this thread's CG columns of row `key` of a [128 keys][64 rows] bf16 tile (128-byte swizzled rows)
   auto store_row = [&](uint8_t* base, const uint32_t* v) {
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const uint32_t ch = (uint32_t)(4 * g + x);
+    for (int x = 0; x < CG / 8; ++x) {
+      const uint32_t ch = (uint32_t)((CG / 8) * g + x);
       *reinterpret_cast<uint4*>(base + key * 128 + (((ch ^ swz) & 7) << 4)) = make_uint4(v[4 * x], v[4 * x + 1], v[4 * x + 2], v[4 * x + 3]);
     }
   };
 
-  // The 64 x D fp32 tile in Y (dQ_rj or dK_j, rows on lanes 0..63) is added to rows [y, y + 64) of a global accumulator:
-  // the four warps of lanes 0..63 move it into the staging tile (boxes of [64][32] floats) and their leader issues
-  // TMA reduce-adds, which run behind whatever follows.
-  int yc = 0;
-  bool pending = false;
-  const CUtensorMap* pend_map = nullptr;
-  int pend_row = 0;
-  auto drain = [&]() -> bool {
-    if (!pending) return true;
-    pending = false;
-    const int use = yc++;
-    if (!is_drain) return true;
-    if (!c.wait_w(qYFull, use)) return false;
-    tc_fence_after();
-    if (drain_leader) bulk_wait_read_all();           // the previous reduce-add has read the staging tile
-    named_bar_sync(kBarDrain, 128);
-    constexpr int kBlk = D / 64;                      // 32-column blocks per thread
-#pragma unroll
-    for (int hb = 0; hb < kBlk; ++hb) {
-      uint32_t o[32];
-      tmem_ld32(c.tmem + Cfg::tY + lane_base + (D / 2) * g + 32 * hb, o);
-      tc_wait_ld();
-      if (hb == kBlk - 1) {
-        tc_fence_before();
-        c.arrive_w(qYFree);
-      }
-      uint8_t* box = sStage + (kBlk * g + hb) * 8192 + key * 128;
-#pragma unroll
-      for (int x = 0; x < 8; ++x)
-        *reinterpret_cast<uint4*>(box + ((((uint32_t)x ^ swz) & 7) << 4)) = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
-    }
-    fence_proxy_async();
-    named_bar_sync(kBarDrain, 128);
-    if (drain_leader) {
-#pragma unroll
-      for (int bx = 0; bx < D / 32; ++bx) tma_reduce_add_2d(pend_map, 32 * bx, pend_row, smem_u32(sStage) + bx * 8192);
-      bulk_commit_group();
-    }
-    __syncwarp();
-    return true;
-  };
-
   // ---- prologue: tables of the first half tile / first head ----
-  if (slotw == 0) sLse[col0 + lane] = fetch_lse(0) * kLog2e;
-  if (slotw == 1) sCc[col0 + lane] = fetch_cc(0);
-  if (slotw == 2) sT3[col0 + lane] = fetch_t3(0);
+  if (helper && quad == 0) sLse[col0 + lane] = lse_value(fetch_lse(0));
+  if (helper && quad == 1) sCc[col0 + lane] = cc_value(fetch_cc(0));
+  if (helper && quad == 2) sT3[col0 + lane] = t3_value(fetch_t3(0));
   float carry_next = carry_at(0);
   float suffix = 0.f, ds_acc = 0.f;
-  named_bar_sync(kBarAll, 256);
+  named_bar_sync(kBarAll, kWorkers);
 
   int u = 0, hc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
@@ -425,184 +598,247 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     const int qbase = 64 * half + col0;            // row of this thread's first column inside the 128-row tile
     const float* t3v = sT3 + (ht & 1) * 64 + col0;
 
-    // ================= decay recomputation: C2 = log2(e) * decay prefix of (key, 32 rows) =================
-    float c2[32];
+    // ================= decay recomputation: c2 = log2(e) * decay prefix of (key, CG rows) =================
+    float2 c2[H2];
     {
       const float carry = carry_next;
       const int b = u % Cfg::kNB;
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
       tc_fence_after();
-      uint32_t gr[32];
-      tmem_ld32(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, gr);
+      uint32_t gr[CG];
+      tmem_ld_n<CG>(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, gr);
+      float2 t3p[H2];
+      load_pairs(t3v, t3p);
       tc_wait_ld();
       tc_fence_before();
       c.arrive_w(qLdDone + b);
       ++u;
+      // log-retention in log2 units: lg2(1 - min(a, hi)), a = relu(g)^(2/3) s^(1/3) t^(1/3)
       float run = 0.f;
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        float e = log_retention(gated_affinity(gram_pow23(__uint_as_float(gr[x])), s3, t3v[x]));
-        if (diag && qbase + x <= key) e = 0.f;
-        run += e;
-        c2[x] = run;
+      for (int x = 0; x < H2; ++x) {
+        const float2 pw = make_float2(gram_pow23(__uint_as_float(gr[2 * x])), gram_pow23(__uint_as_float(gr[2 * x + 1])));
+        const float2 a = fmul2(fmul2(pw, s32), t3p[x]);
+        float e0 = lg2(1.0f - fminf(a.x, clamp_hi())), e1 = lg2(1.0f - fminf(a.y, clamp_hi()));
+        if (diag) {
+          if (qbase + 2 * x <= key) e0 = 0.f;
+          if (qbase + 2 * x + 1 <= key) e1 = 0.f;
+        }
+        run += e0;
+        c2[x].x = run;
+        run += e1;
+        c2[x].y = run;
       }
-      if (g == 0) sXch[key] = run;
-      named_bar_sync(kBarAll, 256);
-      const float base = carry + (g == 1 ? sXch[key] : 0.f);
+      sXch[g * 128 + key] = run;
+      named_bar_sync(kBarAll, kWorkers);
+      float base = carry * kLog2e;
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        float v = base + c2[x];
-        if (diag && qbase + x < key) v = mask_value();
-        c2[x] = v * kLog2e;
+      for (int q = 0; q < NG - 1; ++q)
+        if (q < g) base += sXch[q * 128 + key];
+      const float2 base2 = make_float2(base, base);
+#pragma unroll
+      for (int x = 0; x < H2; ++x) c2[x] = fadd2(c2[x], base2);
+      if (diag) {
+#pragma unroll
+        for (int x = 0; x < H2; ++x) {
+          if (qbase + 2 * x < key) c2[x].x = mask_value();
+          if (qbase + 2 * x + 1 < key) c2[x].y = mask_value();
+        }
       }
     }
+    UQ(0)
 
     // ================= heads =================
-    float dc[32];
+    float2 dc[H2];
 #pragma unroll
-    for (int x = 0; x < 32; ++x) dc[x] = 0.f;
+    for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);
     for (int r = 0; r < R; ++r, ++hc) {
       const bool has_next = hc + 1 < total_heads;
-      float pre = 0.f;                             // next head's table entry, stored below (its load latency is hidden)
-      if (has_next && slotw == 0) pre = fetch_lse(hc + 1) * kLog2e;
-      if (has_next && slotw == 1) pre = fetch_cc(hc + 1);
+      float pre_l = 0.f;                           // next head's table entries: loads issued here, values used below
+      uint32_t pre_c = 0u;
+      if (has_next && helper && quad == 0) pre_l = fetch_lse(hc + 1);
+      if (has_next && helper && quad == 1) pre_c = fetch_cc(hc + 1);
       const int b = u % Cfg::kNB, tb = hc % 3, db = hc % Cfg::kDs;
+      if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 1 : 5) }
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
+      if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 2 : 6) }
+      UQ(1)
       tc_fence_after();
-      float pv[32];
-      uint32_t dp[32];
+      float2 pv[H2], dp[H2];
       {
-        uint32_t sr[32];
-        tmem_ld32(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, sr);
-        tmem_ld32(c.tmem + (b ? Cfg::tP1 : Cfg::tP0) + lane_base + col0, dp);
+        uint32_t sr[CG], dr[CG];
+        tmem_ld_n<CG>(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, sr);
+        tmem_ld_n<CG>(c.tmem + (b ? Cfg::tP1 : Cfg::tP0) + lane_base + col0, dr);
+        float2 nl[H2];
+        load_pairs(sLse + tb * 64 + col0, nl);                       // -lse * log2(e)
         tc_wait_ld();
         tc_fence_before();
         c.arrive_w(qLdDone + b);
+        if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 3 : 7) }
         ++u;
-        const float* l2 = sLse + tb * 64 + col0;
 #pragma unroll
-        for (int x = 0; x < 32; ++x) pv[x] = ex2(fmaf(__uint_as_float(sr[x]), kLog2e, c2[x] - l2[x]));
+        for (int x = 0; x < H2; ++x) {
+          const float2 sv = make_float2(__uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]));
+          const float2 arg = ffma2(sv, kLog2e2, fadd2(c2[x], nl[x]));
+          pv[x] = make_float2(ex2(arg.x), ex2(arg.y));
+          dp[x] = make_float2(__uint_as_float(dr[2 * x]), __uint_as_float(dr[2 * x + 1]));
+        }
       }
       if (kMode == 1) {
-        float e[32];
+        float e[CG];
 #pragma unroll
-        for (int x = 0; x < 32; ++x) e[x] = pv[x] * __uint_as_float(dp[x]);
-        const float part = warp_transpose_reduce(e, lane);           // this warp's 32 keys, column col0 + lane
-        atomicAdd(sCc + tb * 64 + col0 + lane, -part);
+        for (int x = 0; x < H2; ++x) {
+          const float2 ev = fmul2(pv[x], dp[x]);
+          e[2 * x] = ev.x;
+          e[2 * x + 1] = ev.y;
+        }
+        const float part = warp_colsum<CG>(e, scr, lane);            // this warp's 32 keys, column col0 + lane % CG
+        if (helper) atomicAdd(sCc + tb * 64 + col0 + lane, -part);
       }
-      if (has_next && slotw == 0) sLse[((hc + 1) % 3) * 64 + col0 + lane] = pre;
-      if (has_next && slotw == 1) sCc[((hc + 1) % 3) * 64 + col0 + lane] = pre;
-      if (!drain()) return;                        // the previous head's dQ (or the previous half tile's dK_j)
+      if (has_next && helper && quad == 0) sLse[((hc + 1) % 3) * 64 + col0 + lane] = lse_value(pre_l);
+      if (has_next && helper && quad == 1) sCc[((hc + 1) % 3) * 64 + col0 + lane] = cc_value(pre_c);
+      UQ(2)
       named_bar_sync(kBarGroup + g, 128);
-      uint32_t pk[16], dk[16];
+      UQ(4)
+      uint32_t pk[H2], dk[H2];
       {
-        const float* cc = sCc + tb * 64 + col0;
+        float2 cc[H2];
+        load_pairs(sCc + tb * 64 + col0, cc);
 #pragma unroll
-        for (int x = 0; x < 16; ++x) {
-          const float d0 = pv[2 * x] * (__uint_as_float(dp[2 * x]) + cc[2 * x]);
-          const float d1 = pv[2 * x + 1] * (__uint_as_float(dp[2 * x + 1]) + cc[2 * x + 1]);
-          dc[2 * x] += d0;
-          dc[2 * x + 1] += d1;
-          __nv_bfloat162 hp = __floats2bfloat162_rn(pv[2 * x], pv[2 * x + 1]), hd = __floats2bfloat162_rn(d0, d1);
+        for (int x = 0; x < H2; ++x) {
+          const float2 ds = fmul2(pv[x], fadd2(dp[x], cc[x]));
+          dc[x] = fadd2(dc[x], ds);
+          __nv_bfloat162 hp = __floats2bfloat162_rn(pv[x].x, pv[x].y), hd = __floats2bfloat162_rn(ds.x, ds.y);
           pk[x] = *reinterpret_cast<uint32_t*>(&hp);
           dk[x] = *reinterpret_cast<uint32_t*>(&hd);
         }
       }
       if (hc >= Cfg::kDs && !c.wait_w(qDsFree + db, hc / Cfg::kDs - 1)) return;
+      UQ(5)
       store_row(c.smem + Cfg::oDs + db * 16384, dk);
-      tmem_st16(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, pk);      // P^T over this group's own S columns
+      // P^T (rows CG g + 2x, 2x + 1 as one 32-bit column): in its own buffer, or over this group's own S columns
+      {
+        if (Cfg::kPtSeparate && hc >= 2 && !c.wait_w(qPtFree + (hc & 1), (hc >> 1) - 1)) return;
+        const uint32_t pt = Cfg::kPtSeparate ? c.tmem + Cfg::tPT + 32 * (hc & 1) + col0 / 2
+                                             : c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + col0;
+        if (CG == 32) tmem_st16(pt + lane_base, pk);
+        else tmem_st8(pt + lane_base, pk);
+      }
       tc_wait_st();
       fence_proxy_async();
       tc_fence_before();
       c.arrive_w(qDsReady + db);
-      pending = true;
-      pend_map = tmDQ;
-      pend_row = (c.bh * R + r) * L + row0;
+      UQ(6)
     }
 
     // ================= decay gradient =================
     {
       const bool more = ht + 1 < c.nht;
       if (more) carry_next = carry_at(ht + 1);
-      float t3pre = 0.f;
-      if (more && slotw == 2) t3pre = fetch_t3(ht + 1);
+      TG t3pre = TG();
+      if (more && helper && quad == 2) t3pre = fetch_t3(ht + 1);
       float run = 0.f;
 #pragma unroll
-      for (int x = 31; x >= 0; --x) {
-        run += dc[x];
-        dc[x] = run;                               // sum of dC over this thread's columns x .. 31
+      for (int x = H2 - 1; x >= 0; --x) {
+        run += dc[x].y;
+        dc[x].y = run;                             // sum of dC over this thread's columns from here to its last one
+        run += dc[x].x;
+        dc[x].x = run;
       }
-      sXch[(1 + g) * 128 + key] = run;
-      if (more && slotw == 2) sT3[((ht + 1) & 1) * 64 + col0 + lane] = t3pre;
-      if (!drain()) return;                        // the last head's dQ
-      named_bar_sync(kBarAll, 256);
-      const float other = sXch[(2 - g) * 128 + key];
-      const float add = suffix + (g == 0 ? other : 0.f);      // rows after this thread's block
-      suffix = suffix + run + other;                          // ... after this half tile (the next one lies below it)
+      sXch[(NG + g) * 128 + key] = run;
+      if (more && helper && quad == 2) sT3[((ht + 1) & 1) * 64 + col0 + lane] = t3_value(t3pre);
+      UQ(7)
+      named_bar_sync(kBarAll, kWorkers);
+      UQ(8)
+      float later = 0.f, others = 0.f;             // totals of the groups to the right / of all other groups
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        if (q == g) continue;
+        const float v = sXch[(NG + q) * 128 + key];
+        others += v;
+        if (q > g) later += v;
+      }
+      const float add = suffix + later;            // rows after this thread's block
+      suffix = suffix + run + others;              // ... after this half tile (the next one lies below it)
+      const float2 add2 = make_float2(add, add);
 
       const int b = u % Cfg::kNB;
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
+      UQ(9)
       tc_fence_after();
-      uint32_t gr[32];
-      tmem_ld32(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, gr);
+      uint32_t gr[CG];
+      tmem_ld_n<CG>(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, gr);
+      float2 t3p[H2];
+      load_pairs(t3v, t3p);
       tc_wait_ld();
       tc_fence_before();
       c.arrive_w(qLdDone + b);
       ++u;
-      uint32_t pk[16];
-      float dg_hold = 0.f;
+      uint32_t pk[H2];
+      float dtv[CG];
+      float2 dsa = make_float2(0.f, 0.f);
+      const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), km13 = make_float2(-1.0f / 3.0f, -1.0f / 3.0f);
 #pragma unroll
-      for (int x = 31; x >= 0; --x) {
-        float dl = dc[x] + add;
-        if (diag && qbase + x <= key) dl = 0.f;
-        const float gv = __uint_as_float(gr[x]);
-        const float t3 = t3v[x];
-        const float lg = lg2(gv);                                  // NaN for gv < 0: guarded below
-        const float pw = gv > 0.f ? ex2(lg * (2.0f / 3.0f)) : 0.f;
-        const float a = gated_affinity(pw, s3, t3);
-        float da = __fdividef(dl, fminf(fmaxf(a, clamp_lo_bwd()), clamp_hi()) - 1.0f);
-        if (!(a <= clamp_hi())) da = 0.f;
-        const float dstat = da * pw;
-        ds_acc = fmaf(dstat, t3, ds_acc);
-        dc[x] = dstat * s3;                                        // reuse: per-(key, row) term of d static_dest
-        float dg = __bfloat162float(__float2bfloat16_rn(da * s3 * t3));
-        dg = gv > 0.f ? dg * (2.0f / 3.0f) * ex2(lg * (-1.0f / 3.0f)) : 0.f;
-        if (x & 1) {
-          dg_hold = dg;
-        } else {
-          __nv_bfloat162 h = __floats2bfloat162_rn(dg, dg_hold);
-          pk[x >> 1] = *reinterpret_cast<uint32_t*>(&h);
+      for (int x = 0; x < H2; ++x) {
+        float2 dl = fadd2(dc[x], add2);
+        if (diag) {
+          if (qbase + 2 * x <= key) dl.x = 0.f;
+          if (qbase + 2 * x + 1 <= key) dl.y = 0.f;
         }
+        const float g0 = __uint_as_float(gr[2 * x]), g1 = __uint_as_float(gr[2 * x + 1]);
+        const float2 lg = make_float2(lg2(fmaxf(g0, 0.f)), lg2(fmaxf(g1, 0.f)));      // -inf for g <= 0: pw = 0
+        const float2 e23 = fmul2(lg, k23), e13 = fmul2(lg, km13);
+        const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
+        const float2 st = fmul2(pw, s32);
+        const float2 a = fmul2(st, t3p[x]);
+        const float2 am = make_float2(fminf(fmaxf(a.x, clamp_lo_bwd()), clamp_hi()) - 1.0f,
+                                      fminf(fmaxf(a.y, clamp_lo_bwd()), clamp_hi()) - 1.0f);
+        float2 da = fmul2(dl, make_float2(rcp_approx(am.x), rcp_approx(am.y)));
+        if (!(a.x <= clamp_hi())) da.x = 0.f;
+        if (!(a.y <= clamp_hi())) da.y = 0.f;
+        const float2 dstat = fmul2(da, pw);
+        dsa = ffma2(dstat, t3p[x], dsa);
+        const float2 dt = fmul2(dstat, s32);                       // per-(key, row) term of d static_dest
+        dtv[2 * x] = dt.x;
+        dtv[2 * x + 1] = dt.y;
+        // dG = dA s^(1/3) t^(1/3) (2/3) g^(-1/3) for g > 0
+        float2 dg = fmul2(fmul2(fmul2(da, s32), t3p[x]), fmul2(k23, make_float2(ex2(e13.x), ex2(e13.y))));
+        if (!(g0 > 0.f)) dg.x = 0.f;
+        if (!(g1 > 0.f)) dg.y = 0.f;
+        __nv_bfloat162 h = __floats2bfloat162_rn(dg.x, dg.y);
+        pk[x] = *reinterpret_cast<uint32_t*>(&h);
       }
+      ds_acc += dsa.x + dsa.y;
       if (ht >= 1 && !c.wait_w(qDgFree, ht - 1)) return;
       store_row(c.smem + Cfg::oDg, pk);
       fence_proxy_async();
       c.arrive_w(qDgReady);
-      pending = true;
-      pend_map = tmDK;
-      pend_row = c.bh * L + row0;
       // d static_dest: sum over the 128 keys of dstat * src^(1/3)
-      const float colsum = warp_transpose_reduce(dc, lane);
-      const float t3l = t3v[lane];
-      if (colsum != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + row0 + col0 + lane, colsum / (3.0f * t3l * t3l));
+      const float colsum = warp_colsum<CG>(dtv, scr, lane);
+      if (helper && colsum != 0.f) {
+        const float t3l = t3v[lane];
+        atomicAdd(p.acc_dt + (size_t)c.bh * L + row0 + col0 + lane, colsum / (3.0f * t3l * t3l));
+      }
+      UQ(10)
     }
   }
-  if (!drain()) return;                            // the last half tile's dK_j
+  UQ_STORE
 
-  // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, D/2 columns each) ----
+  // ---- end of the sweep: dV_i, dK_i, d static_src (thread = key, D / NG columns each) ----
   if (!c.wait_w(qFinal, 0)) return;
   tc_fence_after();
   const size_t krow = (size_t)c.bh * L + c.i * 128 + key;
+  constexpr int kPer = D / NG;
 #pragma unroll
-  for (int hb = 0; hb < D / 64; ++hb) {
-    const int d0 = (D / 2) * g + 32 * hb;
-    uint32_t o[32];
-    tmem_ld32(c.tmem + Cfg::tDV + lane_base + d0, o);
+  for (int pc = 0; pc < kPer / 16; ++pc) {
+    const int d0 = kPer * g + 16 * pc;
+    uint32_t o[16];
+    tmem_ld16(c.tmem + Cfg::tDV + lane_base + d0, o);
     tc_wait_ld();
     if (p.acc_dv_in) {
       const float4* extra = reinterpret_cast<const float4*>(p.acc_dv_in + krow * D + d0);
 #pragma unroll
-      for (int x = 0; x < 8; ++x) {
+      for (int x = 0; x < 4; ++x) {
         const float4 ev = extra[x];
         o[4 * x] = __float_as_uint(__uint_as_float(o[4 * x]) + ev.x);
         o[4 * x + 1] = __float_as_uint(__uint_as_float(o[4 * x + 1]) + ev.y);
@@ -610,34 +846,40 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         o[4 * x + 3] = __float_as_uint(__uint_as_float(o[4 * x + 3]) + ev.w);
       }
     }
-    uint32_t pk[16];
+    uint32_t pk[8];
 #pragma unroll
-    for (int x = 0; x < 16; ++x) {
+    for (int x = 0; x < 8; ++x) {
       __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * x]), __uint_as_float(o[2 * x + 1]));
       pk[x] = *reinterpret_cast<uint32_t*>(&h);
     }
     uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * D + d0);
-#pragma unroll
-    for (int x = 0; x < 4; ++x) dst[x] = make_uint4(pk[4 * x], pk[4 * x + 1], pk[4 * x + 2], pk[4 * x + 3]);
-    tmem_ld32(c.tmem + Cfg::tDK + lane_base + d0, o);
+    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    tmem_ld16(c.tmem + Cfg::tDK + lane_base + d0, o);
     tc_wait_ld();
     float* dkp = p.acc_dk + krow * D + d0;
 #pragma unroll
-    for (int x = 0; x < 8; ++x)
+    for (int x = 0; x < 4; ++x)
       red_add_v4(dkp + 4 * x, __uint_as_float(o[4 * x]), __uint_as_float(o[4 * x + 1]), __uint_as_float(o[4 * x + 2]),
                  __uint_as_float(o[4 * x + 3]));
   }
-  if (g == 1) sXch[key] = ds_acc;
-  named_bar_sync(kBarAll, 256);
-  if (g == 0) Num<TG>::st(static_cast<TG*>(p.dss) + krow, (ds_acc + sXch[key]) / (3.0f * s3 * s3));
+  sXch[g * 128 + key] = ds_acc;
+  named_bar_sync(kBarAll, kWorkers);
+  if (g == 0) {
+    float tot = 0.f;
+#pragma unroll
+    for (int q = 0; q < NG; ++q) tot += sXch[q * 128 + key];
+    Num<TG>::st(static_cast<TG*>(p.dss) + krow, tot / (3.0f * s3 * s3));
+  }
 }
 
-template <int D, typename TG, int kMode>
-__global__ void __launch_bounds__(320, 1)
+template <int D, typename TG, int kMode, int CG>
+__global__ void __launch_bounds__(32 * (8 + 4 * (64 / CG)), 1)
 bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
             const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK, Bwd2Params p) {
   using Cfg = Bwd2Cfg<D>;
+  constexpr int NG = 64 / CG;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint32_t* misc = reinterpret_cast<uint32_t*>(smem + Cfg::oMisc);      // [0] TMEM base, [1] abort flag, [2] failure note
@@ -657,8 +899,9 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     misc[2] = 0;
     for (int b = 0; b < qNumBars; ++b) {
       uint32_t count = 1;
-      if (b == qLdDone || b == qLdDone + 1 || b == qDsReady || b == qDsReady + 1 || b == qDgReady) count = 8;   // one arrival per worker warp
-      if (b == qYFree) count = 4;                                                                            // the four draining warps
+      if (b == qLdDone || b == qLdDone + 1 || b == qDsReady || b == qDsReady + 1 || b == qDgReady) count = 4 * NG;   // one arrival per worker warp
+      if (b == qYFree) count = 2;                                                                                  // the two draining warps
+      if (b == qDsFree || b == qDsFree + 1 || b == qDgFree || b == qFinal) count = 2;                               // both back issuers
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
@@ -674,13 +917,33 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
   tc_fence_after();
   c.tmem = misc[0];
 
-  if (warp == 0) {
-    if (lane == 0) bwd2_front<D, kMode>(c, p, &tmK, &tmV, &tmQ, &tmG);
-  } else if (warp == 1) {
-    if (lane == 0) bwd2_back<D>(c, p);
+  // Register reallocation between the warpgroups: the single-thread roles and the drain warps need few registers, the
+  // workers (who keep a half tile's decay prefix, its gradient and a head's probabilities in registers) many.  The block
+  // is launched with kLaunchRegs per thread (the most its thread count allows); the first two warpgroups give back what
+  // they do not need and every worker warpgroup takes an equal share of it.  (The sums are checked at compile time: a
+  // worker request beyond what was given back would never be granted.)
+  constexpr int kThreads = 32 * (8 + 4 * NG);
+  constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
+  constexpr int kRoleRegs = 56, kDrainRegs = 72;
+  constexpr int kWorkerRegs = kLaunchRegs + ((2 * kLaunchRegs - kRoleRegs - kDrainRegs) * 128 / (128 * NG)) / 8 * 8;
+  static_assert(kRoleRegs <= kLaunchRegs && kDrainRegs <= kLaunchRegs, "setmaxnreg.dec must not ask for more");
+  static_assert(128 * (kRoleRegs + kDrainRegs) + 128 * NG * kWorkerRegs <= kThreads * kLaunchRegs, "register pool");
+  static_assert(kWorkerRegs <= 232, "setmaxnreg range");
+  // warps 0-3: the four single-thread roles; warps 4-5: drain warps (6-7 complete their warpgroup); warps 8..: workers
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRoleRegs));
+    if (lane == 0) {
+      if (warp == 0) bwd2_front<D>(c, p);
+      else if (warp == 1) bwd2_back<D, CG>(c, p, 0);
+      else if (warp == 2) bwd2_producer<D, kMode>(c, p, &tmK, &tmV, &tmQ, &tmG);
+      else bwd2_back<D, CG>(c, p, 1);
+    }
+  } else if (warp < 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDrainRegs));
+    if (warp < 6) bwd2_drain<D>(c, p, &tmDQ, &tmDK);
   } else {
-    bwd2_worker<D, TG, kMode>(c, p, &tmDQ, &tmDK);
-    if (warp == 4 && lane == 0) bulk_wait_all();      // the leader's reduce-adds have landed before the block retires
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
+    bwd2_worker<D, TG, kMode, CG>(c, p);
   }
 
   tc_fence_before();

@@ -73,6 +73,27 @@ __device__ __forceinline__ float log_retention(float a) {
   return lg2(1.0f - fminf(a, clamp_hi())) * 0.6931471805599453f;
 }
 
+// packed fp32 pairs (one instruction for two lanes of work: the element-wise phases are bound by instruction issue)
+__device__ __forceinline__ float2 fadd2(float2 a, float2 b) {
+  float2 d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 fmul2(float2 a, float2 b) {
+  float2 d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)));
+  return d;
+}
+__device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(reinterpret_cast<unsigned long long&>(d))
+      : "l"(reinterpret_cast<unsigned long long&>(a)), "l"(reinterpret_cast<unsigned long long&>(b)),
+        "l"(reinterpret_cast<unsigned long long&>(c)));
+  return d;
+}
+
 template <int D>
 struct FwdCfg {
   static constexpr int kTileBytes = 128 * D * 2;   // one [128][D] bf16 tile
@@ -279,13 +300,18 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
         c.arrive_w(kGFree);
       }
       if (cb == 2 && carry_row) carry_row[128] = cval;      // prefix after the first 64 rows of the tile
-      float v[32];
+      float v[32], t3r[32];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        const float4 t4 = reinterpret_cast<const float4*>(t3buf + cb * 32)[x];
+        t3r[4 * x] = t4.x; t3r[4 * x + 1] = t4.y; t3r[4 * x + 2] = t4.z; t3r[4 * x + 3] = t4.w;
+      }
       float local = 0.f;
 #pragma unroll
       for (int x = 0; x < 32; ++x) {
         const int q = cb * 32 + x;
         const float gv = __uint_as_float(g[x]);
-        float ell = log_retention(gated_affinity(gram_pow23(gv), s3, t3buf[q]));
+        float ell = log_retention(gated_affinity(gram_pow23(gv), s3, t3r[x]));
         if (diag && q <= k) ell = 0.f;
         local += ell;
         cval = carry + (tprev + local);
@@ -320,7 +346,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
 template <int D>
 __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams& p, int me) {
   using Cfg = FwdCfg<D>;
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int R = p.s.R, N = p.s.N;
   const int row = threadIdx.x & 127;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
   const uint8_t* sCrow0 = c.smem + Cfg::oCs + row * 512;
@@ -362,11 +388,11 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         for (int u = 0; u < 16; ++u) {
           const int chunk = cb * 16 + u;
           const float4 cv = *reinterpret_cast<const float4*>(sCrow + (((chunk ^ (row & 7)) & 31) << 4));
-          float a0 = __uint_as_float(s[u * 4 + 0]) + cv.x, a1 = __uint_as_float(s[u * 4 + 1]) + cv.y;
-          float a2 = __uint_as_float(s[u * 4 + 2]) + cv.z, a3 = __uint_as_float(s[u * 4 + 3]) + cv.w;
-          m = fmaxf(m, fmaxf(fmaxf(a0, a1), fmaxf(a2, a3)));
-          s[u * 4 + 0] = __float_as_uint(a0); s[u * 4 + 1] = __float_as_uint(a1);
-          s[u * 4 + 2] = __float_as_uint(a2); s[u * 4 + 3] = __float_as_uint(a3);
+          const float2 a01 = fadd2(make_float2(__uint_as_float(s[u * 4 + 0]), __uint_as_float(s[u * 4 + 1])), make_float2(cv.x, cv.y));
+          const float2 a23 = fadd2(make_float2(__uint_as_float(s[u * 4 + 2]), __uint_as_float(s[u * 4 + 3])), make_float2(cv.z, cv.w));
+          m = fmaxf(m, fmaxf(fmaxf(a01.x, a01.y), fmaxf(a23.x, a23.y)));
+          s[u * 4 + 0] = __float_as_uint(a01.x); s[u * 4 + 1] = __float_as_uint(a01.y);
+          s[u * 4 + 2] = __float_as_uint(a23.x); s[u * 4 + 3] = __float_as_uint(a23.y);
         }
         tmem_st32(tS + cb * 64, s);
         tmem_st32(tS + cb * 64 + 32, s + 32);
@@ -376,7 +402,8 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       if (r == last_r) c.arrive_w(kCFree + cbuf);
       // pass 2: P = exp(s - m) as bf16 into the first 64 columns of the S buffer
       const float mb = m * kLog2e;
-      float l = 0.f;
+      const float2 kL2 = make_float2(kLog2e, kLog2e), nmb2 = make_float2(-mb, -mb);
+      float2 l2 = make_float2(0.f, 0.f);
 #pragma unroll 1
       for (int cb = 0; cb < 2; ++cb) {
         uint32_t s[64];
@@ -386,12 +413,12 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         uint32_t pk[32];
 #pragma unroll
         for (int u = 0; u < 32; ++u) {
-          const float p0 = ex2(fmaf(__uint_as_float(s[2 * u]), kLog2e, -mb));
-          const float p1 = ex2(fmaf(__uint_as_float(s[2 * u + 1]), kLog2e, -mb));
-          __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+          const float2 arg = ffma2(make_float2(__uint_as_float(s[2 * u]), __uint_as_float(s[2 * u + 1])), kL2, nmb2);
+          const float2 pe = make_float2(ex2(arg.x), ex2(arg.y));
+          __nv_bfloat162 h = __floats2bfloat162_rn(pe.x, pe.y);
           // the row sum uses the unrounded probabilities: the reference normalises in fp32 and rounds P afterwards
           // (universal_attention_autograd.py:158-159)
-          l += p0 + p1;
+          l2 = fadd2(l2, pe);
           pk[u] = *reinterpret_cast<uint32_t*>(&h);
         }
         tmem_st32(tS + cb * 32, pk);
@@ -401,6 +428,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       c.arrive_w(kPReady + sb);
       UF(4)
       const int qg = p.r0 + (c.j0 + T - p.j_begin) * 128 + row;      // row index inside the slab
+      const float l = l2.x + l2.y;
       const float lse = m + lg2(l) * kLn2;
       const size_t orow = (chunk_id * R + r) * p.Lr + qg;
       p.lse[orow] = lse;
@@ -422,9 +450,11 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         }
         if (!p.out) continue;                 // statistics-only run (the log-sum-exp for a backward that was not given one)
         uint32_t pk[16];
+        const float2 linv2 = make_float2(linv, linv);
 #pragma unroll
         for (int u = 0; u < 16; ++u) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * u]) * linv, __uint_as_float(o[2 * u + 1]) * linv);
+          const float2 ov = fmul2(make_float2(__uint_as_float(o[2 * u]), __uint_as_float(o[2 * u + 1])), linv2);
+          __nv_bfloat162 h = __floats2bfloat162_rn(ov.x, ov.y);
           pk[u] = *reinterpret_cast<uint32_t*>(&h);
         }
         uint4* dst = reinterpret_cast<uint4*>(orow_ptr + cb * 32);

@@ -152,6 +152,11 @@ inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void
 
 // Keys-on-lanes backward over the whole sequence (rows that see the chunk only).  kMode 1: per-chunk log-sum-exp and
 // g_denom; kMode 2: merged upstream gradient.  The caller zeroes the fp32 accumulators.
+#ifndef UA_BWD2_COLS
+#define UA_BWD2_COLS 32
+#endif
+constexpr int kBwd2Cols = UA_BWD2_COLS;      // columns of a half tile per worker thread (32: eight worker warps with ~190 registers each; 16: sixteen)
+
 template <int D, typename TG, int kMode>
 int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const Bwd2Params& p,
                   cudaStream_t st) {
@@ -163,9 +168,9 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
       !make_rows_map(&tmG, g_out, (kMode == 2 ? BH : BH * s.N) * s.R * s.L, D, 64) ||
       !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * s.L, D, 64) || !make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L, D, 64))
     return UA_ERR_CUDA;
-  auto kern = bwd2_kernel<D, TG, kMode>;
+  auto kern = bwd2_kernel<D, TG, kMode, kBwd2Cols>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 320, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
+  kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
