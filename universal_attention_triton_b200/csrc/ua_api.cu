@@ -79,11 +79,12 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
 }
 
 struct BwdWorkspaceTc {
-  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, acc_bytes, total;
+  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, off_gd, acc_bytes, total;
 };
 
 // Scratch of the tensor-core backward: status | fp32 accumulators dK, dV (the part from the rows before a chunk), dQ,
-// d dest | decay-prefix table (two entries per 128-row tile) | log-sum-exp (only written when the caller has none).
+// d dest | decay-prefix table (two entries per 128-row tile) | log-sum-exp (only written when the caller has none) |
+// fp32 copy of g_denom (only written when the caller's is bf16).
 BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   BwdWorkspaceTc w;
   const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
@@ -95,6 +96,7 @@ BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   w.acc_bytes = o;
   w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 256 * f, 256);
   w.off_lse = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
+  w.off_gd = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
   w.total = o;
   return w;
 }
@@ -115,6 +117,12 @@ int launch_simt_bwd(const ua::simt::BwdParams& p, cudaStream_t st) {
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<p.s.B * p.s.H * p.s.N, ua::simt::kThreads, smem, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+__global__ void widen_bf16_kernel(const bf16* __restrict__ src, float* __restrict__ dst, size_t n) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < n; idx += stride) dst[idx] = __bfloat162float(src[idx]);
 }
 
 template <typename T>
@@ -487,9 +495,19 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
       }
       if (e) return e;
     }
+    // the kernel's producer copies rows of lse / g_denom with 16-byte bulk copies: fp32, 16-byte aligned
+    const float* gd32 = static_cast<const float*>(g_denom_cm);
+    if (g_denom_dtype != UA_F32) {
+      float* tmp = reinterpret_cast<float*>(ws + w.off_gd);
+      const size_t n_gd = BHs * s.N * (size_t)s.R * s.L;
+      widen_bf16_kernel<<<148 * 8, 256, 0, st>>>(static_cast<const bf16*>(g_denom_cm), tmp, n_gd);
+      if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+      gd32 = tmp;
+    }
+    if (!aligned16(gd32) || !aligned16(lse) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
     ua::sm100::Bwd2Params qp;
     qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest;
-    qp.g_denom = g_denom_cm; qp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+    qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
     qp.acc_dv_in = (!skip_masked && s.N > 1) ? acc_dv : nullptr;
@@ -767,7 +785,8 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
     if ((e = ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st))) return e;
   }
   ua::sm100::Bwd2Params qp;
-  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr; qp.g_denom_is_f32 = 1;
+  if (!aligned16(row_lse) || !aligned16(row_delta) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
+  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr;
   qp.lse = nullptr; qp.row_lse = row_lse; qp.row_delta = row_delta; qp.carry = carry_tab;
   qp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
   qp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);

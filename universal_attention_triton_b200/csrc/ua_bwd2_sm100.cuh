@@ -42,8 +42,7 @@ struct Bwd2Params {
   Shape s;
   const void* ssrc;
   const void* sdest;
-  const void* g_denom;       // (b,h,n,r,L) fp32 or bf16                     [mode 1]
-  int g_denom_is_f32;
+  const float* g_denom;      // (b,h,n,r,L) fp32                             [mode 1]
   const float* lse;          // (b,h,n,r,L) fp32: the forward's log-sum-exp   [mode 1]
   const float* row_lse;      // (b,h,r,L) fp32: log-sum-exp over all keys     [mode 2]
   const float* row_delta;    // (b,h,r,L) fp32: g . merged                    [mode 2]
@@ -75,12 +74,16 @@ struct Bwd2Cfg {
   static constexpr int oDs = oSlot + kNS * kSlot;          // kDs x 16 KB [128 keys][64 rows] bf16, then dG, then the staging tile
   static constexpr int oDg = oDs + kDs * 16384;
   static constexpr int oStage = oDg + 16384;               // [64][D] fp32 as D/32 boxes of [64][32], 128-byte swizzle
-  static constexpr int oT3 = oStage + 256 * D;             // float [2][64]
-  static constexpr int oLse = oT3 + 512;                   // float [3][64]  lse * log2(e) of the head's rows
-  static constexpr int oCc = oLse + 768;                   // float [3][64]  g_denom - sum_k P dP  (or -delta)
-  static constexpr int oXch = oCc + 768;                   // float [8][128] totals crossing the column groups
+  static constexpr int oT3 = oStage + 256 * D;             // float [2][64]: static_dest^(1/3) of a half tile's rows
+  static constexpr int oDt = oT3 + 512;                    // float [2][64]: d static_dest of a half tile, flushed by the drain warps
+  // per-row tables that the producer copies next to the tiles (no global load is ever issued by a worker):
+  static constexpr int oHeadTab = oDt + 512;               // kNS x { float lse[64]; float cc[64] }: log-sum-exp and g_denom (or delta) of a head's rows
+  static constexpr int kTab = 3;                           // half-tile tables in flight
+  static constexpr int kHtTab = 768;                       // { float carry[128]; raw static_dest[64] (<= 256 B) }
+  static constexpr int oHtTab = oHeadTab + kNS * 512;
+  static constexpr int oXch = oHtTab + kTab * kHtTab;      // float [8][128] totals crossing the column groups
   static constexpr int oBar = oXch + 4096;
-  static constexpr int oMisc = oBar + 256;
+  static constexpr int oMisc = oBar + 256;      // (31 barriers of 8 bytes)
   // per-warp scratch tiles for the column sums over the keys ([32 lanes][CG] floats each, 32 KB in all); head_dim 128
   // has no room for them and transposes with shuffles
   static constexpr bool kScratch = (D == 64);
@@ -103,7 +106,9 @@ enum Bwd2Bar {
   qInFull = 5, qInFree = 9,        // [4]
   qSFull = 13, qLdDone = 15, qPtFree = 17,   // [2] per (S, dP) buffer / per probability buffer
   qDsReady = 19, qDsFree = 21,     // [2] per dS buffer
-  qYFull = 23, qYFree = 24, qDgReady = 25, qDgFree = 26, qFinal = 27, qNumBars = 28
+  qYFull = 23, qYFree = 24, qDgReady = 25, qDgFree = 26, qFinal = 27,
+  qTabFull = 28,                   // [3] per half-tile table buffer
+  qNumBars = 31
 };
 
 struct Bwd2Ctx {
@@ -184,7 +189,7 @@ __device__ __forceinline__ void mma4_ts(uint32_t d, uint32_t a0, uint32_t a1, ui
 }
 
 // ------------------------------------------------------------- TMA producer --
-template <int D, int kMode>
+template <int D, typename TG, int kMode>
 __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
                                               const CUtensorMap* tmQ, const CUtensorMap* tmG) {
   using Cfg = Bwd2Cfg<D>;
@@ -200,11 +205,24 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
       tma_load_2d(sb + Cfg::oKi + b * 16384 + h * 8192, tmK, b * 64, krow + h * 64, c.bar(qKvFull));
       tma_load_2d(sb + Cfg::oVi + b * 16384 + h * 8192, tmV, b * 64, krow + h * 64, c.bar(qKvFull));
     }
-  // in sweep order: K_j of half tile ht, then the (Q, dO) pairs of its heads; a slot is refilled as soon as the MMAs
-  // that read it have completed
+  // per-half-tile tables: decay prefix of the 128 keys at the start of the half tile, raw static_dest of its 64 rows
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
+  auto load_tables = [&](int ht) -> bool {
+    const int tb = ht % Cfg::kTab, use = ht / Cfg::kTab;
+    if (use >= 1 && !c.wait(qDgReady, ht - Cfg::kTab)) return false;      // the half tile that used the buffer is done with it
+    const uint32_t dst = sb + Cfg::oHtTab + tb * Cfg::kHtTab;
+    mbar_expect_tx(c.bar(qTabFull + tb), 512 + 64 * (uint32_t)sizeof(TG));
+    bulk_load_1d(dst, p.carry + ((chunk_id * N + c.tile_j(ht, N)) * 2 + c.half_of(ht)) * 128, 512, c.bar(qTabFull + tb));
+    bulk_load_1d(dst + 512, sd + c.row0_of(ht, N), 64 * (uint32_t)sizeof(TG), c.bar(qTabFull + tb));
+    return true;
+  };
+  if (!load_tables(0)) return;
+  // in sweep order: K_j of half tile ht, then the (Q, dO) pairs of its heads (with the log-sum-exp and g_denom rows of
+  // the head); a slot is refilled as soon as the MMAs that read it have completed
   int hc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
     const int row0 = c.row0_of(ht, N);
+    if (ht + 1 < c.nht && !load_tables(ht + 1)) return;
     {
       const int sl = ht % Cfg::kKj, use = ht / Cfg::kKj;
       if (use >= 1 && !c.wait(qKjFree + sl, use - 1)) return;
@@ -218,12 +236,19 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
       if (use >= 1 && !c.wait(qInFree + sl, use - 1)) return;
       const int qrow = (c.bh * R + r) * L + row0;
       const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * L + row0);
-      const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot;
-      mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf);
+      const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot, tab = sb + Cfg::oHeadTab + sl * 512;
+      mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf + 512);
 #pragma unroll
       for (int b = 0; b < Cfg::kBoxes; ++b) {
         tma_load_2d(dst + b * 8192, tmQ, b * 64, qrow, c.bar(qInFull + sl));
         tma_load_2d(dst + Cfg::kHalf + b * 8192, tmG, b * 64, grow, c.bar(qInFull + sl));
+      }
+      if (kMode == 2) {
+        bulk_load_1d(tab, p.row_lse + qrow, 256, c.bar(qInFull + sl));
+        bulk_load_1d(tab + 256, p.row_delta + qrow, 256, c.bar(qInFull + sl));
+      } else {
+        bulk_load_1d(tab, p.lse + grow, 256, c.bar(qInFull + sl));
+        bulk_load_1d(tab + 256, p.g_denom + grow, 256, c.bar(qInFull + sl));
       }
     }
   }
@@ -475,6 +500,14 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
     for (int r = 0; r <= R; ++r, ++yc) {
       if (!c.wait_w(qYFull, yc)) return;
       tc_fence_after();
+      if (r == R) {
+        // d static_dest of the half tile: the workers have added their column sums in shared memory (complete before dK_j
+        // was issued); one global add per row, and the buffer is zero again before this Y is released
+        float* dt = reinterpret_cast<float*>(c.smem + Cfg::oDt) + (ht & 1) * 64 + row;
+        const float v = *dt;
+        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + row0 + row, v);
+        *dt = 0.f;
+      }
       if (leader) bulk_wait_read_all();                 // the previous reduce-add has read the staging tile
       named_bar_sync(kBarDrain, 64);
 #pragma unroll 1
@@ -522,48 +555,26 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   const int col0 = CG * g;
   const bool helper = lane < CG;                 // lanes that fetch table entries (lane = column of the group)
   const float kLog2e = 1.4426950408889634f;
-  const float2 kLog2e2 = make_float2(kLog2e, kLog2e);
-  const size_t chunk_id = (size_t)c.bh * N + c.i;
+  const float2 kLog2e2 = make_float2(kLog2e, kLog2e), kNegLog2e2 = make_float2(-kLog2e, -kLog2e);
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
-  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + key));
   const float2 s32 = make_float2(s3, s3);
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
-  float* sLse = reinterpret_cast<float*>(c.smem + Cfg::oLse);
-  float* sCc = reinterpret_cast<float*>(c.smem + Cfg::oCc);
+  float* sDt = reinterpret_cast<float*>(c.smem + Cfg::oDt);
   float* sXch = reinterpret_cast<float*>(c.smem + Cfg::oXch);
   float* scr = Cfg::kScratch ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * CG) : nullptr;
   const uint32_t swz = (uint32_t)(key & 7);
-  const int total_heads = c.nht * R;
   UQ_DECL
 
-  auto row0_of = [&](int ht) { return c.tile_j(ht, N) * 128 + 64 * c.half_of(ht); };
-  auto carry_at = [&](int ht) -> float {
-    return p.carry[((chunk_id * N + c.tile_j(ht, N)) * 2 + c.half_of(ht)) * 128 + key];
+  // Per-row tables arrive in shared memory with the tiles (the TMA producer copies them): the workers issue no global
+  // load inside the sweep.  (One coalesced load per head cost every warp ~1000 cycles here: it queues behind the
+  // shared-memory traffic of all the other warps.)
+  auto ht_table = [&](int ht) -> const uint8_t* { return c.smem + Cfg::oHtTab + (ht % Cfg::kTab) * Cfg::kHtTab; };
+  // static_dest^(1/3) of half tile ht's rows, from the raw gate values of its table (lane = column of this group)
+  auto t3_from_table = [&](int ht) -> float {
+    const TG* raw = reinterpret_cast<const TG*>(ht_table(ht) + 512);
+    return cbrtf(Num<TG>::ld(raw + col0 + lane));
   };
-  // helper duties, one warp of each group per table, lane = column: values of head hc for the group's columns.  The
-  // fetch_* functions only ISSUE the global load and return its raw bits; the arithmetic on them (*_value) is done where
-  // the value is stored, a whole phase later, so that the load's latency never stalls the warp.
-  auto fetch_lse = [&](int hc) -> float {
-    const int ht = hc / R, r = hc - ht * R;
-    const int row = row0_of(ht) + col0 + lane;
-    return (kMode == 2) ? p.row_lse[((size_t)c.bh * R + r) * L + row] : p.lse[(chunk_id * R + r) * L + row];
-  };
-  auto lse_value = [&](float raw) -> float { return -raw * kLog2e; };
-  auto fetch_cc = [&](int hc) -> uint32_t {
-    const int ht = hc / R, r = hc - ht * R;
-    const int row = row0_of(ht) + col0 + lane;
-    if (kMode == 2) return __float_as_uint(p.row_delta[((size_t)c.bh * R + r) * L + row]);
-    const size_t o = (chunk_id * R + r) * L + row;
-    return p.g_denom_is_f32 ? __float_as_uint(static_cast<const float*>(p.g_denom)[o])
-                            : (uint32_t) static_cast<const unsigned short*>(p.g_denom)[o];
-  };
-  auto cc_value = [&](uint32_t raw) -> float {
-    if (kMode == 2) return -__uint_as_float(raw);
-    return p.g_denom_is_f32 ? __uint_as_float(raw) : __uint_as_float(raw << 16);
-  };
-  auto fetch_t3 = [&](int ht) -> TG { return sd[row0_of(ht) + col0 + lane]; };
-  auto t3_value = [&](TG raw) -> float { return cbrtf(Num<TG>::ld(&raw)); };
   // CG floats of a table row for this group's columns, as pairs
   auto load_pairs = [&](const float* src, float2* dst) {
 #pragma unroll
@@ -583,11 +594,10 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     }
   };
 
-  // ---- prologue: tables of the first half tile / first head ----
-  if (helper && quad == 0) sLse[col0 + lane] = lse_value(fetch_lse(0));
-  if (helper && quad == 1) sCc[col0 + lane] = cc_value(fetch_cc(0));
-  if (helper && quad == 2) sT3[col0 + lane] = t3_value(fetch_t3(0));
-  float carry_next = carry_at(0);
+  // ---- prologue: static_dest^(1/3) of the first half tile ----
+  if (!c.wait_w(qTabFull, 0)) return;
+  if (helper && quad == 2) sT3[col0 + lane] = t3_from_table(0);
+  if (g == 0) sDt[key] = 0.f;                    // both half-tile parities of the d static_dest buffer
   float suffix = 0.f, ds_acc = 0.f;
   named_bar_sync(kBarAll, kWorkers);
 
@@ -601,7 +611,8 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     // ================= decay recomputation: c2 = log2(e) * decay prefix of (key, CG rows) =================
     float2 c2[H2];
     {
-      const float carry = carry_next;
+      if (!c.wait_w(qTabFull + ht % Cfg::kTab, ht / Cfg::kTab)) return;
+      const float carry = reinterpret_cast<const float*>(ht_table(ht))[key];
       const int b = u % Cfg::kNB;
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
       tc_fence_after();
@@ -653,12 +664,10 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
 #pragma unroll
     for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);
     for (int r = 0; r < R; ++r, ++hc) {
-      const bool has_next = hc + 1 < total_heads;
-      float pre_l = 0.f;                           // next head's table entries: loads issued here, values used below
-      uint32_t pre_c = 0u;
-      if (has_next && helper && quad == 0) pre_l = fetch_lse(hc + 1);
-      if (has_next && helper && quad == 1) pre_c = fetch_cc(hc + 1);
-      const int b = u % Cfg::kNB, tb = hc % 3, db = hc % Cfg::kDs;
+      const int b = u % Cfg::kNB, sl = hc % Cfg::kNS, db = hc % Cfg::kDs;
+      float* tabL = reinterpret_cast<float*>(c.smem + Cfg::oHeadTab + sl * 512);      // lse[64] of the head's rows (raw)
+      float* tabC = tabL + 64;                                                         // g_denom[64] (or delta[64])
+      if (!c.wait_w(qInFull + sl, hc / Cfg::kNS)) return;                              // (the tables landed with the tiles)
       if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 1 : 5) }
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
       if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 2 : 6) }
@@ -670,16 +679,17 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         tmem_ld_n<CG>(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, sr);
         tmem_ld_n<CG>(c.tmem + (b ? Cfg::tP1 : Cfg::tP0) + lane_base + col0, dr);
         float2 nl[H2];
-        load_pairs(sLse + tb * 64 + col0, nl);                       // -lse * log2(e)
+        load_pairs(tabL + col0, nl);                                 // lse of the rows
         tc_wait_ld();
         tc_fence_before();
         c.arrive_w(qLdDone + b);
         if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 3 : 7) }
         ++u;
+        UQ(15)
 #pragma unroll
         for (int x = 0; x < H2; ++x) {
           const float2 sv = make_float2(__uint_as_float(sr[2 * x]), __uint_as_float(sr[2 * x + 1]));
-          const float2 arg = ffma2(sv, kLog2e2, fadd2(c2[x], nl[x]));
+          const float2 arg = ffma2(sv, kLog2e2, ffma2(nl[x], kNegLog2e2, c2[x]));
           pv[x] = make_float2(ex2(arg.x), ex2(arg.y));
           dp[x] = make_float2(__uint_as_float(dr[2 * x]), __uint_as_float(dr[2 * x + 1]));
         }
@@ -693,19 +703,18 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           e[2 * x + 1] = ev.y;
         }
         const float part = warp_colsum<CG>(e, scr, lane);            // this warp's 32 keys, column col0 + lane % CG
-        if (helper) atomicAdd(sCc + tb * 64 + col0 + lane, -part);
+        if (helper) atomicAdd(tabC + col0 + lane, -part);           // g_denom - sum_k P dP, in place
       }
-      if (has_next && helper && quad == 0) sLse[((hc + 1) % 3) * 64 + col0 + lane] = lse_value(pre_l);
-      if (has_next && helper && quad == 1) sCc[((hc + 1) % 3) * 64 + col0 + lane] = cc_value(pre_c);
       UQ(2)
       named_bar_sync(kBarGroup + g, 128);
       UQ(4)
       uint32_t pk[H2], dk[H2];
       {
         float2 cc[H2];
-        load_pairs(sCc + tb * 64 + col0, cc);
+        load_pairs(tabC + col0, cc);
 #pragma unroll
         for (int x = 0; x < H2; ++x) {
+          if (kMode == 2) cc[x] = make_float2(-cc[x].x, -cc[x].y);            // merged mode: dS = P (dP - delta)
           const float2 ds = fmul2(pv[x], fadd2(dp[x], cc[x]));
           dc[x] = fadd2(dc[x], ds);
           __nv_bfloat162 hp = __floats2bfloat162_rn(pv[x].x, pv[x].y), hd = __floats2bfloat162_rn(ds.x, ds.y);
@@ -734,9 +743,6 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     // ================= decay gradient =================
     {
       const bool more = ht + 1 < c.nht;
-      if (more) carry_next = carry_at(ht + 1);
-      TG t3pre = TG();
-      if (more && helper && quad == 2) t3pre = fetch_t3(ht + 1);
       float run = 0.f;
 #pragma unroll
       for (int x = H2 - 1; x >= 0; --x) {
@@ -746,7 +752,10 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         dc[x].x = run;
       }
       sXch[(NG + g) * 128 + key] = run;
-      if (more && helper && quad == 2) sT3[((ht + 1) & 1) * 64 + col0 + lane] = t3_value(t3pre);
+      if (more && quad == 2) {                   // static_dest^(1/3) of the next half tile's rows
+        if (!c.wait_w(qTabFull + (ht + 1) % Cfg::kTab, (ht + 1) / Cfg::kTab)) return;
+        if (helper) sT3[((ht + 1) & 1) * 64 + col0 + lane] = t3_from_table(ht + 1);
+      }
       UQ(7)
       named_bar_sync(kBarAll, kWorkers);
       UQ(8)
@@ -811,14 +820,14 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       ds_acc += dsa.x + dsa.y;
       if (ht >= 1 && !c.wait_w(qDgFree, ht - 1)) return;
       store_row(c.smem + Cfg::oDg, pk);
-      fence_proxy_async();
-      c.arrive_w(qDgReady);
-      // d static_dest: sum over the 128 keys of dstat * src^(1/3)
+      // d static_dest: sum over the 128 keys of dstat * src^(1/3), added up in shared memory (the drain warps flush it)
       const float colsum = warp_colsum<CG>(dtv, scr, lane);
       if (helper && colsum != 0.f) {
         const float t3l = t3v[lane];
-        atomicAdd(p.acc_dt + (size_t)c.bh * L + row0 + col0 + lane, colsum / (3.0f * t3l * t3l));
+        atomicAdd(sDt + (ht & 1) * 64 + col0 + lane, colsum / (3.0f * t3l * t3l));
       }
+      fence_proxy_async();
+      c.arrive_w(qDgReady);
       UQ(10)
     }
   }
@@ -935,7 +944,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     if (lane == 0) {
       if (warp == 0) bwd2_front<D>(c, p);
       else if (warp == 1) bwd2_back<D, CG>(c, p, 0);
-      else if (warp == 2) bwd2_producer<D, kMode>(c, p, &tmK, &tmV, &tmQ, &tmG);
+      else if (warp == 2) bwd2_producer<D, TG, kMode>(c, p, &tmK, &tmV, &tmQ, &tmG);
       else bwd2_back<D, CG>(c, p, 1);
     }
   } else if (warp < 8) {
