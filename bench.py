@@ -148,11 +148,28 @@ def make_device_inputs(w, seed, device):
     return host, dev
 
 
+def _load_reference_module():
+    """The reference's own ``universal_attention_autograd`` module when a checkout is named by the environment variable
+    UA_REF_PATH (the GPU box has none: the port is timed there), loaded by file path so that it cannot be confused with
+    this repository's module of the same name."""
+    ref = os.environ.get("UA_REF_PATH")
+    path = os.path.join(ref, "universal_attention_autograd.py") if ref else None
+    if not path or not os.path.exists(path):
+        return None
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_reference_universal_attention_autograd", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def cpu_reference_step_time(w, steps, warmup, unit_budget_s=25.0):
-    """Times the CPU oracle (port of the reference's PyTorch operator, fp32) on ONE
-    (batch, kv-head) unit of the workload, driver flow of main.py:55-62."""
+    """Times the reference's CPU path (fp32) on ONE (batch, kv-head) unit of the workload, driver flow of main.py:55-62:
+    the reference module itself when a checkout is available (kind "reference"), else the oracle port (kind "port").
+    Returns (tokens/s, seconds per unit, sample description, kind)."""
     from oracle import ua_oracle as O
     torch.set_num_threads(os.cpu_count() or 1)
+    ref = _load_reference_module()
     L = w["L"]
     scale = 1.0
     while L > 4096:          # keep the L x L plane in host memory; extrapolate with L^2
@@ -163,7 +180,13 @@ def cpu_reference_step_time(w, steps, warmup, unit_budget_s=25.0):
     times = []
     for it in range(warmup + steps):
         t0 = time.perf_counter()
-        if w["fwd_only"]:
+        if ref is not None:
+            xs = [t.clone().requires_grad_(not w["fwd_only"]) for t in ins]
+            out, denom = ref.UniversalAttention.apply(*xs)
+            merged = ref.SMVecMatMul.apply(out, denom)
+            if not w["fwd_only"]:
+                merged.pow(2).sum().backward()
+        elif w["fwd_only"]:
             O.ua_forward(*ins)
         else:
             O.driver_step(*ins)
@@ -176,20 +199,20 @@ def cpu_reference_step_time(w, steps, warmup, unit_budget_s=25.0):
     tokens_per_unit = w["L"] / w["H"]            # one (b,h) unit is 1/H of a batch row
     sample = (f"1 of {w['B'] * w['H']} (batch, kv-head) units, R={w['R']} L={L} chunk={w['c']} D={w['D']} fp32, "
               f"op+merge+loss fwd+bwd, median of {len(times)}" + (f", time scaled x{scale:g} to L={w['L']}" if scale > 1 else ""))
-    return tokens_per_unit / t_unit, t_unit, sample
+    return tokens_per_unit / t_unit, t_unit, sample, ("reference" if ref is not None else "port")
 
 
 def run_reference(args, w, rank):
     if rank != 0:
         return
-    val, t_unit, sample = cpu_reference_step_time(w, max(1, args.steps), max(0, min(args.warmup, 1)))
+    val, t_unit, sample, kind = cpu_reference_step_time(w, max(1, args.steps), max(0, min(args.warmup, 1)))
     cores = os.cpu_count() or 1
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": t_unit * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, **{k: w[k] for k in ("B", "H", "R", "L", "c", "D")}},
-        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": kind, "sample": sample},
         "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -602,8 +625,8 @@ def main():
                                              "frac": o_f / (o_ms * 1e-3) / 1e12 / peak,
                                              "traffic": NCU_DRAM_BYTES.get(args.workload, {}).get("fwd" if dom_is_bwd else "bwd")}
         if not args.no_cpu_baseline and world == 1:
-            val, t_unit, sample = cpu_reference_step_time(w, 2, 1)
-            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+            val, t_unit, sample, kind = cpu_reference_step_time(w, 2, 1)
+            line["cpu_baseline"] = {"value": val, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": kind,
                                     "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1:

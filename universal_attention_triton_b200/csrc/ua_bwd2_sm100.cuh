@@ -33,6 +33,8 @@
 // Every mbarrier wait is bounded; on a timeout the block raises a shared abort flag, every role
 // leaves, TMEM is freed and status[0] is set (status[1]: where the first block gave up).
 #pragma once
+#include <type_traits>
+
 #include "ua_bwd_sm100.cuh"
 
 namespace ua {
@@ -84,11 +86,11 @@ struct Bwd2Cfg {
   static constexpr int oXch = oHtTab + kTab * kHtTab;      // float [8][128] totals crossing the column groups
   static constexpr int oBar = oXch + 4096;
   static constexpr int oMisc = oBar + 256;      // (31 barriers of 8 bytes)
-  // per-warp scratch tiles for the column sums over the keys ([32 lanes][CG] floats each, 32 KB in all); head_dim 128
-  // has no room for them and transposes with shuffles
+  // per-warp scratch tiles for the column sums over the keys ([32 lanes][CG + 4] floats each, at most 40 KB in all);
+  // head_dim 128 has no room for them and transposes with shuffles
   static constexpr bool kScratch = (D == 64);
   static constexpr int oScr = oMisc + 256;
-  static constexpr int kSmemBytes = oScr + (kScratch ? 32768 : 0) + 1024;     // + slack to align the base to 1024 B
+  static constexpr int kSmemBytes = oScr + (kScratch ? 40960 : 0) + 1024;     // + slack to align the base to 1024 B
   // TMEM columns
   static constexpr uint32_t tDV = 0, tDK = D, tY = 2 * D;
   static constexpr uint32_t tS0 = (D == 64) ? 192 : 384, tP0 = tS0 + 64, tS1 = tS0 + 128, tP1 = tS0 + 192;
@@ -425,9 +427,8 @@ __device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t* r) {
 }
 
 // Sum over the 32 lanes of a warp of v[0..CG): afterwards every lane holds the sum of column (lane % CG).
-// With a per-warp shared-memory scratch tile ([32 lanes][CG] floats, 16-byte chunks XOR-swizzled so that both the row writes
-// and the column reads are conflict free) this costs CG/4 vector stores + 32 * CG / 32 loads and adds per lane; without one
-// it is a shuffle transpose (about 4 instructions per element).
+// With a per-warp shared-memory scratch tile this costs CG/4 vector stores + 32 loads and adds per lane; without one it is
+// a shuffle transpose (about 4 instructions per element).
 template <int CG>
 __device__ __forceinline__ float warp_colsum(float* v, float* scr, int lane) {
   if (scr == nullptr) {
@@ -445,32 +446,33 @@ __device__ __forceinline__ float warp_colsum(float* v, float* scr, int lane) {
     }
     return v[0] + __shfl_xor_sync(0xffffffffu, v[0], 16);
   }
-  constexpr int CH = CG / 4;
-  const int f = (CG == 32) ? (lane & 7) : ((lane >> 1) & 3);
-  float4* row = reinterpret_cast<float4*>(scr + lane * CG);
+  // scratch rows of CG + 4 floats: the 16-byte row writes and the column reads are both conflict free without any
+  // address swizzling, so every access is one instruction with an immediate offset
+  constexpr int PITCH = CG + 4;
+  float4* row = reinterpret_cast<float4*>(scr + lane * PITCH);
 #pragma unroll
-  for (int cidx = 0; cidx < CH; ++cidx) row[cidx ^ f] = make_float4(v[4 * cidx], v[4 * cidx + 1], v[4 * cidx + 2], v[4 * cidx + 3]);
+  for (int cidx = 0; cidx < CG / 4; ++cidx) row[cidx] = make_float4(v[4 * cidx], v[4 * cidx + 1], v[4 * cidx + 2], v[4 * cidx + 3]);
   __syncwarp();
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   if (CG == 32) {
-    const int jc = lane >> 2, jw = lane & 3;
+    const float* col = scr + lane;
 #pragma unroll
     for (int t = 0; t < 32; t += 4) {
-      a0 += scr[(t + 0) * 32 + ((jc ^ ((t + 0) & 7)) << 2) + jw];
-      a1 += scr[(t + 1) * 32 + ((jc ^ ((t + 1) & 7)) << 2) + jw];
-      a2 += scr[(t + 2) * 32 + ((jc ^ ((t + 2) & 7)) << 2) + jw];
-      a3 += scr[(t + 3) * 32 + ((jc ^ ((t + 3) & 7)) << 2) + jw];
+      a0 += col[(t + 0) * PITCH];
+      a1 += col[(t + 1) * PITCH];
+      a2 += col[(t + 2) * PITCH];
+      a3 += col[(t + 3) * PITCH];
     }
   } else {
-    const int j = lane & 15, hi = lane >> 4, jc = j >> 2, jw = j & 3;
+    // lanes 0..15 read rows 0..15, lanes 16..31 rows 16..31 starting four rows further on (opposite bank halves)
+    const int hi = lane >> 4;
+    const float* col = scr + (lane & 15) + hi * (16 + 4) * PITCH;
 #pragma unroll
     for (int t = 0; t < 16; t += 4) {
-#pragma unroll
-      for (int z = 0; z < 4; ++z) {
-        const int r = hi * 16 + ((t + z + hi) & 15);       // the two half warps read rows of opposite bank parity
-        const float val = scr[r * 16 + ((jc ^ ((r >> 1) & 3)) << 2) + jw];
-        if (z == 0) a0 += val; else if (z == 1) a1 += val; else if (z == 2) a2 += val; else a3 += val;
-      }
+      a0 += col[(((t + 0) < 12 || !hi) ? (t + 0) : (t + 0) - 16) * PITCH];
+      a1 += col[(((t + 1) < 12 || !hi) ? (t + 1) : (t + 1) - 16) * PITCH];
+      a2 += col[(((t + 2) < 12 || !hi) ? (t + 2) : (t + 2) - 16) * PITCH];
+      a3 += col[(((t + 3) < 12 || !hi) ? (t + 3) : (t + 3) - 16) * PITCH];
     }
   }
   float acc = (a0 + a1) + (a2 + a3);
@@ -562,7 +564,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   float* sDt = reinterpret_cast<float*>(c.smem + Cfg::oDt);
   float* sXch = reinterpret_cast<float*>(c.smem + Cfg::oXch);
-  float* scr = Cfg::kScratch ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * CG) : nullptr;
+  float* scr = Cfg::kScratch ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * (CG + 4)) : nullptr;
   const uint32_t swz = (uint32_t)(key & 7);
   UQ_DECL
 
@@ -624,22 +626,31 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       tc_fence_before();
       c.arrive_w(qLdDone + b);
       ++u;
-      // log-retention in log2 units: lg2(1 - min(a, hi)), a = relu(g)^(2/3) s^(1/3) t^(1/3)
+      // log-retention in log2 units: lg2(1 - min(a, hi)), a = relu(g)^(2/3) s^(1/3) t^(1/3); relu through lg2(0) = -inf
       float run = 0.f;
+      auto ell_scan = [&](auto on_diag) {
+        constexpr bool kDiag = decltype(on_diag)::value;
+        const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), one2 = make_float2(1.0f, 1.0f);
 #pragma unroll
-      for (int x = 0; x < H2; ++x) {
-        const float2 pw = make_float2(gram_pow23(__uint_as_float(gr[2 * x])), gram_pow23(__uint_as_float(gr[2 * x + 1])));
-        const float2 a = fmul2(fmul2(pw, s32), t3p[x]);
-        float e0 = lg2(1.0f - fminf(a.x, clamp_hi())), e1 = lg2(1.0f - fminf(a.y, clamp_hi()));
-        if (diag) {
-          if (qbase + 2 * x <= key) e0 = 0.f;
-          if (qbase + 2 * x + 1 <= key) e1 = 0.f;
+        for (int x = 0; x < H2; ++x) {
+          const float2 lg = make_float2(lg2(fmaxf(__uint_as_float(gr[2 * x]), 0.f)), lg2(fmaxf(__uint_as_float(gr[2 * x + 1]), 0.f)));
+          const float2 e23 = fmul2(lg, k23);
+          const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
+          const float2 a = fmul2(fmul2(pw, s32), t3p[x]);
+          const float2 om = fadd2(one2, make_float2(-fminf(a.x, clamp_hi()), -fminf(a.y, clamp_hi())));
+          float e0 = lg2(om.x), e1 = lg2(om.y);
+          if (kDiag) {
+            if (qbase + 2 * x <= key) e0 = 0.f;
+            if (qbase + 2 * x + 1 <= key) e1 = 0.f;
+          }
+          run += e0;
+          c2[x].x = run;
+          run += e1;
+          c2[x].y = run;
         }
-        run += e0;
-        c2[x].x = run;
-        run += e1;
-        c2[x].y = run;
-      }
+      };
+      if (diag) ell_scan(std::true_type{});
+      else ell_scan(std::false_type{});
       sXch[g * 128 + key] = run;
       named_bar_sync(kBarAll, kWorkers);
       float base = carry * kLog2e;
@@ -660,17 +671,41 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     UQ(0)
 
     // ================= heads =================
+    // Software pipelining inside the warp: the tail of a head (storing dS and the probabilities, the hand-over to the MMA
+    // issuers) is deferred until the TMEM loads of the NEXT unit have been issued, so that their latency runs under it.
+    // (Only where the next unit's MMAs do not wait for that hand-over: with a single (S, dP) buffer whose S columns also
+    // hold the probabilities, at head_dim 128, the tail comes first.)
+    constexpr bool kDeferTail = Cfg::kPtSeparate;
     float2 dc[H2];
 #pragma unroll
     for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);
+    uint32_t pk[H2], dk[H2];                       // the pending tail: packed probabilities and dS of head tail_hc
+    int tail_hc = -1, tail_b = 0;
+    auto flush_tail = [&]() -> bool {
+      if (tail_hc < 0) return true;
+      const int thc = tail_hc, db = thc % Cfg::kDs;
+      tail_hc = -1;
+      if (thc >= Cfg::kDs && !c.wait_w(qDsFree + db, thc / Cfg::kDs - 1)) return false;
+      store_row(c.smem + Cfg::oDs + db * 16384, dk);
+      // P^T (rows CG g + 2x, 2x + 1 as one 32-bit column): in its own buffer, or over this group's own S columns
+      if (Cfg::kPtSeparate && thc >= 2 && !c.wait_w(qPtFree + (thc & 1), (thc >> 1) - 1)) return false;
+      const uint32_t pt = Cfg::kPtSeparate ? c.tmem + Cfg::tPT + 32 * (thc & 1) + col0 / 2
+                                           : c.tmem + (tail_b ? Cfg::tS1 : Cfg::tS0) + col0;
+      if (CG == 32) tmem_st16(pt + lane_base, pk);
+      else tmem_st8(pt + lane_base, pk);
+      tc_wait_st();
+      fence_proxy_async();
+      tc_fence_before();
+      c.arrive_w(qDsReady + db);
+      return true;
+    };
     for (int r = 0; r < R; ++r, ++hc) {
-      const int b = u % Cfg::kNB, sl = hc % Cfg::kNS, db = hc % Cfg::kDs;
+      const int b = u % Cfg::kNB, sl = hc % Cfg::kNS;
       float* tabL = reinterpret_cast<float*>(c.smem + Cfg::oHeadTab + sl * 512);      // lse[64] of the head's rows (raw)
       float* tabC = tabL + 64;                                                         // g_denom[64] (or delta[64])
+      if (!kDeferTail && !flush_tail()) return;
       if (!c.wait_w(qInFull + sl, hc / Cfg::kNS)) return;                              // (the tables landed with the tiles)
-      if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 1 : 5) }
       if (!c.wait_w(qSFull + b, u / Cfg::kNB)) return;
-      if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 2 : 6) }
       UQ(1)
       tc_fence_after();
       float2 pv[H2], dp[H2];
@@ -678,12 +713,13 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         uint32_t sr[CG], dr[CG];
         tmem_ld_n<CG>(c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + lane_base + col0, sr);
         tmem_ld_n<CG>(c.tmem + (b ? Cfg::tP1 : Cfg::tP0) + lane_base + col0, dr);
+        if (kDeferTail && !flush_tail()) return;                     // the previous head's tail, under the loads
+        UQ(6)
         float2 nl[H2];
         load_pairs(tabL + col0, nl);                                 // lse of the rows
         tc_wait_ld();
         tc_fence_before();
         c.arrive_w(qLdDone + b);
-        if (lane == 0 && (warp == 8 || warp == 12)) { UQ_TRACE(u, warp == 8 ? 3 : 7) }
         ++u;
         UQ(15)
 #pragma unroll
@@ -708,7 +744,6 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       UQ(2)
       named_bar_sync(kBarGroup + g, 128);
       UQ(4)
-      uint32_t pk[H2], dk[H2];
       {
         float2 cc[H2];
         load_pairs(tabC + col0, cc);
@@ -722,26 +757,15 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           dk[x] = *reinterpret_cast<uint32_t*>(&hd);
         }
       }
-      if (hc >= Cfg::kDs && !c.wait_w(qDsFree + db, hc / Cfg::kDs - 1)) return;
+      tail_hc = hc;
+      tail_b = b;
       UQ(5)
-      store_row(c.smem + Cfg::oDs + db * 16384, dk);
-      // P^T (rows CG g + 2x, 2x + 1 as one 32-bit column): in its own buffer, or over this group's own S columns
-      {
-        if (Cfg::kPtSeparate && hc >= 2 && !c.wait_w(qPtFree + (hc & 1), (hc >> 1) - 1)) return;
-        const uint32_t pt = Cfg::kPtSeparate ? c.tmem + Cfg::tPT + 32 * (hc & 1) + col0 / 2
-                                             : c.tmem + (b ? Cfg::tS1 : Cfg::tS0) + col0;
-        if (CG == 32) tmem_st16(pt + lane_base, pk);
-        else tmem_st8(pt + lane_base, pk);
-      }
-      tc_wait_st();
-      fence_proxy_async();
-      tc_fence_before();
-      c.arrive_w(qDsReady + db);
-      UQ(6)
     }
+    if (!kDeferTail && !flush_tail()) return;
 
     // ================= decay gradient =================
     {
+      if (kDeferTail && !flush_tail()) return;     // the last head's tail
       const bool more = ht + 1 < c.nht;
       float run = 0.f;
 #pragma unroll
@@ -786,37 +810,43 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       uint32_t pk[H2];
       float dtv[CG];
       float2 dsa = make_float2(0.f, 0.f);
-      const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), km13 = make_float2(-1.0f / 3.0f, -1.0f / 3.0f);
+      auto decay_grad = [&](auto on_diag) {
+        constexpr bool kDiag = decltype(on_diag)::value;
+        const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), km13 = make_float2(-1.0f / 3.0f, -1.0f / 3.0f);
+        const float2 mone2 = make_float2(-1.0f, -1.0f);
 #pragma unroll
-      for (int x = 0; x < H2; ++x) {
-        float2 dl = fadd2(dc[x], add2);
-        if (diag) {
-          if (qbase + 2 * x <= key) dl.x = 0.f;
-          if (qbase + 2 * x + 1 <= key) dl.y = 0.f;
+        for (int x = 0; x < H2; ++x) {
+          float2 dl = fadd2(dc[x], add2);
+          if (kDiag) {
+            if (qbase + 2 * x <= key) dl.x = 0.f;
+            if (qbase + 2 * x + 1 <= key) dl.y = 0.f;
+          }
+          const float g0 = __uint_as_float(gr[2 * x]), g1 = __uint_as_float(gr[2 * x + 1]);
+          const float2 lg = make_float2(lg2(fmaxf(g0, 0.f)), lg2(fmaxf(g1, 0.f)));      // -inf for g <= 0: pw = 0
+          const float2 e23 = fmul2(lg, k23), e13 = fmul2(lg, km13);
+          const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
+          const float2 st = fmul2(pw, s32);
+          const float2 a = fmul2(st, t3p[x]);
+          const float2 am = fadd2(make_float2(fminf(fmaxf(a.x, clamp_lo_bwd()), clamp_hi()), fminf(fmaxf(a.y, clamp_lo_bwd()), clamp_hi())), mone2);
+          // d affinity = d ell / (clamp(a) - 1), zero above the clamp (the clamp passes no gradient there)
+          float2 da = fmul2(dl, make_float2(rcp_approx(am.x), rcp_approx(am.y)));
+          if (!(a.x <= clamp_hi())) da.x = 0.f;
+          if (!(a.y <= clamp_hi())) da.y = 0.f;
+          const float2 dstat = fmul2(da, pw);
+          dsa = ffma2(dstat, t3p[x], dsa);
+          const float2 dt = fmul2(dstat, s32);                       // per-(key, row) term of d static_dest
+          dtv[2 * x] = dt.x;
+          dtv[2 * x + 1] = dt.y;
+          // dG = dA s^(1/3) t^(1/3) (2/3) g^(-1/3) for g > 0
+          float2 dg = fmul2(fmul2(fmul2(da, s32), t3p[x]), fmul2(k23, make_float2(ex2(e13.x), ex2(e13.y))));
+          if (!(g0 > 0.f)) dg.x = 0.f;
+          if (!(g1 > 0.f)) dg.y = 0.f;
+          __nv_bfloat162 h = __floats2bfloat162_rn(dg.x, dg.y);
+          pk[x] = *reinterpret_cast<uint32_t*>(&h);
         }
-        const float g0 = __uint_as_float(gr[2 * x]), g1 = __uint_as_float(gr[2 * x + 1]);
-        const float2 lg = make_float2(lg2(fmaxf(g0, 0.f)), lg2(fmaxf(g1, 0.f)));      // -inf for g <= 0: pw = 0
-        const float2 e23 = fmul2(lg, k23), e13 = fmul2(lg, km13);
-        const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
-        const float2 st = fmul2(pw, s32);
-        const float2 a = fmul2(st, t3p[x]);
-        const float2 am = make_float2(fminf(fmaxf(a.x, clamp_lo_bwd()), clamp_hi()) - 1.0f,
-                                      fminf(fmaxf(a.y, clamp_lo_bwd()), clamp_hi()) - 1.0f);
-        float2 da = fmul2(dl, make_float2(rcp_approx(am.x), rcp_approx(am.y)));
-        if (!(a.x <= clamp_hi())) da.x = 0.f;
-        if (!(a.y <= clamp_hi())) da.y = 0.f;
-        const float2 dstat = fmul2(da, pw);
-        dsa = ffma2(dstat, t3p[x], dsa);
-        const float2 dt = fmul2(dstat, s32);                       // per-(key, row) term of d static_dest
-        dtv[2 * x] = dt.x;
-        dtv[2 * x + 1] = dt.y;
-        // dG = dA s^(1/3) t^(1/3) (2/3) g^(-1/3) for g > 0
-        float2 dg = fmul2(fmul2(fmul2(da, s32), t3p[x]), fmul2(k23, make_float2(ex2(e13.x), ex2(e13.y))));
-        if (!(g0 > 0.f)) dg.x = 0.f;
-        if (!(g1 > 0.f)) dg.y = 0.f;
-        __nv_bfloat162 h = __floats2bfloat162_rn(dg.x, dg.y);
-        pk[x] = *reinterpret_cast<uint32_t*>(&h);
-      }
+      };
+      if (diag) decay_grad(std::true_type{});
+      else decay_grad(std::false_type{});
       ds_acc += dsa.x + dsa.y;
       if (ht >= 1 && !c.wait_w(qDgFree, ht - 1)) return;
       store_row(c.smem + Cfg::oDg, pk);

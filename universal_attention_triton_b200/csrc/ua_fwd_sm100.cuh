@@ -449,6 +449,9 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           c.arrive_w(kOFree + sb);
         }
         if (!p.out) continue;                 // statistics-only run (the log-sum-exp for a backward that was not given one)
+#ifdef UA_EXPERIMENT_NO_OUT_STORE
+        if (cb >= 0) continue;
+#endif
         uint32_t pk[16];
         const float2 linv2 = make_float2(linv, linv);
 #pragma unroll

@@ -34,11 +34,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// The same test with a suspend-time hint: the hardware may park the thread until the phase completes or about `hint_ns`
+// have passed, instead of returning at once.  A waiter that polls with this form issues a few instructions per hint
+// period rather than a tight loop's worth, which matters when it shares a scheduler with warps that do the real work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
+
+constexpr uint32_t kWaitHintNs = 20000;      // per poll; completion of the phase ends the suspension at once
 
 // Bounded wait: gives up after about `limit_ns` of wall time (or when
 // *abort_flag in shared memory is already set); on giving up it sets the flag so
@@ -49,7 +66,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
     if ((it & 63u) == 0u) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > limit_ns) break;
@@ -71,7 +88,7 @@ __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, vo
   if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) return true;
+    if (__all_sync(0xffffffffu, mbar_try_wait_hint(bar, parity, kWaitHintNs))) return true;
     if ((it & 63u) == 0u) {
       const bool give_up = (*abort_flag != 0) || (globaltimer_ns() - t0 > limit_ns);
       if (__any_sync(0xffffffffu, give_up)) break;
