@@ -278,7 +278,7 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
 
   if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::fwd_supported(s, dtype)) {
-    ua::sm100::FwdParams fp;
+    ua::sm100::FwdParams fp{};
     fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest;
     fp.out = static_cast<bf16*>(out_cm); fp.lse = lse_cm; fp.denom = static_cast<bf16*>(denom_cm);
     fp.status = static_cast<int*>(workspace);
@@ -326,7 +326,7 @@ int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   if ((e = check_rows(s, ua::sm100::fwd_supported(s, dtype), rows))) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::FwdParams fp;
+  ua::sm100::FwdParams fp{};
   fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows;
   fp.out = static_cast<bf16*>(out_cm_rows); fp.lse = lse_cm_rows; fp.denom = static_cast<bf16*>(denom_cm_rows);
   fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
@@ -348,7 +348,7 @@ int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, const Ua
   if ((e = check_rows(s, ua::sm100::fwd_supported(s, dtype), rows))) return e;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::FwdParams fp;
+  ua::sm100::FwdParams fp{};
   fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
   fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
   fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
@@ -385,7 +385,7 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
   if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::BwdParams bp;
+  ua::sm100::BwdParams bp{};
   bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
   bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
   float* carry_tab = reinterpret_cast<float*>(ws + 256);
@@ -394,7 +394,7 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
   bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr;
+  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0; bp.gd_f32 = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
 }
 
@@ -411,12 +411,12 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::BwdParams bp;
+  ua::sm100::BwdParams bp{};
   bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows; bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
   bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
   bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
   bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0;
+  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0; bp.gd_f32 = nullptr;
   return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
 }
 
@@ -460,7 +460,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     // caller that has neither gets both from one statistics-only run of the forward kernel (no output tile is written).
     const float* lse = lse_cm;
     if (!lse || !carry_in) {
-      ua::sm100::FwdParams fp;
+      ua::sm100::FwdParams fp{};
       fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest; fp.out = nullptr; fp.denom = nullptr;
       fp.lse = lse ? nullptr : reinterpret_cast<float*>(ws + w.off_lse);
       fp.status = reinterpret_cast<int*>(ws);
@@ -471,16 +471,26 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
       if (e) return e;
       if (!lse) lse = fp.lse;
     }
+    // the kernel's producer copies rows of lse / g_denom with 16-byte bulk copies: fp32, 16-byte aligned
+    const float* gd32 = static_cast<const float*>(g_denom_cm);
+    if (g_denom_dtype != UA_F32) {
+      float* tmp = reinterpret_cast<float*>(ws + w.off_gd);
+      const size_t n_gd = BHs * s.N * (size_t)s.R * s.L;
+      widen_bf16_kernel<<<148 * 8, 256, 0, st>>>(static_cast<const bf16*>(g_denom_cm), tmp, n_gd);
+      if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+      gd32 = tmp;
+    }
+    if (!aligned16(gd32) || !aligned16(lse) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
     // Rows before a chunk (uniform softmax): their gradient is added to the accumulators by a kernel of its own.
     if (!skip_masked && s.N > 1) {
       if (ua::sm100::bwd_supported(s, dtype)) {
-        ua::sm100::BwdParams bp;
+        ua::sm100::BwdParams bp{};
         bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
         bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
         bp.carry = nullptr; bp.acc_dk = acc_dk; bp.acc_dq = acc_dq; bp.acc_dt = acc_dt;
         bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws); bp.skip_masked = 0;
         ua::sm100::whole_sequence(bp);
-        bp.acc_dv = acc_dv; bp.masked_only = 1;
+        bp.acc_dv = acc_dv; bp.masked_only = 1; bp.gd_f32 = gd32;
         e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, nullptr, false, nullptr, st);
       } else {
         const SimtCfg mcfg = simt_cfg(s.C, s.D, dtype, true);
@@ -495,17 +505,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
       }
       if (e) return e;
     }
-    // the kernel's producer copies rows of lse / g_denom with 16-byte bulk copies: fp32, 16-byte aligned
-    const float* gd32 = static_cast<const float*>(g_denom_cm);
-    if (g_denom_dtype != UA_F32) {
-      float* tmp = reinterpret_cast<float*>(ws + w.off_gd);
-      const size_t n_gd = BHs * s.N * (size_t)s.R * s.L;
-      widen_bf16_kernel<<<148 * 8, 256, 0, st>>>(static_cast<const bf16*>(g_denom_cm), tmp, n_gd);
-      if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
-      gd32 = tmp;
-    }
-    if (!aligned16(gd32) || !aligned16(lse) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
-    ua::sm100::Bwd2Params qp;
+    ua::sm100::Bwd2Params qp{};
     qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest;
     qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
@@ -778,13 +778,13 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
   if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
   float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
   if (!carry_in) {
-    ua::sm100::FwdParams fp;
+    ua::sm100::FwdParams fp{};
     fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
     fp.status = reinterpret_cast<int*>(ws); fp.carry = carry_tab;
     ua::sm100::whole_sequence(fp);
     if ((e = ua::sm100::launch_fwd<true>(s, gate_dtype, kc, nullptr, nullptr, fp, false, st))) return e;
   }
-  ua::sm100::Bwd2Params qp;
+  ua::sm100::Bwd2Params qp{};
   if (!aligned16(row_lse) || !aligned16(row_delta) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
   qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr;
   qp.lse = nullptr; qp.row_lse = row_lse; qp.row_delta = row_delta; qp.carry = carry_tab;

@@ -78,6 +78,8 @@ struct BwdParams {
   int merged;
   const float* row_lse;    // (b,h,r,L) fp32: log-sum-exp of the row over all keys
   const float* row_delta;  // (b,h,r,L) fp32: g . merged
+  const float* gd_f32;     // optional: g_denom as fp32 (16-byte aligned).  The producer then copies each masked step's 128
+                           // values next to its tiles and no worker issues a global load for them
   int masked_only;         // only the rows before the chunk (the rows that see it are another kernel's): dV_i and dK_i are
                            // ADDED to acc_dv / acc_dk, d static_src is left alone
 };
@@ -221,9 +223,11 @@ __device__ __forceinline__ void bwd_producer(const BwdCtx& c, const BwdParams& p
       MaskSlot ms = mask_slot(0, rc);                     // valid tiles: slot 0, phase rc
       if (!valid) ms = mask_slot(rc - rc0, rc0);
       if (ms.phase >= 1 && !c.wait(ms.free_bar, ms.phase - 1)) return;
-      mbar_expect_tx(c.bar(ms.full_bar), 2 * BwdCfg::kTileBytes);
+      const bool copy_gd = !valid && p.gd_f32 != nullptr;
+      mbar_expect_tx(c.bar(ms.full_bar), 2 * BwdCfg::kTileBytes + (copy_gd ? 512 : 0));
       tma_load_2d(sbase + ms.q, tmQ, 0, qrow, c.bar(ms.full_bar));
       tma_load_2d(sbase + ms.go, tmG, 0, grow, c.bar(ms.full_bar));
+      if (copy_gd) bulk_load_1d(sbase + BwdCfg::oXch + ((rc - rc0) & 1) * 512, p.gd_f32 + grow, 512, c.bar(ms.full_bar));
     }
   }
 }
@@ -888,7 +892,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
     };
     // g_denom of row `tid`, fetched two steps ahead: its latency would otherwise sit in every step's chain
     auto load_gd = [&](int m) -> float {
-      if (m >= M || part != 0) return 0.f;
+      if (m >= M || part != 0 || p.gd_f32) return 0.f;
       const size_t grow = (chunk_id * Rq + (m % R)) * p.Lr + (size_t)step_row0(m) + tid;
       return p.g_denom_is_f32 ? static_cast<const float*>(p.g_denom)[grow]
                               : __bfloat162float(static_cast<const __nv_bfloat16*>(p.g_denom)[grow]);
@@ -897,6 +901,7 @@ __device__ __forceinline__ void bwd_worker(const BwdCtx& c, const BwdParams& p, 
       const MaskSlot ms = mask_slot(m, rc0);
       if (!c.wait_w(ms.full_bar, ms.phase)) return false;   // the dO tile has landed ...
       // ... which also means that the slot was free: the MMAs of two steps ago, the readers of this slot's E, are complete
+      if (p.gd_f32) gd = reinterpret_cast<const float*>(c.smem + BwdCfg::oXch)[(m & 1) * 128 + tid];      // (came with the tiles)
       if (part == 0) *reinterpret_cast<__nv_bfloat16*>(c.smem + ms.e + tid * 128 + ((tid & 7) << 4)) = __float2bfloat16_rn(gd);
 #pragma unroll
       for (int u = 0; u < 2; ++u) {                 // 16 columns of row `tid` of dO into the column sums

@@ -265,8 +265,9 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   const int k = threadIdx.x & 127;
   const uint32_t lane_base = (uint32_t)((threadIdx.x >> 5) & 3) * 32u << 16;
   const TG* ss = static_cast<const TG*>(p.ssrc) + (size_t)c.bh * L;
-  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * p.Lr;
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * p.Lr + p.r0 + (c.j0 - p.j_begin) * 128 + k;
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + k));
+  float raw_next = Num<TG>::ld(sd);      // the gate value of the next tile is fetched one pass ahead: its latency hides behind the pass
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
   uint8_t* sCs = c.smem + Cfg::oCs;
   const size_t key_id = ((size_t)c.bh * p.s.N + c.i) * 128 + k;
@@ -278,7 +279,8 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
   for (int T = 0; T < c.ntiles; ++T) {
     const int j = c.j0 + T;
     float* t3buf = sT3 + (T & 1) * 128;
-    t3buf[k] = cbrtf(Num<TG>::ld(sd + p.r0 + (j - p.j_begin) * 128 + k));
+    t3buf[k] = cbrtf(raw_next);
+    if (T + 1 < c.ntiles) raw_next = Num<TG>::ld(sd + (T + 1) * 128);
     c.arrive_w(kT3Ready);
     if (!c.wait_w(kT3Ready, T)) return;
     UF(0)

@@ -109,7 +109,7 @@ inline bool bwd2_supported(const Shape& s, int dtype) { return dtype == UA_BF16 
 inline void whole_sequence(BwdParams& p) {
   p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
   p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0; p.lse = nullptr;
-  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr; p.masked_only = 0;
+  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr; p.masked_only = 0; p.gd_f32 = nullptr;
 }
 
 // Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
@@ -131,7 +131,7 @@ int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
     return UA_ERR_CUDA;
   }
   if (run_prepass && !p.decay_only) {
-    FwdParams fp;
+    FwdParams fp{};
     fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
     fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
     fp.j_begin = p.j_begin; fp.j_end = p.j_end; fp.Lr = p.Lr; fp.r0 = p.r0; fp.carry_in = carry_in; fp.total_out = nullptr;
