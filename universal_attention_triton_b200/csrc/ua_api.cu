@@ -79,7 +79,7 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
 }
 
 struct BwdWorkspaceTc {
-  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, off_gd, acc_bytes, total;
+  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, off_gd, off_mt, off_ksum, off_nacc, acc_bytes, total;
 };
 
 // Scratch of the tensor-core backward: status | fp32 accumulators dK, dV (the part from the rows before a chunk), dQ,
@@ -97,6 +97,10 @@ BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 256 * f, 256);
   w.off_lse = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
   w.off_gd = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
+  // per-chunk constants and partial sums of the rows-before-the-chunk kernels: M^T images, ksum, N / w / u / vbar
+  w.off_mt = o; o = align_up(o + BH * s.N * (size_t)s.D * s.D * 2, 256);
+  w.off_ksum = o; o = align_up(o + BH * s.N * (size_t)s.D * 2, 256);
+  w.off_nacc = o; o = align_up(o + BH * s.N * (size_t)(s.D + 3) * s.D * f, 256);
   w.total = o;
   return w;
 }
@@ -483,7 +487,16 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     if (!aligned16(gd32) || !aligned16(lse) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
     // Rows before a chunk (uniform softmax): their gradient is added to the accumulators by a kernel of its own.
     if (!skip_masked && s.N > 1) {
-      if (ua::sm100::bwd_supported(s, dtype)) {
+      static const bool legacy = getenv("UA_MASKED_LEGACY") != nullptr;
+      if (!legacy) {
+        ua::sm100::MaskedParams mp{};
+        mp.s = s; mp.g_denom = gd32;
+        mp.mt = reinterpret_cast<uint8_t*>(ws + w.off_mt);
+        mp.ksum = reinterpret_cast<__nv_bfloat16*>(ws + w.off_ksum);
+        mp.nacc = reinterpret_cast<float*>(ws + w.off_nacc);
+        mp.acc_dk = acc_dk; mp.acc_dv = acc_dv; mp.status = reinterpret_cast<int*>(ws);
+        e = ua::sm100::launch_masked(s, kc, vc, xq, g_out_cm, acc_dq, mp, st);
+      } else if (ua::sm100::bwd_supported(s, dtype)) {
         ua::sm100::BwdParams bp{};
         bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
         bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);

@@ -6,6 +6,7 @@
 
 #include "../../include/ua_b200.h"
 #include "ua_bwd2_sm100.cuh"
+#include "ua_bwd_masked_sm100.cuh"
 #include "ua_bwd_sm100.cuh"
 #include "ua_fwd_sm100.cuh"
 
@@ -180,6 +181,43 @@ inline int launch_bwd2(const Shape& s, int gate_dtype, bool merged, const void* 
   if (s.D == 64) return gate_dtype == UA_F32 ? UA_BWD2(64, float) : UA_BWD2(64, __nv_bfloat16);
   return gate_dtype == UA_F32 ? UA_BWD2(128, float) : UA_BWD2(128, __nv_bfloat16);
 #undef UA_BWD2
+}
+
+// Rows before a chunk, whole sequence: prep (per-chunk constants), sweep (one pass over the upstream gradient), finish
+// (dK_i, dV_i).  The caller has zeroed acc_dq / acc_dk / acc_dv.
+template <int D>
+int launch_masked_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, float* acc_dq, MaskedParams p,
+                    cudaStream_t st) {
+  using Cfg = MkCfg<D>;
+  const uint64_t BH = (uint64_t)s.B * s.H;
+  CUtensorMap tmQ, tmG, tmDQ;
+  if (!make_rows_map(&tmQ, xq, BH * s.R * s.L, D) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, D) ||
+      !make_f32_rows_map(&tmDQ, acc_dq, BH * s.R * s.L, D))
+    return UA_ERR_CUDA;
+  static const int jp_env = []() { const char* e = getenv("UA_MASKED_TILES"); return e ? atoi(e) : 0; }();
+  p.jp = jp_env > 0 ? jp_env : 8;
+  p.items_per_bh = 0;
+  for (int g = 0; g * Cfg::kG < s.N; ++g) {
+    const int jmax = (((g + 1) * Cfg::kG < s.N) ? (g + 1) * Cfg::kG : s.N) - 1;
+    p.items_per_bh += (jmax + p.jp - 1) / p.jp;
+  }
+  if (p.items_per_bh == 0) return UA_OK;
+  const auto* k16 = static_cast<const __nv_bfloat16*>(kc);
+  const auto* v16 = static_cast<const __nv_bfloat16*>(vc);
+  const int prep_smem = 2 * 128 * D * 2 + 2 * D * 4;
+  auto prep = masked_prep_kernel<D>;
+  if (cudaFuncSetAttribute(prep, cudaFuncAttributeMaxDynamicSharedMemorySize, prep_smem) != cudaSuccess) return UA_ERR_CUDA;
+  prep<<<(unsigned)(BH * s.N), 256, prep_smem, st>>>(k16, v16, p);
+  auto sweep = masked_sweep_kernel<D>;
+  if (cudaFuncSetAttribute(sweep, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
+  sweep<<<(unsigned)(BH * p.items_per_bh * Cfg::kKB), 384, Cfg::kSmemBytes, st>>>(tmQ, tmG, tmDQ, p);
+  masked_finish_kernel<D><<<(unsigned)(BH * s.N), 128, 0, st>>>(v16, p);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+inline int launch_masked(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, float* acc_dq,
+                         const MaskedParams& p, cudaStream_t st) {
+  return s.D == 64 ? launch_masked_t<64>(s, kc, vc, xq, g_out, acc_dq, p, st) : launch_masked_t<128>(s, kc, vc, xq, g_out, acc_dq, p, st);
 }
 
 }  // namespace sm100
