@@ -131,6 +131,13 @@ __global__ void widen_bf16_kernel(const bf16* __restrict__ src, float* __restric
 
 template <typename T>
 int launch_convert(const float* src, void* dst, size_t n, cudaStream_t st) {
+  if (n % 8 == 0 && n >= 8 && aligned16(src) && aligned16(dst)) {
+    const size_t n8 = n / 8;
+    int blocks = (int)((n8 + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    ua::simt::convert8_kernel<T><<<blocks, 256, 0, st>>>(reinterpret_cast<const float4*>(src), static_cast<T*>(dst), n8);
+    return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+  }
   int blocks = (int)((n + 1023) / 1024);
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
@@ -486,6 +493,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     }
     if (!aligned16(gd32) || !aligned16(lse) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
     // Rows before a chunk (uniform softmax): their gradient is added to the accumulators by a kernel of its own.
+    const float* dv_chunk = nullptr;
     if (!skip_masked && s.N > 1) {
       static const bool legacy = getenv("UA_MASKED_LEGACY") != nullptr;
       if (!legacy) {
@@ -494,7 +502,8 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
         mp.mt = reinterpret_cast<uint8_t*>(ws + w.off_mt);
         mp.ksum = reinterpret_cast<__nv_bfloat16*>(ws + w.off_ksum);
         mp.nacc = reinterpret_cast<float*>(ws + w.off_nacc);
-        mp.acc_dk = acc_dk; mp.acc_dv = acc_dv; mp.status = reinterpret_cast<int*>(ws);
+        mp.acc_dk = acc_dk; mp.status = reinterpret_cast<int*>(ws);
+        dv_chunk = mp.nacc + (size_t)(s.D + 1) * s.D;
         e = ua::sm100::launch_masked(s, kc, vc, xq, g_out_cm, acc_dq, mp, st);
       } else if (ua::sm100::bwd_supported(s, dtype)) {
         ua::sm100::BwdParams bp{};
@@ -523,7 +532,8 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
-    qp.acc_dv_in = (!skip_masked && s.N > 1) ? acc_dv : nullptr;
+    qp.acc_dv_in = (!skip_masked && s.N > 1 && !dv_chunk) ? acc_dv : nullptr;
+    qp.dv_chunk = dv_chunk; qp.dv_chunk_stride = (s.D + 3) * s.D;
     qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
     qp.trace = nullptr;
 #ifdef UA_PROFILE_BWD2

@@ -53,6 +53,8 @@ struct Bwd2Params {
   float* acc_dq;             // (b*h, r, L, D) fp32, likewise
   float* acc_dt;             // (b*h, L) fp32, zeroed
   const float* acc_dv_in;    // optional (b*h, L, D) fp32: added to dV_i before it is written (masked-block part)
+  const float* dv_chunk;     // optional: row dv_chunk[chunk * dv_chunk_stride + d] / 128 is added to every key's dV_i (the
+  int dv_chunk_stride;       // masked-block part when it comes from the kernels of the rows before a chunk)
   __nv_bfloat16* dvc;
   void* dss;
   int* status;
@@ -378,7 +380,9 @@ __device__ __forceinline__ void bwd2_back(const Bwd2Ctx& c, const Bwd2Params& p,
         if (yc >= 1 && !c.wait(qYFree, yc - 1)) return;
         UQ(2)
         tc_fence_after();
+#ifndef UA_EXP_NO_DQ_MMA
         mma_rows_out(desc_from_lo(desc_lo(dsb, 16384)));                                  // dQ_rj = dS^T K_i
+#endif
         ++yc;
         tc_commit(c.bar(qYFull));
         tc_commit(c.bar(qDsFree + db));
@@ -521,14 +525,20 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
           tc_fence_before();
           c.arrive_w(qYFree);
         }
+#ifndef UA_EXP_NO_DRAIN
         uint8_t* box = sStage + hb * 8192 + row * 128;
 #pragma unroll
         for (int x = 0; x < 8; ++x)
           *reinterpret_cast<uint4*>(box + ((((uint32_t)x ^ swz) & 7) << 4)) = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
+#endif
       }
       fence_proxy_async();
       named_bar_sync(kBarDrain, 64);
+#ifdef UA_EXP_NO_DRAIN
+      if (false) {
+#else
       if (leader) {
+#endif
         const CUtensorMap* tm = (r < R) ? tmDQ : tmDK;
         const int y = (r < R) ? (c.bh * R + r) * L + row0 : c.bh * L + row0;
 #pragma unroll
@@ -738,7 +748,11 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           e[2 * x] = ev.x;
           e[2 * x + 1] = ev.y;
         }
+#ifdef UA_EXP_NO_COLSUM
+        const float part = e[lane & 1];
+#else
         const float part = warp_colsum<CG>(e, scr, lane);            // this warp's 32 keys, column col0 + lane % CG
+#endif
         if (helper) atomicAdd(tabC + col0 + lane, -part);           // g_denom - sum_k P dP, in place
       }
       UQ(2)
@@ -883,6 +897,17 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         o[4 * x + 1] = __float_as_uint(__uint_as_float(o[4 * x + 1]) + ev.y);
         o[4 * x + 2] = __float_as_uint(__uint_as_float(o[4 * x + 2]) + ev.z);
         o[4 * x + 3] = __float_as_uint(__uint_as_float(o[4 * x + 3]) + ev.w);
+      }
+    }
+    if (p.dv_chunk) {
+      const float4* extra = reinterpret_cast<const float4*>(p.dv_chunk + ((size_t)c.bh * p.s.N + c.i) * p.dv_chunk_stride + d0);
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        const float4 ev = extra[x];
+        o[4 * x] = __float_as_uint(fmaf(ev.x, 1.0f / 128.0f, __uint_as_float(o[4 * x])));
+        o[4 * x + 1] = __float_as_uint(fmaf(ev.y, 1.0f / 128.0f, __uint_as_float(o[4 * x + 1])));
+        o[4 * x + 2] = __float_as_uint(fmaf(ev.z, 1.0f / 128.0f, __uint_as_float(o[4 * x + 2])));
+        o[4 * x + 3] = __float_as_uint(fmaf(ev.w, 1.0f / 128.0f, __uint_as_float(o[4 * x + 3])));
       }
     }
     uint32_t pk[8];

@@ -11,11 +11,11 @@
 // The sweep kernel in the middle is a stream over the upstream gradient, read exactly once from HBM: per row tile and
 // head it loads Q_rj, and for each of the G chunks of its group the gradient tile g (the only large operand), and issues
 //   Y    (+)= g Mt_c^T                 [128 rows][64]   summed over the group's chunks in TMEM, then ONE reduce-add into dQ
-//   Nt_c (+)= [Q | E]^T g              [64 + 16][D]     lanes 0..63: N_c^T, lane 72: u_c   (E: see below)
-//   Wt   (+)= [Q | E]^T E              [64 + 16][16]    column c of lanes 0..63: w_c
-//   Y      = E Ks                      the rank-1 terms gd_c (x) ksum_c / 128 of all chunks in one K = 16 MMA
-// E is a [128 rows][64] bf16 tile beside each Q tile: column c < G holds gd of chunk c for this (row tile, head), column 8
-// holds ones, the rest zeros; it is written by four warps from rows of g_denom that arrive with the producer's copies.
+//   Nt_c (+)= [Q | O]^T g              [64 + 64][D]     lanes 0..63: N_c^T, lane 64: u_c  (O: a constant tile, column 0 = ones)
+// A tcgen05.mma of M = 128, K = 16 takes about 60 cycles at N = 64 and at N = 128 alike (measured), so the N^T products
+// of neighbouring chunks share one instruction: their gradient tiles sit side by side in a 32 KB slot and form one
+// MN-major B operand of N = 128.  The terms in gd stay on the CUDA cores, in fp32: four warps accumulate
+// w_c += gd_c^T Q_rj from the Q tile in shared memory, and the drain warps add gd_c (x) ksum_c / 128 to Y on its way out.
 // head_dim 128 runs as two blocks per work item, one per 64-wide half of the output columns of Y / lanes of Nt.
 // A work item is (batch*head, group of G chunks, range of row tiles); partial N / w / u leave as fp32 global adds.
 #pragma once
@@ -31,7 +31,6 @@ struct MaskedParams {
   __nv_bfloat16* ksum;           // (b*h*n, D): column sums of K_i / 128
   float* nacc;                   // (b*h*n, D + 3, D) fp32: rows 0..D-1 = N^T[d'][d], row D = w[d'], row D + 1 = u[d], row D + 2 = vbar[d]
   float* acc_dk;                 // (b*h*L, D) fp32, added to
-  float* acc_dv;                 // (b*h*L, D) fp32, written (rows of chunk 0 untouched)
   int* status;
   int jp;                        // row tiles per work item
   int items_per_bh;              // sum over groups of ceil(row tiles before the group's last chunk / jp)
@@ -43,26 +42,30 @@ template <int D>
 struct MkCfg {
   static constexpr int kKB = D / 64;
   static constexpr int kG = 256 / D;                       // chunks per group: their N^T accumulators fill 256 TMEM columns
-  static constexpr int kStages = (D == 64) ? 3 : 2;        // ring of upstream-gradient tiles
+  static constexpr int kPer = 128 / D;                     // gradient tiles per 32 KB slot (one N = 128 operand)
+  static constexpr int kUnits = kG / kPer;                 // slots per step when every chunk of the group is active
+  static constexpr int kSlots = 3;
   static constexpr int kDoBytes = kKB * 16384;
-  static constexpr int kStageBufs = (D == 64) ? 2 : 1;     // staging tiles of the dQ reduce-add
+  static constexpr int kAhead = (D == 64) ? 12 : 6;        // gradient tiles requested into L2 ahead of the ring
   static constexpr int kMtBytes = kKB * 8192;              // one half (64 rows d') of a chunk's M^T image
-  static constexpr int oDo = 0;
-  static constexpr int oQE = oDo + kStages * kDoBytes;     // 2 x { Q [128][64] | E [128][64] }
-  static constexpr int oMt = oQE + 2 * 32768;
-  static constexpr int oKs = oMt + kG * kMtBytes;          // [64 d'][64] bf16, column c = ksum_c / 128
-  static constexpr int oStage = oKs + 8192;                // kStageBufs x two [128][32] fp32 boxes
-  static constexpr int oGd = oStage + kStageBufs * 32768;  // 2 x kG x float[128]: g_denom rows of a step
-  static constexpr int oBar = oGd + 2 * kG * 512;
+  static constexpr int oSlot = 0;
+  static constexpr int oQ = oSlot + kSlots * 32768;        // 2 x Q [128][64]
+  static constexpr int oOnes = oQ + 2 * 16384;             // [128][64] bf16: column 0 = 1, the rest 0 (after the Q tiles: the
+                                                           // second 64 lanes of the [Q | O] operand, reached through LBO)
+  static constexpr int oMt = oOnes + 16384;
+  static constexpr int oStage = oMt + kG * kMtBytes;       // two [128][32] fp32 boxes
+  static constexpr int oGd = oStage + 32768;               // 2 x kG x float[128]: g_denom rows of a step
+  static constexpr int oKs = oGd + 2 * kG * 512;           // float [64][kG]: ksum_c / 128 of this block's 64 output columns
+  static constexpr int oBar = oKs + 64 * kG * 4;
   static constexpr int oMisc = oBar + 256;
   static constexpr int kSmemBytes = oMisc + 64 + 1024;     // + slack to align the base to 1024 B
-  static constexpr uint32_t tY0 = 0, tY1 = 64, tN = 128, tW = 128 + kG * D;
-  static_assert(tW + 16 <= 512, "TMEM budget");
+  static constexpr uint32_t tY0 = 0, tY1 = 64, tN = 128;
+  static_assert(tN + kG * D <= 512, "TMEM budget");
   static_assert(kSmemBytes <= 227 * 1024, "shared memory budget");
 };
 
 enum MkBar {
-  mMtFull = 0, mQFull = 1, mQEFree = 3, mEReady = 5, mYFull = 7, mYFree = 9, mDone = 11, mDoFull = 12, mDoFree = 15, mNumBars = 18
+  mMtFull = 0, mQFull = 1, mQFree = 3, mYFull = 5, mYFree = 7, mDone = 9, mSlotFull = 10, mSlotFree = 13, mNumBars = 16
 };
 
 struct MkCtx {
@@ -121,39 +124,53 @@ __global__ void __launch_bounds__(256) masked_prep_kernel(const __nv_bfloat16* _
   }
   __syncthreads();
   uint8_t* img = p.mt + chunk * (size_t)(D * D * 2);
-  for (int o = t; o < D * D / 8; o += 256) {
-    const int dp = o / (D / 8), d0 = (o % (D / 8)) * 8;      // row d' of M^T, eight columns d0..d0+7
-    float acc[8];
+  // each thread: four rows d' (dp0 .. dp0 + 3) x eight columns d0 .. d0 + 7 of M^T, so that a value tile row is converted once per four rows
+  for (int o = t; o < D * D / 32; o += 256) {
+    const int dp0 = (o / (D / 8)) * 4, d0 = (o % (D / 8)) * 8;
+    float acc[4][8];
 #pragma unroll
-    for (int x = 0; x < 8; ++x) acc[x] = 0.f;
-#pragma unroll 4
+    for (int y = 0; y < 4; ++y)
+#pragma unroll
+      for (int x = 0; x < 8; ++x) acc[y][x] = 0.f;
+#pragma unroll 2
     for (int k = 0; k < 128; ++k) {
-      const float kv = __bfloat162float(sK[k * D + dp]);
+      const uint2 kraw = *reinterpret_cast<const uint2*>(sK + k * D + dp0);
+      const float kv[4] = {__uint_as_float(kraw.x << 16), __uint_as_float(kraw.x & 0xffff0000u), __uint_as_float(kraw.y << 16),
+                           __uint_as_float(kraw.y & 0xffff0000u)};
       const uint4 raw = *reinterpret_cast<const uint4*>(sV + k * D + d0);
       const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+      float vv[8];
 #pragma unroll
       for (int x = 0; x < 4; ++x) {
-        const __nv_bfloat162 hv = *reinterpret_cast<const __nv_bfloat162*>(&rw[x]);
-        acc[2 * x] = fmaf(kv, __bfloat162float(hv.x), acc[2 * x]);
-        acc[2 * x + 1] = fmaf(kv, __bfloat162float(hv.y), acc[2 * x + 1]);
+        vv[2 * x] = __uint_as_float(rw[x] << 16);
+        vv[2 * x + 1] = __uint_as_float(rw[x] & 0xffff0000u);
       }
-    }
-    const float ks = sSum[dp] * (1.0f / 128.0f);
-    uint32_t w4[4];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      __nv_bfloat162 hh = __floats2bfloat162_rn((acc[2 * x] - ks * sSum[D + d0 + 2 * x]) * (1.0f / 128.0f),
-                                                (acc[2 * x + 1] - ks * sSum[D + d0 + 2 * x + 1]) * (1.0f / 128.0f));
-      w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+      for (int y = 0; y < 4; ++y)
+#pragma unroll
+        for (int x = 0; x < 8; ++x) acc[y][x] = fmaf(kv[y], vv[x], acc[y][x]);
     }
-    const int half = dp >> 6, row = dp & 63, box = d0 >> 6, chunk16 = (d0 & 63) >> 3;
-    *reinterpret_cast<uint4*>(img + ((size_t)(half * (D / 64) + box) * 64 + row) * 128 + (((chunk16 ^ row) & 7) << 4)) =
-        make_uint4(w4[0], w4[1], w4[2], w4[3]);
+#pragma unroll
+    for (int y = 0; y < 4; ++y) {
+      const int dp = dp0 + y;
+      const float ks = sSum[dp] * (1.0f / 128.0f);
+      uint32_t w4[4];
+#pragma unroll
+      for (int x = 0; x < 4; ++x) {
+        __nv_bfloat162 hh = __floats2bfloat162_rn((acc[y][2 * x] - ks * sSum[D + d0 + 2 * x]) * (1.0f / 128.0f),
+                                                  (acc[y][2 * x + 1] - ks * sSum[D + d0 + 2 * x + 1]) * (1.0f / 128.0f));
+        w4[x] = *reinterpret_cast<uint32_t*>(&hh);
+      }
+      const int half = dp >> 6, row = dp & 63, box = d0 >> 6, chunk16 = (d0 & 63) >> 3;
+      *reinterpret_cast<uint4*>(img + ((size_t)(half * (D / 64) + box) * 64 + row) * 128 + (((chunk16 ^ row) & 7) << 4)) =
+          make_uint4(w4[0], w4[1], w4[2], w4[3]);
+    }
   }
 }
 
 // ---------------------------------------------------------------- finish kernel --
-// One block per chunk i >= 1 (thread = key): dK_i += ((V_i - vbar) N_i + 1 (x) w_i) / 128,  dV_i = 1 (x) u_i / 128.
+// One block per chunk i >= 1 (thread = key): dK_i += ((V_i - vbar) N_i + 1 (x) w_i) / 128.  (dV_i = 1 (x) u_i / 128 is the same row
+// for every key: the main backward kernel adds it from the chunk's u row when it writes dV_i.)
 template <int D>
 __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16* __restrict__ vc, MaskedParams p) {
   __shared__ __align__(16) float sN[32 * D];          // 32 rows d' of N^T at a time
@@ -163,7 +180,6 @@ __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16*
   if (chunk % N == 0) return;           // no rows before the first chunk
   const int key = threadIdx.x;
   const float* nacc = p.nacc + chunk * (size_t)kNaccRows<D>() * D;
-  const float* u = nacc + (size_t)(D + 1) * D;
   const float* vbar = nacc + (size_t)(D + 2) * D;
   float vcen[D];
   {
@@ -182,11 +198,6 @@ __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16*
   }
   for (int x = key; x < D; x += 128) sW[x] = nacc[(size_t)D * D + x];
   float* dk = p.acc_dk + (chunk * 128 + key) * D;
-  float* dv = p.acc_dv + (chunk * 128 + key) * D;
-#pragma unroll 4
-  for (int x = 0; x < D; x += 4)
-    *reinterpret_cast<float4*>(dv + x) = make_float4(u[x] * (1.0f / 128.0f), u[x + 1] * (1.0f / 128.0f), u[x + 2] * (1.0f / 128.0f),
-                                                     u[x + 3] * (1.0f / 128.0f));
 #pragma unroll 1
   for (int blk = 0; blk < D / 32; ++blk) {
     __syncthreads();
@@ -196,9 +207,12 @@ __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16*
     for (int q = 0; q < 32; q += 4) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int d = 0; d < D; ++d) {
+      for (int d = 0; d < D; d += 4) {
 #pragma unroll
-        for (int x = 0; x < 4; ++x) acc[x] = fmaf(vcen[d], sN[(q + x) * D + d], acc[x]);
+        for (int x = 0; x < 4; ++x) {
+          const float4 nv = *reinterpret_cast<const float4*>(sN + (q + x) * D + d);
+          acc[x] = fmaf(vcen[d], nv.x, fmaf(vcen[d + 1], nv.y, fmaf(vcen[d + 2], nv.z, fmaf(vcen[d + 3], nv.w, acc[x]))));
+        }
       }
       float4* dst = reinterpret_cast<float4*>(dk + blk * 32 + q);
       float4 cur = *dst;
@@ -212,6 +226,29 @@ __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16*
 }
 
 // ----------------------------------------------------------------- sweep kernel --
+// Optional phase timing (compile with -DUA_PROFILE_MK=<block>): each role of that block accumulates clock64() deltas per
+// phase and stores them after the status words.
+#ifdef UA_PROFILE_MK
+#define MQ_DECL long long mq_t = clock64(), mq_acc[4] = {0, 0, 0, 0};
+#define MQ(idx) { long long now_ = clock64(); mq_acc[idx] += now_ - mq_t; mq_t = now_; }
+#define MQ_STORE(base) if (blockIdx.x == UA_PROFILE_MK) { for (int z = 0; z < 4; ++z) reinterpret_cast<long long*>(p.status)[2 + (base) + z] = mq_acc[z]; }
+#else
+#define MQ_DECL
+#define MQ(idx)
+#define MQ_STORE(base)
+#endif
+
+// Slot unit u of a step: the chunks [u kPer, (u + 1) kPer) of the group that have the step's row tile before them.
+template <int D>
+struct MkUnit {
+  int lo, hi;
+  __device__ __forceinline__ MkUnit(int u, int c0, int chi) {
+    lo = max(u * MkCfg<D>::kPer, c0);
+    hi = min((u + 1) * MkCfg<D>::kPer, chi);
+  }
+  __device__ __forceinline__ bool active() const { return lo < hi; }
+};
+
 template <int D>
 __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& p, const CUtensorMap* tmQ, const CUtensorMap* tmG) {
   using Cfg = MkCfg<D>;
@@ -225,28 +262,54 @@ __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& 
                    p.mt + ((size_t)c.bh * N + c.i0 + cc) * (size_t)(D * D * 2) + (size_t)c.h * Cfg::kMtBytes, Cfg::kMtBytes,
                    c.bar(mMtFull));
   }
-  int s = 0, dc = 0;
+  // The gradient tiles are asked into L2 kAhead tiles before their turn in the shared-memory ring: the ring alone (a few
+  // tiles per SM) does not cover the latency of HBM at full bandwidth.
+  int pj = c.jlo, pr = 0, pc = c.clo(c.jlo);
+  auto prefetch_next = [&]() {
+    if (pj >= c.jhi) return;
+#pragma unroll
+    for (int b = 0; b < Cfg::kKB; ++b)
+      tma_prefetch_2d(tmG, 64 * b, (int)((((size_t)c.bh * N + c.i0 + pc) * R + pr) * L + (size_t)pj * 128));
+    if (++pc >= c.chi) {
+      if (++pr >= R) { pr = 0; ++pj; }
+      pc = c.clo(pj);
+    }
+  };
+  for (int x = 0; x < Cfg::kAhead; ++x) prefetch_next();
+  int s = 0, uc = 0;
+  MQ_DECL
   for (int j = c.jlo; j < c.jhi; ++j) {
     const int c0 = c.clo(j);
     for (int r = 0; r < R; ++r, ++s) {
       const int qs = s & 1;
-      if (s >= 2 && !c.wait(mQEFree + qs, s / 2 - 1)) return;
+      MQ(0)
+      if (s >= 2 && !c.wait(mQFree + qs, s / 2 - 1)) return;
+      MQ(1)
       mbar_expect_tx(c.bar(mQFull + qs), 16384u + (uint32_t)(c.chi - c0) * 512u);
-      tma_load_2d(sb + Cfg::oQE + qs * 32768, tmQ, 64 * c.h, (c.bh * R + r) * L + j * 128, c.bar(mQFull + qs));
+      tma_load_2d(sb + Cfg::oQ + qs * 16384, tmQ, 64 * c.h, (c.bh * R + r) * L + j * 128, c.bar(mQFull + qs));
       for (int cc = c0; cc < c.chi; ++cc)
         bulk_load_1d(sb + Cfg::oGd + (qs * Cfg::kG + cc) * 512,
                      p.g_denom + (((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)j * 128, 512, c.bar(mQFull + qs));
-      for (int cc = c0; cc < c.chi; ++cc, ++dc) {
-        const int st = dc % Cfg::kStages;
-        if (dc >= Cfg::kStages && !c.wait(mDoFree + st, dc / Cfg::kStages - 1)) return;
-        mbar_expect_tx(c.bar(mDoFull + st), Cfg::kDoBytes);
+      for (int u = 0; u < Cfg::kUnits; ++u) {
+        const MkUnit<D> un(u, c0, c.chi);
+        if (!un.active()) continue;
+        const int sl = uc % Cfg::kSlots;
+        MQ(0)
+        if (uc >= Cfg::kSlots && !c.wait(mSlotFree + sl, uc / Cfg::kSlots - 1)) return;
+        MQ(2)
+        ++uc;
+        mbar_expect_tx(c.bar(mSlotFull + sl), (uint32_t)(un.hi - un.lo) * Cfg::kDoBytes);
+        for (int cc = un.lo; cc < un.hi; ++cc) {
 #pragma unroll
-        for (int b = 0; b < Cfg::kKB; ++b)
-          tma_load_2d(sb + Cfg::oDo + st * Cfg::kDoBytes + b * 16384, tmG, 64 * b,
-                      (int)((((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)j * 128), c.bar(mDoFull + st));
+          for (int b = 0; b < Cfg::kKB; ++b)
+            tma_load_2d(sb + Cfg::oSlot + sl * 32768 + (cc - u * Cfg::kPer) * Cfg::kDoBytes + b * 16384, tmG, 64 * b,
+                        (int)((((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)j * 128), c.bar(mSlotFull + sl));
+          prefetch_next();
+        }
       }
     }
   }
+  MQ_STORE(8)
 }
 
 template <int D>
@@ -255,79 +318,123 @@ __device__ __forceinline__ void mk_issuer(const MkCtx& c, const MaskedParams& p)
   const int R = p.s.R;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_y = idesc_bf16(128, 64, 0, 0);       // rows x 64: A K-major, B K-major
-  constexpr uint32_t id_n = idesc_bf16(128, D, 1, 1);        // [Q | E]^T g: both MN-major
-  constexpr uint32_t id_w = idesc_bf16(128, 16, 1, 1);       // [Q | E]^T E
-  const uint64_t kKs = desc_from_lo(desc_lo(sb + Cfg::oKs, 16));
   if (!c.wait(mMtFull, 0)) return;
-  int s = 0, dc = 0;
+  int s = 0, uc = 0;
+  MQ_DECL
   for (int j = c.jlo; j < c.jhi; ++j) {
     const int c0 = c.clo(j);
     for (int r = 0; r < R; ++r, ++s) {
       const int qs = s & 1;
-      const uint32_t q_addr = sb + Cfg::oQE + qs * 32768, e_addr = q_addr + 16384;
-      if (!c.wait(mQFull + qs, s / 2) || !c.wait(mEReady + qs, s / 2)) return;
+      const uint32_t q_addr = sb + Cfg::oQ + qs * 16384;
+      MQ(3)
+      if (!c.wait(mQFull + qs, s / 2)) return;
+      MQ(0)
       if (s >= 2 && !c.wait(mYFree + qs, s / 2 - 1)) return;
+      MQ(1)
       tc_fence_after();
       const uint32_t Y = c.tmem + (qs ? Cfg::tY1 : Cfg::tY0);
-      const uint64_t mQE = desc_from_lo(desc_lo(q_addr, 16384));     // [K = rows][M = 64 of Q, then 64 of E]
-      const uint64_t mE = desc_from_lo(desc_lo(e_addr, 16384)), kE = desc_from_lo(desc_lo(e_addr, 16));
-      mma_ss(Y, kE, kKs, id_y, 0);                                   // Y = sum_c gd_c (x) ksum_c / 128
-      mma4_ss(c.tmem + Cfg::tW, mQE, mE, 128, 128, id_w, s > 0);     // Wt += [Q | E]^T E
-      mma4_ss(c.tmem + Cfg::tW, mQE + 512, mE + 512, 128, 128, id_w, 1);
-      for (int cc = c0; cc < c.chi; ++cc, ++dc) {
-        const int st = dc % Cfg::kStages;
-        if (!c.wait(mDoFull + st, dc / Cfg::kStages)) return;
+      // [K = rows][M = the 64 columns of Q, then the 64 columns of the ones tile]
+      const uint64_t mQO = desc_from_lo(desc_lo(q_addr, (sb + Cfg::oOnes) - q_addr));
+      uint32_t have_y = 0;
+      for (int u = 0; u < Cfg::kUnits; ++u) {
+        const MkUnit<D> un(u, c0, c.chi);
+        if (!un.active()) continue;
+        const int sl = uc % Cfg::kSlots;
+        MQ(3)
+        if (!c.wait(mSlotFull + sl, uc / Cfg::kSlots)) return;
+        MQ(2)
+        ++uc;
         tc_fence_after();
-        const uint32_t g_addr = sb + Cfg::oDo + st * Cfg::kDoBytes;
+        const uint32_t slot = sb + Cfg::oSlot + sl * 32768;
+        for (int cc = un.lo; cc < un.hi; ++cc) {                     // Y += g Mt_c^T
+          const uint32_t g_addr = slot + (cc - u * Cfg::kPer) * Cfg::kDoBytes;
 #pragma unroll
-        for (int b = 0; b < Cfg::kKB; ++b)                           // Y += g Mt_c^T
-          mma4_ss(Y, desc_from_lo(desc_lo(g_addr + b * 16384, 16)), desc_from_lo(desc_lo(sb + Cfg::oMt + cc * Cfg::kMtBytes + b * 8192, 16)),
-                  2, 2, id_y, 1);
-        const uint64_t mG = desc_from_lo(desc_lo(g_addr, 16384));
-        const uint32_t Nt = c.tmem + Cfg::tN + cc * D;
-        mma4_ss(Nt, mQE, mG, 128, 128, id_n, s > 0);                 // Nt_c += [Q | E]^T g
-        mma4_ss(Nt, mQE + 512, mG + 512, 128, 128, id_n, 1);
-        tc_commit(c.bar(mDoFree + st));
+          for (int b = 0; b < Cfg::kKB; ++b) {
+            mma4_ss(Y, desc_from_lo(desc_lo(g_addr + b * 16384, 16)), desc_from_lo(desc_lo(sb + Cfg::oMt + cc * Cfg::kMtBytes + b * 8192, 16)),
+                    2, 2, id_y, have_y);
+            have_y = 1;
+          }
+        }
+        // Nt_lo.. += [Q | O]^T [g_lo | ..]: the unit's tiles as one MN-major operand, 64-column groups 16 KB apart
+        const uint64_t mG = desc_from_lo(desc_lo(slot + (un.lo - u * Cfg::kPer) * Cfg::kDoBytes, 16384));
+        const uint32_t id_n = idesc_bf16(128, (un.hi - un.lo) * D, 1, 1);
+        const uint32_t Nt = c.tmem + Cfg::tN + un.lo * D;
+        mma4_ss(Nt, mQO, mG, 128, 128, id_n, s > 0);
+        mma4_ss(Nt, mQO + 512, mG + 512, 128, 128, id_n, 1);
+        tc_commit(c.bar(mSlotFree + sl));
       }
       tc_commit(c.bar(mYFull + qs));
-      tc_commit(c.bar(mQEFree + qs));
+      tc_commit(c.bar(mQFree + qs));
     }
   }
   tc_commit(c.bar(mDone));
+  MQ(3)
+  MQ_STORE(0)
 }
 
-// Four warps, thread = row: column c of E <- g_denom of chunk c (bf16), for the chunks that have this row tile before them.
+// Four warps on the CUDA cores: w_c[d'] += sum_rows gd_c[row] Q[row][d'] for the group's chunks, from the Q tile in shared
+// memory.  Warp = 16 of the 64 columns, lane = row (four passes of 32 rows): every shared-memory access is conflict free
+// and nothing is broadcast, so the warps take little of the bandwidth that the MMA operands need.  The sums stay in
+// registers over the whole work item and are added up over the lanes once, at its end.
 template <int D>
-__device__ __forceinline__ void mk_gate_writer(const MkCtx& c, const MaskedParams& p) {
+__device__ __forceinline__ void mk_gate_sums(const MkCtx& c, const MaskedParams& p) {
   using Cfg = MkCfg<D>;
-  const int R = p.s.R;
-  const int row = threadIdx.x & 127;
+  const int R = p.s.R, N = p.s.N;
+  const int t = threadIdx.x & 127, lane = t & 31, w = t >> 5;
+  float acc[Cfg::kG * 16];
+#pragma unroll
+  for (int x = 0; x < Cfg::kG * 16; ++x) acc[x] = 0.f;
   int s = 0;
+  MQ_DECL
   for (int j = c.jlo; j < c.jhi; ++j) {
     const int c0 = c.clo(j);
     for (int r = 0; r < R; ++r, ++s) {
       const int qs = s & 1;
+      MQ(1)
       if (!c.wait_w(mQFull + qs, s / 2)) return;
-      const float* gd = reinterpret_cast<const float*>(c.smem + Cfg::oGd + qs * Cfg::kG * 512) + row;
-      uint32_t w[Cfg::kG / 2];
+      MQ(0)
+      const uint8_t* q = c.smem + Cfg::oQ + qs * 16384;
+      const float* gd = reinterpret_cast<const float*>(c.smem + Cfg::oGd + qs * Cfg::kG * 512);
+#pragma unroll 1
+      for (int pass = 0; pass < 4; ++pass) {
+        const int row = pass * 32 + lane;
+        float g[Cfg::kG];
 #pragma unroll
-      for (int x = 0; x < Cfg::kG / 2; ++x) {
-        const float a = (2 * x >= c0 && 2 * x < c.chi) ? gd[(2 * x) * 128] : 0.f;
-        const float b = (2 * x + 1 >= c0 && 2 * x + 1 < c.chi) ? gd[(2 * x + 1) * 128] : 0.f;
-        __nv_bfloat162 hh = __floats2bfloat162_rn(a, b);
-        w[x] = *reinterpret_cast<uint32_t*>(&hh);
+        for (int cc = 0; cc < Cfg::kG; ++cc)      // (chunks that do not have this row tile before them: their rows of the table are stale)
+          g[cc] = (cc >= c0 && cc < c.chi) ? gd[cc * 128 + row] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(q + row * 128 + ((((2 * w + k) ^ row) & 7) << 4));
+          const uint32_t rw[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const float q0 = __uint_as_float(rw[x] << 16), q1 = __uint_as_float(rw[x] & 0xffff0000u);
+#pragma unroll
+            for (int cc = 0; cc < Cfg::kG; ++cc) {
+              acc[cc * 16 + 8 * k + 2 * x] = fmaf(g[cc], q0, acc[cc * 16 + 8 * k + 2 * x]);
+              acc[cc * 16 + 8 * k + 2 * x + 1] = fmaf(g[cc], q1, acc[cc * 16 + 8 * k + 2 * x + 1]);
+            }
+          }
+        }
       }
-      uint8_t* dst = c.smem + Cfg::oQE + qs * 32768 + 16384 + row * 128 + ((row & 7) << 4);
-      if (Cfg::kG == 4) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[Cfg::kG / 2 - 1]);
-      else *reinterpret_cast<uint32_t*>(dst) = w[0];
-      fence_proxy_async();
-      c.arrive_w(mEReady + qs);
+      c.arrive_w(mQFree + qs);
     }
+  }
+#ifdef UA_PROFILE_MK
+  if (t == 0) { MQ(1) MQ_STORE(12) }
+#endif
+  const int c0 = c.clo(c.jlo);
+#pragma unroll
+  for (int grp = 0; grp < Cfg::kG / 2; ++grp) {
+    const float tot = warp_transpose_reduce(acc + 32 * grp, lane);      // lane l: sum over the lanes of value 32 grp + l
+    const int cc = 2 * grp + (lane >> 4);
+    if (cc >= c0 && cc < c.chi)
+      atomicAdd(p.nacc + ((size_t)c.bh * N + c.i0 + cc) * (size_t)kNaccRows<D>() * D + (size_t)D * D + 64 * c.h + 16 * w + (lane & 15), tot);
   }
 }
 
-// Four warps (TMEM lane quadrant = warp % 4): Y of each step -> staging tile -> TMA reduce-add into the dQ accumulator;
-// after the last step the group's N^T / w / u partial sums -> global adds.
+// Four warps (TMEM lane quadrant = warp % 4): Y of each step, plus sum_c gd_c (x) ksum_c / 128 -> staging tile -> TMA
+// reduce-add into the dQ accumulator; after the last step the group's N^T / u partial sums -> global adds.
 template <int D>
 __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, const CUtensorMap* tmDQ) {
   using Cfg = MkCfg<D>;
@@ -337,19 +444,26 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
   const bool leader = (warp == 4 && lane == 0);
   const uint32_t swz = (uint32_t)(row & 7);
+  uint8_t* stage = c.smem + Cfg::oStage;
+  const float* ks = reinterpret_cast<const float*>(c.smem + Cfg::oKs);
   int s = 0;
+  MQ_DECL
   for (int j = c.jlo; j < c.jhi; ++j) {
+    const int c0 = c.clo(j);
     for (int r = 0; r < R; ++r, ++s) {
       const int qs = s & 1;
-      uint8_t* stage = c.smem + Cfg::oStage + (s % Cfg::kStageBufs) * 32768;
+      MQ(3)
       if (!c.wait_w(mYFull + qs, s / 2)) return;
+      MQ(0)
       tc_fence_after();
-      // the reduce-add that last used this staging tile has read it
-      if (leader) {
-        if (Cfg::kStageBufs == 2) bulk_wait_read_but_last();
-        else bulk_wait_read_all();
-      }
+      float gd[Cfg::kG];
+#pragma unroll
+      for (int cc = 0; cc < Cfg::kG; ++cc)
+        gd[cc] = (cc >= c0 && cc < c.chi) ? reinterpret_cast<const float*>(c.smem + Cfg::oGd + (qs * Cfg::kG + cc) * 512)[row] : 0.f;
+      c.arrive_w(mQFree + qs);                     // the step's g_denom rows have been read
+      if (leader) bulk_wait_read_all();            // the previous reduce-add has read the staging tile
       named_bar_sync(2, 128);
+      MQ(1)
 #pragma unroll 1
       for (int hb = 0; hb < 2; ++hb) {
         uint32_t o[32];
@@ -361,9 +475,23 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
         }
         uint8_t* box = stage + hb * 16384 + row * 128;
 #pragma unroll
-        for (int x = 0; x < 8; ++x)
-          *reinterpret_cast<uint4*>(box + ((((uint32_t)x ^ swz) & 7) << 4)) = make_uint4(o[4 * x], o[4 * x + 1], o[4 * x + 2], o[4 * x + 3]);
+        for (int x = 0; x < 8; ++x) {
+          float v[4];
+#pragma unroll
+          for (int y = 0; y < 4; ++y) {
+            v[y] = __uint_as_float(o[4 * x + y]);
+            if constexpr (Cfg::kG == 4) {
+              const float4 k4 = *reinterpret_cast<const float4*>(ks + (32 * hb + 4 * x + y) * 4);
+              v[y] = fmaf(gd[0], k4.x, fmaf(gd[1], k4.y, fmaf(gd[2], k4.z, fmaf(gd[3], k4.w, v[y]))));
+            } else {
+              const float2 k2 = *reinterpret_cast<const float2*>(ks + (32 * hb + 4 * x + y) * 2);
+              v[y] = fmaf(gd[0], k2.x, fmaf(gd[1], k2.y, v[y]));
+            }
+          }
+          *reinterpret_cast<float4*>(box + ((((uint32_t)x ^ swz) & 7) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        }
       }
+      MQ(2)
       fence_proxy_async();
       named_bar_sync(2, 128);
       if (leader) {
@@ -374,16 +502,16 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
       }
     }
   }
+#ifdef UA_PROFILE_MK
+  if (leader) { MQ(3) MQ_STORE(4) }
+#endif
   if (!c.wait_w(mDone, 0)) {
     if (leader) bulk_wait_all();
     return;
   }
   tc_fence_after();
   const int c0 = c.clo(c.jlo);
-  if ((warp & 3) < 2) {                    // lanes 0..63: rows d' = 64 h + row of N^T, and w
-    uint32_t wv[16];
-    tmem_ld16(c.tmem + Cfg::tW + lane_base, wv);
-    tc_wait_ld();
+  if ((warp & 3) < 2) {                    // lanes 0..63: rows d' = 64 h + row of N^T
     for (int cc = c0; cc < c.chi; ++cc) {
       float* nacc = p.nacc + ((size_t)c.bh * N + c.i0 + cc) * (size_t)kNaccRows<D>() * D;
 #pragma unroll 1
@@ -397,12 +525,8 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
           red_add_v4(dst + 4 * x, __uint_as_float(o[4 * x]), __uint_as_float(o[4 * x + 1]), __uint_as_float(o[4 * x + 2]),
                      __uint_as_float(o[4 * x + 3]));
       }
-      float wsel = 0.f;
-#pragma unroll
-      for (int x = 0; x < Cfg::kG; ++x) wsel = (x == cc) ? __uint_as_float(wv[x]) : wsel;
-      atomicAdd(nacc + (size_t)D * D + 64 * c.h + row, wsel);
     }
-  } else if ((warp & 3) == 2 && c.h == 0) {    // lane 72 (column 8 of E holds ones): u_c = column sums of g
+  } else if ((warp & 3) == 2 && c.h == 0) {    // lane 64 (column 0 of the ones tile): u_c = column sums of g
     for (int cc = c0; cc < c.chi; ++cc) {
       float* nacc = p.nacc + ((size_t)c.bh * N + c.i0 + cc) * (size_t)kNaccRows<D>() * D + (size_t)(D + 1) * D;
 #pragma unroll 1
@@ -410,7 +534,7 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
         uint32_t o[32];
         tmem_ld32(c.tmem + Cfg::tN + cc * D + lane_base + 32 * hb, o);
         tc_wait_ld();
-        if (lane == 8) {
+        if (lane == 0) {
 #pragma unroll
           for (int x = 0; x < 8; ++x)
             red_add_v4(nacc + 32 * hb + 4 * x, __uint_as_float(o[4 * x]), __uint_as_float(o[4 * x + 1]), __uint_as_float(o[4 * x + 2]),
@@ -439,22 +563,26 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   c.abort_flag = reinterpret_cast<volatile int*>(misc + 1);
   {
     // work item -> (batch*head, group, piece of the group's row tiles); the two halves of head_dim 128 are neighbours
-    const int item = blockIdx.x / Cfg::kKB;
+    // Items in launch order: by range of row tiles, then batch*head, then group.  The groups that add to the same rows of
+    // dQ (and read the same Q tiles) therefore run at about the same time, and the fp32 dQ accumulator -- larger than L2
+    // as a whole -- sees each of its tiles come from HBM and go back once instead of once per group.
+    int idx = blockIdx.x / Cfg::kKB;
+    const int BH = p.s.B * p.s.H, groups = (N + Cfg::kG - 1) / Cfg::kG;
     c.h = blockIdx.x % Cfg::kKB;
-    c.bh = item / p.items_per_bh;
-    int rem = item % p.items_per_bh;
     int g = 0;
     bool found = false;
-    for (; g * Cfg::kG < N; ++g) {
-      const int jmax = min((g + 1) * Cfg::kG, N) - 1;                    // row tiles before the group's last chunk
-      const int pieces = (jmax + p.jp - 1) / p.jp;
-      if (rem < pieces) {
-        c.jlo = rem * p.jp;
-        c.jhi = min(c.jlo + p.jp, jmax);
+    for (int piece = 0; piece * p.jp < N - 1; ++piece) {
+      int cnt = 0;                                                       // groups that have row tiles of this range before a chunk
+      for (int gg = 0; gg < groups; ++gg) cnt += (min((gg + 1) * Cfg::kG, N) - 1 > piece * p.jp) ? 1 : 0;
+      if (idx < BH * cnt) {
+        c.bh = idx / cnt;
+        g = groups - 1 - idx % cnt;
+        c.jlo = piece * p.jp;
+        c.jhi = min(c.jlo + p.jp, min((g + 1) * Cfg::kG, N) - 1);
         found = true;
         break;
       }
-      rem -= pieces;
+      idx -= BH * cnt;
     }
     if (!found) return;                                                  // (a grid larger than the item count)
     c.i0 = g * Cfg::kG;
@@ -466,7 +594,8 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     misc[2] = 0;
     for (int b = 0; b < mNumBars; ++b) {
       uint32_t count = 1;
-      if (b == mEReady || b == mEReady + 1 || b == mYFree || b == mYFree + 1) count = 4;     // one arrival per warp
+      if (b == mYFree || b == mYFree + 1) count = 4;     // one arrival per draining warp
+      if (b == mQFree || b == mQFree + 1) count = 9;     // the issuer's commit, the four gate-sum warps, the four draining warps
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
@@ -477,21 +606,16 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     tmem_relinquish();
   }
   if (warp >= 8) {
-    // E tiles: zeros, ones in column 8; Ks: column c = ksum_c / 128 of this block's 64 output columns
+    // ones tile: zeros, ones in column 0; ksum table of this block's 64 output columns
     const int t = threadIdx.x - 256;
-    for (int x = t; x < 4096; x += 128) {
-      const int buf = x >> 11, off = (x & 2047) << 4;
-      *reinterpret_cast<uint4*>(smem + Cfg::oQE + buf * 32768 + 16384 + off) = make_uint4(0u, 0u, 0u, 0u);
-    }
-    for (int x = t; x < 512; x += 128) *reinterpret_cast<uint4*>(smem + Cfg::oKs + (x << 4)) = make_uint4(0u, 0u, 0u, 0u);
+    for (int x = t; x < 1024; x += 128) *reinterpret_cast<uint4*>(smem + Cfg::oOnes + (x << 4)) = make_uint4(0u, 0u, 0u, 0u);
     named_bar_sync(3, 128);
-    for (int buf = 0; buf < 2; ++buf)
-      *reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oQE + buf * 32768 + 16384 + t * 128 + (((1 ^ t) & 7) << 4)) = __float2bfloat16_rn(1.0f);
+    *reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oOnes + t * 128 + ((t & 7) << 4)) = __float2bfloat16_rn(1.0f);
     if (t < 64) {
       const int c0 = c.clo(c.jlo);
-      for (int cc = c0; cc < c.chi; ++cc)
-        *reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oKs + t * 128 + ((t & 7) << 4) + 2 * cc) =
-            p.ksum[((size_t)c.bh * N + c.i0 + cc) * D + 64 * c.h + t];
+      float* ks = reinterpret_cast<float*>(smem + Cfg::oKs) + t * Cfg::kG;
+      for (int cc = 0; cc < Cfg::kG; ++cc)
+        ks[cc] = (cc >= c0 && cc < c.chi) ? __bfloat162float(p.ksum[((size_t)c.bh * N + c.i0 + cc) * D + 64 * c.h + t]) : 0.f;
     }
     fence_proxy_async();
   }
@@ -500,6 +624,9 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   tc_fence_after();
   c.tmem = misc[0];
 
+#ifdef UA_PROFILE_MK
+  const long long mk_t0 = clock64();
+#endif
   if (warp == 0) {
     if (lane == 0) mk_producer<D>(c, p, &tmQ, &tmG);
   } else if (warp == 1) {
@@ -507,11 +634,14 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   } else if (warp >= 4 && warp < 8) {
     mk_drain<D>(c, p, &tmDQ);
   } else if (warp >= 8) {
-    mk_gate_writer<D>(c, p);
+    mk_gate_sums<D>(c, p);
   }
 
   tc_fence_before();
   __syncthreads();
+#ifdef UA_PROFILE_MK
+  if (blockIdx.x == UA_PROFILE_MK && threadIdx.x == 0) reinterpret_cast<long long*>(p.status)[2 + 16] = clock64() - mk_t0;
+#endif
   if (*c.abort_flag) {
     if (threadIdx.x == 0) {
       if (atomicExch(p.status, 3) == 0) p.status[1] = (int)misc[2];

@@ -512,5 +512,24 @@ __global__ void convert_kernel(const float* __restrict__ src, T* __restrict__ ds
   for (; idx < n; idx += stride) Num<T>::st(dst + idx, src[idx]);
 }
 
+// ... eight elements per thread and step (two 16-byte loads, one 16- or 32-byte store); n8 = n / 8, both pointers 16-byte aligned
+template <typename T>
+__global__ void convert8_kernel(const float4* __restrict__ src, T* __restrict__ dst, size_t n8) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; idx < n8; idx += stride) {
+    const float4 a = src[2 * idx], b = src[2 * idx + 1];
+    if (sizeof(T) == 2) {
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(a.x, a.y), h1 = __floats2bfloat162_rn(a.z, a.w);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(b.x, b.y), h3 = __floats2bfloat162_rn(b.z, b.w);
+      reinterpret_cast<uint4*>(dst)[idx] = make_uint4(*reinterpret_cast<uint32_t*>(&h0), *reinterpret_cast<uint32_t*>(&h1),
+                                                      *reinterpret_cast<uint32_t*>(&h2), *reinterpret_cast<uint32_t*>(&h3));
+    } else {
+      reinterpret_cast<float4*>(dst)[2 * idx] = a;
+      reinterpret_cast<float4*>(dst)[2 * idx + 1] = b;
+    }
+  }
+}
+
 }  // namespace simt
 }  // namespace ua

@@ -94,7 +94,24 @@ def _setup_context(ctx, inputs, outputs):
         ctx.ua_has_extras = False
 
 
+def _mark_masked_zero(*tensors):
+    """Notes on gradient tensors that their part for the rows before each chunk is exactly zero (``SMVecMatMul.backward``
+    produces such tensors: the merge weight of a fully masked block is exp(-1e12 - lse) = 0).  The note holds the tensor's
+    version counter, so that an in-place change of the tensor voids it; a tensor that autograd builds from it (a sum with
+    another gradient, a hook's replacement) does not carry it."""
+    for t in tensors:
+        t._ua_masked_zero = t._version
+
+
+def _masked_zero(t) -> bool:
+    v = getattr(t, "_ua_masked_zero", None)
+    return v is not None and v == t._version
+
+
 def _backward(ctx, g_out, g_denom):
+    # Upstream gradients that are known to vanish on the rows before each chunk contribute nothing there: the kernels of
+    # those rows are skipped, with the same result.  Anything else takes the full path (unless strict mode is off).
+    upstream_zero = _masked_zero(g_out) and _masked_zero(g_denom)
     saved = ops.plain(*ctx.saved_tensors)
     g_out, g_denom = ops.plain(g_out, g_denom)
     kc, vc, xq, static_src, static_dest = saved[:5]
@@ -103,7 +120,7 @@ def _backward(ctx, g_out, g_denom):
         carry = saved[6] if ctx.ua_has_carry else None
     else:                      # only the inputs were saved: recompute what the forward would have handed over
         _, lse, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, flags=_lib.FLAG_SKIP_MASKED_FILL, keep_carry=True)
-    flags = 0 if _STRICT_MASKED_GRADS else _lib.FLAG_SKIP_MASKED_GRADS
+    flags = 0 if (_STRICT_MASKED_GRADS and not upstream_zero) else _lib.FLAG_SKIP_MASKED_GRADS
     g_out_cm = ops.out_to_chunk_major(g_out)
     g_denom_cm = ops.denom_to_chunk_major(g_denom)
     return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags, carry=carry, lse=lse)
@@ -175,7 +192,9 @@ class SMVecMatMul(Function):
         mat, vec, g = ops.plain(*ctx.saved_tensors, g)
         g_out_cm, g_lse_cm = ops.merge_bwd_cm(ops.out_to_chunk_major(mat), ops.denom_to_chunk_major(vec), g,
                                               skip_zero_weight_blocks=not _STRICT_MASKED_GRADS)
-        return ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
+        g_mat, g_vec = ops.as_reference_out(g_out_cm), ops.as_reference_denom(g_lse_cm).to(vec.dtype)
+        _mark_masked_zero(g_mat, g_vec)
+        return g_mat, g_vec
 
 
 class UniversalAttentionMerged(Function):
