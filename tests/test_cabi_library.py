@@ -78,6 +78,23 @@ def test_argument_validation_without_gpu(lib):
     assert lib.ua_bwd_workspace_bytes(ctypes.byref(bad_chunk), 0, 0) == 0
 
 
+def test_scratch_plan_routes_wide_chunks_to_the_tensor_core_kernels(lib):
+    """bf16 chunks of 256 / 384 keys at head_dim 64 or 128 are swept as sub-chunks of 128 keys by the tensor-core kernels:
+    the plan then holds a decay-prefix table per sub-chunk and room for the sub-chunk outputs (host-side arithmetic only)."""
+    b, h, r, n, d = 1, 2, 2, 4, 128
+    for c, m in ((256, 2), (384, 3)):
+        dims = UaDims(b, h, r, n, c, d)
+        L = n * c
+        assert lib.ua_carry_bytes(ctypes.byref(dims), 1, 0) == b * h * (n * m) ** 2 * 256 * 4
+        sub_out = b * h * n * m * r * L * d * 2
+        assert lib.ua_fwd_workspace_bytes(ctypes.byref(dims), 1, 0) >= 256 + sub_out
+        assert lib.ua_bwd_workspace_bytes(ctypes.byref(dims), 1, 0) >= 2 * sub_out
+        # fp32, forced generic kernels, other head dims: no sub-chunk plan
+        assert lib.ua_carry_bytes(ctypes.byref(dims), 0, 0) == 0
+        assert lib.ua_carry_bytes(ctypes.byref(dims), 1, 4) == 0 and lib.ua_fwd_workspace_bytes(ctypes.byref(dims), 1, 4) == 256
+    assert lib.ua_fwd_workspace_bytes(ctypes.byref(UaDims(b, h, r, n, 256, 32)), 1, 0) == 256
+
+
 def test_cpu_tensors_are_rejected():
     import torch
     from universal_attention_triton_b200 import UniversalAttention

@@ -76,7 +76,8 @@ def _bf16_case(B, H, R, L, c, D, seed, **kw):
 
 
 @pytest.mark.parametrize("shape", [(1, 2, 2, 512, 128, 64), (2, 1, 4, 256, 64, 64), (1, 1, 1, 512, 128, 128),
-                                   (1, 1, 2, 512, 256, 128)])      # last: the chunk-256 / head-dim-128 tile of the long-context config
+                                   (1, 1, 2, 512, 256, 128),       # the chunk-256 / head-dim-128 tile of the long-context config
+                                   (1, 2, 2, 1024, 256, 64), (1, 1, 3, 768, 384, 64)])      # chunks of 2 and 3 sub-chunks of 128 keys
 def test_bf16_against_oracle(shape):
     B, H, R, L, c, D = shape
     ua = _ua()

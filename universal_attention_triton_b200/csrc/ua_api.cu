@@ -149,6 +149,70 @@ int convert_any(int dtype, const float* src, void* dst, size_t n, cudaStream_t s
   return dtype == UA_F32 ? launch_convert<float>(src, dst, n, st) : launch_convert<bf16>(src, dst, n, st);
 }
 
+// ---- chunks of 256, 384, ... keys on the tensor-core kernels ---------------------------------------------------
+// The softmax of the operator runs over the keys of one chunk (universal_attention_autograd.py:85-93); everything else --
+// affinity, decay prefix along the rows, mask -- is per key.  A chunk of m * 128 keys is therefore swept as m sub-chunks
+// of 128 keys by the kernels above, and the m (out, log-sum-exp) pairs of each chunk are merged with softmax weights
+// exp(lse_sub - lse_chunk): the same merge as SMVecMatMul's, over groups of m neighbouring sub-chunks.  The backward
+// runs the sub-chunk forward again (the merge backward needs its outputs), the merge backward, and the sub-chunk backward.
+int sub_chunks(const ua::Shape& s, int dtype, int flags) {
+  if ((flags & UA_FLAG_FORCE_SIMT) || dtype != UA_BF16 || s.C <= 128 || s.C % 128 != 0 || s.C / 128 > 8) return 0;
+  ua::Shape t = s;
+  t.C = 128; t.N = s.N * (s.C / 128);
+  return (ua::sm100::fwd_supported(t, dtype) && ua::sm100::bwd2_supported(t, dtype)) ? s.C / 128 : 0;
+}
+UaDims sub_dims(const UaDims* d, int m) {
+  UaDims t = *d;
+  t.n_chunks = d->n_chunks * m; t.chunk = 128;
+  return t;
+}
+// the merge kernels' view of the sub-chunk tensors: (batch, kv head, chunk) as the batch, the m sub-chunks as the merged axis
+UaDims group_dims(const UaDims* d, int m) {
+  UaDims t = *d;
+  t.batch = d->batch * d->kv_heads * d->n_chunks; t.kv_heads = 1; t.n_chunks = m; t.chunk = d->n_chunks * d->chunk / m;
+  return t;
+}
+struct SubWorkspace {
+  size_t off_inner, off_out, off_gout, off_lse, off_glse, off_carry, off_status, total;
+};
+SubWorkspace sub_layout(const ua::Shape& s, int m, bool backward, size_t inner_bytes) {
+  SubWorkspace w{};
+  const size_t rows = (size_t)s.B * s.H * s.N * m * s.R * s.L;
+  size_t o = align_up(inner_bytes < 256 ? 256 : inner_bytes, 256);     // the inner call's workspace comes first: its status word is the caller's
+  w.off_out = o; o = align_up(o + rows * s.D * 2, 256);
+  w.off_lse = o; o = align_up(o + rows * sizeof(float), 256);
+  if (backward) {
+    w.off_gout = o; o = align_up(o + rows * s.D * 2, 256);
+    w.off_glse = o; o = align_up(o + rows * sizeof(float), 256);
+    w.off_carry = o; o = align_up(o + (size_t)s.B * s.H * s.N * m * s.N * m * 256 * sizeof(float), 256);
+    w.off_status = o; o += 256;
+  }
+  w.total = o;
+  return w;
+}
+
+// g_lse_sub += g_denom_chunk * exp(lse_sub - lse_chunk): the chunk's denom is the log-sum-exp over its sub-chunks
+template <typename TD>
+__global__ void group_denom_grad_kernel(const float* __restrict__ lse_sub, const TD* __restrict__ g_denom, float* __restrict__ g_lse_sub,
+                                        size_t groups, size_t rl, int m) {
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < groups * rl; idx += stride) {
+    const size_t grp = idx / rl, x = idx - grp * rl;
+    const float* l = lse_sub + grp * m * rl + x;
+    float mx = l[0];
+    for (int q = 1; q < m; ++q) mx = fmaxf(mx, l[q * rl]);
+    float z = 0.f;
+    for (int q = 0; q < m; ++q) z += expf(l[q * rl] - mx);
+    const float g = ua::Num<TD>::ld(g_denom + idx) / z;
+    float* gl = g_lse_sub + grp * m * rl + x;
+    for (int q = 0; q < m; ++q) gl[q * rl] += g * expf(l[q * rl] - mx);
+  }
+}
+// a status word raised by an inner call on its own buffer is carried over to the caller's
+__global__ void carry_status_kernel(const int* __restrict__ from, int* __restrict__ to) {
+  if (from[0] != 0 && atomicCAS(to, 0, from[0]) == 0) to[1] = from[1];
+}
+
 bool dtype_ok(int dtype, int gate_dtype) {
   if (dtype != UA_F32 && dtype != UA_BF16) return false;
   if (gate_dtype != UA_F32 && gate_dtype != UA_BF16) return false;
@@ -248,13 +312,20 @@ const char* ua_error_string(int code) {
 }
 
 size_t ua_fwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
-  (void)dims; (void)dtype; (void)flags;
+  if (check_dims(dims) == UA_OK) {
+    ua::Shape s = to_shape(dims);
+    if (const int m = sub_chunks(s, dtype, flags)) return sub_layout(s, m, false, 256).total;
+  }
   return 256;   // status word
 }
 
 size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
+  if (const int m = sub_chunks(s, dtype, flags)) {
+    const UaDims sd = sub_dims(dims, m);
+    return sub_layout(s, m, true, bwd_layout_tc(to_shape(&sd)).total).total;
+  }
   if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd2_supported(s, dtype)) return bwd_layout_tc(s).total;
   const SimtCfg cfg = simt_cfg(s.C, s.D, dtype, true);
   if (!cfg.rt) return 0;
@@ -264,6 +335,7 @@ size_t ua_bwd_workspace_bytes(const UaDims* dims, int dtype, int flags) {
 size_t ua_carry_bytes(const UaDims* dims, int dtype, int flags) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
+  if (const int m = sub_chunks(s, dtype, flags)) return (size_t)s.B * s.H * s.N * m * s.N * m * 256 * sizeof(float);
   if ((flags & UA_FLAG_FORCE_SIMT) || !ua::sm100::bwd2_supported(s, dtype)) return 0;
   return (size_t)s.B * s.H * s.N * s.N * 256 * sizeof(float);
 }
@@ -286,6 +358,21 @@ int ua_fwd_keep(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ua::Shape s = to_shape(dims);
+  if (const int m = sub_chunks(s, dtype, flags)) {
+    // sub-chunks of 128 keys, then the merge inside each chunk (see sub_chunks)
+    const SubWorkspace w = sub_layout(s, m, false, 256);
+    if (workspace_bytes < w.total) return UA_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    const UaDims sd = sub_dims(dims, m), gd = group_dims(dims, m);
+    void* out_sub = ws + w.off_out;
+    float* lse_sub = reinterpret_cast<float*>(ws + w.off_lse);
+    if ((e = ua_fwd_keep(&sd, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, out_sub, lse_sub, nullptr, carry_out, workspace,
+                         256, flags & ~UA_FLAG_SKIP_MASKED_FILL, stream)))
+      return e;
+    if ((e = ua_merge_fwd_stats(&gd, dtype, out_sub, lse_sub, out_cm, lse_cm, stream))) return e;
+    if (denom_cm) e = convert_any(dtype, lse_cm, denom_cm, (size_t)s.B * s.H * s.N * s.R * s.L, st);
+    return e;
+  }
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
 
   if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::fwd_supported(s, dtype)) {
@@ -453,6 +540,39 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(g_out_cm)) return UA_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   ua::Shape s = to_shape(dims);
+
+  if (const int m = sub_chunks(s, dtype, flags)) {
+    // chunks of m * 128 keys (see sub_chunks): sub-chunk forward again, merge backward inside each chunk, sub-chunk backward.
+    // (lse_cm, the chunks' log-sum-exp, is not what the sub-chunk kernels need; carry_in is already per sub-chunk.)
+    const UaDims sd = sub_dims(dims, m), gd = group_dims(dims, m);
+    const size_t inner = bwd_layout_tc(to_shape(&sd)).total;
+    const SubWorkspace w = sub_layout(s, m, true, inner);
+    if (!workspace || workspace_bytes < w.total || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+    char* ws = static_cast<char*>(workspace);
+    void* out_sub = ws + w.off_out;
+    void* g_out_sub = ws + w.off_gout;
+    float* lse_sub = reinterpret_cast<float*>(ws + w.off_lse);
+    float* g_lse_sub = reinterpret_cast<float*>(ws + w.off_glse);
+    void* carry_sub = carry_in ? nullptr : static_cast<void*>(ws + w.off_carry);
+    if ((e = ua_fwd_keep(&sd, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, out_sub, lse_sub, nullptr, carry_sub,
+                         ws + w.off_status, 256, flags & ~UA_FLAG_SKIP_MASKED_FILL, stream)))
+      return e;
+    if ((e = ua_merge_bwd(&gd, dtype, out_sub, lse_sub, g_out_cm, g_out_sub, g_lse_sub, 0, stream))) return e;
+    {
+      const size_t groups = (size_t)s.B * s.H * s.N, rl = (size_t)s.R * s.L;
+      if (g_denom_dtype == UA_F32)
+        group_denom_grad_kernel<float><<<148 * 8, 256, 0, st>>>(lse_sub, static_cast<const float*>(g_denom_cm), g_lse_sub, groups, rl, m);
+      else
+        group_denom_grad_kernel<bf16><<<148 * 8, 256, 0, st>>>(lse_sub, static_cast<const bf16*>(g_denom_cm), g_lse_sub, groups, rl, m);
+      if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+    }
+    if ((e = ua_bwd_kept(&sd, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_sub, g_lse_sub, UA_F32,
+                         carry_in ? carry_in : carry_sub, lse_sub, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, inner, flags,
+                         stream)))
+      return e;
+    carry_status_kernel<<<1, 1, 0, st>>>(reinterpret_cast<const int*>(ws + w.off_status), reinterpret_cast<int*>(ws));
+    return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+  }
 
   if (!(flags & UA_FLAG_FORCE_SIMT) && ua::sm100::bwd2_supported(s, dtype)) {
     if (!aligned16(dvc) || !aligned16(dkc) || !aligned16(dxq)) return UA_ERR_ALIGNMENT;
