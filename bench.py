@@ -52,11 +52,12 @@ METRIC = "fwd+bwd tokens/sec"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
-# DRAM bytes per launch of the backward kernel at workload c2, from one ncu capture of a slice of 2 of the 32 (batch,
-# kv-head) units (159.26 MB read + 8.13 MB written); the traffic grows in proportion to the units.  No figure is given for
-# the forward: a capture of that slice ends with part of the 134 MB it writes still in the 126 MB L2, so its DRAM write
-# count understates a full launch.
-NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (159.264512e6 + 8.125952e6)}}
+# DRAM bytes per backward call at workload c2, from one ncu capture of a slice of 2 of the 32 (batch, kv-head) units: the
+# keys-on-lanes kernel (91.94 MB read + 3.78 MB written) plus the sweep over the rows before each chunk (80.87 + 2.55 MB);
+# the small per-chunk kernels and the fp32 -> bf16 conversions are not in the figure.  The traffic grows in proportion to
+# the units.  No figure is given for the forward: a capture of that slice ends with part of the 134 MB it writes still in
+# the 126 MB L2, so its DRAM write count understates a full launch.
+NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (91.942400e6 + 3.775744e6 + 80.872448e6 + 2.554624e6)}}
 
 
 def flops(w):
@@ -599,7 +600,9 @@ def main():
             "tflops": (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12,
             "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms_per_step * 1e-3) / 1e12 / peak,
             "fwd_ms": fwd_avg, "bwd_ms": bwd_avg,
-            "gpu_launches": K * (1 + (0 if w["fwd_only"] else 4)),      # forward kernel; backward kernel + three fp32 -> dtype conversions
+            # forward kernel; backward: keys-on-lanes kernel + three fp32 -> dtype conversions, and with the gradient through
+            # the rows before each chunk three more (per-chunk constants, sweep, per-chunk finish)
+            "gpu_launches": K * (1 + (0 if w["fwd_only"] else (4 if args.skip_masked_grads else 7))),
             "clocks": clocks,
             "roofline": {"kernel": "ua backward" if dom_is_bwd else "ua forward", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,

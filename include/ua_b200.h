@@ -237,6 +237,15 @@ int ua_static_status(void* stream);
  * in the reference (its kernels have no device-side waits). */
 int ua_workspace_status(const void* workspace, void* stream);
 
+/* Self-test of that give-up path, for a host that wants to see it work before it relies on it: launches one block
+ * whose two waiters (a single thread and a whole warp, the two forms the kernels use) wait on an mbarrier that
+ * nothing ever completes, with a wall-time limit of limit_us microseconds (1 .. 100000) instead of the kernels'
+ * 2 s.  The waits run out, the block sets the status word of `workspace` (>= 256 bytes, 256-byte aligned) the way the
+ * kernels do and returns; nothing traps and the context stays usable.  ua_workspace_status(workspace) then reports
+ * UA_ERR_TIMEOUT, and the second word holds (barrier index + 1) | thread << 8 of the first waiter to give up.
+ * No counterpart in the reference. */
+int ua_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned limit_us, void* stream);
+
 /* Input prologue.  The reference's driver builds the operator's inputs from token-major projections with transposes
  * and views (main.py:24-31): query_state (b,s,n,d) -> xq (b,n_kv,rep,s,d) (query head kv * rep + r), key_state /
  * value_state (b,s,n_kv,d) -> kc / vc (b,n_kv,s,d) (= (b,n_kv,n_chunks,chunk,d)), gate_state (b,s,2,n_kv) ->

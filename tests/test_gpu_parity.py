@@ -624,3 +624,35 @@ def test_status_word_path_reports_a_timeout_without_any_kernel():
         _lib.check(rc, "status")
     ws.zero_()
     assert lib.ua_workspace_status(ctypes.c_void_p(ws.data_ptr()), stream) == 0
+
+
+def test_bounded_wait_gives_up_and_reports_it():
+    """The give-up path of the kernels' device-side waits, run for real but in 2 ms instead of 2 s: a one-block self-test
+    whose two waiters (single thread, whole warp) wait on an mbarrier that nothing completes.  The waits run out, the block
+    returns with the status word set as the kernels set it, ``ua_workspace_status`` reports UA_ERR_TIMEOUT with the note of
+    the first waiter to give up, and the context stays usable (a forward call runs right after).  Nothing traps or hangs."""
+    import ctypes, time
+    from universal_attention_triton_b200 import _lib
+    lib = _lib.load()
+    ws = torch.zeros(256, dtype=torch.uint8, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    assert lib.ua_selftest_wait_timeout(ctypes.c_void_p(ws.data_ptr()), 256, 2000, stream) == 0
+    rc = lib.ua_workspace_status(ctypes.c_void_p(ws.data_ptr()), stream)
+    elapsed = time.perf_counter() - t0
+    assert rc == 9
+    assert 0.002 <= elapsed < 1.0, elapsed             # gave up after the 2 ms limit, far from the kernels' 2 s
+    words = ws[:8].cpu().view(torch.int32)
+    assert int(words[0]) == 3
+    note = int(words[1])
+    assert (note & 0xff) == 1 and (note >> 8) in (0, 32), note      # barrier 0; thread 0 or the leader of warp 1
+    # bad arguments are refused before any launch
+    assert lib.ua_selftest_wait_timeout(ctypes.c_void_p(ws.data_ptr()), 255, 2000, stream) == 4
+    assert lib.ua_selftest_wait_timeout(ctypes.c_void_p(ws.data_ptr()), 256, 0, stream) == 1
+    # the context is intact
+    ua = _ua()
+    ins, ins32 = _bf16_case(1, 1, 1, 256, 128, 64, seed=1)
+    out, denom = ua.UniversalAttention.apply(*_cuda(*ins))
+    ref_out, _, _ = O.ua_forward(*ins32)
+    assert fwd_errors(out.float().cpu(), denom.float().cpu(), ref_out, ref_out.new_zeros(denom.shape), 128)["out_masked"] <= 2e-2

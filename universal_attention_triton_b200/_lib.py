@@ -54,6 +54,7 @@ SIGNATURES = {
     "ua_bwd_static": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ua_static_status": (_i, [_vp]),
     "ua_workspace_status": (_i, [_vp, _vp]),
+    "ua_selftest_wait_timeout": (_i, [_vp, ctypes.c_size_t, ctypes.c_uint, _vp]),
     "ua_relayout": (_i, [_dp, _i, _i, _i, _vp, _vp, _vp]),
     "ua_merge_fwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp]),
     "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),

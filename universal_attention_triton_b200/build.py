@@ -16,6 +16,9 @@ PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG_DIR, "csrc")
 LIB_PATH = os.path.join(PKG_DIR, "libua_b200.so")
 SOURCES = ["ua_api.cu"]
+# developer micro-benchmark (stand-alone executable, not loaded by the package): `--tools` builds it next to the library
+TOOL_SOURCE = "mma_timing.cu"
+TOOL_PATH = os.path.join(PKG_DIR, "mma_timing.bin")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared",
@@ -52,5 +55,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+def build_tools() -> str:
+    """Compile the stand-alone MMA timing micro-benchmark (run it on a B200: ``./mma_timing.bin 256``)."""
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--expt-relaxed-constexpr",
+           os.path.join(CSRC, TOOL_SOURCE), "-o", TOOL_PATH, "-lcuda"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed building the MMA timing micro-benchmark")
+    return TOOL_PATH
+
+
 if __name__ == "__main__":
     print(build(force=True, verbose="--verbose" in sys.argv))
+    if "--tools" in sys.argv:
+        print(build_tools())

@@ -208,6 +208,29 @@ __global__ void group_denom_grad_kernel(const float* __restrict__ lse_sub, const
     for (int q = 0; q < m; ++q) gl[q * rl] += g * expf(l[q * rl] - mx);
   }
 }
+// One block, two waiters on an mbarrier that nothing completes: thread 0 with the single-thread wait, warp 1 with the
+// warp-collective one, both with a short wall-time limit.  Both give up, and the block reports it as the kernels do.
+__global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar_mem;
+  __shared__ int flags[2];      // [0] abort flag, [1] note of the first waiter to give up
+  const uint32_t bar = ua::ptx::smem_u32(&bar_mem);
+  if (threadIdx.x == 0) {
+    flags[0] = 0; flags[1] = 0;
+    ua::ptx::mbar_init(bar, 1);
+    ua::ptx::mbar_init_fence();
+  }
+  __syncthreads();
+  volatile int* abort_flag = flags;
+  bool ok = true;
+  if (threadIdx.x == 0) ok = ua::ptx::mbar_wait(bar, 0, abort_flag, limit_ns);
+  else if (threadIdx.x >= 32) ok = ua::ptx::mbar_wait_warp(bar, 0, abort_flag, limit_ns);
+  if (!ok && (threadIdx.x & 31) == 0) atomicCAS(flags + 1, 0, 1 | ((int)threadIdx.x << 8));
+  __syncthreads();
+  if (threadIdx.x == 0 && flags[0]) {
+    if (atomicExch(status, 3) == 0) status[1] = flags[1];
+  }
+}
+
 // a status word raised by an inner call on its own buffer is carried over to the caller's
 __global__ void carry_status_kernel(const int* __restrict__ from, int* __restrict__ to) {
   if (from[0] != 0 && atomicCAS(to, 0, from[0]) == 0) to[1] = from[1];
@@ -225,24 +248,15 @@ bool dtype_ok(int dtype, int gate_dtype) {
 constexpr size_t kStaticScratchBytes = UA_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
-std::mutex g_static_mutex;
-void* g_static_ptr[kMaxDevices] = {};      // device address of g_static_scratch, per device ordinal
-
 // In host code `g_static_scratch` is only a handle for the runtime, not an address a
-// kernel can use; the device address has to be asked for, once per device, with that
-// device current.
+// kernel can use; the device address has to be asked for, with that device current.
 int static_scratch_for_current_device(void** out) {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return UA_ERR_CUDA;
-  if (dev < 0 || dev >= kMaxDevices) return UA_ERR_UNSUPPORTED;
-  std::lock_guard<std::mutex> lock(g_static_mutex);
-  if (!g_static_ptr[dev]) {
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return UA_ERR_CUDA;
-    g_static_ptr[dev] = ptr;
-  }
-  *out = g_static_ptr[dev];
+  // Asked for on every call rather than remembered: after a cudaDeviceReset the module is loaded again into the new
+  // context and a remembered address would belong to the context that is gone.  (The runtime keeps its own table; the
+  // query neither allocates nor synchronises once the module is loaded.)
+  void* ptr = nullptr;
+  if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess || !ptr) return UA_ERR_CUDA;
+  *out = ptr;
   return UA_OK;
 }
 
@@ -725,6 +739,16 @@ int ua_static_status(void* stream) {
   int e = static_scratch_for_current_device(&scratch);
   if (e) return e;
   return ua_workspace_status(scratch, stream);
+}
+
+int ua_selftest_wait_timeout(void* workspace, size_t workspace_bytes, unsigned limit_us, void* stream) {
+  if (!workspace) return UA_ERR_NULL_POINTER;
+  if (workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  if (limit_us < 1 || limit_us > 100000) return UA_ERR_BAD_DIMS;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  wait_selftest_kernel<<<1, 64, 0, st>>>(static_cast<int*>(workspace), (unsigned long long)limit_us * 1000ull);
+  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 
 int ua_workspace_status(const void* workspace, void* stream) {

@@ -380,6 +380,8 @@ __device__ __forceinline__ void bwd2_back(const Bwd2Ctx& c, const Bwd2Params& p,
         if (yc >= 1 && !c.wait(qYFree, yc - 1)) return;
         UQ(2)
         tc_fence_after();
+        // (UA_EXP_NO_DQ_MMA / UA_EXP_NO_DRAIN / UA_EXP_NO_COLSUM: builds for timing experiments only -- each leaves one
+        // piece of the work out, with wrong results, to show what the kernel time does NOT depend on)
 #ifndef UA_EXP_NO_DQ_MMA
         mma_rows_out(desc_from_lo(desc_lo(dsb, 16384)));                                  // dQ_rj = dS^T K_i
 #endif
