@@ -30,6 +30,62 @@ def test_functions_follow_the_new_style_protocol():
     assert list(inspect.signature(smv.forward).parameters) == ["mat", "vec"]
 
 
+def test_note_on_gradients_that_vanish_before_each_chunk():
+    """The note SMVecMatMul.backward leaves on its results (host logic, no GPU): it holds the tensor's version counter,
+    an in-place change voids it, and tensors that autograd derives (a sum of two gradients, a hook's replacement) do not carry
+    it -- so the operator's backward falls back to the full path whenever the zeros are not guaranteed."""
+    from universal_attention_triton_b200 import universal_attention_autograd as M
+    g = torch.zeros(2, 3)
+    assert not M._masked_zero(g)
+    M._mark_masked_zero(g)
+    assert M._masked_zero(g)
+    assert not M._masked_zero(g + 0)             # a new tensor
+    assert not M._masked_zero(g.clone())
+    g.add_(1.0)                                  # in-place change: the note is void
+    assert not M._masked_zero(g)
+
+    # through autograd: the note reaches the next node only when the tensor itself is handed on
+    seen = []
+
+    class Probe(torch.autograd.Function):
+        @staticmethod
+        def forward(x):
+            return x * 1.0
+
+        @staticmethod
+        def setup_context(ctx, inputs, output):
+            pass
+
+        @staticmethod
+        def backward(ctx, g):
+            seen.append(M._masked_zero(g))
+            return g
+
+    class Source(torch.autograd.Function):
+        @staticmethod
+        def forward(x):
+            return x.sum()
+
+        @staticmethod
+        def setup_context(ctx, inputs, output):
+            ctx.shape = inputs[0].shape
+
+        @staticmethod
+        def backward(ctx, g):
+            out = torch.ones(ctx.shape) * g
+            M._mark_masked_zero(out)
+            return out
+
+    x = torch.randn(4, requires_grad=True)
+    Source.apply(Probe.apply(x)).backward()                                  # single consumer: handed on
+    y = Probe.apply(x)
+    (Source.apply(y) + y.sum()).backward()                                   # two consumers: autograd sums the gradients
+    y = Probe.apply(x)
+    y.register_hook(lambda g: g * 1.0)                                       # a hook replaces the tensor
+    Source.apply(y).backward()
+    assert seen == [True, False, False]
+
+
 def test_cpu_tensors_are_refused_not_computed():
     ua1 = _classes()[0]
     b, h, r, n, c, d = 1, 1, 1, 2, 16, 8
