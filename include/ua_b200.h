@@ -181,6 +181,14 @@ int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
                 const void* static_src, const void* static_dest_rows, const float* carry_in,
                 void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
+/* ua_fwd_rows that also hands over the decay-prefix table of the range's row tiles (carry_table_out:
+ * ua_carry_bytes(dims, dtype, 0) bytes; entries of other row tiles are left alone, so the ranges of one rank can share
+ * one table), for ua_bwd_rows_kept. */
+int ua_fwd_rows_keep(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
+                     const void* kc, const void* vc, const void* xq_rows,
+                     const void* static_src, const void* static_dest_rows, const float* carry_in,
+                     void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, float* carry_table_out,
+                     void* workspace, size_t workspace_bytes, int flags, void* stream);
 size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype);
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                 const void* kc, const void* vc, const void* xq_rows,
@@ -189,6 +197,15 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
                 const float* carry_in, const float* suffix_in,
                 float* dk_f32, float* dv_f32, float* dxq_rows_f32, float* dsrc_f32, float* ddest_rows_f32, float* dctot_out,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
+/* ua_bwd_rows given what the forward of the same range produced: carry_table (ua_fwd_rows_keep) and the fp32
+ * lse_cm_rows slab (ua_fwd_rows); with both, no part of the forward is run again (carry_in is then not read). */
+int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
+                     const void* kc, const void* vc, const void* xq_rows,
+                     const void* static_src, const void* static_dest_rows,
+                     const void* g_out_cm_rows, const void* g_denom_cm_rows, int g_denom_dtype,
+                     const float* carry_in, const float* suffix_in, const float* carry_table, const float* lse_cm_rows,
+                     float* dk_f32, float* dv_f32, float* dxq_rows_f32, float* dsrc_f32, float* ddest_rows_f32, float* dctot_out,
+                     void* workspace, size_t workspace_bytes, int flags, void* stream);
 int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                        const void* kc, const void* vc, const void* static_src, const void* static_dest_rows,
                        const float* suffix, float* dk_f32, float* dsrc_f32, float* ddest_rows_f32,

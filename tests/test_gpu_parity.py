@@ -351,11 +351,14 @@ def test_backward_over_row_ranges_matches_whole_backward(ranges, skip):
         assert rel_fro(got.float().cpu(), want.float().cpu()) <= 1e-2, (key, rel_fro(got.float().cpu(), want.float().cpu()))
 
 
-def test_two_row_ranges_sharing_slabs_zigzag_style():
+@pytest.mark.parametrize("D,skip", [(64, False), (128, True)])
+def test_two_row_ranges_sharing_slabs_zigzag_style(D, skip):
     """One owner of the row-tile blocks {0, 3} and another of {1, 2} (the zig-zag assignment of two ranks), every owner
-    with its two blocks in shared slabs (row_offset): forward and backward against the whole-sequence kernels."""
-    from universal_attention_triton_b200 import ops
-    shape = (1, 1, 2, 1024, 128, 64)
+    with its two blocks in shared slabs (row_offset): forward and backward against the whole-sequence kernels.  The first
+    owner hands the forward's decay-prefix table and log-sum-exp to its backward, the second lets the backward recompute
+    them.  (head_dim 128: without the gradient through the rows before a chunk, which has no row-range kernel there.)"""
+    from universal_attention_triton_b200 import _lib, ops
+    shape = (1, 1, 2, 1024, 128, D)
     B, H, R, L, c, D = shape
     n, nb = L // c, 2                                       # 4 blocks of 2 tiles
     ins, _ = _bf16_case(*shape, seed=81)
@@ -363,8 +366,13 @@ def test_two_row_ranges_sharing_slabs_zigzag_style():
     gen = torch.Generator(device="cuda").manual_seed(10)
     g_out = torch.randn(B, H, n, R, L, D, generator=gen, device="cuda", dtype=torch.bfloat16)
     g_lse = torch.randn(B, H, n, R, L, generator=gen, device="cuda")
+    flags = _lib.FLAG_SKIP_MASKED_GRADS if skip else 0
+    if skip:
+        valid = (torch.arange(L).view(1, L) >= torch.arange(n).view(n, 1) * c).cuda().view(1, 1, n, 1, L)
+        g_out = g_out * valid.unsqueeze(-1)
+        g_lse = g_lse * valid
     out_full, lse_full, _ = ops.forward_cm(kc, vc, xq, ss, sd)
-    ref = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse)
+    ref = ops.backward_cm(kc, vc, xq, ss, sd, g_out, g_lse, flags=flags)
     owners = [[0, 3], [1, 2]]
     rows_of = lambda blks: torch.cat([torch.arange(p * nb * 128, (p + 1) * nb * 128) for p in blks]).cuda()
     # decay totals of every block, carries in block order
@@ -378,12 +386,15 @@ def test_two_row_ranges_sharing_slabs_zigzag_style():
         carries[p] = run
         run = run + totals[p]
     results = []
-    for blks in owners:
+    for oi, blks in enumerate(owners):
         idx = rows_of(blks)
         xq_l, sd_l = xq[:, :, :, idx].contiguous(), sd[:, :, idx].contiguous()
         out = ops.alloc_forward_rows(kc, xq_l)
+        table = ops.alloc_carry_table(kc) if oi == 0 else None
+        assert oi == 1 or table is not None
         for li, p in enumerate(blks):
-            ops.forward_rows_cm(kc, vc, xq_l, ss, sd_l, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * 128, out=out)
+            ops.forward_rows_cm(kc, vc, xq_l, ss, sd_l, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * 128, out=out,
+                                carry_table=table)
         assert ((out[1] - lse_full[:, :, :, :, idx]).abs() <= 1e-3 + 1e-6 * lse_full[:, :, :, :, idx].abs()).all()
         err = (out[0].float() - out_full[:, :, :, :, idx].float()).abs()
         assert (err <= 2e-2 + out_full[:, :, :, :, idx].float().abs() * 2.0 ** -7).all()
@@ -391,8 +402,9 @@ def test_two_row_ranges_sharing_slabs_zigzag_style():
         go, gl = g_out[:, :, :, :, idx].contiguous(), g_lse[:, :, :, :, idx].contiguous()
         dct = {}
         for li, p in enumerate(blks):
+            kept = {"carry_table": table, "lse_cm_rows": out[1]} if table is not None else {}
             dct[p] = ops.backward_rows(kc, vc, xq_l, ss, sd_l, go, gl, p * nb, (p + 1) * nb, carry_in=carries[p],
-                                       row_offset=li * nb * 128, acc=acc)[5]
+                                       row_offset=li * nb * 128, acc=acc, flags=flags, **kept)[5]
         results.append((blks, idx, sd_l, acc, dct))
     all_dct = {}
     for r_ in results:

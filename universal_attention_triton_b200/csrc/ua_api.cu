@@ -428,6 +428,14 @@ int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
                 const void* xq_rows, const void* static_src, const void* static_dest_rows, const float* carry_in,
                 void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, void* workspace, size_t workspace_bytes,
                 int flags, void* stream) {
+  return ua_fwd_rows_keep(dims, dtype, gate_dtype, rows, kc, vc, xq_rows, static_src, static_dest_rows, carry_in, out_cm_rows,
+                          lse_cm_rows, denom_cm_rows, nullptr, workspace, workspace_bytes, flags, stream);
+}
+
+int ua_fwd_rows_keep(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
+                     const void* xq_rows, const void* static_src, const void* static_dest_rows, const float* carry_in,
+                     void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, float* carry_table_out, void* workspace,
+                     size_t workspace_bytes, int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -441,7 +449,7 @@ int ua_fwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
   ua::sm100::FwdParams fp{};
   fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows;
   fp.out = static_cast<bf16*>(out_cm_rows); fp.lse = lse_cm_rows; fp.denom = static_cast<bf16*>(denom_cm_rows);
-  fp.status = static_cast<int*>(workspace); fp.carry = nullptr;
+  fp.status = static_cast<int*>(workspace); fp.carry = carry_table_out;
   fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
   fp.carry_in = carry_in; fp.total_out = nullptr;
   return ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq_rows, fp, !(flags & UA_FLAG_SKIP_MASKED_FILL), st);
@@ -471,8 +479,10 @@ int ua_decay_totals_rows(const UaDims* dims, int dtype, int gate_dtype, const Ua
 size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
-  if (!ua::sm100::bwd_supported(s, dtype)) return 0;
-  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 256 * sizeof(float), 256);      // status | decay-prefix table
+  if (!ua::sm100::bwd2_supported(s, dtype)) return 0;
+  // status | decay-prefix table | log-sum-exp of the range's rows | fp32 copy of a bf16 g_denom (both sized for Ls = L)
+  const size_t rows = (size_t)s.B * s.H * s.N * s.R * s.L;
+  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 256 * sizeof(float), 256) + 2 * align_up(rows * sizeof(float), 256);
 }
 
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
@@ -480,6 +490,17 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
                 const void* g_denom_cm_rows, int g_denom_dtype, const float* carry_in, const float* suffix_in,
                 float* dk_f32, float* dv_f32, float* dxq_rows_f32, float* dsrc_f32, float* ddest_rows_f32,
                 float* dctot_out, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  return ua_bwd_rows_kept(dims, dtype, gate_dtype, rows, kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows,
+                          g_denom_cm_rows, g_denom_dtype, carry_in, suffix_in, nullptr, nullptr, dk_f32, dv_f32, dxq_rows_f32,
+                          dsrc_f32, ddest_rows_f32, dctot_out, workspace, workspace_bytes, flags, stream);
+}
+
+int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
+                     const void* xq_rows, const void* static_src, const void* static_dest_rows, const void* g_out_cm_rows,
+                     const void* g_denom_cm_rows, int g_denom_dtype, const float* carry_in, const float* suffix_in,
+                     const float* carry_table, const float* lse_cm_rows, float* dk_f32, float* dv_f32, float* dxq_rows_f32,
+                     float* dsrc_f32, float* ddest_rows_f32, float* dctot_out, void* workspace, size_t workspace_bytes,
+                     int flags, void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -491,23 +512,61 @@ int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* row
       !aligned16(dv_f32) || !aligned16(dxq_rows_f32))
     return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
-  if ((e = check_rows(s, ua::sm100::bwd_supported(s, dtype), rows))) return e;
+  if ((e = check_rows(s, ua::sm100::bwd2_supported(s, dtype), rows))) return e;
+  const bool skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) != 0;
+  // the gradient through the rows before a chunk has a row-range kernel at head_dim 64 only
+  if (!skip_masked && !ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
   const size_t need = ua_bwd_rows_workspace_bytes(dims, dtype);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   char* ws = static_cast<char*>(workspace);
   if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::BwdParams bp{};
-  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
-  bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-  float* carry_tab = reinterpret_cast<float*>(ws + 256);
-  bp.carry = carry_tab;
-  bp.acc_dk = dk_f32; bp.acc_dq = dxq_rows_f32; bp.acc_dt = ddest_rows_f32;
-  bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws);
-  bp.skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) ? 1 : 0;
-  bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix_in; bp.dctot_out = dctot_out; bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.decay_only = 0; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0; bp.gd_f32 = nullptr;
-  return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, carry_tab, true, carry_in, st);
+  const size_t BHs = (size_t)s.B * s.H;
+  const size_t tab_bytes = align_up(BHs * s.N * (size_t)s.N * 256 * sizeof(float), 256);
+  const size_t row_elems = BHs * s.N * (size_t)s.R * rows->rows_total;
+  const float* carry_tab = carry_table;
+  const float* lse_rows = lse_cm_rows;
+  float* gd_tmp = reinterpret_cast<float*>(ws + 256 + tab_bytes + align_up(BHs * s.N * (size_t)s.R * s.L * sizeof(float), 256));
+  // (1) log-sum-exp and decay-prefix table of the range, unless the forward handed them over: the forward kernel without
+  // its output (carry_in enters here)
+  if (!carry_table || !lse_cm_rows) {
+    float* tab = reinterpret_cast<float*>(ws + 256);
+    float* lse_ws = reinterpret_cast<float*>(ws + 256 + tab_bytes);
+    carry_tab = tab; lse_rows = lse_ws;
+    ua::sm100::FwdParams fp{};
+    fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows; fp.out = nullptr; fp.denom = nullptr; fp.lse = lse_ws;
+    fp.status = reinterpret_cast<int*>(ws); fp.carry = tab;
+    fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
+    fp.carry_in = carry_in; fp.total_out = nullptr;
+    if ((e = ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq_rows, fp, false, st))) return e;
+  }
+  const float* gd32 = static_cast<const float*>(g_denom_cm_rows);
+  if (g_denom_dtype != UA_F32) {
+    widen_bf16_kernel<<<148 * 8, 256, 0, st>>>(static_cast<const bf16*>(g_denom_cm_rows), gd_tmp, row_elems);
+    if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+    gd32 = gd_tmp;
+  }
+  if (!aligned16(gd32) || !aligned16(static_dest_rows) || !aligned16(carry_tab) || !aligned16(lse_rows)) return UA_ERR_ALIGNMENT;
+  // (2) rows of the range that lie before a chunk (uniform softmax): the closed-form phase of the rows-on-lanes kernel
+  if (!skip_masked) {
+    ua::sm100::BwdParams bp{};
+    bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
+    bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
+    bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = dxq_rows_f32; bp.acc_dt = ddest_rows_f32;
+    bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws); bp.skip_masked = 0;
+    ua::sm100::whole_sequence(bp);
+    bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
+    bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.masked_only = 1; bp.gd_f32 = gd32;
+    if ((e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, nullptr, false, nullptr, st))) return e;
+  }
+  // (3) the rows that see their chunk: the keys-on-lanes kernel over the range
+  ua::sm100::Bwd2Params qp{};
+  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = gd32; qp.lse = lse_rows; qp.carry = carry_tab;
+  qp.acc_dk = dk_f32; qp.acc_dq = dxq_rows_f32; qp.acc_dt = ddest_rows_f32; qp.acc_dv_in = nullptr; qp.dv_chunk = nullptr;
+  qp.dvc = nullptr; qp.dss = nullptr; qp.status = reinterpret_cast<int*>(ws); qp.trace = nullptr;
+  qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
+  qp.heads = s.R; qp.suffix_in = suffix_in; qp.dctot_out = dctot_out; qp.acc_dv = dv_f32; qp.acc_ds = dsrc_f32;
+  return ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, xq_rows, g_out_cm_rows, qp, st);
 }
 
 int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
@@ -519,17 +578,19 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   if (!kc || !vc || !static_src || !static_dest_rows || !suffix || !dk_f32 || !dsrc_f32 || !ddest_rows_f32) return UA_ERR_NULL_POINTER;
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(dk_f32)) return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
-  if ((e = check_rows(s, ua::sm100::bwd_supported(s, dtype), rows))) return e;
+  if ((e = check_rows(s, ua::sm100::bwd2_supported(s, dtype), rows))) return e;
   if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  if (!aligned16(static_dest_rows)) return UA_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
-  ua::sm100::BwdParams bp{};
-  bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows; bp.g_denom = nullptr; bp.g_denom_is_f32 = 1;
-  bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = nullptr; bp.acc_dt = ddest_rows_f32; bp.dvc = nullptr; bp.dss = nullptr;
-  bp.status = static_cast<int*>(workspace); bp.skip_masked = 1;
-  bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-  bp.suffix_in = suffix; bp.dctot_out = nullptr; bp.acc_dv = nullptr; bp.acc_ds = dsrc_f32; bp.decay_only = 1; bp.lse = nullptr; bp.merged = 0; bp.row_lse = nullptr; bp.row_delta = nullptr; bp.masked_only = 0; bp.gd_f32 = nullptr;
-  return ua::sm100::launch_bwd(s, gate_dtype, kc, vc, nullptr, nullptr, bp, nullptr, false, nullptr, st);
+  // the keys-on-lanes kernel without heads: recomputed G, the decay gradient that `suffix` induces, the two dK products
+  ua::sm100::Bwd2Params qp{};
+  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = nullptr; qp.lse = nullptr; qp.carry = nullptr;
+  qp.acc_dk = dk_f32; qp.acc_dq = nullptr; qp.acc_dt = ddest_rows_f32; qp.acc_dv_in = nullptr; qp.dv_chunk = nullptr;
+  qp.dvc = nullptr; qp.dss = nullptr; qp.status = static_cast<int*>(workspace); qp.trace = nullptr;
+  qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
+  qp.heads = 0; qp.suffix_in = suffix; qp.dctot_out = nullptr; qp.acc_dv = nullptr; qp.acc_ds = dsrc_f32;
+  return ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, nullptr, nullptr, qp, st);
 }
 
 int ua_bwd(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
@@ -662,7 +723,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
       if (e) return e;
     }
     ua::sm100::Bwd2Params qp{};
-    qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest;
+    qp.s = s; ua::sm100::whole_sequence(qp); qp.ssrc = static_src; qp.sdest = static_dest;
     qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
@@ -953,7 +1014,7 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
   }
   ua::sm100::Bwd2Params qp{};
   if (!aligned16(row_lse) || !aligned16(row_delta) || !aligned16(static_dest) || !aligned16(carry_tab)) return UA_ERR_ALIGNMENT;
-  qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr;
+  qp.s = s; ua::sm100::whole_sequence(qp); qp.ssrc = static_src; qp.sdest = static_dest; qp.g_denom = nullptr;
   qp.lse = nullptr; qp.row_lse = row_lse; qp.row_delta = row_delta; qp.carry = carry_tab;
   qp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
   qp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);

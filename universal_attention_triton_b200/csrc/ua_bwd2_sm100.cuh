@@ -59,6 +59,15 @@ struct Bwd2Params {
   void* dss;
   int* status;
   long long* trace;          // profile builds only: per-unit time stamps of block UA_PROFILE_BLOCK (else null)
+  // Range of row tiles [j_begin, j_end) (sequence-chunk sharding; whole sequence: 0, N, L, 0).  The row-indexed tensors
+  // (xq, g_out, g_denom, lse, static_dest, acc_dq, acc_dt) are slabs of Lr rows that hold the range at row r0; keys,
+  // values, static_src and the key-side accumulators always span the whole sequence.
+  int j_begin, j_end, Lr, r0;
+  int heads;                 // query heads to process: R, or 0 for the correction pass (only what suffix_in induces)
+  const float* suffix_in;    // optional (b*h*n, 128): reverse decay carry entering from the rows after the range
+  float* dctot_out;          // optional (b*h*n, 128): per key, sum of dC over the rows of the range (what earlier ranges need)
+  float* acc_dv;             // optional (b*h, L, D) fp32: dV_i is ADDED here instead of being written to dvc
+  float* acc_ds;             // optional (b*h, L) fp32: d static_src is ADDED here instead of being written to dss
 };
 
 template <int D>
@@ -121,6 +130,7 @@ struct Bwd2Ctx {
   uint32_t tmem;
   volatile int* abort_flag;
   int i, bh, nht;
+  int jtop, jb, r0;          // the sweep starts at row tile jtop - 1; the slabs hold row tile jb at row r0
   __device__ __forceinline__ uint32_t bar(int idx) const { return bars + 8u * idx; }
   __device__ __forceinline__ void note_failure(int idx, uint32_t parity) const {
     atomicCAS(const_cast<int*>(abort_flag) + 1, 0, (idx + 1) | ((int)threadIdx.x << 8) | ((int)(parity & 0x7ff) << 20));
@@ -137,9 +147,11 @@ struct Bwd2Ctx {
   }
   __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
   // half tile ht of the sweep: row tile j (descending), upper half first
-  __device__ __forceinline__ int tile_j(int ht, int N) const { return N - 1 - (ht >> 1); }
+  __device__ __forceinline__ int tile_j(int ht) const { return jtop - 1 - (ht >> 1); }
   __device__ __forceinline__ int half_of(int ht) const { return 1 - (ht & 1); }
-  __device__ __forceinline__ int row0_of(int ht, int N) const { return tile_j(ht, N) * 128 + 64 * half_of(ht); }
+  // first row of half tile ht: in the sequence (keys of the same positions, the diagonal), and inside the slabs
+  __device__ __forceinline__ int row0_of(int ht) const { return tile_j(ht) * 128 + 64 * half_of(ht); }
+  __device__ __forceinline__ int srow0_of(int ht) const { return r0 + (tile_j(ht) - jb) * 128 + 64 * half_of(ht); }
 };
 
 // Optional phase timing (compile with -DUA_PROFILE_BWD2): thread 0 of worker warp 4 of block UA_PROFILE_BLOCK accumulates
@@ -210,14 +222,17 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
       tma_load_2d(sb + Cfg::oVi + b * 16384 + h * 8192, tmV, b * 64, krow + h * 64, c.bar(qKvFull));
     }
   // per-half-tile tables: decay prefix of the 128 keys at the start of the half tile, raw static_dest of its 64 rows
-  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * L;
+  const TG* sd = static_cast<const TG*>(p.sdest) + (size_t)c.bh * p.Lr;
+  const int Rh = p.heads;
   auto load_tables = [&](int ht) -> bool {
     const int tb = ht % Cfg::kTab, use = ht / Cfg::kTab;
     if (use >= 1 && !c.wait(qDgReady, ht - Cfg::kTab)) return false;      // the half tile that used the buffer is done with it
     const uint32_t dst = sb + Cfg::oHtTab + tb * Cfg::kHtTab;
-    mbar_expect_tx(c.bar(qTabFull + tb), 512 + 64 * (uint32_t)sizeof(TG));
-    bulk_load_1d(dst, p.carry + ((chunk_id * N + c.tile_j(ht, N)) * 2 + c.half_of(ht)) * 128, 512, c.bar(qTabFull + tb));
-    bulk_load_1d(dst + 512, sd + c.row0_of(ht, N), 64 * (uint32_t)sizeof(TG), c.bar(qTabFull + tb));
+    // (the correction pass has no heads and needs no decay prefix: only the gate values travel)
+    mbar_expect_tx(c.bar(qTabFull + tb), (Rh > 0 ? 512u : 0u) + 64 * (uint32_t)sizeof(TG));
+    if (Rh > 0)
+      bulk_load_1d(dst, p.carry + ((chunk_id * N + c.tile_j(ht)) * 2 + c.half_of(ht)) * 128, 512, c.bar(qTabFull + tb));
+    bulk_load_1d(dst + 512, sd + c.srow0_of(ht), 64 * (uint32_t)sizeof(TG), c.bar(qTabFull + tb));
     return true;
   };
   if (!load_tables(0)) return;
@@ -225,7 +240,7 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
   // the head); a slot is refilled as soon as the MMAs that read it have completed
   int hc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
-    const int row0 = c.row0_of(ht, N);
+    const int row0 = c.row0_of(ht), srow0 = c.srow0_of(ht);
     if (ht + 1 < c.nht && !load_tables(ht + 1)) return;
     {
       const int sl = ht % Cfg::kKj, use = ht / Cfg::kKj;
@@ -235,11 +250,11 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
       for (int b = 0; b < Cfg::kBoxes; ++b)
         tma_load_2d(sb + Cfg::oKj + sl * Cfg::kHalf + b * 8192, tmK, b * 64, c.bh * L + row0, c.bar(qKjFull + sl));
     }
-    for (int r = 0; r < R; ++r, ++hc) {
+    for (int r = 0; r < Rh; ++r, ++hc) {
       const int sl = hc % Cfg::kNS, use = hc / Cfg::kNS;
       if (use >= 1 && !c.wait(qInFree + sl, use - 1)) return;
-      const int qrow = (c.bh * R + r) * L + row0;
-      const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * L + row0);
+      const int qrow = (c.bh * R + r) * p.Lr + srow0;
+      const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * p.Lr + srow0);
       const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot, tab = sb + Cfg::oHeadTab + sl * 512;
       mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf + 512);
 #pragma unroll
@@ -263,7 +278,7 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
 template <int D>
 __device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p) {
   using Cfg = Bwd2Cfg<D>;
-  const int R = p.s.R;
+  const int R = p.heads;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_g = idesc_bf16(128, 64, 0, 0);
   // D[128 keys x 64 rows] = A[128][D] B[64][D]^T, both K-major; A boxes 16 KB apart, B boxes 8 KB apart
@@ -300,7 +315,7 @@ __device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p
   UQ_DECL
   for (int ht = 0; ht < c.nht; ++ht) {
     if (!c.wait(qKjFull + ht % Cfg::kKj, ht / Cfg::kKj)) return;
-    if (!unit_g(ht)) return;                                        // G for the decay recomputation
+    if (R > 0 && !unit_g(ht)) return;                               // G for the decay recomputation (none without heads)
     UQ(0)
     for (int r = 0; r < R; ++r, ++hc) {
       const int sl = hc % Cfg::kNS, b = u % Cfg::kNB;
@@ -333,7 +348,7 @@ __device__ __forceinline__ void bwd2_front(const Bwd2Ctx& c, const Bwd2Params& p
 template <int D, int CG>
 __device__ __forceinline__ void bwd2_back(const Bwd2Ctx& c, const Bwd2Params& p, const int which) {
   using Cfg = Bwd2Cfg<D>;
-  const int R = p.s.R;
+  const int R = p.heads;
   const uint32_t sb = smem_u32(c.smem);
   constexpr uint32_t id_kn = idesc_bf16(128, D, 0, 1);     // A K-major (or TMEM), B MN-major
   constexpr uint32_t id_tn = idesc_bf16(128, D, 1, 1);     // A MN-major, B MN-major
@@ -495,7 +510,7 @@ __device__ __forceinline__ float warp_colsum(float* v, float* scr, int lane) {
 template <int D>
 __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmDQ, const CUtensorMap* tmDK) {
   using Cfg = Bwd2Cfg<D>;
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int L = p.s.L, R = p.s.R, Rh = p.heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = (warp & 3) * 32 + lane;               // 0..63
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -504,16 +519,16 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
   uint8_t* sStage = c.smem + Cfg::oStage;
   int yc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
-    const int row0 = c.row0_of(ht, N);
-    for (int r = 0; r <= R; ++r, ++yc) {
+    const int row0 = c.row0_of(ht), srow0 = c.srow0_of(ht);
+    for (int r = 0; r <= Rh; ++r, ++yc) {
       if (!c.wait_w(qYFull, yc)) return;
       tc_fence_after();
-      if (r == R) {
+      if (r == Rh) {
         // d static_dest of the half tile: the workers have added their column sums in shared memory (complete before dK_j
         // was issued); one global add per row, and the buffer is zero again before this Y is released
         float* dt = reinterpret_cast<float*>(c.smem + Cfg::oDt) + (ht & 1) * 64 + row;
         const float v = *dt;
-        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * L + row0 + row, v);
+        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + srow0 + row, v);
         *dt = 0.f;
       }
       if (leader) bulk_wait_read_all();                 // the previous reduce-add has read the staging tile
@@ -541,8 +556,8 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
 #else
       if (leader) {
 #endif
-        const CUtensorMap* tm = (r < R) ? tmDQ : tmDK;
-        const int y = (r < R) ? (c.bh * R + r) * L + row0 : c.bh * L + row0;
+        const CUtensorMap* tm = (r < Rh) ? tmDQ : tmDK;
+        const int y = (r < Rh) ? (c.bh * R + r) * p.Lr + srow0 : c.bh * L + row0;
 #pragma unroll
         for (int bx = 0; bx < D / 32; ++bx) tma_reduce_add_2d(tm, 32 * bx, y, smem_u32(sStage) + bx * 8192);
         bulk_commit_group();
@@ -560,7 +575,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   constexpr int NG = 64 / CG;                    // column groups
   constexpr int H2 = CG / 2;                     // packed pairs per thread
   constexpr int kWorkers = 128 * NG;
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int L = p.s.L, R = p.heads, N = p.s.N;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = (warp - 8) >> 2;                 // column group: columns [CG g, CG g + CG) of a half tile
   const int quad = warp & 3;                     // TMEM lane quadrant this warp may touch; also its helper duty inside the group
@@ -612,19 +627,20 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   if (!c.wait_w(qTabFull, 0)) return;
   if (helper && quad == 2) sT3[col0 + lane] = t3_from_table(0);
   if (g == 0) sDt[key] = 0.f;                    // both half-tile parities of the d static_dest buffer
-  float suffix = 0.f, ds_acc = 0.f;
+  const size_t key_id = ((size_t)c.bh * N + c.i) * 128 + key;
+  float suffix = p.suffix_in ? p.suffix_in[key_id] : 0.f, ds_acc = 0.f, dct = 0.f;
   named_bar_sync(kBarAll, kWorkers);
 
   int u = 0, hc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
-    const int j = c.tile_j(ht, N), half = c.half_of(ht), row0 = j * 128 + 64 * half;
+    const int j = c.tile_j(ht), half = c.half_of(ht);
     const bool diag = (j == c.i);
     const int qbase = 64 * half + col0;            // row of this thread's first column inside the 128-row tile
     const float* t3v = sT3 + (ht & 1) * 64 + col0;
 
     // ================= decay recomputation: c2 = log2(e) * decay prefix of (key, CG rows) =================
     float2 c2[H2];
-    {
+    if (R > 0) {                                   // (the correction pass has no heads: no prefix, no first G unit)
       if (!c.wait_w(qTabFull + ht % Cfg::kTab, ht / Cfg::kTab)) return;
       const float carry = reinterpret_cast<const float*>(ht_table(ht))[key];
       const int b = u % Cfg::kNB;
@@ -809,6 +825,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       }
       const float add = suffix + later;            // rows after this thread's block
       suffix = suffix + run + others;              // ... after this half tile (the next one lies below it)
+      dct += run + others;                         // the range's own dC (without what came in from the rows after it)
       const float2 add2 = make_float2(add, add);
 
       const int b = u % Cfg::kNB;
@@ -883,11 +900,13 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   if (!c.wait_w(qFinal, 0)) return;
   tc_fence_after();
   const size_t krow = (size_t)c.bh * L + c.i * 128 + key;
+  if (g == 0 && p.dctot_out) p.dctot_out[key_id] = dct;
   constexpr int kPer = D / NG;
 #pragma unroll
   for (int pc = 0; pc < kPer / 16; ++pc) {
     const int d0 = kPer * g + 16 * pc;
     uint32_t o[16];
+    if (R > 0) {                                   // (the correction pass has no heads: no dV)
     tmem_ld16(c.tmem + Cfg::tDV + lane_base + d0, o);
     tc_wait_ld();
     if (p.acc_dv_in) {
@@ -912,15 +931,24 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         o[4 * x + 3] = __float_as_uint(fmaf(ev.w, 1.0f / 128.0f, __uint_as_float(o[4 * x + 3])));
       }
     }
-    uint32_t pk[8];
+    if (p.acc_dv) {                                // several row ranges add to the same keys
+      float* dvp = p.acc_dv + krow * D + d0;
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * x]), __uint_as_float(o[2 * x + 1]));
-      pk[x] = *reinterpret_cast<uint32_t*>(&h);
+      for (int x = 0; x < 4; ++x)
+        red_add_v4(dvp + 4 * x, __uint_as_float(o[4 * x]), __uint_as_float(o[4 * x + 1]), __uint_as_float(o[4 * x + 2]),
+                   __uint_as_float(o[4 * x + 3]));
+    } else {
+      uint32_t pk[8];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[2 * x]), __uint_as_float(o[2 * x + 1]));
+        pk[x] = *reinterpret_cast<uint32_t*>(&h);
+      }
+      uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * D + d0);
+      dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+      dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
     }
-    uint4* dst = reinterpret_cast<uint4*>(p.dvc + krow * D + d0);
-    dst[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-    dst[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+    }
     tmem_ld16(c.tmem + Cfg::tDK + lane_base + d0, o);
     tc_wait_ld();
     float* dkp = p.acc_dk + krow * D + d0;
@@ -935,7 +963,8 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     float tot = 0.f;
 #pragma unroll
     for (int q = 0; q < NG; ++q) tot += sXch[q * 128 + key];
-    Num<TG>::st(static_cast<TG*>(p.dss) + krow, tot / (3.0f * s3 * s3));
+    if (p.acc_ds) atomicAdd(p.acc_ds + krow, tot / (3.0f * s3 * s3));
+    else Num<TG>::st(static_cast<TG*>(p.dss) + krow, tot / (3.0f * s3 * s3));
   }
 }
 
@@ -958,7 +987,13 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
   c.abort_flag = reinterpret_cast<volatile int*>(misc + 1);
   c.i = blockIdx.x / BH;                       // heavy chunks (small i: most rows) first
   c.bh = blockIdx.x - c.i * BH;
-  c.nht = 2 * (p.s.N - c.i);
+  c.jtop = p.j_end; c.jb = p.j_begin; c.r0 = p.r0;
+  c.nht = 2 * (p.j_end - (c.i > p.j_begin ? c.i : p.j_begin));
+  if (c.nht <= 0) {
+    // no row of the range sees this chunk (sequence sharding only): nothing to add anywhere
+    if (p.dctot_out && threadIdx.x < 128) p.dctot_out[((size_t)c.bh * p.s.N + c.i) * 128 + threadIdx.x] = 0.f;
+    return;
+  }
 
   if (threadIdx.x == 0) {
     misc[1] = 0;

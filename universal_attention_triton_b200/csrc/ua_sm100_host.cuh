@@ -158,6 +158,14 @@ inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void
 #endif
 constexpr int kBwd2Cols = UA_BWD2_COLS;      // columns of a half tile per worker thread (32: eight worker warps with ~190 registers each; 16: sixteen)
 
+// Fills the row-range fields of Bwd2Params for a call over the whole sequence.
+inline void whole_sequence(Bwd2Params& p) {
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.heads = p.s.R;
+  p.suffix_in = nullptr; p.dctot_out = nullptr; p.acc_dv = nullptr; p.acc_ds = nullptr;
+}
+
+// Backward over the row tiles [p.j_begin, p.j_end) (the caller sets the range fields, e.g. with whole_sequence()).
+// With p.heads == 0 (correction pass) xq, g_out and p.acc_dq are not touched and may be null.
 template <int D, typename TG, int kMode>
 int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const Bwd2Params& p,
                   cudaStream_t st) {
@@ -165,10 +173,15 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
   CUtensorMap tmK, tmV, tmQ, tmG, tmDQ, tmDK;
   const uint64_t BH = (uint64_t)s.B * s.H;
   if (!make_rows_map(&tmK, kc, BH * s.L, D, 64) || !make_rows_map(&tmV, vc, BH * s.L, D, 64) ||
-      !make_rows_map(&tmQ, xq, BH * s.R * s.L, D, 64) ||
-      !make_rows_map(&tmG, g_out, (kMode == 2 ? BH : BH * s.N) * s.R * s.L, D, 64) ||
-      !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * s.L, D, 64) || !make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L, D, 64))
+      !make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L, D, 64))
     return UA_ERR_CUDA;
+  if (p.heads == 0) {
+    tmQ = tmK; tmG = tmK; tmDQ = tmDK;       // never used
+  } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, D, 64) ||
+             !make_rows_map(&tmG, g_out, (kMode == 2 ? BH : BH * s.N) * s.R * p.Lr, D, 64) ||
+             !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr, D, 64)) {
+    return UA_ERR_CUDA;
+  }
   auto kern = bwd2_kernel<D, TG, kMode, kBwd2Cols>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);

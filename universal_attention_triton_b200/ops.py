@@ -373,8 +373,18 @@ def alloc_forward_rows(kc, xq_rows):
             torch.empty(b, h, n, r, Ls, dtype=dt, device=dev))
 
 
+def alloc_carry_table(kc):
+    """The decay-prefix table that ``forward_rows_cm(carry_table=...)`` fills and ``backward_rows(carry_table=...)`` reads
+    (one table serves all the row ranges of a rank), or ``None`` for shapes whose backward does not use one."""
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    dims = UaDims(b, h, 1, n, c, d)
+    nbytes = lib.ua_carry_bytes(ctypes.byref(dims), _dtype_code(kc.dtype), 0)
+    return torch.empty(nbytes // 4, dtype=torch.float32, device=kc.device) if nbytes else None
+
+
 def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: int, tile_end: int, carry_in=None,
-                    flags: int = 0, row_offset: int = 0, out=None):
+                    flags: int = 0, row_offset: int = 0, out=None, carry_table=None):
     """Forward for the row tiles [tile_begin, tile_end), written into the rows [row_offset, ...) of the output slabs
     ``out`` (from ``alloc_forward_rows``; allocated here when None).  ``kc``, ``vc``, ``static_src`` cover the whole
     sequence; ``xq_rows`` (b,h,r,Ls,d) / ``static_dest_rows`` (b,h,Ls) are slabs; ``carry_in`` (b,h,n,128): sum of the
@@ -394,9 +404,9 @@ def forward_rows_cm(kc, vc, xq_rows, static_src, static_dest_rows, tile_begin: i
         out_cm, lse_cm, denom_cm = out if out is not None else alloc_forward_rows(kc, q)
         ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
         ci = carry_in.float().contiguous() if carry_in is not None else None
-        rc = lib.ua_fwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
-                             _ptr(ss), _ptr(sd), _ptr(ci), _ptr(out_cm), _ptr(lse_cm), _ptr(denom_cm), _ptr(ws), 256, flags,
-                             _stream())
+        rc = lib.ua_fwd_rows_keep(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
+                                  _ptr(ss), _ptr(sd), _ptr(ci), _ptr(out_cm), _ptr(lse_cm), _ptr(denom_cm), _ptr(carry_table),
+                                  _ptr(ws), 256, flags, _stream())
         _lib.check(rc, "ua_fwd_rows")
         _check_status(lib, ws, "ua_fwd_rows")
     return out_cm, lse_cm, denom_cm
@@ -412,10 +422,13 @@ def alloc_backward_rows(kc, xq_rows):
 
 
 def backward_rows(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows, tile_begin: int,
-                  tile_end: int, carry_in=None, suffix_in=None, flags: int = 0, row_offset: int = 0, acc=None):
+                  tile_end: int, carry_in=None, suffix_in=None, flags: int = 0, row_offset: int = 0, acc=None,
+                  carry_table=None, lse_cm_rows=None):
     """Backward for the row tiles [tile_begin, tile_end) (sequence sharding), ADDED into the fp32 accumulators ``acc``
     (from ``alloc_backward_rows``; allocated here when None).  Returns ``(dk, dv, dxq, dsrc, ddest, dctot)``: dk, dv,
-    dsrc are partial sums over ALL keys; dctot (b,h,n,128) is the per-key sum of the decay-prefix gradient over the rows."""
+    dsrc are partial sums over ALL keys; dctot (b,h,n,128) is the per-key sum of the decay-prefix gradient over the rows.
+    ``carry_table`` / ``lse_cm_rows``: what ``forward_rows_cm`` produced for the same range (table from
+    ``alloc_carry_table``, the fp32 log-sum-exp slab); with both, no part of the forward is run again."""
     _require_cuda(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, g_denom_cm_rows)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
@@ -439,10 +452,13 @@ def backward_rows(kc, vc, xq_rows, static_src, static_dest_rows, g_out_cm_rows, 
         ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
         ci = carry_in.float().contiguous() if carry_in is not None else None
         si = suffix_in.float().contiguous() if suffix_in is not None else None
-        rc = lib.ua_bwd_rows(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
-                             _ptr(ss), _ptr(sd), _ptr(g_out_cm_rows), _ptr(g_denom_cm_rows), _dtype_code(g_denom_cm_rows.dtype),
-                             _ptr(ci), _ptr(si), _ptr(dk), _ptr(dv), _ptr(dxq), _ptr(dsrc), _ptr(ddest), _ptr(dctot),
-                             _ptr(ws), ws_bytes, flags, _stream())
+        if lse_cm_rows is not None:
+            assert lse_cm_rows.dtype == torch.float32 and lse_cm_rows.is_contiguous()
+        rc = lib.ua_bwd_rows_kept(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc), _ptr(q),
+                                  _ptr(ss), _ptr(sd), _ptr(g_out_cm_rows), _ptr(g_denom_cm_rows),
+                                  _dtype_code(g_denom_cm_rows.dtype), _ptr(ci), _ptr(si), _ptr(carry_table), _ptr(lse_cm_rows),
+                                  _ptr(dk), _ptr(dv), _ptr(dxq), _ptr(dsrc), _ptr(ddest), _ptr(dctot),
+                                  _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_bwd_rows")
         _check_status(lib, ws, "ua_bwd_rows")
     return dk, dv, dxq, dsrc, ddest, dctot

@@ -46,6 +46,7 @@ class CudaBackend:
     backward_rows = staticmethod(ops.backward_rows)
     backward_rows_suffix = staticmethod(ops.backward_rows_suffix)
     alloc_backward_rows = staticmethod(ops.alloc_backward_rows)
+    alloc_carry_table = staticmethod(ops.alloc_carry_table)     # (backends without it: the backward recomputes)
 
 
 def owned_blocks(world: int, rank: int, zigzag: bool):
@@ -160,11 +161,15 @@ def sp_forward(kc_local, vc_local, xq_local, static_src_local, static_dest_local
     world, rank, P, mine, nb, kc, vc, ss, sd, carries = setup
     xq = xq_local.contiguous()
     out = backend.alloc_forward_rows(kc, xq)
+    # with return_ctx the forward also hands its decay-prefix table and log-sum-exp to the backward
+    table = backend.alloc_carry_table(kc) if (return_ctx and hasattr(backend, "alloc_carry_table")) else None
+    extra = {"carry_table": table} if table is not None else {}
     for li, p in enumerate(mine):
-        backend.forward_rows_cm(kc, vc, xq, ss, sd, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * kc.shape[3], out=out)
+        backend.forward_rows_cm(kc, vc, xq, ss, sd, p * nb, (p + 1) * nb, carries[p], row_offset=li * nb * kc.shape[3], out=out,
+                                **extra)
     out_cm, lse_cm, denom_cm = out
     res = (ops.as_reference_out(out_cm), ops.as_reference_denom(denom_cm), ops.as_reference_denom(lse_cm))
-    return res + (setup,) if return_ctx else res
+    return res + (setup + ((table, lse_cm) if table is not None else ()),) if return_ctx else res
 
 
 def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_local, g_out_local, g_denom_local,
@@ -175,7 +180,8 @@ def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_loca
     from . import _lib
     if ctx is None:         # ``ctx``: what ``sp_forward(return_ctx=True)`` returned for the same inputs and assignment
         ctx = _setup(kc_local, vc_local, static_src_local, static_dest_local, group, backend, zigzag)
-    world, rank, P, mine, nb, kc, vc, ss, sd, carries = ctx
+    world, rank, P, mine, nb, kc, vc, ss, sd, carries = ctx[:10]
+    kept = {"carry_table": ctx[10], "lse_cm_rows": ctx[11]} if len(ctx) > 10 else {}
     flags = _lib.FLAG_SKIP_MASKED_GRADS if skip_masked_grads else 0
     xq = xq_local.contiguous()
     g_out_cm = ops.out_to_chunk_major(g_out_local)
@@ -184,7 +190,7 @@ def sp_backward(kc_local, vc_local, xq_local, static_src_local, static_dest_loca
     dctots = []
     for li, p in enumerate(mine):
         res = backend.backward_rows(kc, vc, xq, ss, sd, g_out_cm, g_den_cm, p * nb, (p + 1) * nb, carry_in=carries[p],
-                                    flags=flags, row_offset=li * nb * kc.shape[3], acc=acc)
+                                    flags=flags, row_offset=li * nb * kc.shape[3], acc=acc, **kept)
         dctots.append(res[5])
     dk, dv, dxq, dsrc, ddest = acc
     all_dct = _gather_block_tables(dctots, world, rank, zigzag, group)
