@@ -79,18 +79,17 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
 }
 
 struct BwdWorkspaceTc {
-  size_t off_dk, off_dv, off_dq, off_dt, off_carry, off_lse, off_gd, off_mt, off_ksum, off_nacc, acc_bytes, total;
+  size_t off_dk, off_dq, off_dt, off_carry, off_lse, off_gd, off_mt, off_ksum, off_nacc, acc_bytes, total;
 };
 
-// Scratch of the tensor-core backward: status | fp32 accumulators dK, dV (the part from the rows before a chunk), dQ,
-// d dest | decay-prefix table (two entries per 128-row tile) | log-sum-exp (only written when the caller has none) |
-// fp32 copy of g_denom (only written when the caller's is bf16).
+// Scratch of the tensor-core backward: status | fp32 accumulators dK, dQ, d dest | decay-prefix table (two entries per
+// 128-row tile) | log-sum-exp (only written when the caller has none) | fp32 copy of g_denom (only written when the
+// caller's is bf16) | per-chunk data of the kernels for the rows before a chunk.
 BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   BwdWorkspaceTc w;
   const size_t BH = (size_t)s.B * s.H, f = sizeof(float);
   size_t o = 256;   // [0, 256): status word
   w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
-  w.off_dv = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
   w.off_dt = o; o = align_up(o + BH * s.L * f, 256);
   w.acc_bytes = o;
@@ -480,9 +479,11 @@ size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
   if (!ua::sm100::bwd2_supported(s, dtype)) return 0;
-  // status | decay-prefix table | log-sum-exp of the range's rows | fp32 copy of a bf16 g_denom (both sized for Ls = L)
-  const size_t rows = (size_t)s.B * s.H * s.N * s.R * s.L;
-  return 256 + align_up((size_t)s.B * s.H * s.N * (size_t)s.N * 256 * sizeof(float), 256) + 2 * align_up(rows * sizeof(float), 256);
+  // status | decay-prefix table | log-sum-exp of the range's rows | fp32 copy of a bf16 g_denom (both sized for Ls = L) |
+  // per-chunk data of the kernels for the rows before a chunk (M^T images, ksum, N / w / u / vbar)
+  const size_t rows = (size_t)s.B * s.H * s.N * s.R * s.L, chunks = (size_t)s.B * s.H * s.N;
+  return 256 + align_up(chunks * (size_t)s.N * 256 * sizeof(float), 256) + 2 * align_up(rows * sizeof(float), 256) +
+         align_up(chunks * s.D * s.D * 2, 256) + align_up(chunks * s.D * 2, 256) + align_up(chunks * (s.D + 3) * s.D * sizeof(float), 256);
 }
 
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
@@ -514,8 +515,6 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
   ua::Shape s = to_shape(dims);
   if ((e = check_rows(s, ua::sm100::bwd2_supported(s, dtype), rows))) return e;
   const bool skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) != 0;
-  // the gradient through the rows before a chunk has a row-range kernel at head_dim 64 only
-  if (!skip_masked && !ua::sm100::bwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
   const size_t need = ua_bwd_rows_workspace_bytes(dims, dtype);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -547,22 +546,24 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
     gd32 = gd_tmp;
   }
   if (!aligned16(gd32) || !aligned16(static_dest_rows) || !aligned16(carry_tab) || !aligned16(lse_rows)) return UA_ERR_ALIGNMENT;
-  // (2) rows of the range that lie before a chunk (uniform softmax): the closed-form phase of the rows-on-lanes kernel
-  if (!skip_masked) {
-    ua::sm100::BwdParams bp{};
-    bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest_rows;
-    bp.g_denom = g_denom_cm_rows; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-    bp.carry = nullptr; bp.acc_dk = dk_f32; bp.acc_dq = dxq_rows_f32; bp.acc_dt = ddest_rows_f32;
-    bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws); bp.skip_masked = 0;
-    ua::sm100::whole_sequence(bp);
-    bp.j_begin = rows->tile_begin; bp.j_end = rows->tile_end; bp.Lr = rows->rows_total; bp.r0 = rows->row_offset;
-    bp.acc_dv = dv_f32; bp.acc_ds = dsrc_f32; bp.masked_only = 1; bp.gd_f32 = gd32;
-    if ((e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq_rows, g_out_cm_rows, bp, nullptr, false, nullptr, st))) return e;
+  // (2) rows of the range that lie before a chunk (uniform softmax): their own three kernels, over the range
+  if (!skip_masked && s.N > 1) {
+    const size_t chunks = BHs * s.N;
+    char* q = ws + 256 + tab_bytes + 2 * align_up(BHs * s.N * (size_t)s.R * s.L * sizeof(float), 256);
+    ua::sm100::MaskedParams mp{};
+    mp.s = s; mp.g_denom = gd32;
+    mp.mt = reinterpret_cast<uint8_t*>(q); q += align_up(chunks * s.D * s.D * 2, 256);
+    mp.ksum = reinterpret_cast<__nv_bfloat16*>(q); q += align_up(chunks * s.D * 2, 256);
+    mp.nacc = reinterpret_cast<float*>(q);
+    mp.acc_dk = dk_f32; mp.status = reinterpret_cast<int*>(ws);
+    mp.j_begin = rows->tile_begin; mp.j_end = rows->tile_end; mp.Lr = rows->rows_total; mp.r0 = rows->row_offset;
+    mp.acc_dv = dv_f32;
+    if ((e = ua::sm100::launch_masked(s, kc, vc, xq_rows, g_out_cm_rows, dxq_rows_f32, mp, st))) return e;
   }
   // (3) the rows that see their chunk: the keys-on-lanes kernel over the range
   ua::sm100::Bwd2Params qp{};
   qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = gd32; qp.lse = lse_rows; qp.carry = carry_tab;
-  qp.acc_dk = dk_f32; qp.acc_dq = dxq_rows_f32; qp.acc_dt = ddest_rows_f32; qp.acc_dv_in = nullptr; qp.dv_chunk = nullptr;
+  qp.acc_dk = dk_f32; qp.acc_dq = dxq_rows_f32; qp.acc_dt = ddest_rows_f32; qp.dv_chunk = nullptr;
   qp.dvc = nullptr; qp.dss = nullptr; qp.status = reinterpret_cast<int*>(ws); qp.trace = nullptr;
   qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
   qp.heads = s.R; qp.suffix_in = suffix_in; qp.dctot_out = dctot_out; qp.acc_dv = dv_f32; qp.acc_ds = dsrc_f32;
@@ -586,7 +587,7 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   // the keys-on-lanes kernel without heads: recomputed G, the decay gradient that `suffix` induces, the two dK products
   ua::sm100::Bwd2Params qp{};
   qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = nullptr; qp.lse = nullptr; qp.carry = nullptr;
-  qp.acc_dk = dk_f32; qp.acc_dq = nullptr; qp.acc_dt = ddest_rows_f32; qp.acc_dv_in = nullptr; qp.dv_chunk = nullptr;
+  qp.acc_dk = dk_f32; qp.acc_dq = nullptr; qp.acc_dt = ddest_rows_f32; qp.dv_chunk = nullptr;
   qp.dvc = nullptr; qp.dss = nullptr; qp.status = static_cast<int*>(workspace); qp.trace = nullptr;
   qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
   qp.heads = 0; qp.suffix_in = suffix; qp.dctot_out = nullptr; qp.acc_dv = nullptr; qp.acc_ds = dsrc_f32;
@@ -657,7 +658,6 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     if (cudaMemsetAsync(ws, 0, w.acc_bytes, st) != cudaSuccess) return UA_ERR_CUDA;
     float* carry_tab = carry_in ? const_cast<float*>(static_cast<const float*>(carry_in)) : reinterpret_cast<float*>(ws + w.off_carry);
     float* acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
-    float* acc_dv = reinterpret_cast<float*>(ws + w.off_dv);
     float* acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
     float* acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
     const bool skip_masked = (flags & UA_FLAG_SKIP_MASKED_GRADS) != 0;
@@ -690,36 +690,14 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     // Rows before a chunk (uniform softmax): their gradient is added to the accumulators by a kernel of its own.
     const float* dv_chunk = nullptr;
     if (!skip_masked && s.N > 1) {
-      static const bool legacy = getenv("UA_MASKED_LEGACY") != nullptr;
-      if (!legacy) {
-        ua::sm100::MaskedParams mp{};
-        mp.s = s; mp.g_denom = gd32;
-        mp.mt = reinterpret_cast<uint8_t*>(ws + w.off_mt);
-        mp.ksum = reinterpret_cast<__nv_bfloat16*>(ws + w.off_ksum);
-        mp.nacc = reinterpret_cast<float*>(ws + w.off_nacc);
-        mp.acc_dk = acc_dk; mp.status = reinterpret_cast<int*>(ws);
-        dv_chunk = mp.nacc + (size_t)(s.D + 1) * s.D;
-        e = ua::sm100::launch_masked(s, kc, vc, xq, g_out_cm, acc_dq, mp, st);
-      } else if (ua::sm100::bwd_supported(s, dtype)) {
-        ua::sm100::BwdParams bp{};
-        bp.s = s; bp.ssrc = static_src; bp.sdest = static_dest;
-        bp.g_denom = g_denom_cm; bp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-        bp.carry = nullptr; bp.acc_dk = acc_dk; bp.acc_dq = acc_dq; bp.acc_dt = acc_dt;
-        bp.dvc = nullptr; bp.dss = nullptr; bp.status = reinterpret_cast<int*>(ws); bp.skip_masked = 0;
-        ua::sm100::whole_sequence(bp);
-        bp.acc_dv = acc_dv; bp.masked_only = 1; bp.gd_f32 = gd32;
-        e = ua::sm100::launch_bwd(s, gate_dtype, kc, vc, xq, g_out_cm, bp, nullptr, false, nullptr, st);
-      } else {
-        const SimtCfg mcfg = simt_cfg(s.C, s.D, dtype, true);
-        if (!mcfg.rt) return UA_ERR_UNSUPPORTED;
-        ua::simt::BwdParams mp;
-        mp.s = s; mp.kc = kc; mp.vc = vc; mp.xq = xq; mp.ssrc = static_src; mp.sdest = static_dest;
-        mp.g_out = g_out_cm; mp.g_denom = g_denom_cm; mp.g_denom_is_f32 = (g_denom_dtype == UA_F32);
-        mp.acc_dk = acc_dk; mp.acc_dv = acc_dv; mp.acc_dq = acc_dq; mp.acc_ds = acc_dt; mp.acc_dt = acc_dt;   // (nothing is added to the gates)
-        mp.carry = nullptr; mp.rt = mcfg.rt; mp.skip_masked = 0; mp.masked_only = 1;
-        if (mcfg.compact) e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, bf16>(mp, st) : launch_simt_bwd<bf16, bf16, bf16>(mp, st);
-        else e = gate_dtype == UA_F32 ? launch_simt_bwd<bf16, float, float>(mp, st) : launch_simt_bwd<bf16, bf16, float>(mp, st);
-      }
+      ua::sm100::MaskedParams mp{};
+      mp.s = s; ua::sm100::whole_sequence(mp); mp.g_denom = gd32;
+      mp.mt = reinterpret_cast<uint8_t*>(ws + w.off_mt);
+      mp.ksum = reinterpret_cast<__nv_bfloat16*>(ws + w.off_ksum);
+      mp.nacc = reinterpret_cast<float*>(ws + w.off_nacc);
+      mp.acc_dk = acc_dk; mp.status = reinterpret_cast<int*>(ws);
+      dv_chunk = mp.nacc + (size_t)(s.D + 1) * s.D;
+      e = ua::sm100::launch_masked(s, kc, vc, xq, g_out_cm, acc_dq, mp, st);
       if (e) return e;
     }
     ua::sm100::Bwd2Params qp{};
@@ -727,7 +705,6 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
-    qp.acc_dv_in = (!skip_masked && s.N > 1 && !dv_chunk) ? acc_dv : nullptr;
     qp.dv_chunk = dv_chunk; qp.dv_chunk_stride = (s.D + 3) * s.D;
     qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
     qp.trace = nullptr;
@@ -1019,7 +996,6 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
   qp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
   qp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
   qp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
-  qp.acc_dv_in = nullptr;
   qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
   qp.trace = nullptr;
   e = ua::sm100::launch_bwd2(s, gate_dtype, true, kc, vc, xq, g_merged, qp, st);

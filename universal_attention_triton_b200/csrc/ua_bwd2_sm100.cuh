@@ -35,7 +35,7 @@
 #pragma once
 #include <type_traits>
 
-#include "ua_bwd_sm100.cuh"
+#include "ua_fwd_sm100.cuh"
 
 namespace ua {
 namespace sm100 {
@@ -52,7 +52,6 @@ struct Bwd2Params {
   float* acc_dk;             // (b*h, L, D) fp32, zeroed (or holding the masked-block part)
   float* acc_dq;             // (b*h, r, L, D) fp32, likewise
   float* acc_dt;             // (b*h, L) fp32, zeroed
-  const float* acc_dv_in;    // optional (b*h, L, D) fp32: added to dV_i before it is written (masked-block part)
   const float* dv_chunk;     // optional: row dv_chunk[chunk * dv_chunk_stride + d] / 128 is added to every key's dV_i (the
   int dv_chunk_stride;       // masked-block part when it comes from the kernels of the rows before a chunk)
   __nv_bfloat16* dvc;
@@ -519,7 +518,6 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
   uint8_t* sStage = c.smem + Cfg::oStage;
   int yc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
-    const int row0 = c.row0_of(ht), srow0 = c.srow0_of(ht);
     for (int r = 0; r <= Rh; ++r, ++yc) {
       if (!c.wait_w(qYFull, yc)) return;
       tc_fence_after();
@@ -528,7 +526,7 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
         // was issued); one global add per row, and the buffer is zero again before this Y is released
         float* dt = reinterpret_cast<float*>(c.smem + Cfg::oDt) + (ht & 1) * 64 + row;
         const float v = *dt;
-        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + srow0 + row, v);
+        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + c.srow0_of(ht) + row, v);
         *dt = 0.f;
       }
       if (leader) bulk_wait_read_all();                 // the previous reduce-add has read the staging tile
@@ -557,7 +555,7 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
       if (leader) {
 #endif
         const CUtensorMap* tm = (r < Rh) ? tmDQ : tmDK;
-        const int y = (r < Rh) ? (c.bh * R + r) * p.Lr + srow0 : c.bh * L + row0;
+        const int y = (r < Rh) ? (c.bh * R + r) * p.Lr + c.srow0_of(ht) : c.bh * L + c.row0_of(ht);
 #pragma unroll
         for (int bx = 0; bx < D / 32; ++bx) tma_reduce_add_2d(tm, 32 * bx, y, smem_u32(sStage) + bx * 8192);
         bulk_commit_group();
@@ -569,13 +567,15 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
 }
 
 // CG: columns of a half tile per thread (32: two column groups, 8 worker warps; 16: four groups, 16 worker warps)
-template <int D, typename TG, int kMode, int CG>
+// kHeads = false: the correction pass (p.heads == 0).  A compile-time switch: as a run-time condition around the decay
+// recomputation it cost the whole-sequence kernel 2 % (measured).
+template <int D, typename TG, int kMode, int CG, bool kHeads>
 __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& p) {
   using Cfg = Bwd2Cfg<D>;
   constexpr int NG = 64 / CG;                    // column groups
   constexpr int H2 = CG / 2;                     // packed pairs per thread
   constexpr int kWorkers = 128 * NG;
-  const int L = p.s.L, R = p.heads, N = p.s.N;
+  const int L = p.s.L, R = kHeads ? p.heads : 0, N = p.s.N;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = (warp - 8) >> 2;                 // column group: columns [CG g, CG g + CG) of a half tile
   const int quad = warp & 3;                     // TMEM lane quadrant this warp may touch; also its helper duty inside the group
@@ -627,20 +627,19 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   if (!c.wait_w(qTabFull, 0)) return;
   if (helper && quad == 2) sT3[col0 + lane] = t3_from_table(0);
   if (g == 0) sDt[key] = 0.f;                    // both half-tile parities of the d static_dest buffer
-  const size_t key_id = ((size_t)c.bh * N + c.i) * 128 + key;
-  float suffix = p.suffix_in ? p.suffix_in[key_id] : 0.f, ds_acc = 0.f, dct = 0.f;
+  float suffix = p.suffix_in ? p.suffix_in[((size_t)c.bh * N + c.i) * 128 + key] : 0.f, ds_acc = 0.f;
   named_bar_sync(kBarAll, kWorkers);
 
   int u = 0, hc = 0;
   for (int ht = 0; ht < c.nht; ++ht) {
-    const int j = c.tile_j(ht), half = c.half_of(ht);
+    const int j = p.j_end - 1 - (ht >> 1), half = c.half_of(ht);
     const bool diag = (j == c.i);
     const int qbase = 64 * half + col0;            // row of this thread's first column inside the 128-row tile
     const float* t3v = sT3 + (ht & 1) * 64 + col0;
 
     // ================= decay recomputation: c2 = log2(e) * decay prefix of (key, CG rows) =================
     float2 c2[H2];
-    if (R > 0) {                                   // (the correction pass has no heads: no prefix, no first G unit)
+    if (kHeads) {                                  // (the correction pass has no heads: no prefix, no first G unit)
       if (!c.wait_w(qTabFull + ht % Cfg::kTab, ht / Cfg::kTab)) return;
       const float carry = reinterpret_cast<const float*>(ht_table(ht))[key];
       const int b = u % Cfg::kNB;
@@ -825,7 +824,6 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       }
       const float add = suffix + later;            // rows after this thread's block
       suffix = suffix + run + others;              // ... after this half tile (the next one lies below it)
-      dct += run + others;                         // the range's own dC (without what came in from the rows after it)
       const float2 add2 = make_float2(add, add);
 
       const int b = u % Cfg::kNB;
@@ -900,26 +898,18 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   if (!c.wait_w(qFinal, 0)) return;
   tc_fence_after();
   const size_t krow = (size_t)c.bh * L + c.i * 128 + key;
-  if (g == 0 && p.dctot_out) p.dctot_out[key_id] = dct;
+  if (g == 0 && p.dctot_out) {                     // the range's own dC: what left minus what came in from the rows after it
+    const size_t key_id = ((size_t)c.bh * N + c.i) * 128 + key;
+    p.dctot_out[key_id] = suffix - (p.suffix_in ? p.suffix_in[key_id] : 0.f);
+  }
   constexpr int kPer = D / NG;
 #pragma unroll
   for (int pc = 0; pc < kPer / 16; ++pc) {
     const int d0 = kPer * g + 16 * pc;
     uint32_t o[16];
-    if (R > 0) {                                   // (the correction pass has no heads: no dV)
+    if (kHeads) {                                  // (the correction pass has no heads: no dV)
     tmem_ld16(c.tmem + Cfg::tDV + lane_base + d0, o);
     tc_wait_ld();
-    if (p.acc_dv_in) {
-      const float4* extra = reinterpret_cast<const float4*>(p.acc_dv_in + krow * D + d0);
-#pragma unroll
-      for (int x = 0; x < 4; ++x) {
-        const float4 ev = extra[x];
-        o[4 * x] = __float_as_uint(__uint_as_float(o[4 * x]) + ev.x);
-        o[4 * x + 1] = __float_as_uint(__uint_as_float(o[4 * x + 1]) + ev.y);
-        o[4 * x + 2] = __float_as_uint(__uint_as_float(o[4 * x + 2]) + ev.z);
-        o[4 * x + 3] = __float_as_uint(__uint_as_float(o[4 * x + 3]) + ev.w);
-      }
-    }
     if (p.dv_chunk) {
       const float4* extra = reinterpret_cast<const float4*>(p.dv_chunk + ((size_t)c.bh * p.s.N + c.i) * p.dv_chunk_stride + d0);
 #pragma unroll
@@ -968,7 +958,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   }
 }
 
-template <int D, typename TG, int kMode, int CG>
+template <int D, typename TG, int kMode, int CG, bool kHeads>
 __global__ void __launch_bounds__(32 * (8 + 4 * (64 / CG)), 1)
 bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
@@ -1044,7 +1034,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     if (warp < 6) bwd2_drain<D>(c, p, &tmDQ, &tmDK);
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
-    bwd2_worker<D, TG, kMode, CG>(c, p);
+    bwd2_worker<D, TG, kMode, CG, kHeads>(c, p);
   }
 
   tc_fence_before();

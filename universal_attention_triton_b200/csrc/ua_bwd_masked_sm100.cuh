@@ -19,7 +19,7 @@
 // head_dim 128 runs as two blocks per work item, one per 64-wide half of the output columns of Y / lanes of Nt.
 // A work item is (batch*head, group of G chunks, range of row tiles); partial N / w / u leave as fp32 global adds.
 #pragma once
-#include "ua_bwd_sm100.cuh"
+#include "ua_fwd_sm100.cuh"
 
 namespace ua {
 namespace sm100 {
@@ -33,7 +33,11 @@ struct MaskedParams {
   float* acc_dk;                 // (b*h*L, D) fp32, added to
   int* status;
   int jp;                        // row tiles per work item
-  int items_per_bh;              // sum over groups of ceil(row tiles before the group's last chunk / jp)
+  int items_per_bh;              // number of (group, piece of row tiles) items per batch*head (set by the launcher)
+  // Range of row tiles [j_begin, j_end) (sequence-chunk sharding; whole sequence: 0, N, L, 0): xq, g_out, g_denom and
+  // the dQ accumulator are slabs of Lr rows that hold the range at row r0.
+  int j_begin, j_end, Lr, r0;
+  float* acc_dv;                 // row ranges only: (b*h, L, D) fp32, dV_i = 1 (x) u_i / 128 is ADDED here by the finish kernel
 };
 
 template <int D> __host__ __device__ constexpr int kNaccRows() { return D + 3; }
@@ -90,6 +94,8 @@ struct MkCtx {
   __device__ __forceinline__ void arrive_w(int idx) const { mbar_arrive_warp(bar(idx)); }
   // first chunk of the group that has row tile j before it
   __device__ __forceinline__ int clo(int j) const { return max(0, j + 1 - i0); }
+  int jb, r0;                          // the slabs hold row tile jb at row r0
+  __device__ __forceinline__ int srow(int j) const { return r0 + (j - jb) * 128; }
 };
 
 // ------------------------------------------------------------------ prep kernel --
@@ -198,6 +204,17 @@ __global__ void __launch_bounds__(128) masked_finish_kernel(const __nv_bfloat16*
   }
   for (int x = key; x < D; x += 128) sW[x] = nacc[(size_t)D * D + x];
   float* dk = p.acc_dk + (chunk * 128 + key) * D;
+  if (p.acc_dv) {                       // row ranges: the same row u / 128 for every key, added to the shared fp32 buffer
+    const float* u = nacc + (size_t)(D + 1) * D;
+    float4* dv = reinterpret_cast<float4*>(p.acc_dv + (chunk * 128 + key) * D);
+#pragma unroll 4
+    for (int x = 0; x < D / 4; ++x) {
+      float4 cur = dv[x];
+      cur.x += u[4 * x] * (1.0f / 128.0f); cur.y += u[4 * x + 1] * (1.0f / 128.0f);
+      cur.z += u[4 * x + 2] * (1.0f / 128.0f); cur.w += u[4 * x + 3] * (1.0f / 128.0f);
+      dv[x] = cur;
+    }
+  }
 #pragma unroll 1
   for (int blk = 0; blk < D / 32; ++blk) {
     __syncthreads();
@@ -252,7 +269,7 @@ struct MkUnit {
 template <int D>
 __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& p, const CUtensorMap* tmQ, const CUtensorMap* tmG) {
   using Cfg = MkCfg<D>;
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int L = p.Lr, R = p.s.R, N = p.s.N;      // (L: rows per slab of the row-indexed tensors)
   const uint32_t sb = smem_u32(c.smem);
   {
     const int c0 = c.clo(c.jlo);
@@ -269,7 +286,7 @@ __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& 
     if (pj >= c.jhi) return;
 #pragma unroll
     for (int b = 0; b < Cfg::kKB; ++b)
-      tma_prefetch_2d(tmG, 64 * b, (int)((((size_t)c.bh * N + c.i0 + pc) * R + pr) * L + (size_t)pj * 128));
+      tma_prefetch_2d(tmG, 64 * b, (int)((((size_t)c.bh * N + c.i0 + pc) * R + pr) * L + (size_t)c.srow(pj)));
     if (++pc >= c.chi) {
       if (++pr >= R) { pr = 0; ++pj; }
       pc = c.clo(pj);
@@ -286,10 +303,10 @@ __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& 
       if (s >= 2 && !c.wait(mQFree + qs, s / 2 - 1)) return;
       MQ(1)
       mbar_expect_tx(c.bar(mQFull + qs), 16384u + (uint32_t)(c.chi - c0) * 512u);
-      tma_load_2d(sb + Cfg::oQ + qs * 16384, tmQ, 64 * c.h, (c.bh * R + r) * L + j * 128, c.bar(mQFull + qs));
+      tma_load_2d(sb + Cfg::oQ + qs * 16384, tmQ, 64 * c.h, (c.bh * R + r) * L + c.srow(j), c.bar(mQFull + qs));
       for (int cc = c0; cc < c.chi; ++cc)
         bulk_load_1d(sb + Cfg::oGd + (qs * Cfg::kG + cc) * 512,
-                     p.g_denom + (((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)j * 128, 512, c.bar(mQFull + qs));
+                     p.g_denom + (((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)c.srow(j), 512, c.bar(mQFull + qs));
       for (int u = 0; u < Cfg::kUnits; ++u) {
         const MkUnit<D> un(u, c0, c.chi);
         if (!un.active()) continue;
@@ -303,7 +320,7 @@ __device__ __forceinline__ void mk_producer(const MkCtx& c, const MaskedParams& 
 #pragma unroll
           for (int b = 0; b < Cfg::kKB; ++b)
             tma_load_2d(sb + Cfg::oSlot + sl * 32768 + (cc - u * Cfg::kPer) * Cfg::kDoBytes + b * 16384, tmG, 64 * b,
-                        (int)((((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)j * 128), c.bar(mSlotFull + sl));
+                        (int)((((size_t)c.bh * N + c.i0 + cc) * R + r) * L + (size_t)c.srow(j)), c.bar(mSlotFull + sl));
           prefetch_next();
         }
       }
@@ -438,7 +455,7 @@ __device__ __forceinline__ void mk_gate_sums(const MkCtx& c, const MaskedParams&
 template <int D>
 __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, const CUtensorMap* tmDQ) {
   using Cfg = MkCfg<D>;
-  const int L = p.s.L, R = p.s.R, N = p.s.N;
+  const int L = p.Lr, R = p.s.R, N = p.s.N;      // (L: rows per slab of the row-indexed tensors)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = (warp & 3) * 32 + lane;
   const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -495,7 +512,7 @@ __device__ __forceinline__ void mk_drain(const MkCtx& c, const MaskedParams& p, 
       fence_proxy_async();
       named_bar_sync(2, 128);
       if (leader) {
-        const int y = (c.bh * R + r) * L + j * 128;
+        const int y = (c.bh * R + r) * L + c.srow(j);
         tma_reduce_add_2d(tmDQ, 64 * c.h, y, smem_u32(stage));
         tma_reduce_add_2d(tmDQ, 64 * c.h + 32, y, smem_u32(stage) + 16384);
         bulk_commit_group();
@@ -571,14 +588,18 @@ masked_sweep_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     c.h = blockIdx.x % Cfg::kKB;
     int g = 0;
     bool found = false;
-    for (int piece = 0; piece * p.jp < N - 1; ++piece) {
-      int cnt = 0;                                                       // groups that have row tiles of this range before a chunk
-      for (int gg = 0; gg < groups; ++gg) cnt += (min((gg + 1) * Cfg::kG, N) - 1 > piece * p.jp) ? 1 : 0;
+    c.jb = p.j_begin; c.r0 = p.r0;
+    // row tiles of the range that lie before the last chunk of group gg: [j_begin, min(j_end, last chunk of gg))
+    auto jmax_of = [&](int gg) { return min(min((gg + 1) * Cfg::kG, N) - 1, p.j_end); };
+    for (int piece = 0; p.j_begin + piece * p.jp < min(N - 1, p.j_end); ++piece) {
+      const int jlo = p.j_begin + piece * p.jp;
+      int cnt = 0;                                                       // groups that have row tiles of this piece before a chunk
+      for (int gg = 0; gg < groups; ++gg) cnt += (jmax_of(gg) > jlo) ? 1 : 0;
       if (idx < BH * cnt) {
         c.bh = idx / cnt;
         g = groups - 1 - idx % cnt;
-        c.jlo = piece * p.jp;
-        c.jhi = min(c.jlo + p.jp, min((g + 1) * Cfg::kG, N) - 1);
+        c.jlo = jlo;
+        c.jhi = min(c.jlo + p.jp, jmax_of(g));
         found = true;
         break;
       }

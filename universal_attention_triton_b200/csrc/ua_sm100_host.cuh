@@ -7,7 +7,6 @@
 #include "../../include/ua_b200.h"
 #include "ua_bwd2_sm100.cuh"
 #include "ua_bwd_masked_sm100.cuh"
-#include "ua_bwd_sm100.cuh"
 #include "ua_fwd_sm100.cuh"
 
 namespace ua {
@@ -100,59 +99,9 @@ int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, c
                               : launch_fwd_t<128, __nv_bfloat16, kCarryOnly>(s, kc, vc, xq, p, fill_masked, st);
 }
 
-// Shapes of the first tensor-core backward kernel (rows-on-lanes): still the kernel of the row-range entry points and of
-// the rows before a chunk.
-inline bool bwd_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && s.D == 64; }
 // Shapes of the keys-on-lanes backward kernel.
 inline bool bwd2_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128); }
 
-// Fills the row-range / sharding fields of BwdParams for a call over the whole sequence.
-inline void whole_sequence(BwdParams& p) {
-  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.suffix_in = nullptr; p.dctot_out = nullptr;
-  p.acc_dv = nullptr; p.acc_ds = nullptr; p.decay_only = 0; p.lse = nullptr;
-  p.merged = 0; p.row_lse = nullptr; p.row_delta = nullptr; p.masked_only = 0; p.gd_f32 = nullptr;
-}
-
-// Backward over the row tiles [p.j_begin, p.j_end): (1) unless the caller supplied the decay-prefix table, a
-// decay-only run of the forward kernel fills it (starting from carry_in for a row range), (2) the backward kernel.
-// The caller zeroes the fp32 accumulators.
-template <typename TG>
-int launch_bwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, const BwdParams& p,
-                 float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
-  CUtensorMap tmK, tmV, tmQ, tmG, tmDQ, tmDK;
-  const uint64_t BH = (uint64_t)s.B * s.H;
-  if (!make_rows_map(&tmK, kc, BH * s.L, 64) || !make_rows_map(&tmV, vc, BH * s.L, 64)) return UA_ERR_CUDA;
-  if (!make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L)) return UA_ERR_CUDA;
-  if (p.decay_only) tmDQ = tmDK;   // no query gradient in the correction pass
-  else if (!make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr)) return UA_ERR_CUDA;
-  if (p.decay_only) {
-    tmQ = tmK; tmG = tmK;          // the correction pass touches neither queries nor upstream gradients
-  } else if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, 64) ||
-             !make_rows_map(&tmG, g_out, (p.merged ? BH : BH * s.N) * s.R * p.Lr, 64)) {
-    return UA_ERR_CUDA;
-  }
-  if (run_prepass && !p.decay_only) {
-    FwdParams fp{};
-    fp.s = s; fp.ssrc = p.ssrc; fp.sdest = p.sdest; fp.out = nullptr; fp.lse = nullptr; fp.denom = nullptr;
-    fp.status = p.status; fp.carry = carry; fp.vc = nullptr; fp.fill_masked = 0;
-    fp.j_begin = p.j_begin; fp.j_end = p.j_end; fp.Lr = p.Lr; fp.r0 = p.r0; fp.carry_in = carry_in; fp.total_out = nullptr;
-    int e = launch_fwd_t<64, TG, true>(s, kc, nullptr, nullptr, fp, false, st);
-    if (e) return e;
-  }
-  auto kern = p.merged ? bwd_kernel<TG, 2> : (p.lse ? bwd_kernel<TG, 1> : bwd_kernel<TG, 0>);
-  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdCfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 640, BwdCfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
-  return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
-}
-
-inline int launch_bwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const void* g_out,
-                      const BwdParams& p, float* carry, bool run_prepass, const float* carry_in, cudaStream_t st) {
-  return gate_dtype == UA_F32 ? launch_bwd_t<float>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st)
-                              : launch_bwd_t<__nv_bfloat16>(s, kc, vc, xq, g_out, p, carry, run_prepass, carry_in, st);
-}
-
-// Keys-on-lanes backward over the whole sequence (rows that see the chunk only).  kMode 1: per-chunk log-sum-exp and
-// g_denom; kMode 2: merged upstream gradient.  The caller zeroes the fp32 accumulators.
 #ifndef UA_BWD2_COLS
 #define UA_BWD2_COLS 32
 #endif
@@ -182,7 +131,7 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
              !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr, D, 64)) {
     return UA_ERR_CUDA;
   }
-  auto kern = bwd2_kernel<D, TG, kMode, kBwd2Cols>;
+  auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kBwd2Cols, true> : bwd2_kernel<D, TG, kMode, kBwd2Cols, false>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
@@ -196,23 +145,30 @@ inline int launch_bwd2(const Shape& s, int gate_dtype, bool merged, const void* 
 #undef UA_BWD2
 }
 
-// Rows before a chunk, whole sequence: prep (per-chunk constants), sweep (one pass over the upstream gradient), finish
-// (dK_i, dV_i).  The caller has zeroed acc_dq / acc_dk / acc_dv.
+// Fills the row-range fields of MaskedParams for a call over the whole sequence.
+inline void whole_sequence(MaskedParams& p) {
+  p.j_begin = 0; p.j_end = p.s.N; p.Lr = p.s.L; p.r0 = 0; p.acc_dv = nullptr;
+}
+
+// Rows before a chunk over the row tiles [p.j_begin, p.j_end): prep (per-chunk constants), sweep (one pass over the upstream
+// gradient), finish (dK_i, and dV_i for a row range).  The caller has zeroed (or shares) acc_dq / acc_dk / acc_dv.
 template <int D>
 int launch_masked_t(const Shape& s, const void* kc, const void* vc, const void* xq, const void* g_out, float* acc_dq, MaskedParams p,
                     cudaStream_t st) {
   using Cfg = MkCfg<D>;
   const uint64_t BH = (uint64_t)s.B * s.H;
   CUtensorMap tmQ, tmG, tmDQ;
-  if (!make_rows_map(&tmQ, xq, BH * s.R * s.L, D) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * s.L, D) ||
-      !make_f32_rows_map(&tmDQ, acc_dq, BH * s.R * s.L, D))
+  if (!make_rows_map(&tmQ, xq, BH * s.R * p.Lr, D) || !make_rows_map(&tmG, g_out, BH * s.N * s.R * p.Lr, D) ||
+      !make_f32_rows_map(&tmDQ, acc_dq, BH * s.R * p.Lr, D))
     return UA_ERR_CUDA;
   static const int jp_env = []() { const char* e = getenv("UA_MASKED_TILES"); return e ? atoi(e) : 0; }();
   p.jp = jp_env > 0 ? jp_env : 8;
   p.items_per_bh = 0;
+  const int jcap = (s.N - 1 < p.j_end) ? s.N - 1 : p.j_end;      // no row tile at or after the last chunk is before any chunk
   for (int g = 0; g * Cfg::kG < s.N; ++g) {
-    const int jmax = (((g + 1) * Cfg::kG < s.N) ? (g + 1) * Cfg::kG : s.N) - 1;
-    p.items_per_bh += (jmax + p.jp - 1) / p.jp;
+    int jmax = (((g + 1) * Cfg::kG < s.N) ? (g + 1) * Cfg::kG : s.N) - 1;
+    if (jmax > jcap) jmax = jcap;
+    if (jmax > p.j_begin) p.items_per_bh += (jmax - p.j_begin + p.jp - 1) / p.jp;
   }
   if (p.items_per_bh == 0) return UA_OK;
   const auto* k16 = static_cast<const __nv_bfloat16*>(kc);
