@@ -1015,7 +1015,7 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
   // worker request beyond what was given back would never be granted.)
   constexpr int kThreads = 32 * (8 + 4 * NG);
   constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
-  constexpr int kRoleRegs = 56, kDrainRegs = 72;
+  constexpr int kRoleRegs = 48, kDrainRegs = 64;
   constexpr int kWorkerRegs = kLaunchRegs + ((2 * kLaunchRegs - kRoleRegs - kDrainRegs) * 128 / (128 * NG)) / 8 * 8;
   static_assert(kRoleRegs <= kLaunchRegs && kDrainRegs <= kLaunchRegs, "setmaxnreg.dec must not ask for more");
   static_assert(128 * (kRoleRegs + kDrainRegs) + 128 * NG * kWorkerRegs <= kThreads * kLaunchRegs, "register pool");
