@@ -510,7 +510,10 @@ def main():
 
         def e2e_timed():
             nonlocal cmp_done
-            e2e_run(2)
+            # warm-up: as many steps as the device-resident leg, and at least four: the pipelined pattern (buffers held
+            # across streams until their copies have run) needs a few steps before the caching allocator stops growing,
+            # and a cudaMalloc inside the timed region would be timed as a step
+            e2e_run(max(W, 4))
             cmp_done = [None, None]
             barrier()
             a, b = ev(), ev()
