@@ -328,7 +328,7 @@ def main():
     ap.add_argument("--e2e-loss-only", action="store_true",
                     help="end-to-end leg: return only the loss to the host (default: the loss and the five gradients); "
                          "the default run reports both variants")
-    ap.add_argument("--merged-entry", default=None, choices=["composed", "fused"],
+    ap.add_argument("--merged-entry", default=None, choices=["composed", "fused", "low_memory"],
                     help="end-to-end leg through UniversalAttentionMerged (the additional one-call entry point, with the "
                          "given backward) instead of the drop-in pair UniversalAttention + SMVecMatMul")
     ap.add_argument("--skip-masked-grads", action="store_true",
@@ -361,7 +361,11 @@ def main():
     from universal_attention_triton_b200 import (SMVecMatMul, UniversalAttention, UniversalAttentionMerged, _lib, ops,
                                                 set_merged_backward, set_strict_masked_grads)
     if args.merged_entry:
-        set_merged_backward(args.merged_entry)
+        # "low_memory": the two-pass forward that never writes `out`, with the one-kernel backward
+        set_merged_backward("fused" if args.merged_entry == "low_memory" else args.merged_entry)
+        if args.merged_entry == "low_memory":
+            from universal_attention_triton_b200 import set_merged_forward
+            set_merged_forward("low_memory")
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path for the operator)")
     _lib.load()

@@ -312,6 +312,19 @@ int ua_merge_fwd(const UaDims* dims, int dtype, const void* out_cm, const float*
 int ua_merge_fwd_stats(const UaDims* dims, int dtype, const void* out_cm, const float* lse_cm,
                        void* merged, float* row_lse, void* stream);
 
+/* The merged output WITHOUT the (b,h,n,r,L,d) tensor `out`: merged (b,h,r,L,d) = SMVecMatMul(UniversalAttention(...))
+ * (main.py:55-56; universal_attention_autograd.py:9-38, :278-283) and row_lse (b,h,r,L) fp32, in two passes of the forward
+ * kernel: the first leaves only the per-chunk log-sum-exp, the second adds every chunk's share exp(m - row_lse) P~ V to
+ * an fp32 accumulator, which is rounded once at the end.  Memory: (b,h,n,r,L) + (b,h,r,L,d) floats of scratch instead of
+ * two n-fold tensors; time: about 1.7 forwards.  carry_out as for ua_fwd_keep (NULL allowed).  Pairs with ua_bwd_merged.
+ * bf16, chunk 128, head_dim 64 or 128.  No counterpart in the reference. */
+size_t ua_fwd_merged_workspace_bytes(const UaDims* dims, int dtype);
+int ua_fwd_merged(const UaDims* dims, int dtype, int gate_dtype,
+                  const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest,
+                  void* merged, float* row_lse, void* carry_out,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
 /* out[row] = a[row] . b[row] for `rows` rows of head_dim elements (fp32 result).  With a = the gradient of the merged
  * output and b = the merged output this is the row_delta of ua_bwd_merged. */
 int ua_row_dot(long long rows, int head_dim, int dtype, const void* a, const void* b, float* out, void* stream);
@@ -324,7 +337,7 @@ int ua_row_dot(long long rows, int head_dim, int dtype, const void* a, const voi
  * `out` itself is read, and the rows before a key chunk contribute nothing.  The reference has no fused form; values
  * equal ua_merge_bwd followed by ua_bwd up to rounding (the reference rounds the merge weights and `out` to the input
  * dtype).  carry_in as for ua_bwd_kept (NULL allowed).  Workspace: ua_bwd_workspace_bytes().  bf16, chunk 128,
- * head_dim 64 only (UA_ERR_UNSUPPORTED otherwise: use ua_merge_bwd + ua_bwd). */
+ * head_dim 64 or 128 (UA_ERR_UNSUPPORTED otherwise: use ua_merge_bwd + ua_bwd). */
 int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype,
                   const void* kc, const void* vc, const void* xq,
                   const void* static_src, const void* static_dest,

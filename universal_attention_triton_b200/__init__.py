@@ -7,9 +7,10 @@ from .universal_attention_autograd import (  # noqa: F401
     UniversalAttention2,
     UniversalAttentionMerged,
     set_merged_backward,
+    set_merged_forward,
     set_output_layout,
     set_strict_masked_grads,
 )
 
-__all__ = ["UniversalAttention", "UniversalAttention2", "UniversalAttentionMerged", "SMVecMatMul", "set_output_layout", "set_merged_backward",
+__all__ = ["UniversalAttention", "UniversalAttention2", "UniversalAttentionMerged", "SMVecMatMul", "set_output_layout", "set_merged_backward", "set_merged_forward",
            "set_strict_masked_grads", "ops"]

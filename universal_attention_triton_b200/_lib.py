@@ -62,6 +62,8 @@ SIGNATURES = {
     "ua_merge_bwd": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "ua_merge_fwd_stats": (_i, [_dp, _i, _vp, _vp, _vp, _vp, _vp]),
     "ua_row_dot": (_i, [ctypes.c_longlong, _i, _i, _vp, _vp, _vp, _vp]),
+    "ua_fwd_merged_workspace_bytes": (_sz, [_dp, _i]),
+    "ua_fwd_merged": (_i, [_dp, _i, _i] + [_vp] * 9 + [_sz, _vp]),
     "ua_bwd_merged": (_i, [_dp, _i, _i] + [_vp] * 15 + [_sz, _vp]),
     "ua_decode_step": (_i, [_dp, _i, _i, _i] + [_vp] * 9),
     "ua_prepare_inputs": (_i, [_i] * 7 + [_vp] * 11),

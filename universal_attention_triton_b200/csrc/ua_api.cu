@@ -230,6 +230,25 @@ __global__ void wait_selftest_kernel(int* status, unsigned long long limit_ns) {
   }
 }
 
+// log-sum-exp of every row over the key chunks that hold keys at or before it (the later chunks are fully masked for the
+// row; their entries of lse_cm need not have been written)
+__global__ void row_lse_kernel(const float* __restrict__ lse_cm, float* __restrict__ row_lse, size_t bh_count, int N, int R, int L) {
+  const size_t total = bh_count * R * L, stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += stride) {
+    const int l = (int)(idx % L);
+    const size_t br = idx / L;                  // bh * R + r
+    const size_t bh = br / R, r = br % R;
+    const float* src = lse_cm + ((bh * N) * R + r) * (size_t)L + l;
+    const size_t nstride = (size_t)R * L;
+    const int last = l / 128;
+    float mx = src[0];
+    for (int i = 1; i <= last; ++i) mx = fmaxf(mx, src[i * nstride]);
+    float z = 0.f;
+    for (int i = 0; i <= last; ++i) z += expf(src[i * nstride] - mx);
+    row_lse[idx] = mx + logf(z);
+  }
+}
+
 // a status word raised by an inner call on its own buffer is carried over to the caller's
 __global__ void carry_status_kernel(const int* __restrict__ from, int* __restrict__ to) {
   if (from[0] != 0 && atomicCAS(to, 0, from[0]) == 0) to[1] = from[1];
@@ -937,6 +956,49 @@ int ua_merge_fwd_stats(const UaDims* dims, int dtype, const void* out_cm, const 
   else return UA_ERR_UNSUPPORTED;
 #undef UA_MERGE_FWD
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
+}
+
+size_t ua_fwd_merged_workspace_bytes(const UaDims* dims, int dtype) {
+  if (check_dims(dims) != UA_OK) return 0;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::fwd_supported(s, dtype)) return 0;
+  const size_t BH = (size_t)s.B * s.H;
+  return 256 + align_up(BH * s.N * (size_t)s.R * s.L * sizeof(float), 256) + align_up(BH * s.R * (size_t)s.L * s.D * sizeof(float), 256);
+}
+
+int ua_fwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                  const void* static_src, const void* static_dest, void* merged, float* row_lse, void* carry_out,
+                  void* workspace, size_t workspace_bytes, void* stream) {
+  int e = check_dims(dims);
+  if (e) return e;
+  if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
+  if (!kc || !vc || !xq || !static_src || !static_dest || !merged || !row_lse) return UA_ERR_NULL_POINTER;
+  if (!aligned16(kc) || !aligned16(vc) || !aligned16(xq) || !aligned16(merged)) return UA_ERR_ALIGNMENT;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::fwd_supported(s, dtype)) return UA_ERR_UNSUPPORTED;
+  const size_t need = ua_fwd_merged_workspace_bytes(dims, dtype);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  char* ws = static_cast<char*>(workspace);
+  const size_t BH = (size_t)s.B * s.H;
+  float* lse_cm = reinterpret_cast<float*>(ws + 256);
+  float* acc = reinterpret_cast<float*>(ws + 256 + align_up(BH * s.N * (size_t)s.R * s.L * sizeof(float), 256));
+  if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(acc, 0, BH * s.R * (size_t)s.L * s.D * sizeof(float), st) != cudaSuccess) return UA_ERR_CUDA;
+  // pass 1: the per-chunk log-sum-exp of every row (no output tile is written) and, on request, the decay-prefix table
+  ua::sm100::FwdParams fp{};
+  fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest; fp.out = nullptr; fp.denom = nullptr; fp.lse = lse_cm;
+  fp.status = reinterpret_cast<int*>(ws);
+  fp.carry = ua_carry_bytes(dims, dtype, 0) ? static_cast<float*>(carry_out) : nullptr;
+  ua::sm100::whole_sequence(fp);
+  if ((e = ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq, fp, false, st))) return e;
+  // the row's log-sum-exp over all key chunks
+  row_lse_kernel<<<148 * 8, 256, 0, st>>>(lse_cm, row_lse, BH, s.N, s.R, s.L);
+  if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
+  // pass 2: every (chunk, row tile, head) adds exp(m - row_lse) P~ V to the fp32 merged accumulator
+  fp.lse = nullptr; fp.carry = nullptr; fp.merged_acc = acc; fp.row_lse = row_lse;
+  if ((e = ua::sm100::launch_fwd_merge(s, gate_dtype, kc, vc, xq, fp, st))) return e;
+  return convert_any(dtype, acc, merged, BH * s.R * (size_t)s.L * s.D, st);
 }
 
 int ua_row_dot(long long rows, int head_dim, int dtype, const void* a, const void* b, float* out, void* stream) {

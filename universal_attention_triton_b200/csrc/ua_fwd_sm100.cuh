@@ -61,6 +61,10 @@ struct FwdParams {
   const float* carry_in;   // optional (b*h*n, 128): decay prefix of key k at its first row tile of the range
   float* total_out;        // optional (b*h*n, 128): decay prefix after the last row tile of the range
   float* carry;          // optional (required in carry-only mode): (b*h*n, n, 2, 128) decay prefix of key k at the start of each 64-row half of row tile j
+  // merged-output mode (fwd_kernel<..., kMerge = true>): instead of writing `out`, every (chunk, row tile, head) adds its
+  // share of the row's softmax over ALL keys, exp(m - row_lse) * (P~ V) with P~ = exp(s - m) unnormalised, to merged_acc
+  float* merged_acc;     // (b,h,r,L,d) fp32, zeroed by the caller
+  const float* row_lse;  // (b,h,r,L) fp32: log-sum-exp of every row over all key chunks (from a statistics-only run)
 };
 
 // Gated affinity and log-retention of one (key, row) pair from the Gram value
@@ -345,7 +349,7 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
 }
 
 // ------------------------------------------------------------ softmax groups --
-template <int D>
+template <int D, bool kMerge>
 __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams& p, int me) {
   using Cfg = FwdCfg<D>;
   const int R = p.s.R, N = p.s.N;
@@ -433,9 +437,17 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
       const float l = l2.x + l2.y;
       const float lse = m + lg2(l) * kLn2;
       const size_t orow = (chunk_id * R + r) * p.Lr + qg;
-      p.lse[orow] = lse;
-      if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
-      const float linv = 1.0f / l;
+      const size_t mrow = ((size_t)c.bh * R + r) * p.Lr + qg;       // the row in (b,h,r,L) order (merged-output mode)
+      float linv;
+      if (kMerge) {
+        // exp(lse - row_lse) / l = exp(m - row_lse): weight of this chunk in the row's softmax over all keys, applied
+        // to the unnormalised P~ V (the load's latency runs under the wait for the PV product)
+        linv = ex2((m - p.row_lse[mrow]) * kLog2e);
+      } else {
+        p.lse[orow] = lse;
+        if (p.denom) p.denom[orow] = __float2bfloat16_rn(lse);
+        linv = 1.0f / l;
+      }
       UF(5)
       if (!c.wait_w(kOFull + sb, t >> 1)) return;
       UF(6)
@@ -449,6 +461,14 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         if (cb == D / 32 - 1) {
           tc_fence_before();
           c.arrive_w(kOFree + sb);
+        }
+        if (kMerge) {
+          float* dst = p.merged_acc + mrow * D + cb * 32;
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+            red_add_v4(dst + 4 * u, __uint_as_float(o[4 * u]) * linv, __uint_as_float(o[4 * u + 1]) * linv,
+                       __uint_as_float(o[4 * u + 2]) * linv, __uint_as_float(o[4 * u + 3]) * linv);
+          continue;
         }
         if (!p.out) continue;                 // statistics-only run (the log-sum-exp for a backward that was not given one)
 #ifdef UA_EXPERIMENT_NO_OUT_STORE
@@ -506,7 +526,7 @@ __device__ __forceinline__ void fwd_fill_rows(const FwdCtx<D>& c, const FwdParam
   }
 }
 
-template <int D, typename TG, bool kCarryOnly>
+template <int D, typename TG, bool kCarryOnly, bool kMerge = false>
 __global__ void __launch_bounds__(512, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, FwdParams p) {
@@ -560,7 +580,7 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
       p.total_out[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] =
           p.carry_in ? p.carry_in[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] : 0.f;
   } else if (warp >= 8 && !kCarryOnly) {
-    if (c.ntiles > 0) fwd_softmax<D>(c, p, (warp - 8) >> 2);
+    if (c.ntiles > 0) fwd_softmax<D, kMerge>(c, p, (warp - 8) >> 2);
   } else if ((warp == 2 || warp == 3) && !kCarryOnly && p.fill_masked && c.i > p.j_begin) {
     fwd_fill_rows<D>(c, p, reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oFill));
   }

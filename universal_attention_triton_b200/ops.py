@@ -251,6 +251,40 @@ def merge_fwd_stats_cm(out_cm, lse_cm):
     return merged, row_lse
 
 
+def forward_merged_lowmem(kc, vc, xq, static_src, static_dest):
+    """``merged (b,h,r,L,d)`` and ``row_lse (b,h,r,L)`` fp32 of ``SMVecMatMul(UniversalAttention(...))`` without the
+    (b,h,n,r,L,d) tensor ``out`` (``ua_fwd_merged``: two passes of the forward kernel), plus the decay-prefix table for
+    ``backward_merged`` (or ``None``).  Returns ``None`` for shapes the tensor-core forward does not take."""
+    _require_cuda(kc, vc, xq, static_src, static_dest)
+    lib = _lib.load()
+    b, h, n, c, d = kc.shape
+    r = xq.shape[2]
+    L = n * c
+    dt = xq.dtype
+    code = _dtype_code(dt)
+    dims = UaDims(b, h, r, n, c, d)
+    ws_bytes = lib.ua_fwd_merged_workspace_bytes(ctypes.byref(dims), code)
+    if not ws_bytes:
+        return None
+    kcc, vcc = kc.contiguous(), vc.contiguous()
+    q = xq.reshape(b, h, r, L, d).contiguous()
+    ss = _gate_cast(static_src.reshape(b, h, L), dt)
+    sd = _gate_cast(static_dest.reshape(b, h, L), dt)
+    if ss.dtype != sd.dtype:
+        ss, sd = ss.float(), sd.float()
+    with torch.cuda.device(kc.device):
+        merged = torch.empty(b, h, r, L, d, dtype=dt, device=kc.device)
+        row_lse = torch.empty(b, h, r, L, dtype=torch.float32, device=kc.device)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=kc.device)
+        cbytes = lib.ua_carry_bytes(ctypes.byref(dims), code, 0)
+        carry = torch.empty(cbytes // 4, dtype=torch.float32, device=kc.device) if cbytes else None
+        rc = lib.ua_fwd_merged(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
+                               _ptr(merged), _ptr(row_lse), _ptr(carry), _ptr(ws), ws_bytes, _stream())
+        _lib.check(rc, "ua_fwd_merged")
+        _check_status(lib, ws, "ua_fwd_merged")
+    return merged, row_lse, carry
+
+
 def row_dot(a, b):
     """fp32 ``(a * b).sum(-1)`` of two equally shaped contiguous tensors (rows of head_dim elements)."""
     _require_cuda(a, b)

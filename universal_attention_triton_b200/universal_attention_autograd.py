@@ -55,6 +55,20 @@ def set_merged_backward(mode: str) -> None:
     _MERGED_BACKWARD = mode
 
 
+_MERGED_FORWARD = "materialise"
+
+
+def set_merged_forward(mode: str) -> None:
+    """Forward of ``UniversalAttentionMerged``.  ``"materialise"`` (default): the operator's forward, then the merge over
+    key chunks (the (b,h,n,r,L,d) tensor ``out`` lives inside the forward).  ``"low_memory"``: two passes of the forward
+    kernel that never write ``out`` (``ua_fwd_merged``): (b,h,n,r,L) + (b,h,r,L,d) floats of scratch instead of two n-fold
+    tensors, about 1 ms more per step at B4 H8 R4 L4096 D64; implies the fused backward (there is no ``out`` to merge
+    backwards through); shapes the tensor-core kernels do not take fall back to ``"materialise"``."""
+    global _MERGED_FORWARD
+    assert mode in ("materialise", "low_memory")
+    _MERGED_FORWARD = mode
+
+
 def set_strict_masked_grads(on: bool) -> None:
     """When off, backward skips the gradient through fully masked blocks (rows
     before a key chunk).  That gradient is exactly zero when ``SMVecMatMul``
@@ -212,6 +226,13 @@ class UniversalAttentionMerged(Function):
         assert vc.shape == kc.shape and static_src.shape == (b, h, n, c)
         assert xq.shape[:2] == (b, h) and xq.shape[-1] == d and xq[0, 0, 0].numel() == n * c * d
         assert static_dest.numel() == b * h * n * c
+        if _MERGED_FORWARD == "low_memory" and ops.merged_backward_supported(kc, xq):
+            res = ops.forward_merged_lowmem(kc, vc, xq, static_src, static_dest)
+            if res is not None:
+                merged, row_lse, carry = res
+                merged = merged.view(*xq.shape)
+                merged._ua_extras = (True, (merged, row_lse), carry)
+                return merged
         out_cm, lse_cm, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, keep_carry=True)
         merged, row_lse = ops.merge_fwd_stats_cm(out_cm, lse_cm)
         fused = _MERGED_BACKWARD == "fused" and ops.merged_backward_supported(kc, xq)
