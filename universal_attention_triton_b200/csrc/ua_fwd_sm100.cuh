@@ -98,6 +98,10 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
+// What the softmax groups produce: the per-chunk output tiles (and log-sum-exp), the merged-output contribution, or the
+// log-sum-exp alone (then no probabilities are written, no PV product is issued, nothing is drained).
+enum FwdOut { kOutTiles = 0, kOutMerged = 1, kOutStats = 2 };
+
 template <int D>
 struct FwdCfg {
   static constexpr int kTileBytes = 128 * D * 2;   // one [128][D] bf16 tile
@@ -187,7 +191,7 @@ __device__ __forceinline__ void fwd_producer(const FwdCtx<D>& c, const FwdParams
 }
 
 // ---------------------------------------------------------------- MMA issuer --
-template <int D, bool kCarryOnly>
+template <int D, bool kCarryOnly, int kOut>
 __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) {
   using Cfg = FwdCfg<D>;
   const int R = p.s.R;
@@ -222,7 +226,8 @@ __device__ __forceinline__ void fwd_mma(const FwdCtx<D>& c, const FwdParams& p) 
   };
   auto issue_pv = [&](int tt) -> bool {
     const int sb = tt & 1, ob = tt % Cfg::kOBufs;
-    if (!c.wait(kPReady + sb, tt >> 1)) return false;
+    if (!c.wait(kPReady + sb, tt >> 1)) return false;       // (statistics only: the group is done with the S buffer)
+    if (kOut == kOutStats) return true;
     // the O buffer must have been drained by the epilogue that used it last
     // (barriers are per softmax group so that each waiter sees consecutive phases)
     if (Cfg::kOBufs == 2) {
@@ -349,8 +354,9 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
 }
 
 // ------------------------------------------------------------ softmax groups --
-template <int D, bool kMerge>
+template <int D, int kOut>
 __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams& p, int me) {
+  constexpr bool kMerge = (kOut == kOutMerged);
   using Cfg = FwdCfg<D>;
   const int R = p.s.R, N = p.s.N;
   const int row = threadIdx.x & 127;
@@ -427,9 +433,9 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           l2 = fadd2(l2, pe);
           pk[u] = *reinterpret_cast<uint32_t*>(&h);
         }
-        tmem_st32(tS + cb * 32, pk);
+        if (kOut != kOutStats) tmem_st32(tS + cb * 32, pk);
       }
-      tc_wait_st();
+      if (kOut != kOutStats) tc_wait_st();
       tc_fence_before();
       c.arrive_w(kPReady + sb);
       UF(4)
@@ -449,6 +455,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
         linv = 1.0f / l;
       }
       UF(5)
+      if (kOut == kOutStats) continue;
       if (!c.wait_w(kOFull + sb, t >> 1)) return;
       UF(6)
       tc_fence_after();
@@ -526,7 +533,7 @@ __device__ __forceinline__ void fwd_fill_rows(const FwdCtx<D>& c, const FwdParam
   }
 }
 
-template <int D, typename TG, bool kCarryOnly, bool kMerge = false>
+template <int D, typename TG, bool kCarryOnly, int kOut = kOutTiles>
 __global__ void __launch_bounds__(512, 1)
 fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
            const __grid_constant__ CUtensorMap tmQ, FwdParams p) {
@@ -573,14 +580,14 @@ fwd_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUte
   if (warp == 0) {
     if (lane == 0 && c.ntiles > 0) fwd_producer<D, kCarryOnly>(c, p, &tmK, &tmV, &tmQ);
   } else if (warp == 1) {
-    if (lane == 0 && c.ntiles > 0) fwd_mma<D, kCarryOnly>(c, p);
+    if (lane == 0 && c.ntiles > 0) fwd_mma<D, kCarryOnly, kOut>(c, p);
   } else if (warp >= 4 && warp < 8) {
     if (c.ntiles > 0) fwd_decay<D, TG, kCarryOnly>(c, p);
     else if (p.total_out)      // no row of the range sees this chunk: its prefix does not move
       p.total_out[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] =
           p.carry_in ? p.carry_in[((size_t)c.bh * p.s.N + c.i) * 128 + (threadIdx.x & 127)] : 0.f;
   } else if (warp >= 8 && !kCarryOnly) {
-    if (c.ntiles > 0) fwd_softmax<D, kMerge>(c, p, (warp - 8) >> 2);
+    if (c.ntiles > 0) fwd_softmax<D, kOut>(c, p, (warp - 8) >> 2);
   } else if ((warp == 2 || warp == 3) && !kCarryOnly && p.fill_masked && c.i > p.j_begin) {
     fwd_fill_rows<D>(c, p, reinterpret_cast<__nv_bfloat16*>(smem + Cfg::oFill));
   }

@@ -67,7 +67,7 @@ inline void whole_sequence(FwdParams& p) {
 
 // Forward (kCarryOnly = false) or decay-only pass (kCarryOnly = true: no values, queries or outputs) over the row
 // tiles [p.j_begin, p.j_end).  xq / static_dest / out hold p.Lr rows; keys, values, static_src the whole sequence.
-template <int D, typename TG, bool kCarryOnly, bool kMerge = false>
+template <int D, typename TG, bool kCarryOnly, int kOut = kOutTiles>
 int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq, const FwdParams& p, bool fill_masked,
                  cudaStream_t st) {
   using Cfg = FwdCfg<D>;
@@ -79,7 +79,9 @@ int launch_fwd_t(const Shape& s, const void* kc, const void* vc, const void* xq,
   } else if (!make_rows_map(&tmV, vc, BH * s.L, D) || !make_rows_map(&tmQ, xq, BH * s.R * p.Lr, D)) {
     return UA_ERR_CUDA;
   }
-  auto kern = fwd_kernel<D, TG, kCarryOnly, kMerge>;
+  // without an output tensor only the log-sum-exp (and the decay-prefix table) is wanted: the statistics-only kernel
+  auto kern = (!kCarryOnly && kOut == kOutTiles && p.out == nullptr) ? fwd_kernel<D, TG, kCarryOnly, kOutStats>
+                                                                     : fwd_kernel<D, TG, kCarryOnly, kOut>;
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
   FwdParams q = p;
   q.vc = vc;
@@ -103,11 +105,11 @@ int launch_fwd(const Shape& s, int gate_dtype, const void* kc, const void* vc, c
 inline int launch_fwd_merge(const Shape& s, int gate_dtype, const void* kc, const void* vc, const void* xq, const FwdParams& p,
                             cudaStream_t st) {
   if (s.D == 64) {
-    return gate_dtype == UA_F32 ? launch_fwd_t<64, float, false, true>(s, kc, vc, xq, p, false, st)
-                                : launch_fwd_t<64, __nv_bfloat16, false, true>(s, kc, vc, xq, p, false, st);
+    return gate_dtype == UA_F32 ? launch_fwd_t<64, float, false, kOutMerged>(s, kc, vc, xq, p, false, st)
+                                : launch_fwd_t<64, __nv_bfloat16, false, kOutMerged>(s, kc, vc, xq, p, false, st);
   }
-  return gate_dtype == UA_F32 ? launch_fwd_t<128, float, false, true>(s, kc, vc, xq, p, false, st)
-                              : launch_fwd_t<128, __nv_bfloat16, false, true>(s, kc, vc, xq, p, false, st);
+  return gate_dtype == UA_F32 ? launch_fwd_t<128, float, false, kOutMerged>(s, kc, vc, xq, p, false, st)
+                              : launch_fwd_t<128, __nv_bfloat16, false, kOutMerged>(s, kc, vc, xq, p, false, st);
 }
 
 // Shapes of the keys-on-lanes backward kernel.
