@@ -102,6 +102,13 @@ __device__ __forceinline__ float2 ffma2(float2 a, float2 b, float2 c) {
 // log-sum-exp alone (then no probabilities are written, no PV product is issued, nothing is drained).
 enum FwdOut { kOutTiles = 0, kOutMerged = 1, kOutStats = 2 };
 
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 template <int D>
 struct FwdCfg {
   static constexpr int kTileBytes = 128 * D * 2;   // one [128][D] bf16 tile
@@ -402,7 +409,7 @@ __device__ __forceinline__ void fwd_softmax(const FwdCtx<D>& c, const FwdParams&
           const float4 cv = *reinterpret_cast<const float4*>(sCrow + (((chunk ^ (row & 7)) & 31) << 4));
           const float2 a01 = fadd2(make_float2(__uint_as_float(s[u * 4 + 0]), __uint_as_float(s[u * 4 + 1])), make_float2(cv.x, cv.y));
           const float2 a23 = fadd2(make_float2(__uint_as_float(s[u * 4 + 2]), __uint_as_float(s[u * 4 + 3])), make_float2(cv.z, cv.w));
-          m = fmaxf(m, fmaxf(fmaxf(a01.x, a01.y), fmaxf(a23.x, a23.y)));
+          m = fmax3(m, fmax3(a01.x, a01.y, a23.x), a23.y);
           s[u * 4 + 0] = __float_as_uint(a01.x); s[u * 4 + 1] = __float_as_uint(a01.y);
           s[u * 4 + 2] = __float_as_uint(a23.x); s[u * 4 + 3] = __float_as_uint(a23.y);
         }
