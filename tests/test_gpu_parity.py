@@ -710,3 +710,29 @@ def test_bounded_wait_gives_up_and_reports_it():
     out, denom = ua.UniversalAttention.apply(*_cuda(*ins))
     ref_out, _, _ = O.ua_forward(*ins32)
     assert fwd_errors(out.float().cpu(), denom.float().cpu(), ref_out, ref_out.new_zeros(denom.shape), 128)["out_masked"] <= 2e-2
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1, 128, 128, 64),        # a single chunk: no rows before any chunk, one tile
+                                   (1, 1, 1, 128, 128, 128),
+                                   (1, 3, 5, 384, 128, 64),        # odd head counts, R = 5
+                                   (2, 1, 8, 256, 128, 128),       # R = 8 at head_dim 128
+                                   (3, 1, 1, 640, 128, 64)])       # five chunks: a group of chunks that is not full
+def test_small_and_odd_shapes_on_the_tensor_core_kernels(shape):
+    """Edge shapes of the tensor-core path (one chunk, head counts that are not powers of two, chunk counts that do not fill
+    a group of the rows-before-a-chunk kernels) against the fp32 oracle: out <= 2e-2, gradients <= 5e-2 rel-Frobenius, with
+    random upstream gradients on every block (the gradient through the rows before each chunk included)."""
+    B, H, R, L, c, D = shape
+    ua = _ua()
+    ins, ins32 = _bf16_case(*shape, seed=31)
+    gen = torch.Generator().manual_seed(13)
+    n = L // c
+    g_out = torch.randn(B, H, R, L, D, n, generator=gen).bfloat16()
+    g_denom = torch.randn(B, H, R, L, n, generator=gen)
+    ref_out, ref_denom, _ = O.ua_forward(*ins32)
+    ref_grads = O.ua_backward(*ins32, g_out.float(), g_denom)
+    out, denom, grads = _run_op(ua.UniversalAttention.apply, _cuda(*ins), g_out.cuda(), g_denom.cuda())
+    e = fwd_errors(out.float().cpu(), denom.float().cpu(), ref_out, ref_denom, c)
+    assert e["out_masked"] <= 2e-2 and e["masked_denom_ok"], e
+    for got, ref, key in zip(grads, ref_grads, GRADS):
+        assert torch.isfinite(got.float()).all(), key
+        assert rel_fro(got.float().cpu(), ref) <= 5e-2, (key, rel_fro(got.float().cpu(), ref))
