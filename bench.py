@@ -53,11 +53,11 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 
 # DRAM bytes per backward call at workload c2, from one ncu capture of a slice of 2 of the 32 (batch, kv-head) units: the
-# keys-on-lanes kernel (91.94 MB read + 3.78 MB written) plus the sweep over the rows before each chunk (80.87 + 2.55 MB);
+# keys-on-lanes kernel (91.79 MB read + 3.19 MB written) plus the sweep over the rows before each chunk (80.87 + 2.47 MB);
 # the small per-chunk kernels and the fp32 -> bf16 conversions are not in the figure.  The traffic grows in proportion to
 # the units.  No figure is given for the forward: a capture of that slice ends with part of the 134 MB it writes still in
 # the 126 MB L2, so its DRAM write count understates a full launch.
-NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (91.942400e6 + 3.775744e6 + 80.872448e6 + 2.554624e6)}}
+NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (91.794688e6 + 3.192832e6 + 80.872192e6 + 2.467328e6)}}
 
 
 def flops(w):
