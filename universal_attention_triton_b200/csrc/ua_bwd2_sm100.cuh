@@ -766,7 +766,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           e[2 * x + 1] = ev.y;
         }
 #ifdef UA_EXP_NO_COLSUM
-        const float part = e[lane & 1];
+        const float part = e[0] + e[1];
 #else
         const float part = warp_colsum<CG>(e, scr, lane);            // this warp's 32 keys, column col0 + lane % CG
 #endif
