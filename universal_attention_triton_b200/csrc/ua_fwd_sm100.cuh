@@ -26,6 +26,7 @@
 // Every mbarrier wait is bounded; on a timeout the block raises a shared abort
 // flag, every role leaves its loop, TMEM is freed and status[0] is set.
 #pragma once
+#include <type_traits>
 #include "ua_common.cuh"
 #include "ua_ptx.cuh"
 
@@ -325,16 +326,33 @@ __device__ __forceinline__ void fwd_decay(const FwdCtx<D>& c, const FwdParams& p
         t3r[4 * x] = t4.x; t3r[4 * x + 1] = t4.y; t3r[4 * x + 2] = t4.z; t3r[4 * x + 3] = t4.w;
       }
       float local = 0.f;
+      // (the diagonal tile is the only one with masked pairs: its tests are compiled into a path of its own)
+      auto scan32 = [&](auto on_diag) {
+        constexpr bool kDiag = decltype(on_diag)::value;
+        const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), s32 = make_float2(s3, s3), one2 = make_float2(1.0f, 1.0f),
+                     mone2 = make_float2(-1.0f, -1.0f), ln2 = make_float2(0.6931471805599453f, 0.6931471805599453f);
 #pragma unroll
-      for (int x = 0; x < 32; ++x) {
-        const int q = cb * 32 + x;
-        const float gv = __uint_as_float(g[x]);
-        float ell = log_retention(gated_affinity(gram_pow23(gv), s3, t3r[x]));
-        if (diag && q <= k) ell = 0.f;
-        local += ell;
-        cval = carry + (tprev + local);
-        v[x] = (diag && q < k) ? mask_value() : cval;
-      }
+        for (int x = 0; x < 32; x += 2) {
+          // two rows at a time with packed fp32 arithmetic: relu(g)^(2/3) through lg2(max(g, 0)) = -inf for g <= 0
+          const float2 lg = make_float2(lg2(fmaxf(__uint_as_float(g[x]), 0.f)), lg2(fmaxf(__uint_as_float(g[x + 1]), 0.f)));
+          const float2 e23 = fmul2(lg, k23);
+          const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
+          const float2 a = fmul2(fmul2(pw, s32), make_float2(t3r[x], t3r[x + 1]));
+          const float2 om = ffma2(make_float2(fminf(a.x, clamp_hi()), fminf(a.y, clamp_hi())), mone2, one2);
+          const float2 el = fmul2(make_float2(lg2(om.x), lg2(om.y)), ln2);
+#pragma unroll
+          for (int y = 0; y < 2; ++y) {
+            const int q = cb * 32 + x + y;
+            float ell = y ? el.y : el.x;
+            if (kDiag && q <= k) ell = 0.f;
+            local += ell;
+            cval = carry + (tprev + local);
+            v[x + y] = (kDiag && q < k) ? mask_value() : cval;
+          }
+        }
+      };
+      if (diag) scan32(std::true_type{});
+      else scan32(std::false_type{});
       tprev += local;
       if (!kCarryOnly) {
         UF(2)
