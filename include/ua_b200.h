@@ -139,6 +139,20 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
                 const float* lse_cm,
                 void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
                 void* workspace, size_t workspace_bytes, int flags, void* stream);
+/* ua_bwd_kept() for a caller that still holds the forward's output tiles out_cm (b,h,n,r,L,d), as an autograd graph does
+ * whenever a later node saved them (SMVecMatMul does: universal_attention_autograd.py:286-288).  The softmax gradient
+ * needs sum_k P dP per row; since P V = out, that is the dot product of the row's output and its upstream gradient, which
+ * the tensor-core kernel then takes from the tiles instead of summing over the keys (about a tenth of its time).  out_cm
+ * must be what ua_fwd wrote for the same inputs (rows before a chunk are not read); NULL: ua_bwd_kept().  Kernels
+ * other than the tensor-core one ignore it.  The reference recomputes everything (universal_attention_autograd.py:
+ * 166-169); its Triton backward has no use for the tiles. */
+int ua_bwd_saved(const UaDims* dims, int dtype, int gate_dtype,
+                 const void* kc, const void* vc, const void* xq,
+                 const void* static_src, const void* static_dest,
+                 const void* g_out_cm, const void* g_denom_cm, int g_denom_dtype, const void* carry_in,
+                 const float* lse_cm, const void* out_cm,
+                 void* dkc, void* dvc, void* dxq, void* dstatic_src, void* dstatic_dest,
+                 void* workspace, size_t workspace_bytes, int flags, void* stream);
 
 /* ---- Sequence-chunk sharding (long contexts).  No counterpart in the reference, which is single-device. ----
  *
@@ -164,7 +178,9 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
  *   ua_bwd_rows_suffix    every gradient is linear in the reverse carry: after exchanging the dctot tables,
  *                         suffix = sum of dctot over the ranges AFTER this one, and this decay-only pass adds what it
  *                         induces into dk_f32, dsrc_f32 and ddest_rows_f32 (no queries, values or upstream gradients).
- * Workspace: 256 bytes, except ua_bwd_rows: ua_bwd_rows_workspace_bytes(). */
+ * Workspace: 256 bytes, except ua_bwd_rows (ua_bwd_rows_workspace_bytes()) and ua_bwd_rows_suffix
+ * (ua_bwd_rows_suffix_workspace_bytes(): an fp32 (b*h, L, d) scratch for the row-side dK, from which d static_dest
+ * is taken after the sweep). */
 typedef struct UaRows {
   int32_t tile_begin;   /* first row tile of the range (global tile index) */
   int32_t tile_end;     /* one past the last */
@@ -190,6 +206,7 @@ int ua_fwd_rows_keep(const UaDims* dims, int dtype, int gate_dtype, const UaRows
                      void* out_cm_rows, float* lse_cm_rows, void* denom_cm_rows, float* carry_table_out,
                      void* workspace, size_t workspace_bytes, int flags, void* stream);
 size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype);
+size_t ua_bwd_rows_suffix_workspace_bytes(const UaDims* dims, int dtype);
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows,
                 const void* kc, const void* vc, const void* xq_rows,
                 const void* static_src, const void* static_dest_rows,

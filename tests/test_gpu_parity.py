@@ -174,8 +174,9 @@ def test_tensor_core_forward_matches_simt_forward(shape):
 def test_tensor_core_backward_config2_length_against_oracle(L):
     """Backward at the sequence length of BASELINE config 2 (L=4096, chunk 128, D=64; one (b, h) unit, R=2) and at twice
     that against the CPU oracle with random upstream gradients (masked-block gradients included): 5e-2
-    relative-Frobenius as the task states, through both the plain backward and the one that takes the forward's table
-    and log-sum-exp; the forward's log-sum-exp along the way."""
+    relative-Frobenius as the task states, through the plain backward, the one that takes the forward's table and
+    log-sum-exp, and the one that also takes the forward's output tiles (row term of the softmax gradient from
+    out . g_out); the forward's log-sum-exp along the way."""
     from universal_attention_triton_b200 import ops
     from tests._util import valid_row_mask
     shape = (1, 1, 2, L, 128, 64)
@@ -193,7 +194,7 @@ def test_tensor_core_backward_config2_length_against_oracle(L):
     dl = (ops.as_reference_denom(lse_cm).cpu() - ref_lse).abs()
     assert ((dl <= 2e-2 + 1e-5 * ref_lse.abs()) | ~valid_row_mask(L, n, c)).all()
     del ref_lse, dl
-    for kwargs in ({}, {"carry": carry, "lse": lse_cm}):
+    for kwargs in ({}, {"carry": carry, "lse": lse_cm}, {"carry": carry, "lse": lse_cm, "out_cm": out_cm}):
         got = ops.backward_cm(*cu, g_out_cm, g_den_cm, **kwargs)
         check_backward(f"L={L} {sorted(kwargs)}", got, ins32, g_out.float(), g_den)      # 5e-2, noise-pinned
 
@@ -217,10 +218,13 @@ def test_tensor_core_backward_matches_simt_backward(shape, skip):
         g_lse = g_lse * valid
     flags = _lib.FLAG_SKIP_MASKED_GRADS if skip else 0
     tc = ops.backward_cm(*cu, g_out, g_lse, flags=flags)
+    out_cm = ops.forward_cm(*cu)[0]
+    tc_out = ops.backward_cm(*cu, g_out, g_lse, flags=flags, out_cm=out_cm)      # row term from the forward's output tiles
     sm = ops.backward_cm(*cu, g_out, g_lse, flags=_lib.FLAG_FORCE_SIMT)
-    for a, b, key in zip(tc, sm, GRADS):
-        assert torch.isfinite(a.float()).all(), key
-        assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, rel_fro(a.float().cpu(), b.float().cpu()))
+    for got in (tc, tc_out):
+        for a, b, key in zip(got, sm, GRADS):
+            assert torch.isfinite(a.float()).all(), key
+            assert rel_fro(a.float().cpu(), b.float().cpu()) <= 2e-2, (key, rel_fro(a.float().cpu(), b.float().cpu()))
 
 
 @pytest.mark.parametrize("skip", [False, True])

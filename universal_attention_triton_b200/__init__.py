@@ -9,8 +9,9 @@ from .universal_attention_autograd import (  # noqa: F401
     set_merged_backward,
     set_merged_forward,
     set_output_layout,
+    set_save_output,
     set_strict_masked_grads,
 )
 
 __all__ = ["UniversalAttention", "UniversalAttention2", "UniversalAttentionMerged", "SMVecMatMul", "set_output_layout", "set_merged_backward", "set_merged_forward",
-           "set_strict_masked_grads", "ops"]
+           "set_save_output", "set_strict_masked_grads", "ops"]

@@ -45,10 +45,12 @@ SIGNATURES = {
     "ua_carry_bytes": (_sz, [_dp, _i, _i]),
     "ua_fwd_keep": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_bwd_kept": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
+    "ua_bwd_saved": (_i, [_dp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_fwd_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_decay_totals_rows": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "ua_fwd_rows_keep": (_i, [_dp, _i, _i, _rp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp]),
     "ua_bwd_rows_workspace_bytes": (_sz, [_dp, _i]),
+    "ua_bwd_rows_suffix_workspace_bytes": (_sz, [_dp, _i]),
     "ua_bwd_rows_kept": (_i, [_dp, _i, _i, _rp] + [_vp] * 7 + [_i] + [_vp] * 11 + [_sz, _i, _vp]),
     "ua_bwd_rows": (_i, [_dp, _i, _i, _rp] + [_vp] * 7 + [_i] + [_vp] * 9 + [_sz, _i, _vp]),
     "ua_bwd_rows_suffix": (_i, [_dp, _i, _i, _rp] + [_vp] * 9 + [_sz, _vp]),

@@ -79,10 +79,10 @@ BwdWorkspace bwd_layout(const ua::Shape& s, int rt) {
 }
 
 struct BwdWorkspaceTc {
-  size_t off_dk, off_dq, off_dt, off_carry, off_lse, off_gd, off_mt, off_ksum, off_nacc, acc_bytes, total;
+  size_t off_dk, off_dq, off_dt, off_dkr, off_carry, off_lse, off_gd, off_mt, off_ksum, off_nacc, acc_bytes, total;
 };
 
-// Scratch of the tensor-core backward: status | fp32 accumulators dK, dQ, d dest | decay-prefix table (two entries per
+// Scratch of the tensor-core backward: status | fp32 accumulators dK, dQ, d dest, row-side dK | decay-prefix table (two entries per
 // 128-row tile) | log-sum-exp (only written when the caller has none) | fp32 copy of g_denom (only written when the
 // caller's is bf16) | per-chunk data of the kernels for the rows before a chunk.
 BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
@@ -92,6 +92,7 @@ BwdWorkspaceTc bwd_layout_tc(const ua::Shape& s) {
   w.off_dk = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.off_dq = o; o = align_up(o + BH * s.R * s.L * s.D * f, 256);
   w.off_dt = o; o = align_up(o + BH * s.L * f, 256);
+  w.off_dkr = o; o = align_up(o + BH * s.L * s.D * f, 256);
   w.acc_bytes = o;
   w.off_carry = o; o = align_up(o + BH * s.N * (size_t)s.N * 256 * f, 256);
   w.off_lse = o; o = align_up(o + BH * s.N * (size_t)s.R * s.L * f, 256);
@@ -498,11 +499,21 @@ size_t ua_bwd_rows_workspace_bytes(const UaDims* dims, int dtype) {
   if (check_dims(dims) != UA_OK) return 0;
   ua::Shape s = to_shape(dims);
   if (!ua::sm100::bwd2_supported(s, dtype)) return 0;
-  // status | decay-prefix table | log-sum-exp of the range's rows | fp32 copy of a bf16 g_denom (both sized for Ls = L) |
-  // per-chunk data of the kernels for the rows before a chunk (M^T images, ksum, N / w / u / vbar)
+  // status | row-side dK scratch (as for ua_bwd_rows_suffix) | decay-prefix table | log-sum-exp of the range's rows | fp32
+  // copy of a bf16 g_denom (both sized for Ls = L) | per-chunk data of the kernels for the rows before a chunk (M^T images,
+  // ksum, N / w / u / vbar)
   const size_t rows = (size_t)s.B * s.H * s.N * s.R * s.L, chunks = (size_t)s.B * s.H * s.N;
-  return 256 + align_up(chunks * (size_t)s.N * 256 * sizeof(float), 256) + 2 * align_up(rows * sizeof(float), 256) +
-         align_up(chunks * s.D * s.D * 2, 256) + align_up(chunks * s.D * 2, 256) + align_up(chunks * (s.D + 3) * s.D * sizeof(float), 256);
+  return ua_bwd_rows_suffix_workspace_bytes(dims, dtype) + align_up(chunks * (size_t)s.N * 256 * sizeof(float), 256) +
+         2 * align_up(rows * sizeof(float), 256) + align_up(chunks * s.D * s.D * 2, 256) + align_up(chunks * s.D * 2, 256) +
+         align_up(chunks * (s.D + 3) * s.D * sizeof(float), 256);
+}
+
+size_t ua_bwd_rows_suffix_workspace_bytes(const UaDims* dims, int dtype) {
+  if (check_dims(dims) != UA_OK) return 0;
+  ua::Shape s = to_shape(dims);
+  if (!ua::sm100::bwd2_supported(s, dtype)) return 0;
+  // status | fp32 (b*h, L, d) scratch for the row-side dK, from which d static_dest is taken
+  return 256 + align_up((size_t)s.B * s.H * s.L * s.D * sizeof(float), 256);
 }
 
 int ua_bwd_rows(const UaDims* dims, int dtype, int gate_dtype, const UaRows* rows, const void* kc, const void* vc,
@@ -537,8 +548,11 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
   const size_t need = ua_bwd_rows_workspace_bytes(dims, dtype);
   if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  char* ws = static_cast<char*>(workspace);
-  if (cudaMemsetAsync(ws, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  const size_t head = ua_bwd_rows_suffix_workspace_bytes(dims, dtype);       // status word + row-side dK scratch, both zeroed
+  if (cudaMemsetAsync(workspace, 0, head, st) != cudaSuccess) return UA_ERR_CUDA;
+  float* acc_dkr = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
+  int* status = static_cast<int*>(workspace);
+  char* ws = static_cast<char*>(workspace) + head - 256;                    // (the offsets below count from a 256-byte header)
   const size_t BHs = (size_t)s.B * s.H;
   const size_t tab_bytes = align_up(BHs * s.N * (size_t)s.N * 256 * sizeof(float), 256);
   const size_t row_elems = BHs * s.N * (size_t)s.R * rows->rows_total;
@@ -553,7 +567,7 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
     carry_tab = tab; lse_rows = lse_ws;
     ua::sm100::FwdParams fp{};
     fp.s = s; fp.ssrc = static_src; fp.sdest = static_dest_rows; fp.out = nullptr; fp.denom = nullptr; fp.lse = lse_ws;
-    fp.status = reinterpret_cast<int*>(ws); fp.carry = tab;
+    fp.status = status; fp.carry = tab;
     fp.j_begin = rows->tile_begin; fp.j_end = rows->tile_end; fp.Lr = rows->rows_total; fp.r0 = rows->row_offset;
     fp.carry_in = carry_in; fp.total_out = nullptr;
     if ((e = ua::sm100::launch_fwd<false>(s, gate_dtype, kc, vc, xq_rows, fp, false, st))) return e;
@@ -574,7 +588,7 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
     mp.mt = reinterpret_cast<uint8_t*>(q); q += align_up(chunks * s.D * s.D * 2, 256);
     mp.ksum = reinterpret_cast<__nv_bfloat16*>(q); q += align_up(chunks * s.D * 2, 256);
     mp.nacc = reinterpret_cast<float*>(q);
-    mp.acc_dk = dk_f32; mp.status = reinterpret_cast<int*>(ws);
+    mp.acc_dk = dk_f32; mp.status = status;
     mp.j_begin = rows->tile_begin; mp.j_end = rows->tile_end; mp.Lr = rows->rows_total; mp.r0 = rows->row_offset;
     mp.acc_dv = dv_f32;
     if ((e = ua::sm100::launch_masked(s, kc, vc, xq_rows, g_out_cm_rows, dxq_rows_f32, mp, st))) return e;
@@ -583,9 +597,10 @@ int ua_bwd_rows_kept(const UaDims* dims, int dtype, int gate_dtype, const UaRows
   ua::sm100::Bwd2Params qp{};
   qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = gd32; qp.lse = lse_rows; qp.carry = carry_tab;
   qp.acc_dk = dk_f32; qp.acc_dq = dxq_rows_f32; qp.acc_dt = ddest_rows_f32; qp.dv_chunk = nullptr;
-  qp.dvc = nullptr; qp.dss = nullptr; qp.status = reinterpret_cast<int*>(ws); qp.trace = nullptr;
+  qp.dvc = nullptr; qp.dss = nullptr; qp.status = status; qp.trace = nullptr;
   qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
   qp.heads = s.R; qp.suffix_in = suffix_in; qp.dctot_out = dctot_out; qp.acc_dv = dv_f32; qp.acc_ds = dsrc_f32;
+  qp.acc_dkr = acc_dkr;
   return ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, xq_rows, g_out_cm_rows, qp, st);
 }
 
@@ -599,16 +614,18 @@ int ua_bwd_rows_suffix(const UaDims* dims, int dtype, int gate_dtype, const UaRo
   if (!aligned16(kc) || !aligned16(vc) || !aligned16(dk_f32)) return UA_ERR_ALIGNMENT;
   ua::Shape s = to_shape(dims);
   if ((e = check_rows(s, ua::sm100::bwd2_supported(s, dtype), rows))) return e;
-  if (!workspace || workspace_bytes < 256 || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
+  const size_t need = ua_bwd_rows_suffix_workspace_bytes(dims, dtype);
+  if (!workspace || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u)) return UA_ERR_WORKSPACE;
   if (!aligned16(static_dest_rows)) return UA_ERR_ALIGNMENT;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (cudaMemsetAsync(workspace, 0, 256, st) != cudaSuccess) return UA_ERR_CUDA;
+  if (cudaMemsetAsync(workspace, 0, need, st) != cudaSuccess) return UA_ERR_CUDA;
   // the keys-on-lanes kernel without heads: recomputed G, the decay gradient that `suffix` induces, the two dK products
   ua::sm100::Bwd2Params qp{};
   qp.s = s; qp.ssrc = static_src; qp.sdest = static_dest_rows; qp.g_denom = nullptr; qp.lse = nullptr; qp.carry = nullptr;
   qp.acc_dk = dk_f32; qp.acc_dq = nullptr; qp.acc_dt = ddest_rows_f32; qp.dv_chunk = nullptr;
   qp.dvc = nullptr; qp.dss = nullptr; qp.status = static_cast<int*>(workspace); qp.trace = nullptr;
   qp.j_begin = rows->tile_begin; qp.j_end = rows->tile_end; qp.Lr = rows->rows_total; qp.r0 = rows->row_offset;
+  qp.acc_dkr = reinterpret_cast<float*>(static_cast<char*>(workspace) + 256);
   qp.heads = 0; qp.suffix_in = suffix; qp.dctot_out = nullptr; qp.acc_dv = nullptr; qp.acc_ds = dsrc_f32;
   return ua::sm100::launch_bwd2(s, gate_dtype, false, kc, vc, nullptr, nullptr, qp, st);
 }
@@ -625,6 +642,15 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
                 const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
                 int g_denom_dtype, const void* carry_in, const float* lse_cm, void* dkc, void* dvc, void* dxq,
                 void* dstatic_src, void* dstatic_dest, void* workspace, size_t workspace_bytes, int flags, void* stream) {
+  return ua_bwd_saved(dims, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, g_denom_dtype,
+                      carry_in, lse_cm, nullptr, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, workspace_bytes, flags, stream);
+}
+
+int ua_bwd_saved(const UaDims* dims, int dtype, int gate_dtype, const void* kc, const void* vc, const void* xq,
+                 const void* static_src, const void* static_dest, const void* g_out_cm, const void* g_denom_cm,
+                 int g_denom_dtype, const void* carry_in, const float* lse_cm, const void* out_cm, void* dkc, void* dvc,
+                 void* dxq, void* dstatic_src, void* dstatic_dest, void* workspace, size_t workspace_bytes, int flags,
+                 void* stream) {
   int e = check_dims(dims);
   if (e) return e;
   if (!dtype_ok(dtype, gate_dtype)) return UA_ERR_BAD_DTYPE;
@@ -661,9 +687,10 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
         group_denom_grad_kernel<bf16><<<148 * 8, 256, 0, st>>>(lse_sub, static_cast<const bf16*>(g_denom_cm), g_lse_sub, groups, rl, m);
       if (cudaGetLastError() != cudaSuccess) return UA_ERR_CUDA;
     }
-    if ((e = ua_bwd_kept(&sd, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_sub, g_lse_sub, UA_F32,
-                         carry_in ? carry_in : carry_sub, lse_sub, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace, inner, flags,
-                         stream)))
+    // (the sub-chunk output tiles were just recomputed: the inner call takes its row term from them)
+    if ((e = ua_bwd_saved(&sd, dtype, gate_dtype, kc, vc, xq, static_src, static_dest, g_out_sub, g_lse_sub, UA_F32,
+                          carry_in ? carry_in : carry_sub, lse_sub, out_sub, dkc, dvc, dxq, dstatic_src, dstatic_dest, workspace,
+                          inner, flags, stream)))
       return e;
     carry_status_kernel<<<1, 1, 0, st>>>(reinterpret_cast<const int*>(ws + w.off_status), reinterpret_cast<int*>(ws));
     return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
@@ -724,9 +751,11 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype, const void* kc, c
     qp.g_denom = gd32;
     qp.lse = lse; qp.row_lse = nullptr; qp.row_delta = nullptr; qp.carry = carry_tab;
     qp.acc_dk = acc_dk; qp.acc_dq = acc_dq; qp.acc_dt = acc_dt;
+    qp.acc_dkr = reinterpret_cast<float*>(ws + w.off_dkr);
     qp.dv_chunk = dv_chunk; qp.dv_chunk_stride = (s.D + 3) * s.D;
     qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
     qp.trace = nullptr;
+    qp.out_tiles = (out_cm && aligned16(out_cm)) ? out_cm : nullptr;
 #ifdef UA_PROFILE_BWD2
     if (const char* tp = getenv("UA_TRACE_PTR")) qp.trace = reinterpret_cast<long long*>(strtoull(tp, nullptr, 0));
 #endif
@@ -1058,6 +1087,7 @@ int ua_bwd_merged(const UaDims* dims, int dtype, int gate_dtype, const void* kc,
   qp.acc_dk = reinterpret_cast<float*>(ws + w.off_dk);
   qp.acc_dq = reinterpret_cast<float*>(ws + w.off_dq);
   qp.acc_dt = reinterpret_cast<float*>(ws + w.off_dt);
+  qp.acc_dkr = reinterpret_cast<float*>(ws + w.off_dkr);
   qp.dvc = static_cast<bf16*>(dvc); qp.dss = dstatic_src; qp.status = reinterpret_cast<int*>(ws);
   qp.trace = nullptr;
   e = ua::sm100::launch_bwd2(s, gate_dtype, true, kc, vc, xq, g_merged, qp, st);

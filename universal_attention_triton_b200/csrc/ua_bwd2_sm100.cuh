@@ -51,7 +51,8 @@ struct Bwd2Params {
   const float* carry;        // (b*h*n, n, 2, 128): decay prefix of key k at the start of each 64-row half tile
   float* acc_dk;             // (b*h, L, D) fp32, zeroed (or holding the masked-block part)
   float* acc_dq;             // (b*h, r, L, D) fp32, likewise
-  float* acc_dt;             // (b*h, L) fp32, zeroed
+  float* acc_dt;             // (b*h, Lr) fp32: d static_dest is ADDED here (by row_side_finish_kernel, after the sweep)
+  float* acc_dkr;            // (b*h, L, D) fp32 scratch, zeroed: the row-side dK_j = dG^T K_i of all chunks (see there)
   const float* dv_chunk;     // optional: row dv_chunk[chunk * dv_chunk_stride + d] / 128 is added to every key's dV_i (the
   int dv_chunk_stride;       // masked-block part when it comes from the kernels of the rows before a chunk)
   __nv_bfloat16* dvc;
@@ -67,6 +68,10 @@ struct Bwd2Params {
   float* dctot_out;          // optional (b*h*n, 128): per key, sum of dC over the rows of the range (what earlier ranges need)
   float* acc_dv;             // optional (b*h, L, D) fp32: dV_i is ADDED here instead of being written to dvc
   float* acc_ds;             // optional (b*h, L) fp32: d static_src is ADDED here instead of being written to dss
+  // optional [mode 1, head_dim 64]: the forward's output tiles (b,h,n,r,Lr,D), laid out like g_out.  With them the
+  // softmax-gradient row term sum_k P dP is the dot product of a row's output and its upstream gradient (P V = out), which
+  // two otherwise idle warps form ahead of the workers; without them the workers sum P dP over the keys themselves.
+  const void* out_tiles;
 };
 
 template <int D>
@@ -87,20 +92,24 @@ struct Bwd2Cfg {
   static constexpr int oDg = oDs + kDs * 16384;
   static constexpr int oStage = oDg + 16384;               // [64][D] fp32 as D/32 boxes of [64][32], 128-byte swizzle
   static constexpr int oT3 = oStage + 256 * D;             // float [2][64]: static_dest^(1/3) of a half tile's rows
-  static constexpr int oDt = oT3 + 512;                    // float [2][64]: d static_dest of a half tile, flushed by the drain warps
   // per-row tables that the producer copies next to the tiles (no global load is ever issued by a worker):
-  static constexpr int oHeadTab = oDt + 512;               // kNS x { float lse[64]; float cc[64] }: log-sum-exp and g_denom (or delta) of a head's rows
+  static constexpr int oHeadTab = oT3 + 512;               // kNS x { float lse[64]; float cc[64] }: log-sum-exp and g_denom (or delta) of a head's rows
   static constexpr int kTab = 3;                           // half-tile tables in flight
   static constexpr int kHtTab = 768;                       // { float carry[128]; raw static_dest[64] (<= 256 B) }
   static constexpr int oHtTab = oHeadTab + kNS * 512;
   static constexpr int oXch = oHtTab + kTab * kHtTab;      // float [8][128] totals crossing the column groups
   static constexpr int oBar = oXch + 4096;
-  static constexpr int oMisc = oBar + 256;      // (31 barriers of 8 bytes)
+  static constexpr int oMisc = oBar + 320;      // (35 barriers of 8 bytes)
   // per-warp scratch tiles for the column sums over the keys ([32 lanes][CG + 4] floats each, at most 40 KB in all);
   // head_dim 128 has no room for them and transposes with shuffles
   static constexpr bool kScratch = (D == 64);
   static constexpr int oScr = oMisc + 256;
   static constexpr int kSmemBytes = oScr + (kScratch ? 40960 : 0) + 1024;     // + slack to align the base to 1024 B
+  // builds that take the row term from the forward's output tiles (head_dim 64) keep kNS output half tiles where the
+  // scratch tiles would be, and sum the decay gradient's columns with shuffles
+  static constexpr bool kOutTiles = kScratch;
+  static constexpr int oOut = (oScr + 1023) / 1024 * 1024;
+  static_assert(!kOutTiles || oOut + kNS * kHalf <= oScr + 40960, "output tiles fit the scratch area");
   // TMEM columns
   static constexpr uint32_t tDV = 0, tDK = D, tY = 2 * D;
   static constexpr uint32_t tS0 = (D == 64) ? 192 : 384, tP0 = tS0 + 64, tS1 = tS0 + 128, tP1 = tS0 + 192;
@@ -120,7 +129,8 @@ enum Bwd2Bar {
   qDsReady = 19, qDsFree = 21,     // [2] per dS buffer
   qYFull = 23, qYFree = 24, qDgReady = 25, qDgFree = 26, qFinal = 27,
   qTabFull = 28,                   // [3] per half-tile table buffer
-  qNumBars = 31
+  qDelta = 31,                     // [4] per (Q, dO) slot: the row term of the head's table is final (output-tile builds)
+  qNumBars = 35
 };
 
 struct Bwd2Ctx {
@@ -204,9 +214,9 @@ __device__ __forceinline__ void mma4_ts(uint32_t d, uint32_t a0, uint32_t a1, ui
 }
 
 // ------------------------------------------------------------- TMA producer --
-template <int D, typename TG, int kMode>
+template <int D, typename TG, int kMode, bool kOutDelta>
 __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmK, const CUtensorMap* tmV,
-                                              const CUtensorMap* tmQ, const CUtensorMap* tmG) {
+                                              const CUtensorMap* tmQ, const CUtensorMap* tmG, const CUtensorMap* tmO) {
   using Cfg = Bwd2Cfg<D>;
   const int L = p.s.L, R = p.s.R, N = p.s.N;
   const uint32_t sb = smem_u32(c.smem);
@@ -255,7 +265,8 @@ __device__ __forceinline__ void bwd2_producer(const Bwd2Ctx& c, const Bwd2Params
       const int qrow = (c.bh * R + r) * p.Lr + srow0;
       const int grow = (kMode == 2) ? qrow : (int)((chunk_id * R + r) * p.Lr + srow0);
       const uint32_t dst = sb + Cfg::oSlot + sl * Cfg::kSlot, tab = sb + Cfg::oHeadTab + sl * 512;
-      mbar_expect_tx(c.bar(qInFull + sl), 2 * Cfg::kHalf + 512);
+      mbar_expect_tx(c.bar(qInFull + sl), (kOutDelta ? 3 : 2) * Cfg::kHalf + 512);
+      if (kOutDelta) tma_load_2d(sb + Cfg::oOut + sl * Cfg::kHalf, tmO, 0, grow, c.bar(qInFull + sl));
 #pragma unroll
       for (int b = 0; b < Cfg::kBoxes; ++b) {
         tma_load_2d(dst + b * 8192, tmQ, b * 64, qrow, c.bar(qInFull + sl));
@@ -506,6 +517,7 @@ __device__ __forceinline__ float warp_colsum(float* v, float* scr, int lane) {
 // head, then dK_j of the half tile.  The 64 x D fp32 tile is staged in shared memory as boxes of [64][32] floats and
 // leaves as TMA reduce-adds into the fp32 accumulators (other key chunks add to the same rows), which run behind the
 // next unit; the workers never touch it.
+//
 template <int D>
 __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p, const CUtensorMap* tmDQ, const CUtensorMap* tmDK) {
   using Cfg = Bwd2Cfg<D>;
@@ -521,14 +533,6 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
     for (int r = 0; r <= Rh; ++r, ++yc) {
       if (!c.wait_w(qYFull, yc)) return;
       tc_fence_after();
-      if (r == Rh) {
-        // d static_dest of the half tile: the workers have added their column sums in shared memory (complete before dK_j
-        // was issued); one global add per row, and the buffer is zero again before this Y is released
-        float* dt = reinterpret_cast<float*>(c.smem + Cfg::oDt) + (ht & 1) * 64 + row;
-        const float v = *dt;
-        if (v != 0.f) atomicAdd(p.acc_dt + (size_t)c.bh * p.Lr + c.srow0_of(ht) + row, v);
-        *dt = 0.f;
-      }
       if (leader) bulk_wait_read_all();                 // the previous reduce-add has read the staging tile
       named_bar_sync(kBarDrain, 64);
 #pragma unroll 1
@@ -566,10 +570,50 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
   if (leader) bulk_wait_all();                          // the reduce-adds have landed before the block retires
 }
 
+// --------------------------------------------------------------- row-dot warps --
+// Builds that are given the forward's output tiles (head_dim 64): the producer copies the head's output half tile next to
+// its dO half tile, and two warps (thread = row of the half tile) turn the g_denom entry of the head's table into
+// g_denom - out . dO.  They run up to a slot ring ahead of the workers, who then need neither the column sums of P dP over
+// the keys nor the barrier that completed them.  (Fetching the output rows with plain global loads from these warps
+// instead made the kernel slower than the column sums: loads issued inside this kernel queue behind its shared-memory
+// traffic.)
+__device__ __forceinline__ void dot_bf16x8(const uint4& a, const uint4& b, float& lo, float& hi) {
+  const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+  for (int x = 0; x < 4; ++x) {
+    lo = fmaf(__uint_as_float(aw[x] << 16), __uint_as_float(bw[x] << 16), lo);
+    hi = fmaf(__uint_as_float(aw[x] & 0xffff0000u), __uint_as_float(bw[x] & 0xffff0000u), hi);
+  }
+}
+template <int D>
+__device__ __forceinline__ void bwd2_rowdots(const Bwd2Ctx& c, const Bwd2Params& p) {
+  using Cfg = Bwd2Cfg<D>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = (warp - 6) * 32 + lane;               // 0..63
+  const uint32_t swz = (uint32_t)(row & 7);
+  const int total = c.nht * p.heads;
+  for (int hc = 0; hc < total; ++hc) {
+    const int sl = hc % Cfg::kNS;
+    const uint8_t* go = c.smem + Cfg::oSlot + sl * Cfg::kSlot + Cfg::kHalf + row * 128;
+    const uint8_t* oo = c.smem + Cfg::oOut + sl * Cfg::kHalf + row * 128;
+    if (!c.wait_w(qInFull + sl, hc / Cfg::kNS)) return;
+    float lo = 0.f, hi = 0.f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+      const uint32_t off = (((uint32_t)x) ^ swz) << 4;
+      dot_bf16x8(*reinterpret_cast<const uint4*>(oo + off), *reinterpret_cast<const uint4*>(go + off), lo, hi);
+    }
+    float* tabC = reinterpret_cast<float*>(c.smem + Cfg::oHeadTab + sl * 512) + 64;
+    tabC[row] -= lo + hi;
+    c.arrive_w(qDelta + sl);
+  }
+}
+
 // CG: columns of a half tile per thread (32: two column groups, 8 worker warps; 16: four groups, 16 worker warps)
 // kHeads = false: the correction pass (p.heads == 0).  A compile-time switch: as a run-time condition around the decay
 // recomputation it cost the whole-sequence kernel 2 % (measured).
-template <int D, typename TG, int kMode, int CG, bool kHeads>
+// kOutDelta: the row term comes from the delta warps (see bwd2_delta).
+template <int D, typename TG, int kMode, int CG, bool kHeads, bool kOutDelta>
 __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& p) {
   using Cfg = Bwd2Cfg<D>;
   constexpr int NG = 64 / CG;                    // column groups
@@ -589,9 +633,8 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   const float s3 = cbrtf(Num<TG>::ld(ss + c.i * 128 + key));
   const float2 s32 = make_float2(s3, s3);
   float* sT3 = reinterpret_cast<float*>(c.smem + Cfg::oT3);
-  float* sDt = reinterpret_cast<float*>(c.smem + Cfg::oDt);
   float* sXch = reinterpret_cast<float*>(c.smem + Cfg::oXch);
-  float* scr = Cfg::kScratch ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * (CG + 4)) : nullptr;
+  float* scr = (Cfg::kScratch && !kOutDelta) ? reinterpret_cast<float*>(c.smem + Cfg::oScr) + (warp - 8) * (32 * (CG + 4)) : nullptr;
   const uint32_t swz = (uint32_t)(key & 7);
   UQ_DECL
 
@@ -626,7 +669,6 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   // ---- prologue: static_dest^(1/3) of the first half tile ----
   if (!c.wait_w(qTabFull, 0)) return;
   if (helper && quad == 2) sT3[col0 + lane] = t3_from_table(0);
-  if (g == 0) sDt[key] = 0.f;                    // both half-tile parities of the d static_dest buffer
   float suffix = p.suffix_in ? p.suffix_in[((size_t)c.bh * N + c.i) * 128 + key] : 0.f, ds_acc = 0.f;
   named_bar_sync(kBarAll, kWorkers);
 
@@ -757,7 +799,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           dp[x] = make_float2(__uint_as_float(dr[2 * x]), __uint_as_float(dr[2 * x + 1]));
         }
       }
-      if (kMode == 1) {
+      if (kMode == 1 && !kOutDelta) {
         float e[CG];
 #pragma unroll
         for (int x = 0; x < H2; ++x) {
@@ -773,7 +815,11 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
         if (helper) atomicAdd(tabC + col0 + lane, -part);           // g_denom - sum_k P dP, in place
       }
       UQ(2)
-      named_bar_sync(kBarGroup + g, 128);
+      if (kOutDelta) {
+        if (!c.wait_w(qDelta + sl, hc / Cfg::kNS)) return;
+      } else {
+        named_bar_sync(kBarGroup + g, 128);
+      }
       UQ(4)
       {
         float2 cc[H2];
@@ -839,12 +885,11 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       c.arrive_w(qLdDone + b);
       ++u;
       uint32_t pk[H2];
-      float dtv[CG];
       float2 dsa = make_float2(0.f, 0.f);
       auto decay_grad = [&](auto on_diag) {
         constexpr bool kDiag = decltype(on_diag)::value;
         const float2 k23 = make_float2(2.0f / 3.0f, 2.0f / 3.0f), km13 = make_float2(-1.0f / 3.0f, -1.0f / 3.0f);
-        const float2 mone2 = make_float2(-1.0f, -1.0f);
+        const float2 mone2 = make_float2(-1.0f, -1.0f), s32k = fmul2(s32, k23);
 #pragma unroll
         for (int x = 0; x < H2; ++x) {
           float2 dl = fadd2(dc[x], add2);
@@ -854,8 +899,12 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           }
           const float g0 = __uint_as_float(gr[2 * x]), g1 = __uint_as_float(gr[2 * x + 1]);
           const float2 lg = make_float2(lg2(fmaxf(g0, 0.f)), lg2(fmaxf(g1, 0.f)));      // -inf for g <= 0: pw = 0
-          const float2 e23 = fmul2(lg, k23), e13 = fmul2(lg, km13);
-          const float2 pw = make_float2(ex2(e23.x), ex2(e23.y));
+          // g^(2/3) = g * g^(-1/3): one exponential serves both powers (relu: zero for g <= 0, where lg = -inf)
+          const float2 e13 = fmul2(lg, km13);
+          const float2 r13 = make_float2(ex2(e13.x), ex2(e13.y));
+          float2 pw = fmul2(make_float2(g0, g1), r13);
+          if (!(g0 > 0.f)) pw.x = 0.f;
+          if (!(g1 > 0.f)) pw.y = 0.f;
           const float2 st = fmul2(pw, s32);
           const float2 a = fmul2(st, t3p[x]);
           const float2 am = fadd2(make_float2(fminf(fmaxf(a.x, clamp_lo_bwd()), clamp_hi()), fminf(fmaxf(a.y, clamp_lo_bwd()), clamp_hi())), mone2);
@@ -865,11 +914,8 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           if (!(a.y <= clamp_hi())) da.y = 0.f;
           const float2 dstat = fmul2(da, pw);
           dsa = ffma2(dstat, t3p[x], dsa);
-          const float2 dt = fmul2(dstat, s32);                       // per-(key, row) term of d static_dest
-          dtv[2 * x] = dt.x;
-          dtv[2 * x + 1] = dt.y;
           // dG = dA s^(1/3) t^(1/3) (2/3) g^(-1/3) for g > 0
-          float2 dg = fmul2(fmul2(fmul2(da, s32), t3p[x]), fmul2(k23, make_float2(ex2(e13.x), ex2(e13.y))));
+          float2 dg = fmul2(fmul2(da, t3p[x]), fmul2(s32k, r13));
           if (!(g0 > 0.f)) dg.x = 0.f;
           if (!(g1 > 0.f)) dg.y = 0.f;
           __nv_bfloat162 h = __floats2bfloat162_rn(dg.x, dg.y);
@@ -881,12 +927,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       ds_acc += dsa.x + dsa.y;
       if (ht >= 1 && !c.wait_w(qDgFree, ht - 1)) return;
       store_row(c.smem + Cfg::oDg, pk);
-      // d static_dest: sum over the 128 keys of dstat * src^(1/3), added up in shared memory (the drain warps flush it)
-      const float colsum = warp_colsum<CG>(dtv, scr, lane);
-      if (helper && colsum != 0.f) {
-        const float t3l = t3v[lane];
-        atomicAdd(sDt + (ht & 1) * 64 + col0 + lane, colsum / (3.0f * t3l * t3l));
-      }
+      // (d static_dest needs no sum over the keys here: it is taken from dK_j afterwards, see row_side_finish_kernel)
       fence_proxy_async();
       c.arrive_w(qDgReady);
       UQ(10)
@@ -958,11 +999,13 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
   }
 }
 
-template <int D, typename TG, int kMode, int CG, bool kHeads>
+template <int D, typename TG, int kMode, int CG, bool kHeads, bool kOutDelta = false>
 __global__ void __launch_bounds__(32 * (8 + 4 * (64 / CG)), 1)
 bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
             const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
-            const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK, Bwd2Params p) {
+            const __grid_constant__ CUtensorMap tmDQ, const __grid_constant__ CUtensorMap tmDK,
+            const __grid_constant__ CUtensorMap tmO, Bwd2Params p) {
+  static_assert(!kOutDelta || (Bwd2Cfg<D>::kOutTiles && kMode == 1 && kHeads), "output-tile builds: head_dim 64, per-chunk form");
   using Cfg = Bwd2Cfg<D>;
   constexpr int NG = 64 / CG;
   extern __shared__ uint8_t smem_raw[];
@@ -991,13 +1034,14 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     for (int b = 0; b < qNumBars; ++b) {
       uint32_t count = 1;
       if (b == qLdDone || b == qLdDone + 1 || b == qDsReady || b == qDsReady + 1 || b == qDgReady) count = 4 * NG;   // one arrival per worker warp
-      if (b == qYFree) count = 2;                                                                                  // the two draining warps
+      if (b == qYFree || (b >= qDelta && b < qDelta + 4)) count = 2;                                                                                  // the two draining warps
       if (b == qDsFree || b == qDsFree + 1 || b == qDgFree || b == qFinal) count = 2;                               // both back issuers
       mbar_init(c.bar(b), count);
     }
     mbar_init_fence();
     prefetch_tmap(&tmK); prefetch_tmap(&tmV); prefetch_tmap(&tmQ); prefetch_tmap(&tmG);
     prefetch_tmap(&tmDQ); prefetch_tmap(&tmDK);
+    if (kOutDelta) prefetch_tmap(&tmO);
   }
   if (warp == 0) {
     tmem_alloc(smem_u32(misc), 512);
@@ -1026,15 +1070,16 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     if (lane == 0) {
       if (warp == 0) bwd2_front<D>(c, p);
       else if (warp == 1) bwd2_back<D, CG>(c, p, 0);
-      else if (warp == 2) bwd2_producer<D, TG, kMode>(c, p, &tmK, &tmV, &tmQ, &tmG);
+      else if (warp == 2) bwd2_producer<D, TG, kMode, kOutDelta>(c, p, &tmK, &tmV, &tmQ, &tmG, &tmO);
       else bwd2_back<D, CG>(c, p, 1);
     }
   } else if (warp < 8) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kDrainRegs));
     if (warp < 6) bwd2_drain<D>(c, p, &tmDQ, &tmDK);
+    else if (kOutDelta) bwd2_rowdots<D>(c, p);
   } else {
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWorkerRegs));
-    bwd2_worker<D, TG, kMode, CG, kHeads>(c, p);
+    bwd2_worker<D, TG, kMode, CG, kHeads, kOutDelta>(c, p);
   }
 
   tc_fence_before();
@@ -1047,6 +1092,49 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
     __syncthreads();
   }
   if (warp == 0) tmem_dealloc(c.tmem, 512);
+}
+
+// After the sweep: the row-side part of dK joins the accumulator, and d static_dest comes out of it.
+// With a = g^(2/3) s^(1/3) t^(1/3):  t dA/dt = a / 3 = g dA/dg / 2, so d t[row] = sum_k dG[k, row] G[k, row] / (2 t[row]),
+// summed over the keys k of every chunk; and with G = K K^T that sum is the dot product of K[row] with
+// sum_chunks (dG^T K_i)[row] -- the row-side dK_j that the sweep adds up in acc_dkr (with the bf16 dG its MMAs consumed).
+// So the sweep needs no column sums over the keys for d static_dest.  One warp per row of the range.
+template <int D, typename TG>
+__global__ void __launch_bounds__(256)
+row_side_finish_kernel(const __nv_bfloat16* __restrict__ kc, const TG* __restrict__ sdest, const float* __restrict__ dkr,
+                       float* __restrict__ acc_dk, float* __restrict__ acc_dt, int BH, int L, int Lr, int r0, int row_begin,
+                       int row_end) {
+  constexpr int E = D / 32;                             // elements per lane
+  const int lane = threadIdx.x & 31, nrows = row_end - row_begin;
+  const long long wid = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wid >= (long long)BH * nrows) return;
+  const int bh = (int)(wid / nrows), rr = (int)(wid - (long long)bh * nrows);
+  const size_t base = ((size_t)bh * L + row_begin + rr) * D + (size_t)lane * E;
+  float v[E], kf[E];
+  if (E == 2) {
+    const float2 t = *reinterpret_cast<const float2*>(dkr + base);
+    v[0] = t.x; v[1] = t.y;
+    const __nv_bfloat162 kk = *reinterpret_cast<const __nv_bfloat162*>(kc + base);
+    kf[0] = __low2float(kk); kf[1] = __high2float(kk);
+  } else {
+    const float4 t = *reinterpret_cast<const float4*>(dkr + base);
+    v[0] = t.x; v[1] = t.y; v[E - 2] = t.z; v[E - 1] = t.w;
+    const uint2 kk = *reinterpret_cast<const uint2*>(kc + base);
+    kf[0] = __uint_as_float(kk.x << 16); kf[1] = __uint_as_float(kk.x & 0xffff0000u);
+    kf[E - 2] = __uint_as_float(kk.y << 16); kf[E - 1] = __uint_as_float(kk.y & 0xffff0000u);
+  }
+  float dot = 0.f;
+#pragma unroll
+  for (int x = 0; x < E; ++x) {
+    dot = fmaf(v[x], kf[x], dot);
+    acc_dk[base + x] += v[x];
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+  if (lane == 0 && dot != 0.f) {
+    const size_t grow = (size_t)bh * Lr + r0 + rr;
+    acc_dt[grow] += 0.5f * dot / Num<TG>::ld(sdest + grow);
+  }
 }
 
 }  // namespace sm100

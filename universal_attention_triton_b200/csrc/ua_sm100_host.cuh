@@ -135,7 +135,7 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
   CUtensorMap tmK, tmV, tmQ, tmG, tmDQ, tmDK;
   const uint64_t BH = (uint64_t)s.B * s.H;
   if (!make_rows_map(&tmK, kc, BH * s.L, D, 64) || !make_rows_map(&tmV, vc, BH * s.L, D, 64) ||
-      !make_f32_rows_map(&tmDK, p.acc_dk, BH * s.L, D, 64))
+      !make_f32_rows_map(&tmDK, p.acc_dkr, BH * s.L, D, 64))
     return UA_ERR_CUDA;
   if (p.heads == 0) {
     tmQ = tmK; tmG = tmK; tmDQ = tmDK;       // never used
@@ -145,8 +145,23 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
     return UA_ERR_CUDA;
   }
   auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kBwd2Cols, true> : bwd2_kernel<D, TG, kMode, kBwd2Cols, false>;
+  // the forward's output tiles at hand (per-chunk form, head_dim 64): the row term comes from them
+  CUtensorMap tmO = tmG;
+  if constexpr (kMode == 1 && Cfg::kOutTiles) {
+    if (p.heads > 0 && p.out_tiles != nullptr) {
+      if (!make_rows_map(&tmO, p.out_tiles, BH * s.N * s.R * p.Lr, D, 64)) return UA_ERR_CUDA;
+      kern = bwd2_kernel<D, TG, 1, kBwd2Cols, true, true>;
+    }
+  }
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, p);
+  kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, tmO, p);
+  // the row-side dK joins the accumulator; d static_dest of the range's rows comes out of it
+  const int row_begin = p.j_begin * 128, row_end = p.j_end * 128;
+  const long long warps = (long long)BH * (row_end - row_begin);
+  if (warps > 0)
+    row_side_finish_kernel<D, TG><<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(
+        static_cast<const __nv_bfloat16*>(kc), static_cast<const TG*>(p.sdest), p.acc_dkr, p.acc_dk, p.acc_dt, (int)BH, s.L, p.Lr,
+        p.r0, row_begin, row_end);
   return cudaGetLastError() == cudaSuccess ? UA_OK : UA_ERR_CUDA;
 }
 

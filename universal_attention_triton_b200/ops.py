@@ -118,10 +118,12 @@ def forward_cm(kc, vc, xq, static_src, static_dest, flags: int = 0, keep_carry: 
     return out_cm, lse_cm, denom_cm
 
 
-def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0, carry=None, lse=None):
+def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags: int = 0, carry=None, lse=None, out_cm=None):
     """Gradients (dkc, dvc, dxq, dstatic_src, dstatic_dest) shaped and typed like the inputs.
     ``carry``: the table ``forward_cm(keep_carry=True)`` returned for the same inputs (skips the pre-pass).
-    ``lse``: the fp32 ``lse_cm (b,h,n,r,L)`` of the same forward (lets the tensor-core backward skip its row max / sum)."""
+    ``lse``: the fp32 ``lse_cm (b,h,n,r,L)`` of the same forward (lets the tensor-core backward skip its row max / sum).
+    ``out_cm``: the output tiles ``(b,h,n,r,L,d)`` of the same forward, when the caller still holds them (``ua_bwd_saved``:
+    the softmax gradient's row term comes from them instead of a sum over the keys)."""
     _require_cuda(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm)
     lib = _lib.load()
     b, h, n, c, d = kc.shape
@@ -154,8 +156,11 @@ def backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags
             if lse.dtype != torch.float32 or tuple(lse.shape) != (b, h, n, r, L) or not lse.is_cuda:
                 raise ValueError("lse must be the fp32 chunk-major (b,h,n,r,L) log-sum-exp of the forward")
             lse = lse.contiguous()
-        rc = lib.ua_bwd_kept(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
-                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype), _ptr(carry), _ptr(lse),
+        if out_cm is not None and not (out_cm.is_cuda and out_cm.dtype == dt and out_cm.is_contiguous()
+                                       and tuple(out_cm.shape) == (b, h, n, r, L, d)):
+            out_cm = None
+        rc = lib.ua_bwd_saved(ctypes.byref(dims), code, _dtype_code(ss.dtype), _ptr(kcc), _ptr(vcc), _ptr(q), _ptr(ss), _ptr(sd),
+                        _ptr(g_out_cm), _ptr(g_denom_cm), _dtype_code(g_denom_cm.dtype), _ptr(carry), _ptr(lse), _ptr(out_cm),
                         _ptr(dkc), _ptr(dvc), _ptr(dxq), _ptr(dss), _ptr(dsd), _ptr(ws), ws_bytes, flags, _stream())
         _lib.check(rc, "ua_bwd")
         _check_status(lib, ws, "ua_bwd")
@@ -513,10 +518,11 @@ def backward_rows_suffix(kc, vc, static_src, static_dest_rows, tile_begin: int, 
     dims = UaDims(b, h, 1, n, c, d)
     rows = _rows(tile_begin, tile_end, sd.shape[-1], row_offset)
     with torch.cuda.device(kc.device):
-        ws = torch.empty(256, dtype=torch.uint8, device=kc.device)
+        ws_bytes = max(lib.ua_bwd_rows_suffix_workspace_bytes(ctypes.byref(dims), code), 256)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=kc.device)
         sf = suffix.float().contiguous()
         rc = lib.ua_bwd_rows_suffix(ctypes.byref(dims), code, _dtype_code(ss.dtype), ctypes.byref(rows), _ptr(kc), _ptr(vc),
-                                    _ptr(ss), _ptr(sd), _ptr(sf), _ptr(dk), _ptr(dsrc), _ptr(ddest), _ptr(ws), 256, _stream())
+                                    _ptr(ss), _ptr(sd), _ptr(sf), _ptr(dk), _ptr(dsrc), _ptr(ddest), _ptr(ws), ws_bytes, _stream())
         _lib.check(rc, "ua_bwd_rows_suffix")
         _check_status(lib, ws, "ua_bwd_rows_suffix")
 

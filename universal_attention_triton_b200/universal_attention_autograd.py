@@ -69,6 +69,20 @@ def set_merged_forward(mode: str) -> None:
     _MERGED_FORWARD = mode
 
 
+_SAVE_OUTPUT = True
+
+
+def set_save_output(on: bool) -> None:
+    """When on (default), the Functions also save their own output ``out`` for backward (chunk-major layout only).  The
+    tensor-core backward then takes the softmax gradient's row term ``sum_k P dP`` as ``out . g_out`` per row instead of
+    summing over the keys (5 % of the backward at B4 H8 R4 L4096 D64).  ``out`` stays alive until backward has run -- which
+    it does anyway whenever ``SMVecMatMul`` (or any node that saves its input) consumes it -- and, like every saved
+    tensor, must not be modified in place before backward.  Off: exactly the reference's set of saved inputs plus the two
+    small by-products."""
+    global _SAVE_OUTPUT
+    _SAVE_OUTPUT = bool(on)
+
+
 def set_strict_masked_grads(on: bool) -> None:
     """When off, backward skips the gradient through fully masked blocks (rows
     before a key chunk).  That gradient is exactly zero when ``SMVecMatMul``
@@ -101,6 +115,9 @@ def _setup_context(ctx, inputs, outputs):
         del outputs[1]._ua_extras                   # denom must not keep the two tensors alive on its own
         ctx.ua_has_carry = carry is not None
         saved = (kc, vc, xq, static_src, static_dest, lse_cm) + ((carry,) if carry is not None else ())
+        ctx.ua_has_out = _SAVE_OUTPUT and _OUTPUT_LAYOUT == "chunk_major"
+        if ctx.ua_has_out:
+            saved = saved + (outputs[0],)
         ctx.save_for_backward(*saved)
         ctx.ua_has_extras = True
     else:
@@ -129,15 +146,19 @@ def _backward(ctx, g_out, g_denom):
     saved = ops.plain(*ctx.saved_tensors)
     g_out, g_denom = ops.plain(g_out, g_denom)
     kc, vc, xq, static_src, static_dest = saved[:5]
+    out_cm = None
     if getattr(ctx, "ua_has_extras", False):
         lse = saved[5]
         carry = saved[6] if ctx.ua_has_carry else None
+        if getattr(ctx, "ua_has_out", False):
+            v = saved[-1].permute(0, 1, 5, 2, 3, 4)            # the chunk-major storage behind the reference-shaped view
+            out_cm = v if v.is_contiguous() else None
     else:                      # only the inputs were saved: recompute what the forward would have handed over
         _, lse, _, carry = ops.forward_cm(kc, vc, xq, static_src, static_dest, flags=_lib.FLAG_SKIP_MASKED_FILL, keep_carry=True)
     flags = 0 if (_STRICT_MASKED_GRADS and not upstream_zero) else _lib.FLAG_SKIP_MASKED_GRADS
     g_out_cm = ops.out_to_chunk_major(g_out)
     g_denom_cm = ops.denom_to_chunk_major(g_denom)
-    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags, carry=carry, lse=lse)
+    return ops.backward_cm(kc, vc, xq, static_src, static_dest, g_out_cm, g_denom_cm, flags, carry=carry, lse=lse, out_cm=out_cm)
 
 
 class UniversalAttention(Function):
