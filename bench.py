@@ -403,7 +403,8 @@ def main():
         carry = res[3] if len(res) > 3 else None
         e1.record()
         if not w["fwd_only"]:
-            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags, carry=carry, lse=lse_cm)
+            # (the step holds the forward's output tiles, as an autograd graph does: the backward takes its row term from them)
+            grads = ops.backward_cm(kc, vc, xq, ss, sd, g_out_cm, g_lse_cm, flags=bwd_flags, carry=carry, lse=lse_cm, out_cm=out_cm)
         e2.record()
         if record:
             fwd_ms.append((e0, e1)); bwd_ms.append((e1, e2))
@@ -562,7 +563,7 @@ def main():
 
             def strong_step():
                 res = ops.forward_cm(skc, svc, sxq, sss, ssd, keep_carry=True)
-                ops.backward_cm(skc, svc, sxq, sss, ssd, sgo, sgl, flags=bwd_flags, carry=res[3], lse=res[1])
+                ops.backward_cm(skc, svc, sxq, sss, ssd, sgo, sgl, flags=bwd_flags, carry=res[3], lse=res[1], out_cm=res[0])
 
             for _ in range(3):
                 strong_step()
@@ -607,9 +608,9 @@ def main():
             "tflops": (f_fwd + f_bwd) * world / (ms_per_step * 1e-3) / 1e12,
             "frac_of_bf16_peak": (f_fwd + f_bwd) / (ms_per_step * 1e-3) / 1e12 / peak,
             "fwd_ms": fwd_avg, "bwd_ms": bwd_avg,
-            # forward kernel; backward: keys-on-lanes kernel + three fp32 -> dtype conversions, and with the gradient through
-            # the rows before each chunk three more (per-chunk constants, sweep, per-chunk finish)
-            "gpu_launches": K * (1 + (0 if w["fwd_only"] else (4 if args.skip_masked_grads else 7))),
+            # forward kernel; backward: keys-on-lanes kernel, its row-side finish, three fp32 -> dtype conversions, and with the
+            # gradient through the rows before each chunk three more (per-chunk constants, sweep, per-chunk finish)
+            "gpu_launches": K * (1 + (0 if w["fwd_only"] else (5 if args.skip_masked_grads else 8))),
             "clocks": clocks,
             "roofline": {"kernel": "ua backward" if dom_is_bwd else "ua forward", "bound": "tensor",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
