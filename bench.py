@@ -541,8 +541,26 @@ def main():
         grads_to_host = not w["fwd_only"] and not args.e2e_loss_only
         e_ms = e2e_timed() if grads_to_host else loss_only_ms
         d2h = 4 + (h2d if grads_to_host else 0)
+
+        # The host link of this box, measured alone on the largest buffer (pinned memory both ways, nothing else running):
+        # on some hosts of the pool device-to-host copies run far below the link's rate, and the figure with the gradients
+        # returned is then bound by them -- the loss-only figure beside it is not.
+        def link_gbs(dst, src):
+            for _ in range(2):
+                dst.copy_(src, non_blocking=True)
+            torch.cuda.synchronize()
+            a, b = ev(), ev()
+            a.record()
+            for _ in range(3):
+                dst.copy_(src, non_blocking=True)
+            b.record()
+            torch.cuda.synchronize()
+            return 3 * src.numel() * src.element_size() / (a.elapsed_time(b) * 1e-3) / 1e9
+        big = max(range(len(host)), key=lambda i: host[i].numel())
+        host_link = {"h2d_gbs": link_gbs(dev_in[0][big], host[big]), "d2h_gbs": link_gbs(host_grads[big], dev_in[0][big]),
+                     "buffer_bytes": host[big].numel() * host[big].element_size()}
         e2e = {"value": tokens / (e_ms / K * 1e-3), "unit": "tokens/s", "ms_per_step": e_ms / K,
-               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "host_link": host_link,
                "returns": "loss + five gradients" if grads_to_host else "loss",
                "loss_only": {"value": tokens / (loss_only_ms / K * 1e-3), "ms_per_step": loss_only_ms / K, "d2h_bytes_per_step": 4},
                "path": (f"UniversalAttentionMerged.apply ({args.merged_entry} backward)" if args.merged_entry else "UniversalAttention.apply -> SMVecMatMul.apply") +
