@@ -176,3 +176,37 @@ def test_backward_recomputes_when_only_the_inputs_were_saved():
     want = O.ua_backward(*ins, g_out.cpu(), g_denom.cpu())
     for a, b_, name in zip(got, want, ("dkc", "dvc", "dxq", "dsrc", "ddest")):
         assert rel_fro(a.cpu(), b_) <= 1e-4, name
+
+
+@pytest.mark.gpu
+def test_own_output_is_saved_for_backward_unless_switched_off():
+    """By default the Functions save their own output with the inputs (the tensor-core backward takes the row term of the
+    softmax gradient from out . g_out); switched off, they save the reference's five inputs plus the two by-products.
+    Same gradients either way, up to the rounding of the bf16 output."""
+    import universal_attention_triton_b200 as ua
+    from oracle import ua_oracle as O
+    from tests._util import rel_fro
+    from universal_attention_triton_b200 import universal_attention_autograd as M
+    ins = O.make_inputs(1, 2, 2, 512, 128, 64, dtype=torch.bfloat16, seed=9)
+
+    class Ctx:
+        def save_for_backward(self, *ts):
+            self.saved_tensors = ts
+    results = {}
+    try:
+        for on in (True, False):
+            ua.set_save_output(on)
+            xs = [t.cuda() for t in ins]
+            out, denom = M._forward(*xs)
+            ctx = Ctx()
+            M._setup_context(ctx, tuple(xs), (out, denom))
+            assert ctx.ua_has_extras and ctx.ua_has_out == on
+            assert (ctx.saved_tensors[-1] is out) == on
+            gen = torch.Generator(device="cuda").manual_seed(11)
+            g_out = torch.randn(out.shape, generator=gen, device="cuda").to(out.dtype)
+            g_denom = torch.randn(denom.shape, generator=gen, device="cuda")
+            results[on] = [t.float().cpu() for t in M._backward(ctx, g_out, g_denom)]
+    finally:
+        ua.set_save_output(True)
+    for a, b_, name in zip(results[True], results[False], ("dkc", "dvc", "dxq", "dsrc", "ddest")):
+        assert torch.isfinite(a).all() and rel_fro(a, b_) <= 2e-2, (name, rel_fro(a, b_))
