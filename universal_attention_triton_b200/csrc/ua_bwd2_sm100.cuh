@@ -746,8 +746,10 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     // Software pipelining inside the warp: the tail of a head (storing dS and the probabilities, the hand-over to the MMA
     // issuers) is deferred until the TMEM loads of the NEXT unit have been issued, so that their latency runs under it.
     // (Only where the next unit's MMAs do not wait for that hand-over: with a single (S, dP) buffer whose S columns also
-    // hold the probabilities, at head_dim 128, the tail comes first.)
-    constexpr bool kDeferTail = Cfg::kPtSeparate;
+    // hold the probabilities, at head_dim 128, the tail comes first.  So it does in the builds that take the row term from
+    // the forward's output tiles: without the group barrier in the middle of a head, handing dS over at once is 4.6 %
+    // faster than deferring it, while with the barrier deferring is 2 % faster -- both measured.)
+    constexpr bool kDeferTail = Cfg::kPtSeparate && !kOutDelta;
     float2 dc[H2];
 #pragma unroll
     for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);

@@ -119,6 +119,13 @@ inline bool bwd2_supported(const Shape& s, int dtype) { return dtype == UA_BF16 
 #define UA_BWD2_COLS 32
 #endif
 constexpr int kBwd2Cols = UA_BWD2_COLS;      // columns of a half tile per worker thread (32: eight worker warps with ~190 registers each; 16: sixteen)
+// ... in the builds that take the softmax row term from the forward's output tiles.  With the column sums over the keys and
+// the group barrier in every head, sixteen worker warps are slower than eight (the per-head fixed costs double); without
+// them they are 5 % faster (four warps per scheduler hide the TMEM and shared-memory latencies) -- both measured.
+#ifndef UA_BWD2_COLS_OUT
+#define UA_BWD2_COLS_OUT 16
+#endif
+constexpr int kBwd2ColsOut = UA_BWD2_COLS_OUT;
 
 // Fills the row-range fields of Bwd2Params for a call over the whole sequence.
 inline void whole_sequence(Bwd2Params& p) {
@@ -147,14 +154,16 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
   auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kBwd2Cols, true> : bwd2_kernel<D, TG, kMode, kBwd2Cols, false>;
   // the forward's output tiles at hand (per-chunk form, head_dim 64): the row term comes from them
   CUtensorMap tmO = tmG;
+  int threads = 32 * (8 + 4 * (64 / kBwd2Cols));
   if constexpr (kMode == 1 && Cfg::kOutTiles) {
     if (p.heads > 0 && p.out_tiles != nullptr) {
       if (!make_rows_map(&tmO, p.out_tiles, BH * s.N * s.R * p.Lr, D, 64)) return UA_ERR_CUDA;
-      kern = bwd2_kernel<D, TG, 1, kBwd2Cols, true, true>;
+      kern = bwd2_kernel<D, TG, 1, kBwd2ColsOut, true, true>;
+      threads = 32 * (8 + 4 * (64 / kBwd2ColsOut));
     }
   }
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
-  kern<<<(unsigned)(BH * s.N), 32 * (8 + 4 * (64 / kBwd2Cols)), Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, tmO, p);
+  kern<<<(unsigned)(BH * s.N), threads, Cfg::kSmemBytes, st>>>(tmK, tmV, tmQ, tmG, tmDQ, tmDK, tmO, p);
   // the row-side dK joins the accumulator; d static_dest of the range's rows comes out of it
   const int row_begin = p.j_begin * 128, row_end = p.j_end * 128;
   const long long warps = (long long)BH * (row_end - row_begin);
