@@ -573,7 +573,7 @@ __device__ __forceinline__ void bwd2_drain(const Bwd2Ctx& c, const Bwd2Params& p
 // --------------------------------------------------------------- row-dot warps --
 // Builds that are given the forward's output tiles (head_dim 64): the producer copies the head's output half tile next to
 // its dO half tile, and two warps (thread = row of the half tile) turn the g_denom entry of the head's table into
-// g_denom - out . dO.  They run ahead of the workers (inside the same half tile), who then need neither the column sums of
+// g_denom - out . dO.  They run ahead of the workers (up to the slot ring), who then need neither the column sums of
 // P dP over the keys nor the barrier that completed them.  (Fetching the output rows with plain global loads from these warps
 // instead made the kernel slower than the column sums: loads issued inside this kernel queue behind its shared-memory
 // traffic.)
@@ -606,9 +606,6 @@ __device__ __forceinline__ void bwd2_rowdots(const Bwd2Ctx& c, const Bwd2Params&
     float* tabC = reinterpret_cast<float*>(c.smem + Cfg::oHeadTab + sl * 512) + 64;
     tabC[row] -= lo + hi;
     c.arrive_w(qDelta + sl);
-    // not past the half tile the workers are in: with the next half tile's products formed during this one's heads
-    // (where shared memory is busiest) the kernel ran 3 % slower (measured)
-    if ((hc + 1) % p.heads == 0 && !c.wait_w(qDgReady, hc / p.heads)) return;
   }
 }
 
@@ -746,10 +743,11 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     // Software pipelining inside the warp: the tail of a head (storing dS and the probabilities, the hand-over to the MMA
     // issuers) is deferred until the TMEM loads of the NEXT unit have been issued, so that their latency runs under it.
     // (Only where the next unit's MMAs do not wait for that hand-over: with a single (S, dP) buffer whose S columns also
-    // hold the probabilities, at head_dim 128, the tail comes first.  So it does in the builds that take the row term from
-    // the forward's output tiles: without the group barrier in the middle of a head, handing dS over at once is 4.6 %
+    // hold the probabilities, at head_dim 128, the tail comes first.  So it does in the builds whose row term arrives in the
+    // head's table (from the forward's output tiles, or as the merged form's delta): without the group barrier in the middle of a head, handing dS over at once is 4.6 %
     // faster than deferring it, while with the barrier deferring is 2 % faster -- both measured.)
-    constexpr bool kDeferTail = Cfg::kPtSeparate && !kOutDelta;
+    constexpr bool kColSums = (kMode == 1 && !kOutDelta);     // the workers sum P dP over the keys themselves
+    constexpr bool kDeferTail = Cfg::kPtSeparate && kColSums;
     float2 dc[H2];
 #pragma unroll
     for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);
@@ -804,7 +802,7 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
           dp[x] = make_float2(__uint_as_float(dr[2 * x]), __uint_as_float(dr[2 * x + 1]));
         }
       }
-      if (kMode == 1 && !kOutDelta) {
+      if (kColSums) {
         float e[CG];
 #pragma unroll
         for (int x = 0; x < H2; ++x) {
@@ -822,8 +820,8 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
       UQ(2)
       if (kOutDelta) {
         if (!c.wait_w(qDelta + sl, hc / Cfg::kNS)) return;
-      } else {
-        named_bar_sync(kBarGroup + g, 128);
+      } else if (kColSums) {
+        named_bar_sync(kBarGroup + g, 128);           // the group's column sums are complete
       }
       UQ(4)
       {
@@ -1064,7 +1062,8 @@ bwd2_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUt
   // worker request beyond what was given back would never be granted.)
   constexpr int kThreads = 32 * (8 + 4 * NG);
   constexpr int kLaunchRegs = (65536 / kThreads) / 8 * 8;
-  constexpr int kRoleRegs = 48, kDrainRegs = 64;
+  // (sixteen worker warps: 80 registers at launch; the tighter split leaves them 96 instead of 88, measured 2.5 % faster)
+  constexpr int kRoleRegs = (CG == 16) ? 40 : 48, kDrainRegs = (CG == 16) ? 56 : 64;
   constexpr int kWorkerRegs = kLaunchRegs + ((2 * kLaunchRegs - kRoleRegs - kDrainRegs) * 128 / (128 * NG)) / 8 * 8;
   static_assert(kRoleRegs <= kLaunchRegs && kDrainRegs <= kLaunchRegs, "setmaxnreg.dec must not ask for more");
   static_assert(128 * (kRoleRegs + kDrainRegs) + 128 * NG * kWorkerRegs <= kThreads * kLaunchRegs, "register pool");

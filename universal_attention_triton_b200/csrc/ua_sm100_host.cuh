@@ -152,9 +152,15 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
     return UA_ERR_CUDA;
   }
   auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kBwd2Cols, true> : bwd2_kernel<D, TG, kMode, kBwd2Cols, false>;
+  int threads = 32 * (8 + 4 * (64 / kBwd2Cols));
+  if constexpr (kMode == 2 && D == 64) {               // the merged form has no column sums either: sixteen worker warps
+    if (p.heads > 0) {
+      kern = bwd2_kernel<D, TG, 2, kBwd2ColsOut, true>;
+      threads = 32 * (8 + 4 * (64 / kBwd2ColsOut));
+    }
+  }
   // the forward's output tiles at hand (per-chunk form, head_dim 64): the row term comes from them
   CUtensorMap tmO = tmG;
-  int threads = 32 * (8 + 4 * (64 / kBwd2Cols));
   if constexpr (kMode == 1 && Cfg::kOutTiles) {
     if (p.heads > 0 && p.out_tiles != nullptr) {
       if (!make_rows_map(&tmO, p.out_tiles, BH * s.N * s.R * p.Lr, D, 64)) return UA_ERR_CUDA;
