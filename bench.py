@@ -53,12 +53,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 
 # DRAM bytes per backward call at workload c2, from one ncu capture of a slice of 2 of the 32 (batch, kv-head) units: the
-# keys-on-lanes kernel (163.66 MB read, of which 67 MB are the forward's output tiles, + 7.75 MB written), the sweep over
-# the rows before each chunk (80.87 + 3.95 MB) and the row-side finish (5.30 MB); the small per-chunk kernels and the
+# keys-on-lanes kernel (163.69 MB read, of which 67 MB are the forward's output tiles, + 7.74 MB written), the sweep over
+# the rows before each chunk (80.87 + 2.04 MB) and the row-side finish (5.30 MB); the small per-chunk kernels and the
 # fp32 -> bf16 conversions are not in the figure.  The traffic grows in proportion to
 # the units.  No figure is given for the forward: a capture of that slice ends with part of the 134 MB it writes still in
 # the 126 MB L2, so its DRAM write count understates a full launch.
-NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (163.664128e6 + 7.751168e6 + 80.871168e6 + 3.953920e6 + 5.299712e6)}}
+NCU_DRAM_BYTES = {"c2": {"fwd": None, "bwd": 16 * (163.686400e6 + 7.741696e6 + 80.872704e6 + 2.036992e6 + 5.299456e6)}}
 
 
 def flops(w):

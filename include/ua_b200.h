@@ -142,7 +142,7 @@ int ua_bwd_kept(const UaDims* dims, int dtype, int gate_dtype,
 /* ua_bwd_kept() for a caller that still holds the forward's output tiles out_cm (b,h,n,r,L,d), as an autograd graph does
  * whenever a later node saved them (SMVecMatMul does: universal_attention_autograd.py:286-288).  The softmax gradient
  * needs sum_k P dP per row; since P V = out, that is the dot product of the row's output and its upstream gradient, which
- * the tensor-core kernel then takes from the tiles instead of summing over the keys (about a tenth of its time).  out_cm
+ * the tensor-core kernel then takes from the tiles instead of summing over the keys (about a sixth of its time).  out_cm
  * must be what ua_fwd wrote for the same inputs (rows before a chunk are not read); NULL: ua_bwd_kept().  Kernels
  * other than the tensor-core one ignore it.  The reference recomputes everything (universal_attention_autograd.py:
  * 166-169); its Triton backward has no use for the tiles. */

@@ -47,7 +47,7 @@ def set_merged_backward(mode: str) -> None:
     """Backward of ``UniversalAttentionMerged``.  ``"composed"`` (default): the merge backward followed by the
     operator's backward, as accurate as the drop-in pair (gradients within ~5e-3 relative-Frobenius of the fp32
     reference in bf16).  ``"fused"``: one kernel (``ua_bwd_merged``) that forms ``dS = P (dP - g.merged)`` with the
-    bf16 merged output, as flash-attention backwards do with their output; about 15 % faster end to end, but the
+    bf16 merged output, as flash-attention backwards do with their output; about 18 % faster end to end, but the
     rounding of ``merged`` enters the decay gradient through a cumulative sum: gradients within 1-4e-2 of the
     reference at L = 1024..4096 (inside the 5e-2 bar, ten times the composed path's error)."""
     global _MERGED_BACKWARD
@@ -62,7 +62,7 @@ def set_merged_forward(mode: str) -> None:
     """Forward of ``UniversalAttentionMerged``.  ``"materialise"`` (default): the operator's forward, then the merge over
     key chunks (the (b,h,n,r,L,d) tensor ``out`` lives inside the forward).  ``"low_memory"``: two passes of the forward
     kernel that never write ``out`` (``ua_fwd_merged``): (b,h,n,r,L) + (b,h,r,L,d) floats of scratch instead of two n-fold
-    tensors, about 1 ms more per step at B4 H8 R4 L4096 D64; implies the fused backward (there is no ``out`` to merge
+    tensors, about 0.7 ms more per step at B4 H8 R4 L4096 D64; implies the fused backward (there is no ``out`` to merge
     backwards through); shapes the tensor-core kernels do not take fall back to ``"materialise"``."""
     global _MERGED_FORWARD
     assert mode in ("materialise", "low_memory")
@@ -75,7 +75,7 @@ _SAVE_OUTPUT = True
 def set_save_output(on: bool) -> None:
     """When on (default), the Functions also save their own output ``out`` for backward (chunk-major layout only).  The
     tensor-core backward then takes the softmax gradient's row term ``sum_k P dP`` as ``out . g_out`` per row instead of
-    summing over the keys (5 % of the backward at B4 H8 R4 L4096 D64).  ``out`` stays alive until backward has run -- which
+    summing over the keys (the backward kernel then takes 2.15 ms instead of 2.55 at B4 H8 R4 L4096 D64).  ``out`` stays alive until backward has run -- which
     it does anyway whenever ``SMVecMatMul`` (or any node that saves its input) consumes it -- and, like every saved
     tensor, must not be modified in place before backward.  Off: exactly the reference's set of saved inputs plus the two
     small by-products."""
