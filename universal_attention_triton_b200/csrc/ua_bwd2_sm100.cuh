@@ -743,11 +743,11 @@ __device__ __forceinline__ void bwd2_worker(const Bwd2Ctx& c, const Bwd2Params& 
     // Software pipelining inside the warp: the tail of a head (storing dS and the probabilities, the hand-over to the MMA
     // issuers) is deferred until the TMEM loads of the NEXT unit have been issued, so that their latency runs under it.
     // (Only where the next unit's MMAs do not wait for that hand-over: with a single (S, dP) buffer whose S columns also
-    // hold the probabilities, at head_dim 128, the tail comes first.  So it does in the builds whose row term arrives in the
-    // head's table (from the forward's output tiles, or as the merged form's delta): without the group barrier in the middle of a head, handing dS over at once is 4.6 %
-    // faster than deferring it, while with the barrier deferring is 2 % faster -- both measured.)
+    // hold the probabilities, at head_dim 128, the tail comes first.  And only with eight worker warps and the column sums:
+    // sixteen warps do better handing dS over at once (5-6 % against eight that defer, more against sixteen that defer),
+    // and so do eight without the group barrier in the middle of a head (4.6 %) -- all measured.)
     constexpr bool kColSums = (kMode == 1 && !kOutDelta);     // the workers sum P dP over the keys themselves
-    constexpr bool kDeferTail = Cfg::kPtSeparate && kColSums;
+    constexpr bool kDeferTail = Cfg::kPtSeparate && kColSums && (CG == 32);
     float2 dc[H2];
 #pragma unroll
     for (int x = 0; x < H2; ++x) dc[x] = make_float2(0.f, 0.f);

@@ -115,17 +115,17 @@ inline int launch_fwd_merge(const Shape& s, int gate_dtype, const void* kc, cons
 // Shapes of the keys-on-lanes backward kernel.
 inline bool bwd2_supported(const Shape& s, int dtype) { return dtype == UA_BF16 && s.C == 128 && (s.D == 64 || s.D == 128); }
 
-#ifndef UA_BWD2_COLS
-#define UA_BWD2_COLS 32
+// Columns of a half tile per worker thread: 16 (sixteen worker warps, 96 registers each) at head_dim 64, 32 (eight worker
+// warps, ~200 registers each) at head_dim 128.  At head_dim 64 sixteen warps (four per scheduler hide the TMEM and
+// shared-memory latencies) that hand dS over at once are 5-6 % faster than eight that defer the tail of a head, in every
+// build; sixteen that defer are slower than either (measured).
+#ifndef UA_BWD2_COLS_64
+#define UA_BWD2_COLS_64 16
 #endif
-constexpr int kBwd2Cols = UA_BWD2_COLS;      // columns of a half tile per worker thread (32: eight worker warps with ~190 registers each; 16: sixteen)
-// ... in the builds that take the softmax row term from the forward's output tiles.  With the column sums over the keys and
-// the group barrier in every head, sixteen worker warps are slower than eight (the per-head fixed costs double); without
-// them they are 5 % faster (four warps per scheduler hide the TMEM and shared-memory latencies) -- both measured.
-#ifndef UA_BWD2_COLS_OUT
-#define UA_BWD2_COLS_OUT 16
+#ifndef UA_BWD2_COLS_128
+#define UA_BWD2_COLS_128 32
 #endif
-constexpr int kBwd2ColsOut = UA_BWD2_COLS_OUT;
+template <int D> constexpr int bwd2_cols() { return D == 64 ? UA_BWD2_COLS_64 : UA_BWD2_COLS_128; }
 
 // Fills the row-range fields of Bwd2Params for a call over the whole sequence.
 inline void whole_sequence(Bwd2Params& p) {
@@ -151,21 +151,15 @@ int launch_bwd2_t(const Shape& s, const void* kc, const void* vc, const void* xq
              !make_f32_rows_map(&tmDQ, p.acc_dq, BH * s.R * p.Lr, D, 64)) {
     return UA_ERR_CUDA;
   }
-  auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kBwd2Cols, true> : bwd2_kernel<D, TG, kMode, kBwd2Cols, false>;
-  int threads = 32 * (8 + 4 * (64 / kBwd2Cols));
-  if constexpr (kMode == 2 && D == 64) {               // the merged form has no column sums either: sixteen worker warps
-    if (p.heads > 0) {
-      kern = bwd2_kernel<D, TG, 2, kBwd2ColsOut, true>;
-      threads = 32 * (8 + 4 * (64 / kBwd2ColsOut));
-    }
-  }
+  constexpr int kCols = bwd2_cols<D>();
+  auto kern = p.heads > 0 ? bwd2_kernel<D, TG, kMode, kCols, true> : bwd2_kernel<D, TG, kMode, kCols, false>;
+  const int threads = 32 * (8 + 4 * (64 / kCols));
   // the forward's output tiles at hand (per-chunk form, head_dim 64): the row term comes from them
   CUtensorMap tmO = tmG;
   if constexpr (kMode == 1 && Cfg::kOutTiles) {
     if (p.heads > 0 && p.out_tiles != nullptr) {
       if (!make_rows_map(&tmO, p.out_tiles, BH * s.N * s.R * p.Lr, D, 64)) return UA_ERR_CUDA;
-      kern = bwd2_kernel<D, TG, 1, kBwd2ColsOut, true, true>;
-      threads = 32 * (8 + 4 * (64 / kBwd2ColsOut));
+      kern = bwd2_kernel<D, TG, 1, kCols, true, true>;
     }
   }
   if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) != cudaSuccess) return UA_ERR_CUDA;
